@@ -1,0 +1,147 @@
+/*
+ * blaze_b200.h - the thin C ABI that launches the sm_100a kernels of the Blaze quantized-matmul path.
+ *
+ * The acltensor* host API (cann_ops_tensor.h) is built on these entry points; they are exported as well so that a
+ * foreign-function binding (ctypes, cgo, JNI ...) can reach the kernels with plain pointers and sizes.  All pointers
+ * named "device" are CUDA device pointers, `stream` is a cudaStream_t passed as void*.  Every function returns an
+ * acltensorStatus_t value as int (0 = success).  Calls are asynchronous on `stream` unless stated otherwise.
+ *
+ * Each entry point names the part of the reference (Atlas-Ascend-Fork/ops-tensor) it stands in for.
+ */
+#ifndef BLAZE_B200_H
+#define BLAZE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(_WIN32) || defined(__CYGWIN__)
+#define BLAZE_API __declspec(dllexport)
+#else
+#define BLAZE_API __attribute__((visibility("default")))
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element formats of quantized operands (A8/W8/W4). */
+typedef enum {
+    BLAZE_ELEM_E4M3 = 0, /* 8-bit, one byte per element */
+    BLAZE_ELEM_E2M1 = 1  /* 4-bit, two per byte, low nibble = even K index
+                            (include/blaze/gemm/tile/arch35/shift_w4_to_w8.h:88-99) */
+} blazeElem_t;
+
+/* Fused activation, applied after bias and before the residual add. */
+typedef enum { BLAZE_ACT_IDENTITY = 0, BLAZE_ACT_RELU = 1, BLAZE_ACT_GELU_TANH = 2 } blazeActivation_t;
+
+/* How the output tiles are scheduled over the SMs. */
+typedef enum {
+    BLAZE_SCHED_AUTO = 0,          /* heuristic */
+    BLAZE_SCHED_DATA_PARALLEL = 1, /* one CTA per output tile, full K */
+    BLAZE_SCHED_STREAM_K = 2       /* (tile, k-block) units split evenly, fp32 fix-up in workspace */
+} blazeSched_t;
+
+/* ------------------------------------------------------------------------------------------------------------
+ * MX block-scaled GEMM:  D = act(A x B^T + bias) + residual, bf16 output, fp32 accumulation.
+ *   A  [M][lda] codes, K-contiguous (E4M3)                 scaleA [M][ceil(K/64)*2] E8M0 bytes, one per 32 K
+ *   B  [N][ldb] codes, K-contiguous (E4M3 or packed E2M1)  scaleB [N][ceil(K/64)*2]
+ * Stands in for GemmUniversal<KernelMmadWithScaleMx>::operator() and its Params
+ * (include/blaze/gemm/kernel/kernel_qbmm_mx.h:80-115, :154-176) with the scale layouts of
+ * include/tensor_api/impl/tensor_api/tensor/layout_pattern.h:180-226.
+ * Constraints: K % 16 == 0, N % 8 == 0, lda/ldb multiples of 16 bytes, ldd/ldr multiples of 8 elements, all base
+ * pointers 16-byte aligned.
+ * ------------------------------------------------------------------------------------------------------------ */
+typedef struct {
+    size_t struct_size; /* sizeof(blazeMxGemmArgs), for forward compatibility */
+    int32_t M, N, K;
+    int32_t b_elem;          /* blazeElem_t of B; A is always E4M3 */
+    const void* A;           /* device */
+    int64_t lda;             /* bytes between rows of A */
+    const void* B;           /* device */
+    int64_t ldb;             /* bytes between rows of B */
+    const void* scaleA;      /* device, E8M0 */
+    const void* scaleB;      /* device, E8M0 */
+    const void* bias;        /* device bf16[N] or NULL */
+    const void* residual;    /* device bf16 [M][ldr] or NULL */
+    int64_t ldr;             /* elements */
+    void* D;                 /* device bf16 [M][ldd] */
+    int64_t ldd;             /* elements */
+    int32_t activation;      /* blazeActivation_t */
+    int32_t tile_n;          /* 0 = choose; else 128 or 224 */
+    int32_t reuse_b_prepass; /* 1: workspace still holds B's re-tiled scales / expanded codes from the previous call */
+    int32_t sm_limit;        /* 0 = all SMs; else cap on the persistent grid */
+    void* workspace;         /* device, 256-byte aligned */
+    size_t workspace_bytes;
+} blazeMxGemmArgs;
+
+BLAZE_API int blazeMxGemmWorkspaceSize(const blazeMxGemmArgs* args, size_t* bytes);
+BLAZE_API int blazeMxGemm(const blazeMxGemmArgs* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * FP8 GEMM with float32 scales (1x128 groups of A, 128x128 blocks of B), dense or grouped, data-parallel or
+ * stream-K.  D = act(sum_kb sa*sb*(A_kb x B_kb^T) + bias) + residual, bf16 output.
+ *   A  [M][lda] E4M3               scaleA [M][ceil(K/128)] fp32
+ *   B  [G][N][ldb] E4M3            scaleB [G][ceil(K/128)][ceil(N/128)] fp32
+ *   group_rows  device int64[G]: rows of A (and D) belonging to each group, in order; NULL / groups==0 = dense.
+ * The reference only names these modes (QuantMode PERGROUP/PERBLOCK: include/blaze/gemm/utils/common_utils.h:98-107;
+ * groupListGmAddr: include/blaze/gemm/block/block_mmad_matmul_basic.h:68); stream-K follows
+ * GemmUniversal<KernelMultiBlockStreamK> (include/blaze/gemm/kernel/kernel_matmul_streamk.h:71-228) and
+ * BlockEpilogueMatmulStreamK (include/blaze/epilogue/block/block_epilogue_matmul_streamk.h:99-265).
+ * Constraints: K % 16 == 0, N % 8 == 0, groups <= 1024, grouped B is contiguous per group (ldb * N bytes apart).
+ * ------------------------------------------------------------------------------------------------------------ */
+typedef struct {
+    size_t struct_size;
+    int32_t M, N, K;
+    int32_t groups;
+    const void* group_rows; /* device int64[groups] */
+    const void* A;
+    int64_t lda;
+    const void* B;
+    int64_t ldb;
+    const void* scaleA;
+    const void* scaleB;
+    const void* bias;
+    const void* residual;
+    int64_t ldr;
+    void* D;
+    int64_t ldd;
+    int32_t activation;
+    int32_t sched;    /* blazeSched_t */
+    int32_t sm_limit; /* 0 = all SMs */
+    int32_t reserved;
+    void* workspace;
+    size_t workspace_bytes;
+} blazeFp8GemmArgs;
+
+BLAZE_API int blazeFp8GemmWorkspaceSize(const blazeFp8GemmArgs* args, size_t* bytes);
+BLAZE_API int blazeFp8Gemm(const blazeFp8GemmArgs* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Quantisers (fp32 source, round-to-nearest-even, saturating).  The reference has no quantiser; these produce the
+ * operand and scale layouts its MX kernel consumes (include/blaze/gemm/kernel/kernel_qbmm_mx.h:383-404).
+ * ------------------------------------------------------------------------------------------------------------ */
+/* x [rows][ldx] fp32 -> codes [rows][ld_codes bytes], scales [rows][ceil(K/64)*2] E8M0.  K % 4 == 0. */
+BLAZE_API int blazeQuantizeMx(const void* x, int64_t ldx, int32_t rows, int32_t K, int32_t elem, void* codes,
+                              int64_t ld_codes, void* scales, void* stream);
+/* x [rows][ldx] fp32 -> E4M3 codes [rows][ld_codes], scales [rows][ceil(K/128)] fp32 (amax/448). */
+BLAZE_API int blazeQuantizeFp8RowGroups(const void* x, int64_t ldx, int32_t rows, int32_t K, void* codes,
+                                        int64_t ld_codes, void* scales, void* stream);
+/* w [N][ldw] fp32 (K-contiguous weight) -> E4M3 codes [N][ld_codes], scales [ceil(K/128)][ceil(N/128)] fp32. */
+BLAZE_API int blazeQuantizeFp8Blocks(const void* w, int64_t ldw, int32_t N, int32_t K, void* codes, int64_t ld_codes,
+                                     void* scales, void* stream);
+
+/* D = A + C on n floats: the CUDA stand-in for the reference's only shipped operator
+ * (src/add/add_kernel.cpp:173-189). */
+BLAZE_API int blazeAddF32(const void* A, const void* C, void* D, int64_t n, void* stream);
+
+/* Device status word of the current device: 0 while every kernel wait completed, else the code of the first
+ * wait that gave up (see DeviceStatus in csrc/ptx.cuh).  Synchronises the device.  reset != 0 clears it. */
+BLAZE_API int blazeDeviceStatus(int32_t* value, int32_t reset);
+
+/* SM count and compute capability of the current device (the handle's device query). */
+BLAZE_API int blazeDeviceInfo(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BLAZE_B200_H */

@@ -1,0 +1,432 @@
+// G2 / G3 / G4: persistent FP8 (E4M3) GEMM with float32 scales, one per 1x128 K-group of A and one per 128x128 block
+// of B, in three flavours chosen at launch: dense data-parallel, dense stream-K (split along K with a
+// deterministic fix-up, for skinny or K-heavy shapes) and grouped (per-expert B, rows of A partitioned by a
+// device-side group list).
+//
+//   D[m,n] (bf16) = act( sum_kb sa[m,kb] * sb[g,kb,n/128] * (sum_{k in kb} A[m,k] * B[g,n,k]) + bias[n] ) + residual[m,n]
+//
+// The reference names these modes (QuantMode PERGROUP/PERBLOCK, include/blaze/gemm/utils/common_utils.h:98-107;
+// PER_BLOCK_SIZE = 128, :59; 128-aligned tail tiles in include/blaze/gemm/block/block_scheduler_qbmm.h:212-223;
+// groupListGmAddr in include/blaze/gemm/block/block_mmad_matmul_basic.h:68) without implementing them; the split of
+// work along K with an fp32 workspace and an ordered reduction follows its stream-K kernel
+// (include/blaze/gemm/kernel/kernel_matmul_streamk.h:98-228,
+//  include/blaze/epilogue/block/block_epilogue_matmul_streamk.h:123-184).
+//
+// float32 scales cannot ride on the hardware block-scale path, so every 128-deep K block is multiplied into a
+// fresh TMEM accumulator (4 stages of 128 columns) and promoted into registers by the epilogue warps:
+// acc += (sa * sb) * block, while the tensor core works on the next blocks.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace blaze {
+
+constexpr int kFp8MaxGroups = 1024;
+
+struct Fp8GemmParams {
+    int M, N, K;                    // M = total rows of A (all groups)
+    int n_tiles, k_blocks;
+    int m_tiles;                    // dense: ceil(M/128); grouped: unused
+    int window;
+    int groups;                     // 0 = dense
+    const long long* group_rows;    // device int64[groups]
+    const float* sa;                // [M][k_blocks]
+    const float* sb;                // [groups or 1][k_blocks][n_blocks]
+    int n_blocks;                   // ceil(N/128)
+    const __nv_bfloat16* bias;      // [N] or nullptr
+    const __nv_bfloat16* residual;  // [M][ldr] or nullptr
+    long long ldr;
+    __nv_bfloat16* D;
+    long long ldd;
+    int stream_k;                   // 1: split the (tile, k-block) units evenly over the grid
+    float* partials;                // [gridDim.x][128 cols][128 rows] fp32 (stream-K only)
+    int* flags;                     // [gridDim.x], zeroed before the launch (stream-K only)
+    int* status;
+};
+
+template <int kStages>
+struct Fp8GemmSmem {
+    static constexpr int kTile = 128;
+    static constexpr int kABytes = kTile * kTile;
+    static constexpr int kBBytes = kTile * kTile;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarOffset = kStages * kStageBytes;
+    static constexpr int kAccStages = 4;
+    // full[kStages], empty[kStages], tmem_full[4], tmem_empty[4], fixup
+    static constexpr int kNumBars = 2 * kStages + 2 * kAccStages + 1;
+    static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
+    static constexpr int kGroupOffset = kMiscOffset + 16;       // int row_start[G+1], int mtile_start[G+1]
+    static constexpr int kTotal = kGroupOffset + 2 * (kFp8MaxGroups + 1) * 4;
+    static constexpr int kDynamicBytes = kTotal + 1024;
+    static constexpr uint32_t kTxBytes = kABytes + kBBytes;
+};
+
+// One unit of work: K blocks [kb0, kb1) of one output tile.
+struct Fp8Segment {
+    int m0;          // first row of A / D
+    int row_end;     // rows >= row_end are not stored
+    int nt;          // N tile
+    int group;       // expert (0 when dense)
+    int kb0, kb1;
+    int tile;        // linear tile id (stream-K bookkeeping)
+};
+
+// Walks the segments of this CTA.  Every warp role instantiates one with identical arguments, so all roles see
+// the same sequence.
+struct Fp8WorkWalker {
+    const Fp8GemmParams& p;
+    const int* row_start;     // shared memory, grouped only
+    const int* mtile_start;   // shared memory, grouped only
+    int total_m_tiles;
+    int num_tiles;
+    // data-parallel state
+    int next_tile;
+    // stream-K state
+    long long unit, unit_end;
+
+    __device__ Fp8WorkWalker(const Fp8GemmParams& p_, const int* row_start_, const int* mtile_start_)
+        : p(p_), row_start(row_start_), mtile_start(mtile_start_) {
+        total_m_tiles = p.groups > 0 ? mtile_start[p.groups] : p.m_tiles;
+        num_tiles = total_m_tiles * p.n_tiles;
+        next_tile = blockIdx.x;
+        const long long total = (long long)num_tiles * p.k_blocks;
+        unit = total * blockIdx.x / gridDim.x;
+        unit_end = total * (blockIdx.x + 1) / gridDim.x;
+    }
+
+    __device__ void locate(int t, Fp8Segment& s) const {
+        s.tile = t;
+        if (p.groups > 0) {
+            const int gm = t / p.n_tiles;
+            s.nt = t - gm * p.n_tiles;
+            int lo = 0, hi = p.groups;            // largest g with mtile_start[g] <= gm
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (mtile_start[mid] <= gm) lo = mid; else hi = mid;
+            }
+            s.group = lo;
+            s.m0 = row_start[lo] + (gm - mtile_start[lo]) * 128;
+            s.row_end = row_start[lo + 1];
+        } else {
+            int mt;
+            tile_coords_fp8(t, mt, s.nt);
+            s.group = 0;
+            s.m0 = mt * 128;
+            s.row_end = p.M;
+        }
+    }
+
+    __device__ void tile_coords_fp8(int t, int& mt, int& nt) const {
+        const int band_tiles = p.window * p.n_tiles;
+        const int band = t / band_tiles;
+        const int rows = min(p.window, p.m_tiles - band * p.window);
+        const int r = t - band * band_tiles;
+        const int n_idx = r / rows;
+        mt = band * p.window + (r - n_idx * rows);
+        nt = (band & 1) ? (p.n_tiles - 1 - n_idx) : n_idx;
+    }
+
+    __device__ bool next(Fp8Segment& s) {
+        if (p.stream_k) {
+            if (unit >= unit_end) return false;
+            const int t = (int)(unit / p.k_blocks);
+            const int kb = (int)(unit - (long long)t * p.k_blocks);
+            const long long room = unit_end - unit;
+            const int kb1 = (int)min((long long)p.k_blocks, kb + room);
+            locate(t, s);
+            s.kb0 = kb;
+            s.kb1 = kb1;
+            unit += kb1 - kb;
+            return true;
+        }
+        if (next_tile >= num_tiles) return false;
+        locate(next_tile, s);
+        s.kb0 = 0;
+        s.kb1 = p.k_blocks;
+        next_tile += gridDim.x;
+        return true;
+    }
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* ptr) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* ptr, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+
+template <int kStages, int kAct>
+__global__ void __launch_bounds__(192, 1)
+fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const Fp8GemmParams p) {
+    using L = Fp8GemmSmem<kStages>;
+    constexpr int kAccStages = L::kAccStages;
+    constexpr uint32_t kTmemCols = 512;
+
+    extern __shared__ uint8_t smem_unaligned[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + kStages;
+    uint64_t* tmem_full_bar = bars + 2 * kStages;
+    uint64_t* tmem_empty_bar = tmem_full_bar + kAccStages;
+    uint64_t* fix_bar = tmem_empty_bar + kAccStages;
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
+    int* row_start = reinterpret_cast<int*>(smem + L::kGroupOffset);
+    int* mtile_start = row_start + (kFp8MaxGroups + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int s = 0; s < kAccStages; ++s) {
+            mbar_init(&tmem_full_bar[s], 1);
+            mbar_init(&tmem_empty_bar[s], 4);
+        }
+        mbar_init(fix_bar, 128);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (threadIdx.x == 32 && p.groups > 0) {
+        // prefix sums of rows and of 128-row tiles over the group list
+        int rows = 0, tiles = 0;
+        for (int g = 0; g < p.groups; ++g) {
+            row_start[g] = rows;
+            mtile_start[g] = tiles;
+            long long r = p.group_rows[g];
+            if (r < 0) r = 0;
+            if (rows + r > p.M) r = p.M - rows;          // never step outside A
+            rows += (int)r;
+            tiles += (int)((r + 127) >> 7);
+        }
+        row_start[p.groups] = rows;
+        mtile_start[p.groups] = tiles;
+    }
+    if (warp == 5) {
+        tmem_alloc<1>(tmem_base_slot, kTmemCols);
+    }
+    if (warp == 4 && lane == 0) {
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            Fp8WorkWalker walk(p, row_start, mtile_start);
+            Fp8Segment seg;
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            // B is streamed once when there is a single row of tiles; keep A (re-read by every N tile) instead
+            const uint64_t b_hint = (p.groups == 0 && p.m_tiles == 1) ? kEvictFirst : kEvictNormal;
+            while (ok && walk.next(seg)) {
+                const int b_row = seg.group * p.N + seg.nt * 128;
+                for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
+                    ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
+                    if (!ok) break;
+                    uint8_t* a_dst = smem + stage * L::kStageBytes;
+                    uint8_t* b_dst = a_dst + L::kABytes;
+                    mbar_arrive_expect_tx(&full_bar[stage], L::kTxBytes);
+                    tma_load_2d(a_dst, &tmap_a, &full_bar[stage], kb * 128, seg.m0, kEvictNormal);
+                    tma_load_2d(b_dst, &tmap_b, &full_bar[stage], kb * 128, b_row, b_hint);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            Fp8WorkWalker walk(p, row_start, mtile_start);
+            Fp8Segment seg;
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            constexpr uint32_t idesc = umma_idesc_f8(FMT_E4M3, FMT_E4M3, 128, 128);
+            while (ok && walk.next(seg)) {
+                for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
+                    ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                    if (!ok) break;
+                    ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
+                    const uint64_t a_desc = umma_desc_sw128(a_addr);
+                    const uint64_t b_desc = umma_desc_sw128(a_addr + L::kABytes);
+                    const uint32_t d_tmem = tmem_base + acc * 128;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        umma_f8<1>(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, j != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[stage]);
+                    umma_commit(&tmem_full_bar[acc]);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ promotion + epilogue warps 0..3
+        Fp8WorkWalker walk(p, row_start, mtile_start);
+        Fp8Segment seg;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const int r_in_tile = warp * 32 + lane;
+        while (ok && walk.next(seg)) {
+            const int row = seg.m0 + r_in_tile;
+            const bool row_ok = row < seg.row_end;
+            const bool warp_has_rows = seg.m0 + warp * 32 < seg.row_end;      // warp-uniform
+            const float* sa_row = p.sa + (long long)(row_ok ? row : 0) * p.k_blocks;
+            const float* sb_col = p.sb + (long long)seg.group * p.k_blocks * p.n_blocks + seg.nt;
+            float accum[128];
+#pragma unroll
+            for (int j = 0; j < 128; ++j) accum[j] = 0.0f;
+
+            float s_next = row_ok ? __ldg(sa_row + seg.kb0) * __ldg(sb_col + (long long)seg.kb0 * p.n_blocks) : 0.0f;
+            for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
+                const float s = s_next;
+                if (kb + 1 < seg.kb1 && row_ok) {
+                    s_next = __ldg(sa_row + kb + 1) * __ldg(sb_col + (long long)(kb + 1) * p.n_blocks);
+                }
+                ok = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tcgen05_fence_after();
+                if (warp_has_rows) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t v[32];
+                        tmem_ld_32x32(tmem_base + lane_base + acc * 128 + c * 32, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            accum[c * 32 + e] = fmaf(__uint_as_float(v[e]), s, accum[c * 32 + e]);
+                        }
+                    }
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+                if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+            }
+            if (!ok) break;
+
+            const bool full_tile = (seg.kb0 == 0 && seg.kb1 == p.k_blocks);
+            if (!full_tile && seg.kb0 > 0) {
+                // -------- contributor: publish the partial tile, column-major so that a warp writes 128 contiguous bytes
+                float* slot = p.partials + (size_t)blockIdx.x * (128 * 128);
+                if (row_ok) {
+#pragma unroll
+                    for (int j = 0; j < 128; ++j) __stcg(slot + j * 128 + r_in_tile, accum[j]);
+                }
+                __threadfence();
+                mbar_arrive(fix_bar);
+                if (threadIdx.x == 0) {
+                    if (mbar_wait(fix_bar, 0, abort_flag, p.status, DEV_TIMEOUT_FIXUP_FLAG)) {
+                        __threadfence();
+                        st_release_gpu(p.flags + blockIdx.x, 1);
+                    }
+                }
+                continue;
+            }
+            if (!full_tile) {
+                // -------- owner of a split tile: add the later K ranges in CTA order
+                const long long total = (long long)walk.num_tiles * p.k_blocks;
+                const long long tile_end = (long long)(seg.tile + 1) * p.k_blocks;
+                for (int j = blockIdx.x + 1; j < (int)gridDim.x; ++j) {
+                    const long long lo_j = total * j / gridDim.x;
+                    if (lo_j >= tile_end) break;
+                    const long long t0 = clock64();
+                    while (ld_acquire_gpu(p.flags + j) == 0) {
+                        if (*abort_flag != 0) { ok = false; break; }
+                        if (clock64() - t0 > BLAZE_WAIT_LIMIT_CYCLES) {
+                            *abort_flag = 1;
+                            atomicCAS(p.status, 0, DEV_TIMEOUT_FIXUP_FLAG);
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(64);
+                    }
+                    if (!ok) break;
+                    const float* slot = p.partials + (size_t)j * (128 * 128);
+                    if (row_ok) {
+#pragma unroll
+                        for (int c = 0; c < 128; ++c) accum[c] += __ldcg(slot + c * 128 + r_in_tile);
+                    }
+                }
+                ok = __all_sync(0xffffffffu, ok);      // also re-converges the warp after the per-thread polling
+                if (!ok) break;
+            }
+
+            // -------- fused epilogue: bias, activation, residual, bf16
+            if (row_ok) {
+                __nv_bfloat16* d_row = p.D + (long long)row * p.ldd;
+                const __nv_bfloat16* r_row = p.residual ? p.residual + (long long)row * p.ldr : nullptr;
+#pragma unroll
+                for (int q = 0; q < 16; ++q) {
+                    const int n = seg.nt * 128 + q * 8;
+                    if (n < p.N) {
+                        float x[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) x[e] = accum[q * 8 + e];
+                        if (p.bias) {
+                            const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
+                            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                x[2 * e] += __uint_as_float(bw[e] << 16);
+                                x[2 * e + 1] += __uint_as_float(bw[e] & 0xFFFF0000u);
+                            }
+                        }
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) x[e] = apply_act<kAct>(x[e]);
+                        if (r_row) {
+                            const uint4 rv = *reinterpret_cast<const uint4*>(r_row + n);
+                            const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                x[2 * e] += __uint_as_float(rw[e] << 16);
+                                x[2 * e + 1] += __uint_as_float(rw[e] & 0xFFFF0000u);
+                            }
+                        }
+                        uint4 o;
+                        o.x = pack_bf16(x[0], x[1]);
+                        o.y = pack_bf16(x[2], x[3]);
+                        o.z = pack_bf16(x[4], x[5]);
+                        o.w = pack_bf16(x[6], x[7]);
+                        *reinterpret_cast<uint4*>(d_row + n) = o;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    __syncthreads();
+    if (*abort_flag != 0) {
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+        __syncthreads();
+    }
+    if (warp == 5) {
+        __syncwarp();
+        tcgen05_fence_after();
+        tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace blaze

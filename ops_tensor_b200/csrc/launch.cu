@@ -1,0 +1,478 @@
+// C-ABI layer of the kernel library: argument checking, workspace carving, TMA descriptor encoding, tile/grid
+// heuristics and the kernel launches themselves.  Nothing here allocates per call; the only allocation is the
+// 4-byte per-device status word made on first use of a device.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "blaze_b200.h"
+#include "cann_ops_tensor_types.h"
+#include "gemm_fp8.cuh"
+#include "gemm_mx.cuh"
+#include "launch.h"
+
+namespace blaze {
+
+// ------------------------------------------------------------------------------------------------ device context
+
+static std::mutex g_ctx_mutex;
+static DeviceContext g_ctx[64];
+
+DeviceContext* current_context() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    DeviceContext& c = g_ctx[dev];
+    if (c.device == dev) return &c;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    int* word = nullptr;
+    if (cudaMalloc(&word, 256) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    cudaMemset(word, 0, 256);
+    c.sm_count = prop.multiProcessorCount;
+    c.cc_major = prop.major;
+    c.cc_minor = prop.minor;
+    c.status_word = word;
+    c.device = dev;
+    return &c;
+}
+
+// ------------------------------------------------------------------------------------------------ tensor maps
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// Byte matrix [rows][row_bytes valid, pitch bytes apart], boxes of 128 bytes x box_rows, 128-byte swizzle, zero fill
+// outside the matrix.
+static bool make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t pitch,
+                            uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {pitch};
+    const cuuint32_t box[2] = {128, box_rows};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                          elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+static inline size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
+
+static int status_of(cudaError_t e) {
+    if (e == cudaSuccess) return ACLTENSOR_STATUS_SUCCESS;
+    cudaGetLastError();
+    return ACLTENSOR_STATUS_EXECUTION_FAILED;
+}
+
+// ------------------------------------------------------------------------------------------------ MX GEMM
+
+struct MxPlan {
+    int tile_n;
+    int m_tiles, n_tiles, k_steps;
+    size_t sfa_bytes, sfb_bytes, b_expand_bytes;
+    size_t sfa_off, sfb_off, b_expand_off, total;
+};
+
+static int choose_tile_n(int M, int N, int sms, int requested) {
+    if (requested == 128 || requested == 224) return requested;
+    if (N <= 128) return 128;
+    const long long mt = (M + 127) / 128;
+    auto cost = [&](int bn) {
+        const long long tiles = mt * ((N + bn - 1) / bn);
+        const long long waves = (tiles + sms - 1) / sms;
+        return waves * (bn + 24);            // per-tile time ~ tile width plus a fixed ramp
+    };
+    return cost(224) <= cost(128) ? 224 : 128;
+}
+
+static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl) {
+    if (!a || a->struct_size != sizeof(blazeMxGemmArgs)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->M < 0 || a->N < 0 || a->K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->b_elem != BLAZE_ELEM_E4M3 && a->b_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_GELU_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->tile_n != 0 && a->tile_n != 128 && a->tile_n != 224) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if ((a->K % 16) != 0 || (a->N % 8) != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    pl->tile_n = choose_tile_n(a->M, a->N, sms, a->tile_n);
+    pl->m_tiles = (a->M + 127) / 128;
+    pl->n_tiles = (a->N + pl->tile_n - 1) / pl->tile_n;
+    pl->k_steps = (a->K + 127) / 128;
+    pl->sfa_bytes = (size_t)sf_tiled_bytes(a->M, a->K, 128);
+    pl->sfb_bytes = (size_t)sf_tiled_bytes(a->N, a->K, pl->tile_n);
+    pl->b_expand_bytes = a->b_elem == BLAZE_ELEM_E2M1 ? (size_t)a->N * (size_t)a->K : 0;
+    pl->sfa_off = 0;
+    pl->sfb_off = round256(pl->sfa_bytes);
+    pl->b_expand_off = pl->sfb_off + round256(pl->sfb_bytes);
+    pl->total = pl->b_expand_off + round256(pl->b_expand_bytes);
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+template <int kBN, int kAct>
+static cudaError_t launch_mx_instance(const CUtensorMap& ta, const CUtensorMap& tb, const MxGemmParams& p, int grid,
+                                      cudaStream_t stream) {
+    constexpr int kStages = 4;
+    using L = MxGemmSmem<kBN, kStages>;
+    auto kernel = mx_gemm_kernel<kBN, kStages, kAct>;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+        if (e != cudaSuccess) return e;
+        attr_done[dev & 63] = true;
+    }
+    kernel<<<grid, 192, L::kDynamicBytes, stream>>>(ta, tb, p);
+    return cudaGetLastError();
+}
+
+template <int kBN>
+static cudaError_t launch_mx_act(int act, const CUtensorMap& ta, const CUtensorMap& tb, const MxGemmParams& p, int grid,
+                                 cudaStream_t stream) {
+    switch (act) {
+        case BLAZE_ACT_RELU: return launch_mx_instance<kBN, ACT_RELU>(ta, tb, p, grid, stream);
+        case BLAZE_ACT_GELU_TANH: return launch_mx_instance<kBN, ACT_GELU_TANH>(ta, tb, p, grid, stream);
+        default: return launch_mx_instance<kBN, ACT_IDENTITY>(ta, tb, p, grid, stream);
+    }
+}
+
+}  // namespace blaze
+
+using namespace blaze;
+
+extern "C" int blazeMxGemmWorkspaceSize(const blazeMxGemmArgs* args, size_t* bytes) {
+    if (!bytes) return ACLTENSOR_STATUS_INVALID_VALUE;
+    DeviceContext* ctx = current_context();
+    const int sms = ctx ? ctx->sm_count : 148;
+    MxPlan pl;
+    const int st = plan_mx(args, sms, &pl);
+    if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    *bytes = pl.total;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
+    DeviceContext* ctx = current_context();
+    if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    if (ctx->cc_major != 10) return ACLTENSOR_STATUS_ARCH_MISMATCH;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    MxPlan pl;
+    int st = plan_mx(a, ctx->sm_count, &pl);
+    if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    if (a->M == 0 || a->N == 0) return ACLTENSOR_STATUS_SUCCESS;
+    if (!a->A || !a->B || !a->scaleA || !a->scaleB || !a->D) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->K == 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    const int64_t min_ldb = a->b_elem == BLAZE_ELEM_E2M1 ? a->K / 2 : a->K;
+    if (a->lda < a->K || a->ldb < min_ldb || a->ldd < a->N || (a->residual && a->ldr < a->N))
+        return ACLTENSOR_STATUS_INVALID_VALUE;
+    if ((a->lda % 16) || (a->ldb % 16) || (a->ldd % 8) || (a->residual && (a->ldr % 8)))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (!aligned16(a->A) || !aligned16(a->B) || !aligned16(a->D) || !aligned16(a->bias) || !aligned16(a->residual))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->b_elem == BLAZE_ELEM_E2M1 && (a->ldb % 8)) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (pl.total > 0 && (!a->workspace || a->workspace_bytes < pl.total)) return ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(a->workspace) & 255) return ACLTENSOR_STATUS_INVALID_VALUE;
+
+    uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+    uint8_t* sfa_tiled = ws + pl.sfa_off;
+    uint8_t* sfb_tiled = ws + pl.sfb_off;
+    const uint8_t* b_codes = static_cast<const uint8_t*>(a->B);
+    int64_t b_pitch = a->ldb;
+
+    cudaError_t e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleA), a->M, a->K, 128, sfa_tiled, ctx->sm_count,
+                                     stream);
+    if (e != cudaSuccess) return status_of(e);
+    if (a->b_elem == BLAZE_ELEM_E2M1) {
+        b_codes = ws + pl.b_expand_off;
+        b_pitch = a->K;
+    }
+    if (!a->reuse_b_prepass) {
+        e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleB), a->N, a->K, pl.tile_n, sfb_tiled, ctx->sm_count,
+                             stream);
+        if (e != cudaSuccess) return status_of(e);
+        if (a->b_elem == BLAZE_ELEM_E2M1) {
+            e = launch_e2m1_expand(static_cast<const uint8_t*>(a->B), a->ldb, a->N, a->K, ws + pl.b_expand_off, a->K,
+                                   ctx->sm_count, stream);
+            if (e != cudaSuccess) return status_of(e);
+        }
+    }
+
+    CUtensorMap ta, tb;
+    if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
+        !make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n))
+        return ACLTENSOR_STATUS_INTERNAL_ERROR;
+
+    MxGemmParams p;
+    p.M = a->M; p.N = a->N; p.K = a->K;
+    p.m_tiles = pl.m_tiles; p.n_tiles = pl.n_tiles; p.k_steps = pl.k_steps;
+    p.window = pl.m_tiles < 16 ? pl.m_tiles : 16;
+    p.sfa_tiled = sfa_tiled;
+    p.sfb_tiled = sfb_tiled;
+    p.bias = static_cast<const __nv_bfloat16*>(a->bias);
+    p.residual = static_cast<const __nv_bfloat16*>(a->residual);
+    p.ldr = a->ldr;
+    p.D = static_cast<__nv_bfloat16*>(a->D);
+    p.ldd = a->ldd;
+    p.status = ctx->status_word;
+
+    const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
+    int sms = ctx->sm_count;
+    if (a->sm_limit > 0 && a->sm_limit < sms) sms = a->sm_limit;
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    if (pl.tile_n == 224)
+        e = launch_mx_act<224>(a->activation, ta, tb, p, grid, stream);
+    else
+        e = launch_mx_act<128>(a->activation, ta, tb, p, grid, stream);
+    return status_of(e);
+}
+
+// ------------------------------------------------------------------------------------------------ FP8 GEMM
+
+namespace blaze {
+
+struct Fp8Plan {
+    int m_tiles, n_tiles, k_blocks;
+    int grid;
+    int stream_k;
+    size_t flags_bytes, partial_bytes, total;
+};
+
+static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
+    if (!a || a->struct_size != sizeof(blazeFp8GemmArgs)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->M < 0 || a->N < 0 || a->K < 0 || a->groups < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->groups > kFp8MaxGroups) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_GELU_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->sched < BLAZE_SCHED_AUTO || a->sched > BLAZE_SCHED_STREAM_K) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if ((a->K % 16) != 0 || (a->N % 8) != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->groups > 0 && a->sched == BLAZE_SCHED_STREAM_K) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    int sms = sm_count;
+    if (a->sm_limit > 0 && a->sm_limit < sms) sms = a->sm_limit;
+    pl->n_tiles = (a->N + 127) / 128;
+    pl->k_blocks = (a->K + 127) / 128;
+    pl->m_tiles = a->groups > 0 ? (a->M + 127) / 128 + a->groups : (a->M + 127) / 128;   // grouped: upper bound
+    const long long tiles = (long long)pl->m_tiles * pl->n_tiles;
+    int stream_k = 0;
+    if (a->groups == 0 && tiles > 0 && pl->k_blocks >= 2) {
+        if (a->sched == BLAZE_SCHED_STREAM_K) {
+            stream_k = 1;
+        } else if (a->sched == BLAZE_SCHED_AUTO && pl->k_blocks >= 8) {
+            const long long waves = (tiles + sms - 1) / sms;
+            const double fill = (double)tiles / (double)(waves * sms);
+            if (fill < 0.8) stream_k = 1;      // a poorly filled last wave: split along K instead
+        }
+    }
+    pl->stream_k = stream_k;
+    long long grid = tiles < sms ? tiles : sms;
+    if (stream_k) {
+        const long long units = tiles * pl->k_blocks;
+        grid = units < sms ? units : sms;
+    }
+    if (grid < 1) grid = 1;
+    pl->grid = (int)grid;
+    pl->flags_bytes = stream_k ? round256((size_t)grid * sizeof(int)) : 0;
+    pl->partial_bytes = stream_k ? (size_t)grid * 128 * 128 * sizeof(float) : 0;
+    pl->total = pl->flags_bytes + pl->partial_bytes;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+template <int kAct>
+static cudaError_t launch_fp8_instance(const CUtensorMap& ta, const CUtensorMap& tb, const Fp8GemmParams& p, int grid,
+                                       cudaStream_t stream) {
+    constexpr int kStages = 6;
+    using L = Fp8GemmSmem<kStages>;
+    auto kernel = fp8_gemm_kernel<kStages, kAct>;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+        if (e != cudaSuccess) return e;
+        attr_done[dev & 63] = true;
+    }
+    kernel<<<grid, 192, L::kDynamicBytes, stream>>>(ta, tb, p);
+    return cudaGetLastError();
+}
+
+}  // namespace blaze
+
+extern "C" int blazeFp8GemmWorkspaceSize(const blazeFp8GemmArgs* args, size_t* bytes) {
+    if (!bytes) return ACLTENSOR_STATUS_INVALID_VALUE;
+    DeviceContext* ctx = current_context();
+    Fp8Plan pl;
+    const int st = plan_fp8(args, ctx ? ctx->sm_count : 148, &pl);
+    if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    *bytes = pl.total;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
+    DeviceContext* ctx = current_context();
+    if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    if (ctx->cc_major != 10) return ACLTENSOR_STATUS_ARCH_MISMATCH;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    Fp8Plan pl;
+    int st = plan_fp8(a, ctx->sm_count, &pl);
+    if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    if (a->M == 0 || a->N == 0) return ACLTENSOR_STATUS_SUCCESS;
+    if (!a->A || !a->B || !a->scaleA || !a->scaleB || !a->D) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->groups > 0 && !a->group_rows) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->K == 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->lda < a->K || a->ldb < a->K || a->ldd < a->N || (a->residual && a->ldr < a->N))
+        return ACLTENSOR_STATUS_INVALID_VALUE;
+    if ((a->lda % 16) || (a->ldb % 16) || (a->ldd % 8) || (a->residual && (a->ldr % 8)))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (!aligned16(a->A) || !aligned16(a->B) || !aligned16(a->D) || !aligned16(a->bias) || !aligned16(a->residual))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (pl.total > 0 && (!a->workspace || a->workspace_bytes < pl.total)) return ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE;
+    if (pl.total > 0 && (reinterpret_cast<uintptr_t>(a->workspace) & 255)) return ACLTENSOR_STATUS_INVALID_VALUE;
+
+    const int groups = a->groups;
+    const uint64_t b_rows = (uint64_t)(groups > 0 ? groups : 1) * (uint64_t)a->N;
+    CUtensorMap ta, tb;
+    if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
+        !make_tmap_bytes(&tb, a->B, (uint64_t)a->K, b_rows, (uint64_t)a->ldb, 128))
+        return ACLTENSOR_STATUS_INTERNAL_ERROR;
+
+    Fp8GemmParams p;
+    p.M = a->M; p.N = a->N; p.K = a->K;
+    p.n_tiles = pl.n_tiles; p.k_blocks = pl.k_blocks;
+    p.m_tiles = (a->M + 127) / 128;
+    p.window = p.m_tiles < 8 ? p.m_tiles : 8;
+    if (p.window < 1) p.window = 1;
+    p.groups = groups;
+    p.group_rows = static_cast<const long long*>(a->group_rows);
+    p.sa = static_cast<const float*>(a->scaleA);
+    p.sb = static_cast<const float*>(a->scaleB);
+    p.n_blocks = (a->N + 127) / 128;
+    p.bias = static_cast<const __nv_bfloat16*>(a->bias);
+    p.residual = static_cast<const __nv_bfloat16*>(a->residual);
+    p.ldr = a->ldr;
+    p.D = static_cast<__nv_bfloat16*>(a->D);
+    p.ldd = a->ldd;
+    p.stream_k = pl.stream_k;
+    p.flags = nullptr;
+    p.partials = nullptr;
+    p.status = ctx->status_word;
+    if (pl.stream_k) {
+        p.flags = static_cast<int*>(a->workspace);
+        p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + pl.flags_bytes);
+        cudaError_t e = cudaMemsetAsync(p.flags, 0, pl.flags_bytes, stream);
+        if (e != cudaSuccess) return status_of(e);
+    }
+    cudaError_t e;
+    switch (a->activation) {
+        case BLAZE_ACT_RELU: e = launch_fp8_instance<ACT_RELU>(ta, tb, p, pl.grid, stream); break;
+        case BLAZE_ACT_GELU_TANH: e = launch_fp8_instance<ACT_GELU_TANH>(ta, tb, p, pl.grid, stream); break;
+        default: e = launch_fp8_instance<ACT_IDENTITY>(ta, tb, p, pl.grid, stream); break;
+    }
+    return status_of(e);
+}
+
+// ------------------------------------------------------------------------------------------------ quantisers & misc
+
+extern "C" int blazeQuantizeMx(const void* x, int64_t ldx, int32_t rows, int32_t K, int32_t elem, void* codes,
+                               int64_t ld_codes, void* scales, void* stream) {
+    if (rows < 0 || K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (rows == 0 || K == 0) return ACLTENSOR_STATUS_SUCCESS;
+    if (!x || !codes || !scales) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (elem != BLAZE_ELEM_E4M3 && elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if ((K % 4) || (ldx % 4) || !aligned16(x)) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    const int64_t min_ld = elem == BLAZE_ELEM_E2M1 ? K / 2 : K;
+    if (ldx < K || ld_codes < min_ld) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if ((ld_codes % (elem == BLAZE_ELEM_E2M1 ? 2 : 4)) || (reinterpret_cast<uintptr_t>(codes) & 3))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    DeviceContext* ctx = current_context();
+    if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    return status_of(launch_quant_mx(static_cast<const float*>(x), ldx, rows, K, elem == BLAZE_ELEM_E2M1,
+                                     static_cast<uint8_t*>(codes), ld_codes, static_cast<uint8_t*>(scales),
+                                     ctx->sm_count, static_cast<cudaStream_t>(stream)));
+}
+
+extern "C" int blazeQuantizeFp8RowGroups(const void* x, int64_t ldx, int32_t rows, int32_t K, void* codes,
+                                         int64_t ld_codes, void* scales, void* stream) {
+    if (rows < 0 || K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (rows == 0 || K == 0) return ACLTENSOR_STATUS_SUCCESS;
+    if (!x || !codes || !scales) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if ((K % 4) || (ldx % 4) || (ld_codes % 4) || !aligned16(x) || (reinterpret_cast<uintptr_t>(codes) & 3))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (ldx < K || ld_codes < K) return ACLTENSOR_STATUS_INVALID_VALUE;
+    DeviceContext* ctx = current_context();
+    if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    return status_of(launch_quant_fp8_1x128(static_cast<const float*>(x), ldx, rows, K, static_cast<uint8_t*>(codes),
+                                            ld_codes, static_cast<float*>(scales), ctx->sm_count,
+                                            static_cast<cudaStream_t>(stream)));
+}
+
+extern "C" int blazeQuantizeFp8Blocks(const void* w, int64_t ldw, int32_t N, int32_t K, void* codes, int64_t ld_codes,
+                                      void* scales, void* stream) {
+    if (N < 0 || K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (N == 0 || K == 0) return ACLTENSOR_STATUS_SUCCESS;
+    if (!w || !codes || !scales) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if ((K % 4) || (ldw % 4) || (ld_codes % 4) || !aligned16(w) || (reinterpret_cast<uintptr_t>(codes) & 3))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (ldw < K || ld_codes < K) return ACLTENSOR_STATUS_INVALID_VALUE;
+    DeviceContext* ctx = current_context();
+    if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    return status_of(launch_quant_fp8_128x128(static_cast<const float*>(w), ldw, N, K, static_cast<uint8_t*>(codes),
+                                              ld_codes, static_cast<float*>(scales), ctx->sm_count,
+                                              static_cast<cudaStream_t>(stream)));
+}
+
+extern "C" int blazeAddF32(const void* A, const void* C, void* D, int64_t n, void* stream) {
+    if (n < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (n == 0) return ACLTENSOR_STATUS_SUCCESS;
+    if (!A || !C || !D) return ACLTENSOR_STATUS_INVALID_VALUE;
+    DeviceContext* ctx = current_context();
+    if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    return status_of(launch_add_f32(static_cast<const float*>(A), static_cast<const float*>(C), static_cast<float*>(D),
+                                    n, ctx->sm_count, static_cast<cudaStream_t>(stream)));
+}
+
+extern "C" int blazeDeviceStatus(int32_t* value, int32_t reset) {
+    if (!value) return ACLTENSOR_STATUS_INVALID_VALUE;
+    DeviceContext* ctx = current_context();
+    if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    int v = 0;
+    if (cudaMemcpy(&v, ctx->status_word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return status_of(cudaErrorUnknown);
+    *value = v;
+    if (reset && v != 0) cudaMemset(ctx->status_word, 0, sizeof(int));
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+extern "C" int blazeDeviceInfo(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor) {
+    DeviceContext* ctx = current_context();
+    if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    if (sm_count) *sm_count = ctx->sm_count;
+    if (cc_major) *cc_major = ctx->cc_major;
+    if (cc_minor) *cc_minor = ctx->cc_minor;
+    return ACLTENSOR_STATUS_SUCCESS;
+}

@@ -1,0 +1,40 @@
+// Internal C++ declarations shared by the kernel translation units and the C-ABI layer.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+namespace blaze {
+
+struct DeviceContext {
+    int device = -1;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    int* status_word = nullptr;     // device int, zero while no kernel wait has given up
+};
+
+// Per-device context of the current device (created on first use; thread-safe).  nullptr if no usable device.
+DeviceContext* current_context();
+
+// Bytes of the re-tiled scale-factor array for `rows` x K with tiles of `tile_rows` rows.
+inline long long sf_tiled_bytes(int rows, int K, int tile_rows) {
+    const long long tiles = (rows + tile_rows - 1) / tile_rows;
+    const long long k_steps = (K + 127) / 128;
+    const long long atoms = (tile_rows + 127) / 128;
+    return tiles * k_steps * atoms * 512;
+}
+
+cudaError_t launch_quant_mx(const float* x, long long ldx, int rows, int K, bool e2m1, uint8_t* codes,
+                            long long ldc_bytes, uint8_t* scales, int sm_count, cudaStream_t stream);
+cudaError_t launch_quant_fp8_1x128(const float* x, long long ldx, int rows, int K, uint8_t* codes, long long ldc,
+                                   float* scales, int sm_count, cudaStream_t stream);
+cudaError_t launch_quant_fp8_128x128(const float* w, long long ldw, int N, int K, uint8_t* codes, long long ldc,
+                                     float* scales, int sm_count, cudaStream_t stream);
+cudaError_t launch_sf_retile(const uint8_t* in, int rows, int K, int tile_rows, uint8_t* out, int sm_count,
+                             cudaStream_t stream);
+cudaError_t launch_e2m1_expand(const uint8_t* in, long long ld_in, int rows, int K, uint8_t* out, long long ld_out,
+                               int sm_count, cudaStream_t stream);
+cudaError_t launch_add_f32(const float* a, const float* c, float* d, long long n, int sm_count, cudaStream_t stream);
+
+}  // namespace blaze

@@ -1,0 +1,312 @@
+// Q1-Q3 and the small data-layout kernels around the GEMMs.  All of them are HBM-bound streaming kernels: loads and
+// stores are 16-byte (or the widest the element allows) and fully coalesced per warp, grids are sized in multiples
+// of the SM count.
+//
+//   quant_mx          fp32 -> E4M3 or packed E2M1 codes + one E8M0 byte per 32 K        (MX formats)
+//   quant_fp8_1x128   fp32 -> E4M3 codes + one fp32 scale per 128 K of each row          (activations)
+//   quant_fp8_128x128 fp32 -> E4M3 codes + one fp32 scale per 128x128 block              (weights)
+//   sf_retile         row-major E8M0 scale rows -> the 32x16-byte blocks the tensor core's scale copy reads
+//   e2m1_expand       packed E2M1 -> E4M3 codes holding the same values                  (W4 weight pre-pass)
+//   add_f32           D = A + C                                                          (the one elementwise op)
+//
+// Rounding is IEEE round-to-nearest-even with saturation; divisions are IEEE (__fdiv_rn), so results are bit-equal
+// to the numpy oracle.  Scale layouts are the reference's: `[rows][ceil(K/64)*2]` bytes for MX
+// (include/blaze/gemm/kernel/kernel_qbmm_mx.h:383-385), low nibble = even K index for packed E2M1
+// (include/blaze/gemm/tile/arch35/shift_w4_to_w8.h:88-99).
+#include <cuda_fp8.h>
+#include <cuda_fp4.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "launch.h"
+
+namespace blaze {
+
+__device__ __forceinline__ uint8_t cvt_e4m3(float x) {
+    return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+}
+
+__device__ __forceinline__ uint8_t cvt_e2m1(float x) {
+    return (uint8_t)(__nv_cvt_float_to_fp4(x, __NV_E2M1, cudaRoundNearest) & 0xF);
+}
+
+// ---------------------------------------------------------------------------------------------------- MX
+
+// One warp handles 128 consecutive K of one row (4 groups of 32); 8 lanes share a group, 4 floats per lane.
+template <bool kE2M1>
+__global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__ x, long long ldx, int rows, int K,
+                                                       uint8_t* __restrict__ codes, long long ldc_bytes,
+                                                       uint8_t* __restrict__ scales, int scale_cols) {
+    const int chunks_per_row = (K + 127) >> 7;
+    const long long total = (long long)rows * chunks_per_row;
+    const int lane = threadIdx.x & 31;
+    const int emax = kE2M1 ? 2 : 8;
+    const int n_groups = (K + 31) >> 5;
+    for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < total;
+         w += (long long)gridDim.x * (blockDim.x >> 5)) {
+        const int row = (int)(w / chunks_per_row);
+        const int chunk = (int)(w - (long long)row * chunks_per_row);
+        const int k = chunk * 128 + lane * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < K) v = *reinterpret_cast<const float4*>(x + (long long)row * ldx + k);     // K is a multiple of 4
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        int has_nan = (v.x != v.x) | (v.y != v.y) | (v.z != v.z) | (v.w != v.w);
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            has_nan |= __shfl_xor_sync(0xffffffffu, has_nan, o);
+        }
+        const int field = (__float_as_uint(amax) >> 23) & 0xFF;
+        int byte = min(max(field - emax, 0), 254);
+        if (amax == 0.0f) byte = 127;
+        const int eff = byte;
+        if (has_nan) byte = 255;
+        const float inv = (eff == 254) ? __uint_as_float(0x00400000u) : __uint_as_float((uint32_t)(254 - eff) << 23);
+        const float q0 = v.x * inv, q1 = v.y * inv, q2 = v.z * inv, q3 = v.w * inv;
+        if (k < K) {
+            if (kE2M1) {
+                const uint16_t packed = (uint16_t)(cvt_e2m1(q0) | (cvt_e2m1(q1) << 4) | (cvt_e2m1(q2) << 8) |
+                                                   (cvt_e2m1(q3) << 12));
+                *reinterpret_cast<uint16_t*>(codes + (long long)row * ldc_bytes + (k >> 1)) = packed;
+            } else {
+                const uint32_t packed = (uint32_t)cvt_e4m3(q0) | ((uint32_t)cvt_e4m3(q1) << 8) |
+                                        ((uint32_t)cvt_e4m3(q2) << 16) | ((uint32_t)cvt_e4m3(q3) << 24);
+                *reinterpret_cast<uint32_t*>(codes + (long long)row * ldc_bytes + k) = packed;
+            }
+        }
+        const int g = chunk * 4 + (lane >> 3);
+        if ((lane & 7) == 0 && g < scale_cols) {
+            scales[(long long)row * scale_cols + g] = (g < n_groups) ? (uint8_t)byte : (uint8_t)127;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- FP8, fp32 scales
+
+// One warp per (row, 128-wide K group).
+__global__ void __launch_bounds__(256) quant_fp8_1x128_kernel(const float* __restrict__ x, long long ldx, int rows, int K,
+                                                              uint8_t* __restrict__ codes, long long ldc,
+                                                              float* __restrict__ scales, int k_blocks) {
+    const long long total = (long long)rows * k_blocks;
+    const int lane = threadIdx.x & 31;
+    for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < total;
+         w += (long long)gridDim.x * (blockDim.x >> 5)) {
+        const int row = (int)(w / k_blocks);
+        const int kb = (int)(w - (long long)row * k_blocks);
+        const int k = kb * 128 + lane * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < K) v = *reinterpret_cast<const float4*>(x + (long long)row * ldx + k);
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 448.0f);
+        if (k < K) {
+            const uint32_t packed = (uint32_t)cvt_e4m3(__fdiv_rn(v.x, scale)) | ((uint32_t)cvt_e4m3(__fdiv_rn(v.y, scale)) << 8) |
+                                    ((uint32_t)cvt_e4m3(__fdiv_rn(v.z, scale)) << 16) |
+                                    ((uint32_t)cvt_e4m3(__fdiv_rn(v.w, scale)) << 24);
+            *reinterpret_cast<uint32_t*>(codes + (long long)row * ldc + k) = packed;
+        }
+        if (lane == 0) scales[(long long)row * k_blocks + kb] = scale;
+    }
+}
+
+// One CTA (256 threads) per 128x128 block of a K-contiguous weight [N][K]; the block is read twice, the second
+// time out of L1/L2.
+__global__ void __launch_bounds__(256) quant_fp8_128x128_kernel(const float* __restrict__ w, long long ldw, int N, int K,
+                                                                uint8_t* __restrict__ codes, long long ldc,
+                                                                float* __restrict__ scales, int n_blocks, int k_blocks) {
+    __shared__ float warp_max[8];
+    __shared__ float block_scale;
+    const long long total = (long long)n_blocks * k_blocks;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (long long b = blockIdx.x; b < total; b += gridDim.x) {
+        const int nb = (int)(b / k_blocks);
+        const int kb = (int)(b - (long long)nb * k_blocks);
+        const int k = kb * 128 + lane * 4;
+        float amax = 0.0f;
+        for (int r = warp; r < 128; r += 8) {
+            const int n = nb * 128 + r;
+            if (n < N && k < K) {
+                const float4 v = *reinterpret_cast<const float4*>(w + (long long)n * ldw + k);
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            }
+        }
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (lane == 0) warp_max[warp] = amax;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float m = warp_max[0];
+            for (int i = 1; i < 8; ++i) m = fmaxf(m, warp_max[i]);
+            block_scale = (m == 0.0f) ? 1.0f : __fdiv_rn(m, 448.0f);
+            scales[(long long)kb * n_blocks + nb] = block_scale;
+        }
+        __syncthreads();
+        const float scale = block_scale;
+        for (int r = warp; r < 128; r += 8) {
+            const int n = nb * 128 + r;
+            if (n < N && k < K) {
+                const float4 v = *reinterpret_cast<const float4*>(w + (long long)n * ldw + k);
+                const uint32_t packed = (uint32_t)cvt_e4m3(__fdiv_rn(v.x, scale)) |
+                                        ((uint32_t)cvt_e4m3(__fdiv_rn(v.y, scale)) << 8) |
+                                        ((uint32_t)cvt_e4m3(__fdiv_rn(v.z, scale)) << 16) |
+                                        ((uint32_t)cvt_e4m3(__fdiv_rn(v.w, scale)) << 24);
+                *reinterpret_cast<uint32_t*>(codes + (long long)n * ldc + k) = packed;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- layout helpers
+
+// out[tile][k_step][atom][lane 0..31][quarter 0..3][kk 0..3] = scale[row][k_step*4 + kk],
+// row = tile*tile_rows + atom*128 + quarter*32 + lane; anything outside the matrix is 127 (2^0).
+__global__ void __launch_bounds__(256) sf_retile_kernel(const uint8_t* __restrict__ in, int rows, int scale_cols,
+                                                        int valid_groups, int tile_rows, int k_steps,
+                                                        uint32_t* __restrict__ out, long long out_words) {
+    const int atoms = (tile_rows + 127) >> 7;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < out_words;
+         i += (long long)gridDim.x * blockDim.x) {
+        long long r = i;
+        const int quarter = (int)(r & 3); r >>= 2;
+        const int lane = (int)(r & 31); r >>= 5;
+        const int atom = (int)(r % atoms); r /= atoms;
+        const int ks = (int)(r % k_steps);
+        const int tile = (int)(r / k_steps);
+        const int in_tile = atom * 128 + quarter * 32 + lane;
+        const int row = tile * tile_rows + in_tile;
+        uint32_t word = 0x7F7F7F7Fu;
+        if (in_tile < tile_rows && row < rows) {
+            word = 0;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                const int g = ks * 4 + kk;
+                const uint32_t b = (g < valid_groups && g < scale_cols) ? in[(long long)row * scale_cols + g] : 127u;
+                word |= b << (8 * kk);
+            }
+        }
+        out[i] = word;
+    }
+}
+
+// Each thread turns 8 packed bytes (16 E2M1 values) into 16 E4M3 bytes.
+__global__ void __launch_bounds__(256) e2m1_expand_kernel(const uint8_t* __restrict__ in, long long ld_in, int rows,
+                                                          int K, uint8_t* __restrict__ out, long long ld_out) {
+    const int vec_per_row = K >> 4;           // K is a multiple of 16
+    const long long total = (long long)rows * vec_per_row;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int row = (int)(i / vec_per_row);
+        const int v = (int)(i - (long long)row * vec_per_row);
+        const uint2 src = *reinterpret_cast<const uint2*>(in + (long long)row * ld_in + (long long)v * 8);
+        const uint32_t words[2] = {src.x, src.y};
+        uint32_t o[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                uint32_t acc = 0;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t nib = (words[h] >> (16 * q + 4 * e)) & 0xF;
+                    const uint32_t mag = nib & 7;
+                    // 0, .5, 1, 1.5, 2, 3, 4, 6 as E4M3 codes, one byte per magnitude
+                    const uint32_t code = (uint32_t)((0x4C4844403C383000ull >> (8 * mag)) & 0xFF) | ((nib & 8) << 4);
+                    acc |= code << (8 * e);
+                }
+                o[h * 2 + q] = acc;
+            }
+        }
+        *reinterpret_cast<uint4*>(out + (long long)row * ld_out + (long long)v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+__global__ void __launch_bounds__(256) add_f32_kernel(const float* __restrict__ a, const float* __restrict__ c,
+                                                      float* __restrict__ d, long long n) {
+    const long long n4 = n >> 2;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(d)) & 15) == 0;
+    if (aligned) {
+        for (long long i = tid; i < n4; i += stride) {
+            const float4 x = reinterpret_cast<const float4*>(a)[i];
+            const float4 y = reinterpret_cast<const float4*>(c)[i];
+            reinterpret_cast<float4*>(d)[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+        }
+        for (long long i = n4 * 4 + tid; i < n; i += stride) d[i] = a[i] + c[i];
+    } else {
+        for (long long i = tid; i < n; i += stride) d[i] = a[i] + c[i];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- launchers
+
+static int grid_for(long long work_items, int per_block, int sm_count) {
+    long long blocks = (work_items + per_block - 1) / per_block;
+    const long long cap = (long long)sm_count * 8;          // a multiple of the SM count
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+cudaError_t launch_quant_mx(const float* x, long long ldx, int rows, int K, bool e2m1, uint8_t* codes,
+                            long long ldc_bytes, uint8_t* scales, int sm_count, cudaStream_t stream) {
+    if (rows <= 0 || K <= 0) return cudaSuccess;
+    const long long warps = (long long)rows * ((K + 127) / 128);
+    const int grid = grid_for(warps, 8, sm_count);
+    const int scale_cols = ((K + 63) / 64) * 2;
+    if (e2m1)
+        quant_mx_kernel<true><<<grid, 256, 0, stream>>>(x, ldx, rows, K, codes, ldc_bytes, scales, scale_cols);
+    else
+        quant_mx_kernel<false><<<grid, 256, 0, stream>>>(x, ldx, rows, K, codes, ldc_bytes, scales, scale_cols);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_quant_fp8_1x128(const float* x, long long ldx, int rows, int K, uint8_t* codes, long long ldc,
+                                   float* scales, int sm_count, cudaStream_t stream) {
+    if (rows <= 0 || K <= 0) return cudaSuccess;
+    const int k_blocks = (K + 127) / 128;
+    const int grid = grid_for((long long)rows * k_blocks, 8, sm_count);
+    quant_fp8_1x128_kernel<<<grid, 256, 0, stream>>>(x, ldx, rows, K, codes, ldc, scales, k_blocks);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_quant_fp8_128x128(const float* w, long long ldw, int N, int K, uint8_t* codes, long long ldc,
+                                     float* scales, int sm_count, cudaStream_t stream) {
+    if (N <= 0 || K <= 0) return cudaSuccess;
+    const int n_blocks = (N + 127) / 128, k_blocks = (K + 127) / 128;
+    const int grid = grid_for((long long)n_blocks * k_blocks, 1, sm_count);
+    quant_fp8_128x128_kernel<<<grid, 256, 0, stream>>>(w, ldw, N, K, codes, ldc, scales, n_blocks, k_blocks);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_sf_retile(const uint8_t* in, int rows, int K, int tile_rows, uint8_t* out, int sm_count,
+                             cudaStream_t stream) {
+    const int scale_cols = ((K + 63) / 64) * 2;
+    const int valid_groups = (K + 31) / 32;
+    const int k_steps = (K + 127) / 128;
+    const long long words = sf_tiled_bytes(rows, K, tile_rows) / 4;
+    if (words <= 0) return cudaSuccess;
+    const int grid = grid_for(words, 256, sm_count);
+    sf_retile_kernel<<<grid, 256, 0, stream>>>(in, rows, scale_cols, valid_groups, tile_rows, k_steps,
+                                               reinterpret_cast<uint32_t*>(out), words);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_e2m1_expand(const uint8_t* in, long long ld_in, int rows, int K, uint8_t* out, long long ld_out,
+                               int sm_count, cudaStream_t stream) {
+    if (rows <= 0 || K <= 0) return cudaSuccess;
+    const int grid = grid_for((long long)rows * (K / 16), 256, sm_count);
+    e2m1_expand_kernel<<<grid, 256, 0, stream>>>(in, ld_in, rows, K, out, ld_out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_add_f32(const float* a, const float* c, float* d, long long n, int sm_count, cudaStream_t stream) {
+    if (n <= 0) return cudaSuccess;
+    const int grid = grid_for((n + 3) / 4, 256, sm_count);
+    add_f32_kernel<<<grid, 256, 0, stream>>>(a, c, d, n);
+    return cudaGetLastError();
+}
+
+}  // namespace blaze
