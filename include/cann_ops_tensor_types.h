@@ -133,6 +133,8 @@ typedef enum {
     ACLTENSOR_OPERATION_DESCRIPTOR_SPLIT_POLICY = 6,     /* int32: acltensorSplitPolicy_t */
     ACLTENSOR_OPERATION_DESCRIPTOR_TILE_N = 7,           /* int32: 0 = heuristic */
     ACLTENSOR_OPERATION_DESCRIPTOR_SM_LIMIT = 8,         /* int32: 0 = all SMs */
+    ACLTENSOR_OPERATION_DESCRIPTOR_B_IS_STATIC = 9,      /* int32: 1 = B and its scales do not change between calls,
+                                                            so weight pre-passes kept in the workspace are reused */
 } acltensorOperationDescriptorAttribute_t;
 
 /* Opaque handles (reference :128-132). */

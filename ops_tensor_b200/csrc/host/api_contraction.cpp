@@ -1,0 +1,450 @@
+// Quantized contraction: descriptor creation, attributes, workspace estimation, plan completion, execution, and
+// the two registered solutions (MX block-scaled and FP8 with float32 group/block scales) that forward to the
+// kernel C-ABI in launch.cu.
+//
+// The entry-point names are the ones the reference reserves (lib/core/operation_descriptor.cpp:183-189,
+// lib/core/plan_preference.cpp:58, docs/implementation.md:57-74); argument checking follows the conventions of its
+// implemented entry points: NULL required argument -> INVALID_VALUE, anything the build cannot do -> NOT_SUPPORTED.
+#include <cstring>
+#include <new>
+
+#include "blaze_b200.h"
+#include "cann_ops_tensor.h"
+#include "objects.hpp"
+#include "registry.hpp"
+
+using namespace acltensor;
+
+namespace {
+
+int find_mode(const std::vector<int32_t>& modes, int32_t label) {
+    for (size_t i = 0; i < modes.size(); ++i)
+        if (modes[i] == label) return static_cast<int>(i);
+    return -1;
+}
+
+int activation_of(int32_t op) {
+    switch (op) {
+        case ACLTENSOR_OP_IDENTITY: return BLAZE_ACT_IDENTITY;
+        case ACLTENSOR_OP_RELU: return BLAZE_ACT_RELU;
+        case ACLTENSOR_OP_GELU: return BLAZE_ACT_GELU_TANH;
+        default: return -1;
+    }
+}
+
+int sched_of(int32_t policy) {
+    switch (policy) {
+        case ACLTENSOR_SPLIT_DATA_PARALLEL: return BLAZE_SCHED_DATA_PARALLEL;
+        case ACLTENSOR_SPLIT_STREAM_K: return BLAZE_SCHED_STREAM_K;
+        default: return BLAZE_SCHED_AUTO;
+    }
+}
+
+bool fits_int32(int64_t v) { return v >= 0 && v <= 0x7fffffffLL; }
+
+// ---- MX solution ---------------------------------------------------------------------------------------------
+
+void fill_mx_args(const acltensorOperationDescriptor& op, blazeMxGemmArgs* a) {
+    std::memset(a, 0, sizeof(*a));
+    a->struct_size = sizeof(*a);
+    a->M = static_cast<int32_t>(op.M);
+    a->N = static_cast<int32_t>(op.N);
+    a->K = static_cast<int32_t>(op.K);
+    a->b_elem = op.descB->dataType == ACLTENSOR_R_4F_E2M1 ? BLAZE_ELEM_E2M1 : BLAZE_ELEM_E4M3;
+    a->lda = op.lda;                                                  // one byte per element
+    a->ldb = a->b_elem == BLAZE_ELEM_E2M1 ? op.ldb / 2 : op.ldb;      // bytes
+    a->ldr = op.ldc;
+    a->ldd = op.ldd;
+    a->activation = activation_of(op.epilogueAct);
+    a->tile_n = op.tileN;
+    a->sm_limit = op.smLimit;
+}
+
+acltensorStatus_t MxWorkspace(const acltensorOperationDescriptor& op, int32_t, uint64_t* bytes) {
+    blazeMxGemmArgs a;
+    fill_mx_args(op, &a);
+    size_t n = 0;
+    const int st = blazeMxGemmWorkspaceSize(&a, &n);
+    *bytes = n;
+    return static_cast<acltensorStatus_t>(st);
+}
+
+acltensorStatus_t MxExecute(const ContractionArgs& c) {
+    blazeMxGemmArgs a;
+    fill_mx_args(*c.op, &a);
+    a.A = c.A;
+    a.B = c.B;
+    a.scaleA = c.scaleA;
+    a.scaleB = c.scaleB;
+    a.bias = c.bias;
+    a.residual = c.C;
+    a.D = c.D;
+    a.reuse_b_prepass = c.reuseBPrepass ? 1 : 0;
+    a.workspace = c.workspace;
+    a.workspace_bytes = c.workspaceSize;
+    return static_cast<acltensorStatus_t>(blazeMxGemm(&a, c.stream));
+}
+
+// ---- FP8 solution --------------------------------------------------------------------------------------------
+
+void fill_fp8_args(const acltensorOperationDescriptor& op, int32_t splitPolicy, blazeFp8GemmArgs* a) {
+    std::memset(a, 0, sizeof(*a));
+    a->struct_size = sizeof(*a);
+    a->M = static_cast<int32_t>(op.M);
+    a->N = static_cast<int32_t>(op.N);
+    a->K = static_cast<int32_t>(op.K);
+    a->groups = op.groupCount;
+    a->lda = op.lda;
+    a->ldb = op.ldb;
+    a->ldr = op.ldc;
+    a->ldd = op.ldd;
+    a->activation = activation_of(op.epilogueAct);
+    a->sched = sched_of(splitPolicy);
+    a->sm_limit = op.smLimit;
+}
+
+acltensorStatus_t Fp8Workspace(const acltensorOperationDescriptor& op, int32_t splitPolicy, uint64_t* bytes) {
+    blazeFp8GemmArgs a;
+    fill_fp8_args(op, splitPolicy, &a);
+    size_t n = 0;
+    const int st = blazeFp8GemmWorkspaceSize(&a, &n);
+    *bytes = n;
+    return static_cast<acltensorStatus_t>(st);
+}
+
+acltensorStatus_t Fp8Execute(const ContractionArgs& c) {
+    blazeFp8GemmArgs a;
+    fill_fp8_args(*c.op, c.splitPolicy, &a);
+    a.group_rows = c.groupList;
+    a.A = c.A;
+    a.B = c.B;
+    a.scaleA = c.scaleA;
+    a.scaleB = c.scaleB;
+    a.bias = c.bias;
+    a.residual = c.C;
+    a.D = c.D;
+    a.workspace = c.workspace;
+    a.workspace_bytes = c.workspaceSize;
+    return static_cast<acltensorStatus_t>(blazeFp8Gemm(&a, c.stream));
+}
+
+}  // namespace
+
+REGISTER_CONTRACTION_SOLUTION(MxFp8, R_8F_E4M3, R_8F_E4M3, MX_E8M0_VEC32, MX_E8M0_VEC32, 2, MxWorkspace, MxExecute);
+REGISTER_CONTRACTION_SOLUTION(MxW4A8, R_8F_E4M3, R_4F_E2M1, MX_E8M0_VEC32, MX_E8M0_VEC32, 2, MxWorkspace, MxExecute);
+REGISTER_CONTRACTION_SOLUTION(Fp8Block, R_8F_E4M3, R_8F_E4M3, FP32_1X128, FP32_128X128, 0, Fp8Workspace, Fp8Execute);
+
+// ------------------------------------------------------------------------------------------------ descriptor
+
+acltensorStatus_t acltensorCreateContraction(const acltensorHandle_t handle, acltensorOperationDescriptor_t* desc,
+                                             const acltensorTensorDescriptor_t descA, const int32_t modeA[],
+                                             acltensorOperator_t opA, const acltensorTensorDescriptor_t descB,
+                                             const int32_t modeB[], acltensorOperator_t opB,
+                                             const acltensorTensorDescriptor_t descC, const int32_t modeC[],
+                                             acltensorOperator_t opC, const acltensorTensorDescriptor_t descD,
+                                             const int32_t modeD[], const acltensorComputeDescriptor_t descCompute) {
+    (void)handle;
+    if (desc == nullptr || descA == nullptr || descB == nullptr || descD == nullptr)
+        return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (modeA == nullptr || modeB == nullptr || modeD == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (descC != nullptr && modeC == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (opA != ACLTENSOR_OP_IDENTITY || opB != ACLTENSOR_OP_IDENTITY || opC != ACLTENSOR_OP_IDENTITY)
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    const acltensorStatus_t cst = CheckComputeDescriptor(descCompute);
+    if (cst != ACLTENSOR_STATUS_SUCCESS) return cst;
+
+    if (descA->dataType != ACLTENSOR_R_8F_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (descB->dataType != ACLTENSOR_R_8F_E4M3 && descB->dataType != ACLTENSOR_R_4F_E2M1)
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (descD->dataType != ACLTENSOR_R_16BF) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (descC != nullptr && descC->dataType != ACLTENSOR_R_16BF) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (descA->numModes != 2 || descD->numModes != 2 || (descB->numModes != 2 && descB->numModes != 3))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (descC != nullptr && descC->numModes != 2) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+
+    std::vector<int32_t> mA(modeA, modeA + descA->numModes), mB(modeB, modeB + descB->numModes),
+        mD(modeD, modeD + descD->numModes);
+    const int32_t mLabel = mD[0], nLabel = mD[1];
+    if (mLabel == nLabel) return ACLTENSOR_STATUS_INVALID_VALUE;
+    const int aM = find_mode(mA, mLabel);
+    if (aM < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
+    const int aK = 1 - aM;
+    const int32_t kLabel = mA[aK];
+    if (kLabel == mLabel || kLabel == nLabel) return ACLTENSOR_STATUS_INVALID_VALUE;
+    const int bN = find_mode(mB, nLabel), bK = find_mode(mB, kLabel);
+    if (bN < 0 || bK < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
+    int bG = -1;
+    if (descB->numModes == 3) {
+        bG = 3 - bN - bK;
+        if (mB[bG] == mLabel || mB[bG] == nLabel || mB[bG] == kLabel) return ACLTENSOR_STATUS_INVALID_VALUE;
+    }
+    const int64_t M = descD->lens[0], N = descD->lens[1], K = descA->lens[aK];
+    if (descA->lens[aM] != M || descB->lens[bN] != N || descB->lens[bK] != K) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (!fits_int32(M) || !fits_int32(N) || !fits_int32(K)) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    // K must be the contiguous mode of both operands, n the contiguous mode of the output
+    if (descA->strides[aK] != 1 || descB->strides[bK] != 1 || descD->strides[1] != 1)
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (descC != nullptr) {
+        if (modeC[0] != mLabel || modeC[1] != nLabel) return ACLTENSOR_STATUS_INVALID_VALUE;
+        if (descC->lens[0] != M || descC->lens[1] != N) return ACLTENSOR_STATUS_INVALID_VALUE;
+        if (descC->strides[1] != 1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    }
+    int64_t groupStride = 0;
+    int32_t groups = 0;
+    if (bG >= 0) {
+        if (bG != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;                 // group must be the outermost mode
+        groups = static_cast<int32_t>(descB->lens[bG]);
+        groupStride = descB->strides[bG];
+        if (groupStride != N * descB->strides[bN]) return ACLTENSOR_STATUS_NOT_SUPPORTED;   // groups back to back
+        if (descB->dataType != ACLTENSOR_R_8F_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    }
+
+    acltensorOperationDescriptor* d = new (std::nothrow) acltensorOperationDescriptor();
+    if (d == nullptr) return ACLTENSOR_STATUS_ALLOC_FAILED;
+    d->operationType = OperationType::CONTRACTION;
+    d->descA = descA;
+    d->descB = descB;
+    d->descC = descC;
+    d->descD = descD;
+    d->modeA = mA;
+    d->modeB = mB;
+    d->modeD = mD;
+    if (descC != nullptr) d->modeC.assign(modeC, modeC + 2);
+    d->opA = opA;
+    d->opB = opB;
+    d->opC = opC;
+    d->descCompute = descCompute;
+    d->M = M;
+    d->N = N;
+    d->K = K;
+    d->lda = descA->strides[aM];
+    d->ldb = descB->strides[bN];
+    d->ldc = descC ? descC->strides[0] : 0;
+    d->ldd = descD->strides[0];
+    d->groupStrideB = groupStride;
+    d->groupCount = groups;
+    *desc = d;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+namespace {
+
+int32_t* attribute_slot(acltensorOperationDescriptor* d, acltensorOperationDescriptorAttribute_t attr) {
+    switch (attr) {
+        case ACLTENSOR_OPERATION_DESCRIPTOR_SCALE_MODE_A: return &d->scaleModeA;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_SCALE_MODE_B: return &d->scaleModeB;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_EPILOGUE_ACT: return &d->epilogueAct;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_BIAS_TYPE: return &d->biasType;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_GROUP_COUNT: return &d->groupCount;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_SPLIT_POLICY: return &d->splitPolicy;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_TILE_N: return &d->tileN;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_SM_LIMIT: return &d->smLimit;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_B_IS_STATIC: return &d->bIsStatic;
+        default: return nullptr;
+    }
+}
+
+}  // namespace
+
+acltensorStatus_t acltensorOperationDescriptorSetAttribute(const acltensorHandle_t handle,
+                                                           acltensorOperationDescriptor_t desc,
+                                                           acltensorOperationDescriptorAttribute_t attr,
+                                                           const void* buf, size_t sizeInBytes) {
+    (void)handle;
+    if (desc == nullptr || buf == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (sizeInBytes != sizeof(int32_t)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (desc->operationType != OperationType::CONTRACTION) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    int32_t* slot = attribute_slot(desc, attr);
+    if (slot == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    int32_t v;
+    std::memcpy(&v, buf, sizeof(v));
+    switch (attr) {
+        case ACLTENSOR_OPERATION_DESCRIPTOR_SCALE_MODE_A:
+        case ACLTENSOR_OPERATION_DESCRIPTOR_SCALE_MODE_B:
+            if (v < ACLTENSOR_SCALE_NONE || v > ACLTENSOR_SCALE_FP32_128X128) return ACLTENSOR_STATUS_INVALID_VALUE;
+            break;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_EPILOGUE_ACT:
+            if (activation_of(v) < 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+            break;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_BIAS_TYPE:
+            if (v != -1 && v != ACLTENSOR_R_16BF) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+            break;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_GROUP_COUNT:
+            // the group count is fixed by the rank-3 B descriptor; setting it may only restate that value
+            if (v != desc->groupCount) return ACLTENSOR_STATUS_INVALID_VALUE;
+            break;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_SPLIT_POLICY:
+            if (v < ACLTENSOR_SPLIT_AUTO || v > ACLTENSOR_SPLIT_STREAM_K) return ACLTENSOR_STATUS_INVALID_VALUE;
+            break;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_TILE_N:
+            if (v != 0 && v != 128 && v != 224) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+            break;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_SM_LIMIT:
+            if (v < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
+            break;
+        default:
+            break;
+    }
+    *slot = v;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+acltensorStatus_t acltensorOperationDescriptorGetAttribute(const acltensorHandle_t handle,
+                                                           const acltensorOperationDescriptor_t desc,
+                                                           acltensorOperationDescriptorAttribute_t attr, void* buf,
+                                                           size_t sizeInBytes) {
+    (void)handle;
+    if (desc == nullptr || buf == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (sizeInBytes != sizeof(int32_t)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (desc->operationType != OperationType::CONTRACTION) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    const int32_t* slot = attribute_slot(desc, attr);
+    if (slot == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    std::memcpy(buf, slot, sizeof(int32_t));
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------------------ planning
+
+namespace {
+
+std::shared_ptr<ContractionSolution> solution_for(const acltensorOperationDescriptor& op) {
+    ContractionUid uid{op.descA->dataType, op.descB->dataType, op.scaleModeA, op.scaleModeB, op.descB->numModes};
+    return ContractionSolutionRegistry::instance().getSolution(uid);
+}
+
+}  // namespace
+
+acltensorStatus_t acltensorEstimateWorkspaceSize(const acltensorHandle_t handle,
+                                                 const acltensorOperationDescriptor_t desc,
+                                                 const acltensorPlanPreference_t pref,
+                                                 const acltensorWorksizePreference_t workspacePref,
+                                                 uint64_t* workspaceSizeEstimate) {
+    (void)handle;
+    if (desc == nullptr || pref == nullptr || workspaceSizeEstimate == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (workspacePref < ACLTENSOR_WORKSPACE_MIN || workspacePref > ACLTENSOR_WORKSPACE_MAX)
+        return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (desc->operationType == OperationType::ELEMENTWISE_BINARY) {
+        *workspaceSizeEstimate = 0;
+        return ACLTENSOR_STATUS_SUCCESS;
+    }
+    if (desc->operationType != OperationType::CONTRACTION) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    auto solution = solution_for(*desc);
+    if (!solution) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    int32_t policy = desc->splitPolicy;
+    if (workspacePref == ACLTENSOR_WORKSPACE_MIN) policy = ACLTENSOR_SPLIT_DATA_PARALLEL;
+    if (workspacePref == ACLTENSOR_WORKSPACE_MAX && desc->groupCount == 0) policy = ACLTENSOR_SPLIT_STREAM_K;
+    return solution->workspaceSize(*desc, policy, workspaceSizeEstimate);
+}
+
+namespace acltensor {
+
+acltensorStatus_t FinishContractionPlan(acltensorPlan* plan, uint64_t workspaceSizeLimit) {
+    const acltensorOperationDescriptor& op = *plan->opDesc;
+    if (op.descA == nullptr || op.descB == nullptr || op.descD == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    auto solution = solution_for(op);
+    if (!solution) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    int32_t policy = op.splitPolicy;
+    uint64_t need = 0;
+    acltensorStatus_t st = solution->workspaceSize(op, policy, &need);
+    if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    if (need > workspaceSizeLimit && policy != ACLTENSOR_SPLIT_DATA_PARALLEL) {
+        // stream-K needs a fix-up buffer; fall back to whole tiles per CTA when the caller cannot give one
+        uint64_t fallback = 0;
+        st = solution->workspaceSize(op, ACLTENSOR_SPLIT_DATA_PARALLEL, &fallback);
+        if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+        if (fallback <= workspaceSizeLimit) {
+            policy = ACLTENSOR_SPLIT_DATA_PARALLEL;
+            need = fallback;
+        }
+    }
+    if (need > workspaceSizeLimit) return ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE;
+    plan->requiredWorkspace = need;
+    plan->splitPolicy = policy;
+    plan->solution = solution;
+    plan->pref->solution = solution;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+}  // namespace acltensor
+
+// ------------------------------------------------------------------------------------------------ execution
+
+acltensorStatus_t acltensorContract(const acltensorHandle_t handle, const acltensorPlan_t plan, const void* alpha,
+                                    const void* A, const void* B, const void* beta, const void* C, void* D,
+                                    const acltensorContractionAux_t* aux, void* workspace, uint64_t workspaceSize,
+                                    aclrtStream stream) {
+    (void)handle;
+    if (plan == nullptr || A == nullptr || B == nullptr || D == nullptr || aux == nullptr)
+        return ACLTENSOR_STATUS_INVALID_VALUE;
+    acltensorOperationDescriptor* op = plan->opDesc;
+    if (op == nullptr || plan->pref == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (op->operationType != OperationType::CONTRACTION) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (!plan->solution) return ACLTENSOR_STATUS_INTERNAL_ERROR;
+    if (alpha != nullptr && *static_cast<const float*>(alpha) != 1.0f) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    bool use_c = (op->descC != nullptr);
+    if (beta != nullptr) {
+        const float b = *static_cast<const float*>(beta);
+        if (b == 0.0f) use_c = false;
+        else if (b != 1.0f) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+        else if (op->descC == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    }
+    if (use_c && C == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (aux->scaleA == nullptr || aux->scaleB == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (op->biasType >= 0 && aux->bias == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (op->groupCount > 0 && aux->groupList == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (workspaceSize < plan->requiredWorkspace) return ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE;
+    if (plan->requiredWorkspace > 0 && workspace == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+
+    ContractionArgs args;
+    args.op = op;
+    args.splitPolicy = plan->splitPolicy;
+    args.A = A;
+    args.B = B;
+    args.C = use_c ? C : nullptr;
+    args.D = D;
+    args.scaleA = aux->scaleA;
+    args.scaleB = aux->scaleB;
+    args.bias = op->biasType >= 0 ? aux->bias : nullptr;
+    args.groupList = op->groupCount > 0 ? aux->groupList : nullptr;
+    args.workspace = workspace;
+    args.workspaceSize = workspaceSize;
+    args.stream = stream;
+    args.reuseBPrepass = op->bIsStatic != 0 && plan->preparedB == B && plan->preparedScaleB == aux->scaleB &&
+                         plan->preparedWorkspace == workspace && workspace != nullptr;
+    auto solution = std::static_pointer_cast<ContractionSolution>(plan->solution);
+    const acltensorStatus_t st = solution->execute(args);
+    if (st == ACLTENSOR_STATUS_SUCCESS) {
+        plan->preparedB = B;
+        plan->preparedScaleB = aux->scaleB;
+        plan->preparedWorkspace = workspace;
+    } else {
+        plan->preparedB = nullptr;
+    }
+    return st;
+}
+
+acltensorStatus_t acltensorQuantize(const acltensorHandle_t handle, const void* src, int64_t ldSrc, int64_t rows,
+                                    int64_t cols, acltensorScaleMode_t scaleMode, acltensorDataType_t dType,
+                                    void* codes, int64_t ldCodesBytes, void* scales, aclrtStream stream) {
+    (void)handle;
+    if (src == nullptr || codes == nullptr || scales == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (!fits_int32(rows) || !fits_int32(cols)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    const int32_t r = static_cast<int32_t>(rows), c = static_cast<int32_t>(cols);
+    switch (scaleMode) {
+        case ACLTENSOR_SCALE_MX_E8M0_VEC32:
+            if (dType != ACLTENSOR_R_8F_E4M3 && dType != ACLTENSOR_R_4F_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+            return static_cast<acltensorStatus_t>(blazeQuantizeMx(
+                src, ldSrc, r, c, dType == ACLTENSOR_R_4F_E2M1 ? BLAZE_ELEM_E2M1 : BLAZE_ELEM_E4M3, codes, ldCodesBytes,
+                scales, stream));
+        case ACLTENSOR_SCALE_FP32_1X128:
+            if (dType != ACLTENSOR_R_8F_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+            return static_cast<acltensorStatus_t>(
+                blazeQuantizeFp8RowGroups(src, ldSrc, r, c, codes, ldCodesBytes, scales, stream));
+        case ACLTENSOR_SCALE_FP32_128X128:
+            if (dType != ACLTENSOR_R_8F_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+            return static_cast<acltensorStatus_t>(
+                blazeQuantizeFp8Blocks(src, ldSrc, r, c, codes, ldCodesBytes, scales, stream));
+        default:
+            return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    }
+}

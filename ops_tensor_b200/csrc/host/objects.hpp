@@ -1,0 +1,125 @@
+// Host-side objects behind the opaque acltensor* handles.
+//
+// They play the roles of the reference's lib/core structs (handle.hpp:71-74, tensor_descriptor.hpp:28-92,
+// operation_descriptor.hpp:40-84, plan_preference.hpp:33-45, plan.hpp:36-48) with the same ownership rules:
+// an operation descriptor points at, and does not own, its tensor descriptors; a plan points at, and does not own,
+// its operation descriptor and preference; the chosen solution is cached in the preference as a shared_ptr.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <memory>
+#include <vector>
+
+#include "cann_ops_tensor_types.h"
+
+namespace acltensor {
+
+enum class OperationType : uint32_t {
+    ELEMENTWISE_BINARY = 0,
+    ELEMENTWISE_TRINARY = 1,   // reserved by the reference, not implemented there or here
+    CONTRACTION = 2,
+};
+
+// Size of one element in bits (4 for packed E2M1); 0 for a type this build does not know.
+inline uint32_t DataTypeBits(acltensorDataType_t t) {
+    switch (t) {
+        case ACLTENSOR_R_16F: case ACLTENSOR_R_16BF: return 16;
+        case ACLTENSOR_R_32F: case ACLTENSOR_R_32I: case ACLTENSOR_R_32U: return 32;
+        case ACLTENSOR_R_64F: case ACLTENSOR_R_64I: case ACLTENSOR_C_32F: return 64;
+        case ACLTENSOR_C_64F: return 128;
+        case ACLTENSOR_R_8I: case ACLTENSOR_R_8U: case ACLTENSOR_R_8F_E4M3: case ACLTENSOR_R_8F_E5M2:
+        case ACLTENSOR_R_8F_UE8M0: return 8;
+        case ACLTENSOR_R_4F_E2M1: return 4;
+        default: return 0;
+    }
+}
+
+// Byte size for whole-byte types (the reference's GetDataTypeSize, lib/utils/type_utils.hpp:29-58); 0 for sub-byte.
+inline size_t GetDataTypeSize(acltensorDataType_t t) { return DataTypeBits(t) / 8; }
+
+// Types a tensor descriptor may carry in this build.  The reference accepts FP32 only
+// (lib/core/tensor_descriptor.cpp:43-45); the contraction path adds its operand, scale, output and index types.
+inline bool IsDescriptorTypeSupported(acltensorDataType_t t) {
+    switch (t) {
+        case ACLTENSOR_R_32F: case ACLTENSOR_R_16BF: case ACLTENSOR_R_8F_E4M3: case ACLTENSOR_R_4F_E2M1:
+        case ACLTENSOR_R_8F_UE8M0: case ACLTENSOR_R_8U: case ACLTENSOR_R_64I:
+            return true;
+        default:
+            return false;
+    }
+}
+
+acltensorStatus_t CheckOperator(acltensorOperator_t op);
+acltensorStatus_t CheckComputeDescriptor(acltensorComputeDescriptor_t desc);
+
+}  // namespace acltensor
+
+struct acltensorHandle {
+    int32_t deviceId = -1;      // CUDA device current at creation (-1: none visible)
+    int32_t smCount = 0;
+    int32_t ccMajor = 0, ccMinor = 0;
+    char deviceName[64] = {0};
+};
+
+struct acltensorTensorDescriptor {
+    acltensorDataType_t dataType = ACLTENSOR_R_32F;
+    uint32_t numModes = 0;
+    std::vector<int64_t> lens;
+    std::vector<int64_t> strides;          // in elements
+    uint32_t alignmentRequirement = 0;
+    uint32_t elementBits = 0;
+    size_t elementSize = 0;                // bytes; 0 for sub-byte types
+    size_t totalElements = 0;
+    size_t totalBytes = 0;
+    bool isContiguous = true;
+
+    void finalize();                       // fills strides (when absent) and the derived members
+};
+
+struct acltensorOperationDescriptor {
+    acltensor::OperationType operationType = acltensor::OperationType::ELEMENTWISE_BINARY;
+    acltensorTensorDescriptor_t descA = nullptr, descB = nullptr, descC = nullptr, descD = nullptr;
+    std::vector<int32_t> modeA, modeB, modeC, modeD;
+    acltensorOperator_t opA = ACLTENSOR_OP_IDENTITY, opB = ACLTENSOR_OP_IDENTITY, opC = ACLTENSOR_OP_IDENTITY;
+    acltensorOperator_t opAC = ACLTENSOR_OP_ADD, opAB = ACLTENSOR_OP_ADD, opABC = ACLTENSOR_OP_IDENTITY;
+    acltensorComputeDescriptor_t descCompute = ACLTENSOR_COMPUTE_DESC_32F;
+
+    // contraction attributes
+    int32_t scaleModeA = ACLTENSOR_SCALE_NONE, scaleModeB = ACLTENSOR_SCALE_NONE;
+    int32_t epilogueAct = ACLTENSOR_OP_IDENTITY;
+    int32_t biasType = -1;
+    int32_t groupCount = 0;
+    int32_t splitPolicy = ACLTENSOR_SPLIT_AUTO;
+    int32_t tileN = 0;
+    int32_t smLimit = 0;
+    int32_t bIsStatic = 0;
+
+    // contraction geometry, resolved at creation
+    int64_t M = 0, N = 0, K = 0;
+    int64_t lda = 0, ldb = 0, ldc = 0, ldd = 0;       // elements
+    int64_t groupStrideB = 0;                         // elements between consecutive groups of B
+
+    size_t getTotalElements() const { return descD ? descD->totalElements : 0; }
+    acltensorDataType_t getDataType() const { return descD ? descD->dataType : ACLTENSOR_R_32F; }
+};
+
+struct acltensorPlanPreference {
+    acltensorAlgo_t algo = ACLTENSOR_ALGO_DEFAULT;
+    std::vector<void*> candidates;
+    std::shared_ptr<void> solution;       // chosen at first execute (elementwise) or at plan creation (contraction)
+};
+
+struct acltensorPlan {
+    acltensorOperationDescriptor_t opDesc = nullptr;
+    acltensorPlanPreference_t pref = nullptr;
+    uint64_t requiredWorkspace = 0;
+    // contraction plans
+    std::shared_ptr<void> solution;
+    int32_t splitPolicy = ACLTENSOR_SPLIT_AUTO;   // policy after the workspace limit was applied
+    const void* preparedB = nullptr;              // B / scaleB / workspace whose pre-pass results are still valid
+    const void* preparedScaleB = nullptr;
+    const void* preparedWorkspace = nullptr;
+
+    size_t getTotalElements() const { return opDesc ? opDesc->getTotalElements() : 0; }
+};

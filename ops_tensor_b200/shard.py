@@ -1,0 +1,96 @@
+"""Partitioning of the matmul path over the GPUs of one box (host logic only; no collective on the data path).
+
+* Dense GEMMs are split along N: every rank keeps A and its scales, and owns a contiguous range of B's rows
+  (= output columns) whose width is a multiple of 128, so that 128x128 scale blocks and tile boundaries never
+  straddle two ranks.
+* Grouped matmul is split by expert: experts are placed longest-first on the least loaded rank (cost = rows); an
+  expert with more rows than the per-rank target is cut into row ranges that may land on different ranks (its weight
+  is then needed on each of them).
+
+The reference is single-device (its multi-device line is an unchecked roadmap item, docs/implementation.md:168); this
+module is the B200 build's own.  The only collective the path ever needs is an all-gather of output shards when a
+consumer wants the whole matrix (`gather_columns`).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Sequence, Tuple
+
+
+def n_shard(N: int, world: int, rank: int, multiple: int = 128) -> Tuple[int, int]:
+    """Column range [n0, n1) of `rank`: blocks of `multiple` columns dealt as evenly as possible, in rank order."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError("bad rank/world")
+    blocks = -(-N // multiple)
+    base, extra = divmod(blocks, world)
+    b0 = rank * base + min(rank, extra)
+    b1 = b0 + base + (1 if rank < extra else 0)
+    return min(b0 * multiple, N), min(b1 * multiple, N)
+
+
+@dataclass(frozen=True)
+class ExpertPiece:
+    expert: int
+    row_begin: int      # within the expert's rows
+    row_end: int
+
+    @property
+    def rows(self) -> int:
+        return self.row_end - self.row_begin
+
+
+def plan_experts(group_rows: Sequence[int], world: int, allow_split: bool = True, quantum: int = 128) -> List[List[ExpertPiece]]:
+    """Assign experts (or row ranges of oversized experts) to ranks, balancing rows.  Empty experts are dropped.
+    Deterministic: every rank computes the same plan from the same group list."""
+    total = int(sum(int(r) for r in group_rows))
+    target = max(1, -(-total // world))
+    pieces: List[ExpertPiece] = []
+    for e, r in enumerate(group_rows):
+        r = int(r)
+        if r <= 0:
+            continue
+        if allow_split and r > target and world > 1:
+            parts = -(-r // target)
+            step = -(-(-(-r // parts)) // quantum) * quantum
+            b = 0
+            while b < r:
+                pieces.append(ExpertPiece(e, b, min(r, b + step)))
+                b += step
+        else:
+            pieces.append(ExpertPiece(e, 0, r))
+    order = sorted(range(len(pieces)), key=lambda i: (-pieces[i].rows, pieces[i].expert, pieces[i].row_begin))
+    load = [0] * world
+    plan: List[List[ExpertPiece]] = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda j: (load[j], len(plan[j]), j))
+        plan[r].append(pieces[i])
+        load[r] += pieces[i].rows
+    for lst in plan:
+        lst.sort(key=lambda p: (p.expert, p.row_begin))
+    return plan
+
+
+def plan_loads(plan: List[List[ExpertPiece]]) -> List[int]:
+    return [sum(p.rows for p in lst) for lst in plan]
+
+
+def gather_columns(local_out, world: int, group=None):
+    """All-gather N-shards of equal width into the whole [M, N] matrix (NCCL on GPUs, gloo on CPU tensors)."""
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return local_out
+    parts = [torch.empty_like(local_out) for _ in range(world)]
+    dist.all_gather(parts, local_out.contiguous(), group=group)
+    return torch.cat(parts, dim=1)
+
+
+def max_over_ranks(value: float, device=None, group=None) -> float:
+    """Largest `value` among the ranks (used for device-timed durations)."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return float(value)
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device if device is not None else "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t.item())

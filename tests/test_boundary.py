@@ -1,0 +1,294 @@
+"""The C-ABI boundary on a machine without a GPU: exported symbols, object life cycle, every argument check.
+
+The call sequences follow the reference's client helper (tests/test_elementwise.cpp:159-208): handle, tensor
+descriptors, operation descriptor, plan preference, plan, execute, destroy in reverse order."""
+import ctypes as C
+import re
+import threading
+from pathlib import Path
+
+import pytest
+
+from ops_tensor_b200 import host as H
+from ops_tensor_b200 import native
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture(scope="module")
+def api(built_library):
+    return H.api
+
+
+def test_library_exports_every_declared_symbol(built_library):
+    lib = C.CDLL(str(built_library))
+    declared = []
+    for header in sorted((ROOT / "include").glob("*.h")):
+        text = header.read_text()
+        declared += re.findall(r"(?:ACLTENSOR_API|BLAZE_API)\s+[\w\s\*]+?\b(\w+)\s*\(", text)
+    assert len(declared) >= 30, declared
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/ but not exported"
+    for name in ("acltensorCreate", "acltensorDestroy", "acltensorCreateTensorDescriptor",
+                 "acltensorDestroyTensorDescriptor", "acltensorCreateElementwiseBinary",
+                 "acltensorDestroyOperationDescriptor", "acltensorCreatePlanPreference",
+                 "acltensorDestroyPlanPreference", "acltensorCreatePlan", "acltensorDestroyPlan",
+                 "acltensorElementwiseBinaryExecute", "acltensorGetErrorString", "acltensorGetVersion"):
+        assert name in declared                      # the reference's thirteen entry points
+
+
+def test_version_and_error_strings(api):
+    assert api.acltensorGetVersion() == 1 << 16
+    assert H.error_string(0) == "The operation completed successfully."
+    assert H.error_string(7) == "Invalid parameter value."
+    assert H.error_string(15) == "Operation not supported."
+    assert H.error_string(19) == "Insufficient workspace size."
+    assert H.error_string(12345) == "Unknown error."
+
+
+def test_destroy_accepts_null(api):
+    for fn in (api.acltensorDestroy, api.acltensorDestroyTensorDescriptor, api.acltensorDestroyOperationDescriptor,
+               api.acltensorDestroyPlanPreference, api.acltensorDestroyPlan):
+        assert fn(None) == H.STATUS_SUCCESS
+
+
+def test_handle_and_tensor_descriptor_checks(api):
+    assert api.acltensorCreate(None) == H.STATUS_INVALID_VALUE
+    h = H.create_handle()
+    d = C.c_void_p()
+    lens = H.i64([4, 8])
+    assert api.acltensorCreateTensorDescriptor(h, None, 2, lens, None, H.R_32F, 0) == H.STATUS_INVALID_VALUE
+    assert api.acltensorCreateTensorDescriptor(h, C.byref(d), 2, None, None, H.R_32F, 0) == H.STATUS_INVALID_VALUE
+    assert api.acltensorCreateTensorDescriptor(h, C.byref(d), 0, lens, None, H.R_32F, 0) == H.STATUS_INVALID_VALUE
+    for unsupported in (H.R_16F, H.R_64F, H.R_8I, H.C_32F, H.R_8F_E5M2):
+        assert api.acltensorCreateTensorDescriptor(h, C.byref(d), 2, lens, None, unsupported, 0) == H.STATUS_NOT_SUPPORTED
+    for ok in (H.R_32F, H.R_16BF, H.R_8F_E4M3, H.R_4F_E2M1, H.R_8F_UE8M0, H.R_64I):
+        assert api.acltensorCreateTensorDescriptor(h, C.byref(d), 2, lens, None, ok, 0) == H.STATUS_SUCCESS
+        assert api.acltensorDestroyTensorDescriptor(d) == H.STATUS_SUCCESS
+    assert api.acltensorDestroy(h) == H.STATUS_SUCCESS
+
+
+def _ew_descs(h, n=16):
+    return [H.create_tensor_descriptor(h, [n]) for _ in range(3)]
+
+
+def test_elementwise_descriptor_checks(api):
+    h = H.create_handle()
+    da, dc, dd = _ew_descs(h)
+    m = H.i32([0])
+    op = C.c_void_p()
+    f = api.acltensorCreateElementwiseBinary
+    ok_args = (da, m, H.OP_IDENTITY, dc, m, H.OP_IDENTITY, dd, m, H.OP_ADD, H.COMPUTE_DESC_32F)
+    assert f(h, None, *ok_args) == H.STATUS_INVALID_VALUE
+    assert f(h, C.byref(op), None, *ok_args[1:]) == H.STATUS_INVALID_VALUE
+    assert f(h, C.byref(op), da, None, *ok_args[2:]) == H.STATUS_INVALID_VALUE
+    assert f(h, C.byref(op), da, m, H.OP_SQRT, dc, m, H.OP_IDENTITY, dd, m, H.OP_ADD, H.COMPUTE_DESC_32F) == H.STATUS_NOT_SUPPORTED
+    assert f(h, C.byref(op), da, m, H.OP_IDENTITY, dc, m, H.OP_IDENTITY, dd, m, H.OP_MUL, H.COMPUTE_DESC_32F) == H.STATUS_NOT_SUPPORTED
+    assert f(h, C.byref(op), *ok_args[:-1], H.COMPUTE_DESC_NONE) == H.STATUS_INVALID_VALUE
+    assert f(h, C.byref(op), *ok_args[:-1], H.COMPUTE_DESC_16F) == H.STATUS_NOT_SUPPORTED
+    assert f(h, C.byref(op), *ok_args) == H.STATUS_SUCCESS
+
+    pref, plan = C.c_void_p(), C.c_void_p()
+    assert api.acltensorCreatePlanPreference(h, None, H.ALGO_DEFAULT) == H.STATUS_INVALID_VALUE
+    assert api.acltensorCreatePlanPreference(h, C.byref(pref), H.ALGO_DEFAULT_PATIENT) == H.STATUS_NOT_SUPPORTED
+    assert api.acltensorCreatePlanPreference(h, C.byref(pref), H.ALGO_DEFAULT) == H.STATUS_SUCCESS
+    assert api.acltensorCreatePlan(h, None, op, pref, 0) == H.STATUS_INVALID_VALUE
+    assert api.acltensorCreatePlan(h, C.byref(plan), None, pref, 0) == H.STATUS_INVALID_VALUE
+    assert api.acltensorCreatePlan(h, C.byref(plan), op, None, 0) == H.STATUS_INVALID_VALUE
+    assert api.acltensorCreatePlan(h, C.byref(plan), op, pref, 0) == H.STATUS_SUCCESS
+    need = C.c_uint64(99)
+    assert api.acltensorPlanGetRequiredWorkspace(plan, C.byref(need)) == H.STATUS_SUCCESS and need.value == 0
+
+    ex = api.acltensorElementwiseBinaryExecute
+    fake = 4096
+    assert ex(h, None, None, fake, None, fake, fake, None) == H.STATUS_INVALID_VALUE
+    assert ex(h, plan, None, None, None, fake, fake, None) == H.STATUS_INVALID_VALUE
+    assert ex(h, plan, None, fake, None, None, fake, None) == H.STATUS_INVALID_VALUE
+    assert ex(h, plan, None, fake, None, fake, None, None) == H.STATUS_INVALID_VALUE
+    import torch
+    if not torch.cuda.is_available():
+        # no fallback: without a device the call reports that instead of computing on the host
+        assert ex(h, plan, None, fake, None, fake, fake, None) == H.STATUS_NOT_INITIALIZED
+
+    for fn, obj in ((api.acltensorDestroyPlan, plan), (api.acltensorDestroyPlanPreference, pref),
+                    (api.acltensorDestroyOperationDescriptor, op)):
+        assert fn(obj) == H.STATUS_SUCCESS
+    for t in (da, dc, dd):
+        api.acltensorDestroyTensorDescriptor(t)
+    api.acltensorDestroy(h)
+
+
+def _contraction_descs(h, M=256, N=512, K=1024, b_dtype=H.R_8F_E4M3, groups=0):
+    dA = H.create_tensor_descriptor(h, [M, K], None, H.R_8F_E4M3)
+    dB = H.create_tensor_descriptor(h, [groups, N, K] if groups else [N, K], None, b_dtype)
+    dD = H.create_tensor_descriptor(h, [M, N], None, H.R_16BF)
+    return dA, dB, dD
+
+
+def test_contraction_descriptor_checks(api):
+    h = H.create_handle()
+    dA, dB, dD = _contraction_descs(h)
+    op = C.c_void_p()
+    f = api.acltensorCreateContraction
+    mA, mB, mD = H.i32([0, 2]), H.i32([1, 2]), H.i32([0, 1])
+    good = (dA, mA, H.OP_IDENTITY, dB, mB, H.OP_IDENTITY, None, None, H.OP_IDENTITY, dD, mD, H.COMPUTE_DESC_32F)
+    assert f(h, None, *good) == H.STATUS_INVALID_VALUE
+    assert f(h, C.byref(op), None, *good[1:]) == H.STATUS_INVALID_VALUE
+    assert f(h, C.byref(op), dA, None, *good[2:]) == H.STATUS_INVALID_VALUE
+    assert f(h, C.byref(op), dA, mA, H.OP_RELU, *good[3:]) == H.STATUS_NOT_SUPPORTED
+    assert f(h, C.byref(op), *good[:-1], H.COMPUTE_DESC_NONE) == H.STATUS_INVALID_VALUE
+    assert f(h, C.byref(op), *good[:-1], H.COMPUTE_DESC_16BF) == H.STATUS_NOT_SUPPORTED
+    # K extents disagree
+    dBbad = H.create_tensor_descriptor(h, [512, 512], None, H.R_8F_E4M3)
+    assert f(h, C.byref(op), dA, mA, H.OP_IDENTITY, dBbad, mB, H.OP_IDENTITY, None, None, H.OP_IDENTITY, dD, mD,
+             H.COMPUTE_DESC_32F) == H.STATUS_INVALID_VALUE
+    # output must be bf16; A must be E4M3
+    dD32 = H.create_tensor_descriptor(h, [256, 512], None, H.R_32F)
+    assert f(h, C.byref(op), dA, mA, H.OP_IDENTITY, dB, mB, H.OP_IDENTITY, None, None, H.OP_IDENTITY, dD32, mD,
+             H.COMPUTE_DESC_32F) == H.STATUS_NOT_SUPPORTED
+    # K must be the contiguous mode of A
+    dAt = H.create_tensor_descriptor(h, [256, 1024], [1, 256], H.R_8F_E4M3)
+    assert f(h, C.byref(op), dAt, mA, H.OP_IDENTITY, dB, mB, H.OP_IDENTITY, None, None, H.OP_IDENTITY, dD, mD,
+             H.COMPUTE_DESC_32F) == H.STATUS_NOT_SUPPORTED
+    # B described as [K, N] with K contiguous ("column-major") is the same operand
+    dBkn = H.create_tensor_descriptor(h, [1024, 512], [1, 1024], H.R_8F_E4M3)
+    assert f(h, C.byref(op), dA, mA, H.OP_IDENTITY, dBkn, H.i32([2, 1]), H.OP_IDENTITY, None, None, H.OP_IDENTITY, dD,
+             mD, H.COMPUTE_DESC_32F) == H.STATUS_SUCCESS
+    api.acltensorDestroyOperationDescriptor(op)
+    assert f(h, C.byref(op), *good) == H.STATUS_SUCCESS
+
+    # attributes
+    v = C.c_int32(H.SCALE_MX_E8M0_VEC32)
+    sa = api.acltensorOperationDescriptorSetAttribute
+    assert sa(h, None, H.ATTR_SCALE_MODE_A, C.byref(v), 4) == H.STATUS_INVALID_VALUE
+    assert sa(h, op, H.ATTR_SCALE_MODE_A, None, 4) == H.STATUS_INVALID_VALUE
+    assert sa(h, op, H.ATTR_SCALE_MODE_A, C.byref(v), 8) == H.STATUS_INVALID_VALUE
+    assert sa(h, op, 77, C.byref(v), 4) == H.STATUS_INVALID_VALUE
+    assert sa(h, op, H.ATTR_SCALE_MODE_A, C.byref(C.c_int32(9)), 4) == H.STATUS_INVALID_VALUE
+    assert sa(h, op, H.ATTR_EPILOGUE_ACT, C.byref(C.c_int32(H.OP_SILU)), 4) == H.STATUS_NOT_SUPPORTED
+    assert sa(h, op, H.ATTR_TILE_N, C.byref(C.c_int32(96)), 4) == H.STATUS_NOT_SUPPORTED
+    assert sa(h, op, H.ATTR_GROUP_COUNT, C.byref(C.c_int32(4)), 4) == H.STATUS_INVALID_VALUE
+    H.set_attribute(h, op, H.ATTR_EPILOGUE_ACT, H.OP_GELU)
+    assert H.get_attribute(h, op, H.ATTR_EPILOGUE_ACT) == H.OP_GELU
+    assert H.get_attribute(h, op, H.ATTR_BIAS_TYPE) == -1
+
+    # no scale modes yet: no registered solution matches
+    pref, plan = C.c_void_p(), C.c_void_p()
+    H.check(api.acltensorCreatePlanPreference(h, C.byref(pref), H.ALGO_DEFAULT), "pref")
+    assert api.acltensorCreatePlan(h, C.byref(plan), op, pref, 1 << 40) == H.STATUS_NOT_SUPPORTED
+    est = C.c_uint64(0)
+    assert api.acltensorEstimateWorkspaceSize(h, op, pref, H.WORKSPACE_DEFAULT, C.byref(est)) == H.STATUS_NOT_SUPPORTED
+    # MX x FP32 is not a registered pairing either
+    H.set_attribute(h, op, H.ATTR_SCALE_MODE_A, H.SCALE_MX_E8M0_VEC32)
+    H.set_attribute(h, op, H.ATTR_SCALE_MODE_B, H.SCALE_FP32_128X128)
+    assert api.acltensorCreatePlan(h, C.byref(plan), op, pref, 1 << 40) == H.STATUS_NOT_SUPPORTED
+    H.set_attribute(h, op, H.ATTR_SCALE_MODE_B, H.SCALE_MX_E8M0_VEC32)
+    assert api.acltensorEstimateWorkspaceSize(h, op, pref, 0, C.byref(est)) == H.STATUS_INVALID_VALUE
+    assert api.acltensorEstimateWorkspaceSize(h, op, pref, H.WORKSPACE_DEFAULT, C.byref(est)) == H.STATUS_SUCCESS
+    # re-tiled scale factors of A (2 tiles x 8 k-steps x 512 B) and B live in the workspace
+    assert est.value >= 2 * 8 * 512 * 2
+    assert api.acltensorCreatePlan(h, C.byref(plan), op, pref, est.value - 1) == H.STATUS_INSUFFICIENT_WORKSPACE
+    assert api.acltensorCreatePlan(h, C.byref(plan), op, pref, est.value) == H.STATUS_SUCCESS
+
+    aux = H.ContractionAux(4096, 4096, None, None)
+    one, two, zero = C.c_float(1.0), C.c_float(2.0), C.c_float(0.0)
+    ct = api.acltensorContract
+    fake = 4096
+    assert ct(h, None, None, fake, fake, None, None, fake, C.byref(aux), fake, est.value, None) == H.STATUS_INVALID_VALUE
+    assert ct(h, plan, None, None, fake, None, None, fake, C.byref(aux), fake, est.value, None) == H.STATUS_INVALID_VALUE
+    assert ct(h, plan, None, fake, fake, None, None, fake, None, fake, est.value, None) == H.STATUS_INVALID_VALUE
+    assert ct(h, plan, C.byref(two), fake, fake, None, None, fake, C.byref(aux), fake, est.value, None) == H.STATUS_NOT_SUPPORTED
+    assert ct(h, plan, C.byref(one), fake, fake, C.byref(two), None, fake, C.byref(aux), fake, est.value, None) == H.STATUS_NOT_SUPPORTED
+    # beta = 1 asks for a residual the descriptor does not have
+    assert ct(h, plan, None, fake, fake, C.byref(one), fake, fake, C.byref(aux), fake, est.value, None) == H.STATUS_INVALID_VALUE
+    assert ct(h, plan, None, fake, fake, C.byref(zero), None, fake, C.byref(aux), fake, est.value - 1, None) == H.STATUS_INSUFFICIENT_WORKSPACE
+    no_scales = H.ContractionAux(None, 4096, None, None)
+    assert ct(h, plan, None, fake, fake, None, None, fake, C.byref(no_scales), fake, est.value, None) == H.STATUS_INVALID_VALUE
+    # GELU epilogue was requested without bias: fine; with BIAS_TYPE set the pointer becomes mandatory
+    api.acltensorDestroyPlan(plan)
+    H.set_attribute(h, op, H.ATTR_BIAS_TYPE, H.R_16BF)
+    assert api.acltensorCreatePlan(h, C.byref(plan), op, pref, est.value) == H.STATUS_SUCCESS
+    assert ct(h, plan, None, fake, fake, None, None, fake, C.byref(aux), fake, est.value, None) == H.STATUS_INVALID_VALUE
+    # the elementwise entry point refuses a contraction plan
+    assert api.acltensorElementwiseBinaryExecute(h, plan, None, fake, None, fake, fake, None) == H.STATUS_NOT_SUPPORTED
+
+    api.acltensorDestroyPlan(plan)
+    api.acltensorDestroyPlanPreference(pref)
+    api.acltensorDestroyOperationDescriptor(op)
+    for t in (dA, dB, dD, dBbad, dD32, dAt, dBkn):
+        api.acltensorDestroyTensorDescriptor(t)
+    api.acltensorDestroy(h)
+
+
+def test_streamk_plan_falls_back_without_workspace(api):
+    """A plan asked to use stream-K with no workspace allowance degrades to whole tiles per CTA."""
+    with H.Contraction(64, 7168, 18432, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128,
+                       split=H.SPLIT_STREAM_K) as c:
+        assert c.workspace_bytes > 148 * 128 * 128 * 4 // 2
+    with H.Contraction(64, 7168, 18432, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128,
+                       split=H.SPLIT_STREAM_K, workspace_limit=0) as c:
+        assert c.workspace_bytes == 0
+
+
+def test_grouped_and_w4_descriptors(api):
+    with H.Contraction(4096, 768, 2048, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128,
+                       groups=16) as c:
+        assert c.workspace_bytes == 0
+        assert H.get_attribute(c.handle, c.op, H.ATTR_GROUP_COUNT) == 16
+    with pytest.raises(native.BlazeError) as e:           # grouped MX is not registered
+        H.Contraction(4096, 768, 2048, scale_mode_a=H.SCALE_MX_E8M0_VEC32, scale_mode_b=H.SCALE_MX_E8M0_VEC32, groups=4)
+    assert e.value.status == H.STATUS_NOT_SUPPORTED
+    with H.Contraction(256, 512, 1024, scale_mode_a=H.SCALE_MX_E8M0_VEC32, scale_mode_b=H.SCALE_MX_E8M0_VEC32,
+                       b_dtype=H.R_4F_E2M1) as c:
+        assert c.workspace_bytes >= 512 * 1024             # room for the expanded weight
+    with pytest.raises(native.BlazeError) as e:           # K not a multiple of 16 cannot be staged by TMA
+        H.Contraction(256, 512, 1000, scale_mode_a=H.SCALE_MX_E8M0_VEC32, scale_mode_b=H.SCALE_MX_E8M0_VEC32)
+    assert e.value.status == H.STATUS_NOT_SUPPORTED
+
+
+def test_objects_are_independent_across_threads(api):
+    errors = []
+
+    def worker():
+        try:
+            for _ in range(200):
+                with H.Contraction(256, 512, 1024, scale_mode_a=H.SCALE_MX_E8M0_VEC32,
+                                   scale_mode_b=H.SCALE_MX_E8M0_VEC32, activation=H.OP_GELU, bias=True):
+                    pass
+        except Exception as exc:                           # pragma: no cover
+            errors.append(exc)
+
+    threads = [threading.Thread(target=worker) for _ in range(8)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors
+
+
+def test_kernel_abi_argument_checks(built_library):
+    """The launch layer rejects malformed arguments before touching a device."""
+    l = native.lib()
+    n = C.c_size_t(0)
+    a = native.MxGemmArgs()
+    assert l.blazeMxGemmWorkspaceSize(C.byref(a), C.byref(n)) == H.STATUS_INVALID_VALUE        # struct_size unset
+    a.struct_size = C.sizeof(a)
+    a.M, a.N, a.K = 128, 128, 100
+    assert l.blazeMxGemmWorkspaceSize(C.byref(a), C.byref(n)) == H.STATUS_NOT_SUPPORTED        # K % 16
+    a.K = 128
+    a.tile_n = 64
+    assert l.blazeMxGemmWorkspaceSize(C.byref(a), C.byref(n)) == H.STATUS_NOT_SUPPORTED
+    a.tile_n = 0
+    assert l.blazeMxGemmWorkspaceSize(C.byref(a), None) == H.STATUS_INVALID_VALUE
+    assert l.blazeMxGemmWorkspaceSize(C.byref(a), C.byref(n)) == H.STATUS_SUCCESS and n.value == 1024
+    f = native.Fp8GemmArgs()
+    f.struct_size = C.sizeof(f)
+    f.M, f.N, f.K, f.groups = 128, 128, 128, 2000
+    assert l.blazeFp8GemmWorkspaceSize(C.byref(f), C.byref(n)) == H.STATUS_NOT_SUPPORTED       # too many groups
+    f.groups, f.sched = 4, native.SCHED_STREAM_K
+    assert l.blazeFp8GemmWorkspaceSize(C.byref(f), C.byref(n)) == H.STATUS_NOT_SUPPORTED       # grouped stream-K
+    f.groups, f.sched = 0, native.SCHED_DATA_PARALLEL
+    assert l.blazeFp8GemmWorkspaceSize(C.byref(f), C.byref(n)) == H.STATUS_SUCCESS and n.value == 0
+    assert l.blazeQuantizeMx(None, 0, 4, 32, 0, None, 0, None, None) == H.STATUS_INVALID_VALUE
+    assert l.blazeAddF32(None, None, None, 0, None) == H.STATUS_SUCCESS
+    assert l.blazeAddF32(None, None, None, -1, None) == H.STATUS_INVALID_VALUE

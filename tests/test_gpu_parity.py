@@ -1,0 +1,342 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle on the same seeded inputs.
+
+Quantiser outputs must be bit-equal.  GEMM outputs must satisfy max relative error <= 1e-2 against the float64
+de-quantised reference (floor 2^-7 * rms) and must not exceed the error of the reference-style float32 golden
+(or one bf16 ulp, 2^-8, whichever is larger).  At the full benchmark sizes the float64 reference is evaluated on a
+strided sample of rows.
+"""
+import numpy as np
+import pytest
+
+import blaze_oracle as o
+from ops_tensor_b200 import host as H
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2
+
+
+def dev_tensor(x, device):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(x)).to(device)
+
+
+def bf16_tensor(x, device):
+    import torch
+    return dev_tensor(o.bf16_round(x.astype(np.float32)), device).to(torch.bfloat16)
+
+
+def to_np(t):
+    import torch
+    if t.dtype == torch.bfloat16:
+        return t.float().cpu().numpy()
+    return t.cpu().numpy()
+
+
+def assert_gemm_ok(got, ref64, golden=None):
+    got = got.astype(np.float64)
+    assert np.all(np.isfinite(got))
+    e = o.maxrel(got, ref64)
+    assert e <= TOL, f"max relative error {e}"
+    if golden is not None:
+        e_ref = o.maxrel(golden, ref64)
+        assert e <= max(e_ref, 2.0 ** -8), f"error {e} above the float32 golden's {e_ref}"
+    assert H.device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------ elementwise
+
+@pytest.mark.parametrize("n", [3, 8, 100, 1024, 1000003])
+def test_elementwise_add_call_sequence(cuda_device, n):
+    """The reference's ADD cases (src/add/tests/add_test.cpp:27-104: sizes 3..1024, tolerance 1e-6) plus a large one."""
+    rng = np.random.default_rng(n)
+    a = rng.standard_normal(n).astype(np.float32)
+    c = rng.standard_normal(n).astype(np.float32)
+    d = H.elementwise_add(dev_tensor(a, cuda_device), dev_tensor(c, cuda_device))
+    assert np.array_equal(to_np(d), a + c)
+
+
+# ------------------------------------------------------------------------------------------------ quantisers
+
+@pytest.mark.parametrize("rows,K", [(1, 32), (4, 128), (37, 96), (256, 1024), (130, 4160), (515, 2048)])
+def test_quantisers_bit_exact(cuda_device, rows, K):
+    rng = np.random.default_rng(rows * 7919 + K)
+    x = (rng.standard_normal((rows, K)) * rng.choice([1e-4, 1.0, 37.0, 3e4], size=(rows, 1))).astype(np.float32)
+    special = np.array([0, -0.0, 448, 464, 1e9, -1e9, 2 ** -9, 3 * 2 ** -10, 1e-40, np.inf, -np.inf, 6, 5, 0.25, 0.75,
+                        1.75], dtype=np.float32)
+    x[0, :min(K, special.size)] = special[:min(K, special.size)]
+    if rows > 2:
+        x[2, :] = 0.0                                     # all-zero groups
+        x[1, 5] = np.nan                                  # NaN marks its MX group
+    xd = dev_tensor(x, cuda_device)
+    for dtype, name in ((H.R_8F_E4M3, "e4m3"), (H.R_4F_E2M1, "e2m1")):
+        codes, scales = H.quantize(xd, H.SCALE_MX_E8M0_VEC32, dtype)
+        want_codes, want_scales = o.quant_mx(x, name)
+        assert np.array_equal(to_np(scales), want_scales), name
+        assert np.array_equal(to_np(codes), want_codes), name
+    finite = np.nan_to_num(x, nan=1.0, posinf=3e38, neginf=-3e38)
+    fd = dev_tensor(finite, cuda_device)
+    codes, scales = H.quantize(fd, H.SCALE_FP32_1X128)
+    want_codes, want_scales = o.quant_fp8_1x128(finite)
+    assert np.array_equal(to_np(scales).view(np.uint32), want_scales.view(np.uint32))
+    assert np.array_equal(to_np(codes), want_codes)
+    codes, scales = H.quantize(fd, H.SCALE_FP32_128X128)
+    want_codes, want_scales = o.quant_fp8_128x128(finite)
+    assert np.array_equal(to_np(scales).view(np.uint32), want_scales.view(np.uint32))
+    assert np.array_equal(to_np(codes), want_codes)
+    assert H.device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------ FP8, fp32 scales
+
+def fp8_problem(cfg, M, N, K, sigma_b=0.02):
+    a = o.normal_f32(cfg, 0, (M, K), 1.0)
+    w = o.normal_f32(cfg, 1, (N, K), sigma_b)
+    return a, w
+
+
+def run_fp8(device, a, w, *, split=H.SPLIT_AUTO, act=H.OP_IDENTITY, bias=None, residual=None, sm_limit=0,
+            check_quant=True):
+    import torch
+    M, K = a.shape
+    N = w.shape[0]
+    qa, sa = H.quantize(dev_tensor(a, device), H.SCALE_FP32_1X128)
+    qb, sb = H.quantize(dev_tensor(w, device), H.SCALE_FP32_128X128)
+    if check_quant:
+        ra, rsa = o.quant_fp8_1x128(a)
+        rb, rsb = o.quant_fp8_128x128(w)
+        assert np.array_equal(to_np(qa), ra) and np.array_equal(to_np(sa).view(np.uint32), rsa.view(np.uint32))
+        assert np.array_equal(to_np(qb), rb) and np.array_equal(to_np(sb).view(np.uint32), rsb.view(np.uint32))
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=device)
+    bias_t = bf16_tensor(bias, device) if bias is not None else None
+    res_t = bf16_tensor(residual, device) if residual is not None else None
+    with H.Contraction(M, N, K, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128, activation=act,
+                       bias=bias is not None, residual=residual is not None, split=split, sm_limit=sm_limit) as c:
+        ws = None
+        if c.workspace_bytes:
+            ws = torch.full((c.workspace_bytes // 4,), float("nan"), dtype=torch.float32, device=device).view(torch.uint8)
+        c(qa, sa, qb, sb, out, bias=bias_t, residual=res_t, workspace=ws)
+        first = to_np(out).copy()
+        out.fill_(float("nan"))
+        c(qa, sa, qb, sb, out, bias=bias_t, residual=res_t, workspace=ws)
+        assert np.array_equal(to_np(out).view(np.uint32), first.view(np.uint32)), "two runs differ"
+    return first, to_np(qa), to_np(sa), to_np(qb), to_np(sb)
+
+
+def fp8_reference(qa, sa, qb, sb, act=o.ACT_IDENTITY, bias=None, residual=None, rows=None):
+    da = o.dequant_fp8_1x128(qa, sa)
+    db = o.dequant_fp8_128x128(qb, sb)
+    if rows is not None:
+        da = da[rows]
+        residual = residual[rows] if residual is not None else None
+    b16 = o.bf16_round(bias.astype(np.float32)) if bias is not None else None
+    r16 = o.bf16_round(residual.astype(np.float32)) if residual is not None else None
+    ref = o.matmul_ref64(da, db, b16, act, r16)
+    gold = o.matmul_golden32(da.astype(np.float32), db.astype(np.float32), b16, act, r16)
+    return ref, gold
+
+
+ACT = {H.OP_IDENTITY: o.ACT_IDENTITY, H.OP_RELU: o.ACT_RELU, H.OP_GELU: o.ACT_GELU_TANH}
+
+
+@pytest.mark.parametrize("split", [H.SPLIT_DATA_PARALLEL, H.SPLIT_STREAM_K, H.SPLIT_AUTO])
+def test_config1_fp8_per_group(cuda_device, split):
+    """C[256,512] = A[256,1024] x B[1024,512], 1x128 / 128x128 float32 scales, bf16 output, seed 0."""
+    a, w = fp8_problem(1, 256, 512, 1024)
+    got, qa, sa, qb, sb = run_fp8(cuda_device, a, w, split=split)
+    ref, gold = fp8_reference(qa, sa, qb, sb)
+    assert_gemm_ok(got, ref, gold)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8, 16), (128, 128, 128), (100, 264, 1040), (129, 136, 144), (300, 1000, 272)])
+@pytest.mark.parametrize("split", [H.SPLIT_DATA_PARALLEL, H.SPLIT_STREAM_K])
+def test_fp8_ragged_shapes(cuda_device, M, N, K, split):
+    a, w = fp8_problem(11, M, N, K)
+    got, qa, sa, qb, sb = run_fp8(cuda_device, a, w, split=split)
+    ref, gold = fp8_reference(qa, sa, qb, sb)
+    assert_gemm_ok(got, ref, gold)
+
+
+@pytest.mark.parametrize("act", [H.OP_IDENTITY, H.OP_RELU, H.OP_GELU])
+def test_fp8_fused_epilogue(cuda_device, act):
+    M, N, K = 200, 392, 640
+    a, w = fp8_problem(12, M, N, K, sigma_b=0.05)
+    bias = o.normal_f32(12, 2, (N,), 0.5)
+    residual = o.normal_f32(12, 3, (M, N), 1.0)
+    got, qa, sa, qb, sb = run_fp8(cuda_device, a, w, act=act, bias=bias, residual=residual, split=H.SPLIT_STREAM_K,
+                                  sm_limit=37)
+    ref, gold = fp8_reference(qa, sa, qb, sb, ACT[act], bias, residual)
+    assert_gemm_ok(got, ref, gold)
+
+
+@pytest.mark.parametrize("M", [16, 64, 128])
+def test_config5_decode_streamk(cuda_device, M):
+    """Stream-K decode shape: N=7168, K=18432, residual add, bf16; checked on every row."""
+    N, K = 7168, 18432
+    a = o.normal_f32(5, 0, (M, K), 1.0)
+    w = o.normal_f32(5, 1, (N, K), 0.02)
+    residual = o.normal_f32(5, 3, (M, N), 1.0)
+    got, qa, sa, qb, sb = run_fp8(cuda_device, a, w, residual=residual, split=H.SPLIT_AUTO, check_quant=False)
+    ref, gold = fp8_reference(qa, sa, qb, sb, residual=residual)
+    assert_gemm_ok(got, ref, gold)
+
+
+def run_grouped(device, cfg, group_rows, N, K, sigma_b=0.02):
+    import torch
+    G = len(group_rows)
+    M = int(group_rows.sum())
+    a = o.normal_f32(cfg, 0, (M, K), 1.0)
+    w = o.normal_f32(cfg, 1, (G * N, K), sigma_b)
+    qa, sa = H.quantize(dev_tensor(a, device), H.SCALE_FP32_1X128)
+    qb = torch.empty((G, N, K), dtype=torch.uint8, device=device)
+    sb = torch.empty((G, -(-K // 128), -(-N // 128)), dtype=torch.float32, device=device)
+    wd = dev_tensor(w, device)
+    for g in range(G):
+        c, s = H.quantize(wd[g * N:(g + 1) * N], H.SCALE_FP32_128X128)
+        qb[g].copy_(c)
+        sb[g].copy_(s)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=device)
+    rows_t = dev_tensor(group_rows.astype(np.int64), device)
+    with H.Contraction(M, N, K, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128, groups=G) as c:
+        c(qa, sa, qb, sb, out, group_rows=rows_t)
+    got = to_np(out)
+    da = o.dequant_fp8_1x128(to_np(qa), to_np(sa))
+    qb_n, sb_n = to_np(qb), to_np(sb)
+    db = np.stack([o.dequant_fp8_128x128(qb_n[g], sb_n[g]) for g in range(G)])
+    ref = o.grouped_matmul_ref(da, db, group_rows)
+    return got, ref
+
+
+def test_grouped_small_with_empty_groups(cuda_device):
+    rows = np.array([0, 5, 128, 0, 129, 1, 300, 0], dtype=np.int64)
+    got, ref = run_grouped(cuda_device, 14, rows, 264, 400)
+    assert_gemm_ok(got, ref)
+
+
+def test_config4_moe_grouped(cuda_device):
+    """G=128, K=2048, N=768, 32768 tokens split Multinomial(Dirichlet(0.5)): some groups empty, some large."""
+    rows = o.moe_group_rows()
+    got, ref = run_grouped(cuda_device, 4, rows, 768, 2048)
+    assert_gemm_ok(got, ref)
+
+
+# ------------------------------------------------------------------------------------------------ MX
+
+def run_mx(device, a, w, *, b_dtype=H.R_8F_E4M3, act=H.OP_IDENTITY, bias=None, residual=None, tile_n=0,
+           check_quant=True, static_b=False):
+    import torch
+    M, K = a.shape
+    N = w.shape[0]
+    name = "e2m1" if b_dtype == H.R_4F_E2M1 else "e4m3"
+    qa, sa = H.quantize(dev_tensor(a, device), H.SCALE_MX_E8M0_VEC32)
+    qb, sb = H.quantize(dev_tensor(w, device), H.SCALE_MX_E8M0_VEC32, b_dtype)
+    if check_quant:
+        ra, rsa = o.quant_mx(a)
+        rb, rsb = o.quant_mx(w, name)
+        assert np.array_equal(to_np(qa), ra) and np.array_equal(to_np(sa), rsa)
+        assert np.array_equal(to_np(qb), rb) and np.array_equal(to_np(sb), rsb)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=device)
+    bias_t = bf16_tensor(bias, device) if bias is not None else None
+    res_t = bf16_tensor(residual, device) if residual is not None else None
+    with H.Contraction(M, N, K, scale_mode_a=H.SCALE_MX_E8M0_VEC32, scale_mode_b=H.SCALE_MX_E8M0_VEC32, b_dtype=b_dtype,
+                       activation=act, bias=bias is not None, residual=residual is not None, tile_n=tile_n,
+                       b_is_static=static_b) as c:
+        c(qa, sa, qb, sb, out, bias=bias_t, residual=res_t)
+        first = to_np(out).copy()
+        out.fill_(float("nan"))
+        c(qa, sa, qb, sb, out, bias=bias_t, residual=res_t)      # second call may reuse the weight pre-pass
+        assert np.array_equal(to_np(out).view(np.uint32), first.view(np.uint32)), "two runs differ"
+    return first, to_np(qa), to_np(sa), to_np(qb), to_np(sb)
+
+
+def mx_reference(qa, sa, qb, sb, K, name="e4m3", act=o.ACT_IDENTITY, bias=None, residual=None, rows=None):
+    da = o.dequant_mx(qa if rows is None else qa[rows], sa if rows is None else sa[rows], K)
+    db = o.dequant_mx(qb, sb, K, name)
+    if rows is not None and residual is not None:
+        residual = residual[rows]
+    b16 = o.bf16_round(bias.astype(np.float32)) if bias is not None else None
+    r16 = o.bf16_round(residual.astype(np.float32)) if residual is not None else None
+    ref = o.matmul_ref64(da, db, b16, act, r16)
+    gold = o.matmul_golden32(da.astype(np.float32), db.astype(np.float32), b16, act, r16)
+    return ref, gold
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8, 32), (128, 128, 128), (128, 224, 256), (300, 520, 1040), (129, 232, 96),
+                                   (256, 512, 1024), (77, 456, 2064)])
+@pytest.mark.parametrize("tile_n", [128, 224])
+def test_mx_shapes_and_tails(cuda_device, M, N, K, tile_n):
+    a = o.normal_f32(21, 0, (M, K), 1.0)
+    w = o.normal_f32(21, 1, (N, K), 1.0)
+    got, qa, sa, qb, sb = run_mx(cuda_device, a, w, tile_n=tile_n)
+    ref, gold = mx_reference(qa, sa, qb, sb, K)
+    assert_gemm_ok(got, ref, gold)
+
+
+def test_mx_single_group_known_answer(cuda_device):
+    """32 x 1.0 times 32 x 0.5 is exactly 16 (tests/golden/micro_vectors.json, mx_dot)."""
+    a = np.full((128, 32), 1.0, dtype=np.float32)
+    w = np.full((8, 32), 0.5, dtype=np.float32)
+    got, *_ = run_mx(cuda_device, a, w)
+    assert np.all(got == 16.0)
+
+
+def test_mx_scale_extremes(cuda_device):
+    """Rows whose groups differ by 2^40 in magnitude exercise the per-group exponents, not just one scale."""
+    M, N, K = 128, 128, 256
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = rng.standard_normal((N, K)).astype(np.float32)
+    a *= np.exp2(rng.integers(-20, 20, size=(M, K // 32))).repeat(32, axis=1).astype(np.float32)
+    w *= np.exp2(rng.integers(-20, 20, size=(N, K // 32))).repeat(32, axis=1).astype(np.float32)
+    got, qa, sa, qb, sb = run_mx(cuda_device, a, w)
+    ref, gold = mx_reference(qa, sa, qb, sb, K)
+    assert_gemm_ok(got, ref, gold)
+
+
+@pytest.mark.parametrize("act", [H.OP_IDENTITY, H.OP_RELU, H.OP_GELU])
+def test_mx_fused_epilogue(cuda_device, act):
+    M, N, K = 260, 456, 512
+    a = o.normal_f32(22, 0, (M, K), 1.0)
+    w = o.normal_f32(22, 1, (N, K), 0.05)
+    bias = o.normal_f32(22, 2, (N,), 0.5)
+    residual = o.normal_f32(22, 3, (M, N), 1.0)
+    got, qa, sa, qb, sb = run_mx(cuda_device, a, w, act=act, bias=bias, residual=residual)
+    ref, gold = mx_reference(qa, sa, qb, sb, K, "e4m3", ACT[act], bias, residual)
+    assert_gemm_ok(got, ref, gold)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 224, 128), (200, 448, 1024), (64, 1000, 4096)])
+def test_w4a8_mx(cuda_device, M, N, K):
+    a = o.normal_f32(23, 0, (M, K), 1.0)
+    w = o.normal_f32(23, 1, (N, K), 0.02)
+    got, qa, sa, qb, sb = run_mx(cuda_device, a, w, b_dtype=H.R_4F_E2M1, static_b=True)
+    ref, gold = mx_reference(qa, sa, qb, sb, K, "e2m1")
+    assert_gemm_ok(got, ref, gold)
+
+
+def test_config2_mxfp8_8192_bias_gelu(cuda_device):
+    """M=N=K=8192, bf16 bias ~N(0,0.1), GELU(tanh), bf16 out; float64 reference on every 37th row."""
+    M = N = K = 8192
+    a = o.normal_f32(2, 0, (M, K), 1.0)
+    w = o.normal_f32(2, 1, (N, K), 1.0)
+    bias = o.normal_f32(2, 2, (N,), 0.1)
+    got, qa, sa, qb, sb = run_mx(cuda_device, a, w, act=H.OP_GELU, bias=bias, check_quant=False)
+    rows = np.arange(0, M, 37)
+    ref, gold = mx_reference(qa, sa, qb, sb, K, "e4m3", o.ACT_GELU_TANH, bias, rows=rows)
+    assert_gemm_ok(got[rows], ref, gold)
+    # quantisation of the sampled rows is bit-equal to the oracle's
+    ra, rsa = o.quant_mx(a[rows])
+    assert np.array_equal(qa[rows], ra) and np.array_equal(sa[rows], rsa)
+
+
+def test_config3_w4a8_4096x14336x4096(cuda_device):
+    M, N, K = 4096, 14336, 4096
+    a = o.normal_f32(3, 0, (M, K), 1.0)
+    w = o.normal_f32(3, 1, (N, K), 0.02)
+    got, qa, sa, qb, sb = run_mx(cuda_device, a, w, b_dtype=H.R_4F_E2M1, check_quant=False, static_b=True)
+    rows = np.arange(0, M, 29)
+    ref, gold = mx_reference(qa, sa, qb, sb, K, "e2m1", rows=rows)
+    assert_gemm_ok(got[rows], ref, gold)
+    cols = np.arange(0, N, 61)
+    rb, rsb = o.quant_mx(w[cols], "e2m1")
+    assert np.array_equal(qb[cols], rb) and np.array_equal(sb[cols], rsb)
