@@ -1,0 +1,374 @@
+#!/usr/bin/env python
+"""Benchmark of the Blaze quantized-matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c3|c4|c5]
+
+Default workload (the one the metric is quoted on): MXFP8 GEMM M=N=K=8192 with fused bf16 bias + GELU(tanh) and bf16
+output, synthetic seeded inputs.  With N GPUs (one process per GPU, launched by torch.distributed.run) the GEMM is
+sharded along N with no data-path collective: every rank holds A and an 8192-column shard of B, so the global
+problem is M=8192, N=8192*gpus, K=8192 (weak scaling).  One step = one pass of the hot path over that batch.
+
+Prints ONE JSON line: `value` = whole-job TFLOPS with quantized operands resident in HBM; `e2e` = the same metric
+through the acltensor* C API with the step's fp32 activations coming from pinned host memory and the bf16 result
+going back to it (copies and on-device quantisation inside the timed region); `roofline` for the GEMM kernel against
+the measured tensor peak; `cpu_baseline` = the reference-style CPU golden (de-quantise to float32, np.matmul,
+epilogue, bf16) timed on this box's host cores.
+
+`--impl reference` times that CPU golden alone, on the same config and metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (kind, M, N, K, description)
+    "c1": ("fp8", 256, 512, 1024, "FP8 1x128/128x128 GEMM 256x512x1024, bf16 out"),
+    "c2": ("mx", 8192, 8192, 8192, "MXFP8 GEMM 8192^3 + bf16 bias + GELU(tanh), bf16 out"),
+    "c3": ("mx4", 4096, 14336, 4096, "W4A8 MX GEMM 4096x14336x4096, bf16 out"),
+    "c4": ("grouped", 32768, 768, 2048, "MoE grouped FP8 matmul G=128, K=2048, N=768, 32768 tokens"),
+    "c5": ("fp8sk", 128, 7168, 18432, "stream-K decode FP8 GEMM M=128, N=7168, K=18432 + bf16 residual"),
+}
+
+
+def algorithmic_bytes(kind, M, N, K, G=128):
+    """Minimum HBM traffic: operands, scales, epilogue inputs and the output, each moved once."""
+    if kind == "mx":
+        return M * K + N * K + (M + N) * (K // 32) + 2 * N + 2 * M * N
+    if kind == "mx4":
+        return M * K + N * K // 2 + (M + N) * (K // 32) + 2 * M * N
+    if kind == "grouped":
+        return M * K + G * N * K + 4 * M * (K // 128) + 4 * G * (K // 128) * (N // 128) + 8 * G + 2 * M * N
+    kb, nb = -(-K // 128), -(-N // 128)
+    extra = 2 * M * N if kind == "fp8sk" else 0
+    return M * K + N * K + 4 * M * kb + 4 * kb * nb + 2 * M * N + extra
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            busy = [s for s in sm if s > 0.5 * max(sm)] or sm       # idle samples before/after the region
+            out.update(sm_mhz=float(np.median(busy)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons),
+                       samples=len(sm))
+        return out
+
+
+# ---------------------------------------------------------------------------------------------------- CPU golden
+
+CPU_SAMPLE = {"mx": (2048, 4096), "fp8": (256, 512)}        # (rows of A, rows of B) the CPU golden is timed on
+
+
+def make_cpu_golden(workload):
+    """Reference-style CPU golden (de-quantise to float32, np.matmul, epilogue, bf16) on a bounded sample of the
+    workload: the first rows of A against the first rows of B, full K.  Returns (run, flops, description)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import blaze_oracle as o
+    kind, M, N, K, desc = WORKLOADS[workload]
+    rows, cols = CPU_SAMPLE["mx" if kind == "mx" else "fp8"]
+    rows, cols = min(rows, M), min(cols, N)
+    if kind == "mx":
+        a = o.normal_f32(2, 0, (rows, K), 1.0)
+        w = o.normal_f32(2, 1, (cols, K), 1.0)
+        bias = o.bf16_round(o.normal_f32(2, 2, (cols,), 0.1))
+        qa, sa = o.quant_mx(a)
+        qb, sb = o.quant_mx(w)
+
+        def run():
+            da = o.dequant_mx(qa, sa, K, "e4m3", np.float32)
+            db = o.dequant_mx(qb, sb, K, "e4m3", np.float32)
+            return o.matmul_golden32(da, db, bias, o.ACT_GELU_TANH)
+    else:
+        a = o.normal_f32(1, 0, (rows, K), 1.0)
+        w = o.normal_f32(1, 1, (cols, K), 0.02)
+        qa, sa = o.quant_fp8_1x128(a)
+        qb, sb = o.quant_fp8_128x128(w)
+
+        def run():
+            return o.matmul_golden32(o.dequant_fp8_1x128(qa, sa, np.float32), o.dequant_fp8_128x128(qb, sb, np.float32))
+    sample = (f"{rows} rows of A x {cols} rows of B x K={K} of '{desc}' per step: de-quantise to float32, np.matmul, "
+              f"epilogue, bf16")
+    return run, 2.0 * rows * cols * K, sample
+
+
+def time_cpu_golden(run, repeats):
+    run()                                            # warm-up (BLAS thread pool, page faults)
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        run()
+        times.append(time.perf_counter() - t0)
+    return times
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    kind, M, N, K, desc = WORKLOADS[args.workload]
+    wl = args.workload if kind in ("mx", "fp8") else "c1"
+    cores = len(os.sched_getaffinity(0))
+    run, flops, sample = make_cpu_golden(wl)
+    for _ in range(max(1, min(args.warmup, 3))):
+        run()
+    times = []
+    t_all = time.perf_counter()
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        run()
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_all > 200:        # keep the whole run within a few minutes
+            break
+    ms = 1e3 * float(np.mean(times))
+    value = flops / (ms * 1e-3) / 1e12
+    line = {
+        "impl": "reference", "metric": "quantized GEMM TFLOPS", "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
+        "steps": len(times), "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
+        "config": {"workload": WORKLOADS[wl][4], "M": M, "N": N, "K": K, "sharding": "none (CPU golden on rank 0)"},
+        "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------- GPU arm
+
+def gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from ops_tensor_b200 import host as H
+    from ops_tensor_b200 import native, shard
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import blaze_oracle as o
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    native.lib()                                     # fails loudly if the CUDA library is missing
+
+    kind, M, N, K, desc = WORKLOADS[args.workload]
+    flops = 2.0 * M * N * K
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    # ---- inputs (seeded, generated on the host once) -----------------------------------------------------------
+    cfg_id = int(args.workload[1])
+    G = 128
+    group_rows = None
+    a_host = torch.from_numpy(o.normal_f32(cfg_id, 0, (M, K), 1.0)).pin_memory()
+    a_dev = a_host.to(dev, non_blocking=True)
+    sigma_b = 1.0 if kind == "mx" else 0.02
+    b_rows = G * N if kind == "grouped" else N
+    w_dev = torch.from_numpy(o.normal_f32(cfg_id, 1 + 16 * rank, (b_rows, K), sigma_b)).to(dev)
+    bias = residual = None
+    if kind == "mx":
+        bias = torch.from_numpy(o.bf16_round(o.normal_f32(cfg_id, 2, (N,), 0.1))).to(dev).to(torch.bfloat16)
+    if kind == "fp8sk":
+        residual = torch.from_numpy(o.bf16_round(o.normal_f32(cfg_id, 3, (M, N), 1.0))).to(dev).to(torch.bfloat16)
+
+    if kind in ("mx", "mx4"):
+        b_dtype = H.R_4F_E2M1 if kind == "mx4" else H.R_8F_E4M3
+        mode_a = mode_b = H.SCALE_MX_E8M0_VEC32
+        qb, sb = H.quantize(w_dev, mode_b, b_dtype)
+        plan = H.Contraction(M, N, K, scale_mode_a=mode_a, scale_mode_b=mode_b, b_dtype=b_dtype,
+                             activation=H.OP_GELU if kind == "mx" else H.OP_IDENTITY, bias=bias is not None,
+                             b_is_static=True)
+        launches_per_step = 2                        # scale re-tile of A + GEMM (B's pre-pass is reused)
+    else:
+        mode_a, mode_b = H.SCALE_FP32_1X128, H.SCALE_FP32_128X128
+        if kind == "grouped":
+            group_rows = torch.from_numpy(o.moe_group_rows()).to(dev)
+            qb = torch.empty((G, N, K), dtype=torch.uint8, device=dev)
+            sb = torch.empty((G, K // 128, N // 128), dtype=torch.float32, device=dev)
+            for g in range(G):
+                c, s = H.quantize(w_dev[g * N:(g + 1) * N], mode_b)
+                qb[g].copy_(c)
+                sb[g].copy_(s)
+        else:
+            qb, sb = H.quantize(w_dev, mode_b)
+        plan = H.Contraction(M, N, K, scale_mode_a=mode_a, scale_mode_b=mode_b, groups=G if kind == "grouped" else 0,
+                             residual=residual is not None)
+        launches_per_step = 1
+    del w_dev
+    qa, sa = H.quantize(a_dev, mode_a)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    out_host = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    torch.cuda.synchronize()
+
+    def step():
+        plan(qa, sa, qb, sb, out, bias=bias, residual=residual, group_rows=group_rows)
+
+    def step_e2e():
+        a_dev.copy_(a_host, non_blocking=True)
+        qa2, sa2 = H.quantize(a_dev, mode_a)
+        plan(qa2, sa2, qb, sb, out, bias=bias, residual=residual, group_rows=group_rows)
+        out_host.copy_(out, non_blocking=True)
+
+    def timed(fn, n):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        return shard.max_over_ranks(e0.elapsed_time(e1), dev)
+
+    for _ in range(warmup):
+        step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.15)
+    total_ms = timed(step, steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = total_ms / steps
+    e2e_steps = max(3, min(steps, 10))
+    for _ in range(2):
+        step_e2e()
+    e2e_ms = timed(step_e2e, e2e_steps) / e2e_steps
+    status = H.device_status()
+    plan.close()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        value = world * flops / (ms_per_step * 1e-3) / 1e12
+        abytes = algorithmic_bytes(kind, M, N, K)
+        tensor_bound = kind in ("mx", "mx4")
+        if tensor_bound:
+            # FP8 operands run at twice the bf16 MMA rate; the loop is timed back to back, so the burst figure
+            # applies to short runs and the sustained one to runs of a second or more
+            base = peaks["bf16_tflops_sustained"] if total_ms > 1000.0 else peaks["bf16_tflops"]
+            peak = 2.0 * base
+            achieved = flops / (ms_per_step * 1e-3) / 1e12
+            unit = "TFLOP/s"
+        else:
+            peak = peaks["hbm_gbs"]
+            achieved = abytes / (ms_per_step * 1e-3) / 1e9
+            unit = "GB/s"
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(tpath):
+            with open(tpath) as f:
+                traffic = json.load(f).get(args.workload)
+        line = {
+            "metric": "quantized GEMM TFLOPS", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
+            "config": {"workload": desc, "M": M, "N_per_gpu": N, "N_global": N * world, "K": K,
+                       "sharding": f"N-sharded over {world} GPU(s), A replicated, no collective",
+                       "l2": "operands + output exceed the 126 MB L2" if abytes > 126e6 else "fits in L2 (latency config)",
+                       "pct_of_published_dense_fp8_peak": round(100.0 * value / world / 4500.0, 2)},
+            "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak, "unit": unit,
+                         "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
+                         "algorithmic_bytes": abytes, "flops": flops},
+            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
+                    "h2d_bytes_per_step": a_host.numel() * 4, "d2h_bytes_per_step": out_host.numel() * 2,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": launches_per_step * steps,
+            "clocks": clocks,
+            "device_status": status,
+        }
+        if world == 1:
+            cpu_wl = args.workload if kind in ("mx", "fp8") else "c1"
+            run, cpu_flops, sample = make_cpu_golden(cpu_wl)
+            times = time_cpu_golden(run, 3)
+            line["cpu_baseline"] = {"value": cpu_flops / float(np.mean(times)) / 1e12, "unit": "TFLOPS",
+                                    "cores": len(os.sched_getaffinity(0)), "kind": "port",
+                                    "sample": sample + f"; mean of 3 runs, {np.mean(times):.2f} s each"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    if args.impl == "reference":
+        args.steps = min(args.steps, 20)
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

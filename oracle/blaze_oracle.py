@@ -219,9 +219,8 @@ def quant_mx(x: np.ndarray, elem: str = "e4m3"):
     absg = np.abs(g)
     amax = np.max(np.where(np.isnan(absg), 0, absg), axis=2).astype(np.float32)
     anynan = np.isnan(g).any(axis=2)
-    byte = e8m0_from_amax(amax, emax)
-    byte = np.where(anynan, 255, byte).astype(np.uint8)
-    eff = np.where(byte == 255, 127, byte).astype(np.int32)
+    eff = e8m0_from_amax(amax, emax).astype(np.int32)            # exponent from the finite elements of the group
+    byte = np.where(anynan, 255, eff).astype(np.uint8)           # a NaN anywhere marks the whole group
     inv = _pow2_f32(127 - eff)                                   # 2**(-e)
     q = (g * inv[:, :, None]).astype(np.float32)
     if elem == "e4m3":
