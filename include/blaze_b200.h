@@ -77,6 +77,27 @@ typedef struct {
 BLAZE_API int blazeMxGemmWorkspaceSize(const blazeMxGemmArgs* args, size_t* bytes);
 BLAZE_API int blazeMxGemm(const blazeMxGemmArgs* args, void* stream);
 
+/*
+ * The same MX GEMM for hosts that cannot give the library device memory: a serving process that has handed the whole
+ * GPU to its own memory pool, or a latency-critical loop in which a device allocation (which synchronises the GPU)
+ * is forbidden.  No counterpart in the reference.
+ *
+ * args->workspace and args->workspace_bytes are ignored: the re-tiled scale factors live in a fixed 8 MiB array that
+ * is part of the library image (every GPU that loads the library holds those 8 MiB until the process exits).  The
+ * call allocates nothing and frees nothing.  Limits and rules:
+ *   - B must be BLAZE_ELEM_E4M3 (packed E2M1 would need an N x K expansion buffer): NOT_SUPPORTED otherwise;
+ *   - a problem whose re-tiled scales exceed 8 MiB - about 512*(ceil(M/128) + 2*ceil(N/224))*ceil(K/128) bytes, e.g.
+ *     M = N = K = 8192 needs 4.4 MiB - is refused with ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE before anything runs;
+ *   - the first call on a device looks up the array's device address (one-time set-up, with that device current);
+ *     make that first call outside any stream capture;
+ *   - all calls share the one array, which still holds the previous call's tiles; each call rewrites the part it
+ *     uses, so calls must not overlap on the GPU (use one stream, or order them with events) - overlapping calls race;
+ *   - reuse_b_prepass is ignored (the weight's scale tiles are rebuilt every call).
+ * device_status is an optional device pointer to a zero-initialised int32 that receives the code of a kernel wait
+ * that gave up (see blazeDeviceStatus); NULL keeps that code in a word inside the library.
+ */
+BLAZE_API int blazeMxGemmNoAlloc(const blazeMxGemmArgs* args, int32_t* device_status, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------------
  * FP8 GEMM with float32 scales (1x128 groups of A, 128x128 blocks of B), dense or grouped, data-parallel or
  * stream-K.  D = act(sum_kb sa*sb*(A_kb x B_kb^T) + bias) + residual, bf16 output.

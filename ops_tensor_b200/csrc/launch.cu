@@ -476,3 +476,121 @@ extern "C" int blazeDeviceInfo(int32_t* sm_count, int32_t* cc_major, int32_t* cc
     if (cc_minor) *cc_minor = ctx->cc_minor;
     return ACLTENSOR_STATUS_SUCCESS;
 }
+
+// ------------------------------------------------------------------------------------------------ MX GEMM without allocation
+//
+// blazeMxGemm needs caller-provided device scratch for the re-tiled scale factors.  Hosts that hand a plugin no
+// allocator - an inference server that has reserved the whole GPU for its own memory pool, a real-time loop in which
+// a device allocation would synchronise the GPU - cannot size and allocate that buffer.  For them the same GEMM is
+// offered with the scratch held in a fixed 8 MiB array that is part of the library image on every device that loads it.
+
+namespace blaze {
+
+constexpr size_t kNoAllocScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_mx_noalloc_scratch[kNoAllocScratchBytes];
+static __device__ __align__(256) int g_mx_noalloc_status[64];
+
+struct NoAllocDevice {
+    bool ready = false;
+    unsigned char* scratch = nullptr;     // device address of g_mx_noalloc_scratch on this device
+    int* status = nullptr;                // device address of g_mx_noalloc_status on this device
+    int sm_count = 0;
+    int cc_major = 0;
+};
+static std::mutex g_noalloc_mutex;
+static NoAllocDevice g_noalloc[64];
+
+// Resolves, once per device and with that device current, the device addresses behind the two symbols.  In host
+// code the symbol names are only handles; a kernel must be given the addresses returned here.
+static int noalloc_setup(NoAllocDevice** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    NoAllocDevice& d = g_noalloc[dev];
+    if (!d.ready) {
+        void* scratch = nullptr;
+        void* status = nullptr;
+        if (cudaGetSymbolAddress(&scratch, g_mx_noalloc_scratch) != cudaSuccess ||
+            cudaGetSymbolAddress(&status, g_mx_noalloc_status) != cudaSuccess) {
+            cudaGetLastError();
+            return ACLTENSOR_STATUS_NOT_INITIALIZED;
+        }
+        int sms = 0, major = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+            cudaGetLastError();
+            return ACLTENSOR_STATUS_NOT_INITIALIZED;
+        }
+        d.scratch = static_cast<unsigned char*>(scratch);
+        d.status = static_cast<int*>(status);
+        d.sm_count = sms;
+        d.cc_major = major;
+        d.ready = true;
+    }
+    *out = &d;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+}  // namespace blaze
+
+extern "C" int blazeMxGemmNoAlloc(const blazeMxGemmArgs* a, int32_t* device_status, void* stream_v) {
+    NoAllocDevice* nd = nullptr;
+    int st = noalloc_setup(&nd);
+    if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    if (nd->cc_major != 10) return ACLTENSOR_STATUS_ARCH_MISMATCH;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    MxPlan pl;
+    st = plan_mx(a, nd->sm_count, &pl);
+    if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    if (a->b_elem != BLAZE_ELEM_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;      // packed E2M1 needs an N x K expansion buffer
+    if (pl.total > kNoAllocScratchBytes) return ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE;   // problem too large for the fixed array
+    if (a->M == 0 || a->N == 0) return ACLTENSOR_STATUS_SUCCESS;
+    if (!a->A || !a->B || !a->scaleA || !a->scaleB || !a->D) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->K == 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->lda < a->K || a->ldb < a->K || a->ldd < a->N || (a->residual && a->ldr < a->N))
+        return ACLTENSOR_STATUS_INVALID_VALUE;
+    if ((a->lda % 16) || (a->ldb % 16) || (a->ldd % 8) || (a->residual && (a->ldr % 8)))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (!aligned16(a->A) || !aligned16(a->B) || !aligned16(a->D) || !aligned16(a->bias) || !aligned16(a->residual))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+
+    uint8_t* sfa_tiled = nd->scratch + pl.sfa_off;
+    uint8_t* sfb_tiled = nd->scratch + pl.sfb_off;
+    // the array still holds the previous call's tiles: both scale arrays are rebuilt in full on every call
+    cudaError_t e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleA), a->M, a->K, 128, sfa_tiled, nd->sm_count,
+                                     stream);
+    if (e != cudaSuccess) return status_of(e);
+    e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleB), a->N, a->K, pl.tile_n, sfb_tiled, nd->sm_count, stream);
+    if (e != cudaSuccess) return status_of(e);
+
+    CUtensorMap ta, tb;
+    if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
+        !make_tmap_bytes(&tb, a->B, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->ldb, (uint32_t)pl.tile_n))
+        return ACLTENSOR_STATUS_INTERNAL_ERROR;
+
+    MxGemmParams p;
+    p.M = a->M; p.N = a->N; p.K = a->K;
+    p.m_tiles = pl.m_tiles; p.n_tiles = pl.n_tiles; p.k_steps = pl.k_steps;
+    p.window = pl.m_tiles < 16 ? pl.m_tiles : 16;
+    p.sfa_tiled = sfa_tiled;
+    p.sfb_tiled = sfb_tiled;
+    p.bias = static_cast<const __nv_bfloat16*>(a->bias);
+    p.residual = static_cast<const __nv_bfloat16*>(a->residual);
+    p.ldr = a->ldr;
+    p.D = static_cast<__nv_bfloat16*>(a->D);
+    p.ldd = a->ldd;
+    p.status = device_status ? reinterpret_cast<int*>(device_status) : nd->status;
+
+    const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
+    int sms = nd->sm_count;
+    if (a->sm_limit > 0 && a->sm_limit < sms) sms = a->sm_limit;
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    if (pl.tile_n == 224)
+        e = launch_mx_act<224>(a->activation, ta, tb, p, grid, stream);
+    else
+        e = launch_mx_act<128>(a->activation, ta, tb, p, grid, stream);
+    return status_of(e);
+}

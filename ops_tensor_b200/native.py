@@ -90,6 +90,8 @@ def lib() -> C.CDLL:
 def _declare(l: C.CDLL) -> None:
     l.blazeMxGemmWorkspaceSize.argtypes = [C.POINTER(MxGemmArgs), C.POINTER(C.c_size_t)]
     l.blazeMxGemm.argtypes = [C.POINTER(MxGemmArgs), C.c_void_p]
+    l.blazeMxGemmNoAlloc.argtypes = [C.POINTER(MxGemmArgs), C.c_void_p, C.c_void_p]
+    l.blazeMxGemmNoAlloc.restype = C.c_int
     l.blazeFp8GemmWorkspaceSize.argtypes = [C.POINTER(Fp8GemmArgs), C.POINTER(C.c_size_t)]
     l.blazeFp8Gemm.argtypes = [C.POINTER(Fp8GemmArgs), C.c_void_p]
     l.blazeQuantizeMx.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int64,

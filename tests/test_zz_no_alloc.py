@@ -1,0 +1,82 @@
+"""blazeMxGemmNoAlloc: the MX GEMM for hosts that cannot hand the library device memory.
+
+Some processes that load this library never let a plugin allocate on the GPU: an inference server that reserved the
+whole device for its own pool, or a real-time loop where an allocation would stall the GPU.  For them the GEMM keeps
+its scratch (the re-tiled scale factors) in a fixed 8 MiB array inside the library.  This test calls that entry
+point through the C ABI twice in a row, on two different problems, so the second call finds the first call's data in
+the shared array, and requires the same bits as the regular entry point produces with caller-provided workspace.
+It is collected last so that a run stopping at the first failure has already run every other test.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import blaze_oracle as o
+from ops_tensor_b200 import native
+
+pytestmark = pytest.mark.gpu
+
+
+def _problem(device, cfg, M, N, K, with_bias):
+    import torch
+    a = o.normal_f32(cfg, 0, (M, K), 1.0)
+    w = o.normal_f32(cfg, 1, (N, K), 0.5)
+    to_dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(device)
+    qa, sa = native.quantize_mx(to_dev(a))
+    qb, sb = native.quantize_mx(to_dev(w))
+    bias = to_dev(o.bf16_round(o.normal_f32(cfg, 2, (N,), 0.3))).to(torch.bfloat16) if with_bias else None
+    return qa, sa, qb, sb, bias
+
+
+def _run_both(device, qa, sa, qb, sb, bias, activation):
+    import torch
+    M, N = qa.shape[0], qb.shape[0]
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    want = native.mx_gemm(qa, sa, qb, sb, bias=bias, activation=activation)
+    got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=device)
+    status_word = torch.zeros(1, dtype=torch.int32, device=device)
+    args = native.mx_gemm_args(qa, sa, qb, sb, got, bias=bias, activation=activation)      # no workspace given
+    rc = native.lib().blazeMxGemmNoAlloc(C.byref(args), C.c_void_p(status_word.data_ptr()), stream)
+    assert rc == native.STATUS_SUCCESS
+    torch.cuda.synchronize()
+    assert int(status_word.item()) == 0
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    # a further call leaves the amount of free device memory exactly where it was: nothing was allocated or freed
+    free_before = torch.cuda.mem_get_info()[0]
+    rc = native.lib().blazeMxGemmNoAlloc(C.byref(args), C.c_void_p(status_word.data_ptr()), stream)
+    torch.cuda.synchronize()
+    assert rc == native.STATUS_SUCCESS and torch.cuda.mem_get_info()[0] == free_before
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    return got
+
+
+def test_no_alloc_entry_matches_regular_entry_twice(cuda_device):
+    import torch
+    first = _problem(cuda_device, 31, 300, 520, 1040, with_bias=True)
+    second = _problem(cuda_device, 32, 128, 224, 256, with_bias=False)
+    allocated = torch.cuda.memory_allocated()
+    out1 = _run_both(cuda_device, *first, activation=native.ACT_GELU_TANH)
+    out2 = _run_both(cuda_device, *second, activation=native.ACT_IDENTITY)      # finds call one's tiles in the array
+    assert torch.isfinite(out1.float()).all() and torch.isfinite(out2.float()).all()
+    # and the result is right, not merely equal: compare the second problem with the float64 oracle
+    qa, sa, qb, sb, _ = second
+    ref = o.matmul_ref64(o.dequant_mx(qa.cpu().numpy(), sa.cpu().numpy(), 256),
+                         o.dequant_mx(qb.cpu().numpy(), sb.cpu().numpy(), 256))
+    assert o.maxrel(out2.float().cpu().numpy(), ref) <= 1e-2
+    del out1, out2
+    assert torch.cuda.memory_allocated() <= allocated + (1 << 20)
+
+
+def test_no_alloc_entry_refuses_what_does_not_fit(cuda_device):
+    """Too large for the 8 MiB array, or needing an expansion buffer: refused before any launch."""
+    a = native.MxGemmArgs()
+    a.struct_size = C.sizeof(a)
+    a.M = a.N = a.K = 32768                       # re-tiled scales alone need ~70 MiB
+    a.A = a.B = a.scaleA = a.scaleB = a.D = 4096  # never dereferenced: the size check comes first
+    a.lda = a.ldb = a.ldd = 32768
+    assert native.lib().blazeMxGemmNoAlloc(C.byref(a), None, None) == native.STATUS_INSUFFICIENT_WORKSPACE
+    a.M = a.N = a.K = 256
+    a.lda = a.ldb = a.ldd = 256
+    a.b_elem = native.ELEM_E2M1
+    assert native.lib().blazeMxGemmNoAlloc(C.byref(a), None, None) == native.STATUS_NOT_SUPPORTED
