@@ -65,57 +65,67 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock, power and clock-event reasons through NVML (read-only queries) every few milliseconds on a
+    thread while the timed region runs."""
 
-    def __init__(self, gpu_index):
+    def __init__(self, gpu_index, period_s=0.005):
         self.gpu = gpu_index
-        self.proc = None
-        self.path = None
+        self.period = period_s
+        self.samples = []
+        self._stop = False
+        self._thread = None
+        self._max = None
 
     def start(self):
         try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.gpu), "-lms", "100"], stdout=open(self.path, "w"),
-                                         stderr=subprocess.DEVNULL)
-        except OSError:
-            self.proc = None
+            import threading
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self._max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            return
+
+        def loop():
+            while not self._stop:
+                try:
+                    mhz = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                    reasons = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                    watts = pynvml.nvmlDeviceGetPowerUsage(handle) / 1000.0
+                    self.samples.append((float(mhz), int(reasons), watts))
+                except Exception:
+                    pass
+                time.sleep(self.period)
+
+        self._thread = threading.Thread(target=loop, daemon=True)
+        self._thread.start()
+
+    def _physical_index(self):
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if visible:
+            ids = [v.strip() for v in visible.split(",") if v.strip()]
+            if self.gpu < len(ids) and ids[self.gpu].isdigit():
+                return int(ids[self.gpu])
+        return self.gpu
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
+        out = {"sm_mhz": None, "sm_max_mhz": self._max, "reasons": [], "samples": 0, "power_w_max": None}
+        if self._thread is None:
             return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        try:
-            for line in open(self.path):
-                parts = [p.strip() for p in line.split(",")]
-                if len(parts) < 9:
-                    continue
-                try:
-                    sm.append(float(parts[1]))
-                    mx.append(float(parts[2]))
-                except ValueError:
-                    continue
-                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
-                                     parts[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
-            os.unlink(self.path)
-        except OSError:
-            pass
-        if sm:
-            busy = [s for s in sm if s > 0.5 * max(sm)] or sm       # idle samples before/after the region
-            out.update(sm_mhz=float(np.median(busy)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons),
-                       samples=len(sm))
+        self._stop = True
+        self._thread.join(timeout=2)
+        if not self.samples:
+            return out
+        import pynvml
+        top = max(w for _, _, w in self.samples)
+        busy = [x for x in self.samples if x[2] > 0.5 * top] or self.samples      # drop idle samples around the region
+        names = (("hw_slowdown", pynvml.nvmlClocksEventReasonHwSlowdown),
+                 ("hw_thermal_slowdown", pynvml.nvmlClocksEventReasonHwThermalSlowdown),
+                 ("sw_thermal_slowdown", pynvml.nvmlClocksEventReasonSwThermalSlowdown),
+                 ("sw_power_cap", pynvml.nvmlClocksEventReasonSwPowerCap))
+        reasons = sorted({n for n, bit in names for _, r, _ in busy if r & bit})
+        out.update(sm_mhz=float(np.median([m for m, _, _ in busy])), reasons=reasons, samples=len(busy),
+                   power_w_max=round(top, 1))
         return out
 
 
@@ -291,16 +301,18 @@ def gpu_arm(args):
     for _ in range(warmup):
         step()
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and not args.kernel_only:
         sampler.start()
-        time.sleep(0.15)
+        time.sleep(0.05)
     total_ms = timed(step, steps)
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = total_ms / steps
-    e2e_steps = max(3, min(steps, 10))
-    for _ in range(2):
-        step_e2e()
-    e2e_ms = timed(step_e2e, e2e_steps) / e2e_steps
+    e2e_ms = float("nan")
+    if not args.kernel_only:
+        e2e_steps = max(3, min(steps, 10))
+        for _ in range(2):
+            step_e2e()
+        e2e_ms = timed(step_e2e, e2e_steps) / e2e_steps
     status = H.device_status()
     plan.close()
 
@@ -343,7 +355,7 @@ def gpu_arm(args):
             "clocks": clocks,
             "device_status": status,
         }
-        if world == 1:
+        if world == 1 and not args.kernel_only:
             cpu_wl = args.workload if kind in ("mx", "fp8") else "c1"
             run, cpu_flops, sample = make_cpu_golden(cpu_wl)
             times = time_cpu_golden(run, 3)
@@ -362,6 +374,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU-baseline legs (used for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = min(args.steps, 20)
