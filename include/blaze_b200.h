@@ -70,6 +70,8 @@ typedef struct {
     int32_t tile_n;          /* 0 = choose; else 128 or 224 */
     int32_t reuse_b_prepass; /* 1: workspace still holds B's re-tiled scales / expanded codes from the previous call */
     int32_t sm_limit;        /* 0 = all SMs; else cap on the persistent grid */
+    int32_t cta_pair;        /* 0 = choose; 1 = 128-row tiles, one CTA each; 2 = 256 x 224 tiles on 2-CTA clusters */
+    int32_t reserved;
     void* workspace;         /* device, 256-byte aligned */
     size_t workspace_bytes;
 } blazeMxGemmArgs;

@@ -1,0 +1,108 @@
+// Fused epilogue of the MX GEMM kernels: TMEM -> registers -> (bias, activation, residual, bf16) -> shared memory
+// -> TMA store.
+//
+// One warp owns 32 accumulator rows (its TMEM lane quadrant); each thread holds one row.  The tile is drained in
+// chunks of 32 columns: tcgen05.ld brings 32 fp32 values per thread, the fused ops run in registers, the bf16
+// results go to a 32 x 32 staging block in shared memory (64-byte rows, 64-byte swizzle, so the 16-byte writes of a
+// warp are bank-conflict free) and one lane hands the block to TMA, which writes full 32-byte sectors and clips at
+// the matrix edge.  Two staging blocks per warp alternate, so the store of chunk c overlaps the math of chunk c+1.
+// This takes the place of the reference's fix-pipe store with cast (include/blaze/gemm/block/block_mmad_qbmm_mx.h:466-479,
+// cast modes in include/tensor_api/impl/tensor_api/arch/cube/utils/l0c2out_utils.h:122-132), its bias-as-accumulator
+// init (block_mmad_qbmm_mx.h:500-506) and the fusion hook (include/blaze/epilogue/fusion/default_fusion_op.h:28-56).
+#pragma once
+
+#include "ptx.cuh"
+
+namespace blaze {
+
+constexpr int kEpiStageBytesPerWarp = 2 * 32 * 64;      // two 32 x 32 bf16 blocks
+constexpr int kEpiStageBytes = 4 * kEpiStageBytesPerWarp;
+
+struct EpilogueArgs {
+    int M, N;
+    const __nv_bfloat16* bias;
+    const __nv_bfloat16* residual;
+    long long ldr;
+};
+
+// Drains one accumulator tile.  `tmem_tile` = TMEM address of column 0 of the accumulator, lane field already set to
+// this warp's quadrant.  `row0` = global row of lane 0, `col0` = global column of accumulator column 0.  `stage` =
+// this warp's staging area (kEpiStageBytesPerWarp bytes, 512-byte aligned).  `chunk_counter` persists across tiles.
+// Calls `release()` once the last TMEM read of the tile has completed, before the remaining math and stores.
+template <int kBN, int kAct, class Release>
+__device__ __forceinline__ void epilogue_store_tile(uint32_t tmem_tile, const EpilogueArgs& ea,
+                                                    const CUtensorMap* tmap_d, uint8_t* stage, int row0, int col0,
+                                                    int lane, uint32_t& chunk_counter, Release release) {
+    const int row = row0 + lane;
+    const bool row_ok = row < ea.M;
+    const __nv_bfloat16* r_row = (ea.residual && row_ok) ? ea.residual + (long long)row * ea.ldr : nullptr;
+    constexpr int kChunks = kBN / 32;
+#pragma unroll 1
+    for (int c = 0; c < kChunks; ++c) {
+        const int n0 = col0 + c * 32;
+        if (n0 >= ea.N) {                       // whole chunk beyond the matrix: nothing to store
+            if (c == kChunks - 1) release();
+            continue;
+        }
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_tile + c * 32, v);
+        tmem_ld_wait();
+        if (c == kChunks - 1) release();
+
+        uint32_t packed[16];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int n = n0 + q * 8;
+            float x[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[q * 8 + e]);
+            const bool col_ok = n < ea.N;              // N is a multiple of 8
+            if (ea.bias && col_ok) {
+                const uint4 bv = __ldg(reinterpret_cast<const uint4*>(ea.bias + n));
+                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    x[2 * e] += __uint_as_float(bw[e] << 16);
+                    x[2 * e + 1] += __uint_as_float(bw[e] & 0xFFFF0000u);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[e] = apply_act<kAct>(x[e]);
+            if (r_row && col_ok) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(r_row + n);
+                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    x[2 * e] += __uint_as_float(rw[e] << 16);
+                    x[2 * e + 1] += __uint_as_float(rw[e] & 0xFFFF0000u);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) packed[q * 4 + e] = pack_bf16(x[2 * e], x[2 * e + 1]);
+        }
+
+        // staging block: make sure TMA has finished reading it (at most one younger store may still be in flight)
+        uint8_t* block = stage + (chunk_counter & 1) * (32 * 64);
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* my_row = block + lane * 64;
+        const int sw = (lane >> 1) & 3;                // 64-byte swizzle: 16-byte slot ^= (row / 2) % 4
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            *reinterpret_cast<uint4*>(my_row + ((q ^ sw) << 4)) =
+                make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(tmap_d, block, n0, row0);
+            tma_store_commit();
+        }
+        ++chunk_counter;
+    }
+}
+
+// To be called by lane 0 of every epilogue warp before the kernel ends.
+__device__ __forceinline__ void epilogue_drain_stores() { tma_store_wait<0>(); }
+
+}  // namespace blaze

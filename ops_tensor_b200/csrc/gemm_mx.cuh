@@ -13,12 +13,13 @@
 //   * one elected thread of warp 5 copies the scale blocks into TMEM (tcgen05.cp) and issues
 //     tcgen05.mma.kind::mxf8f6f4.block_scale, four K=32 instructions per 128-wide K step,
 //   * warps 0-3 drain a finished fp32 accumulator from TMEM (tcgen05.ld), apply bias / activation / residual and
-//     write bf16, while the tensor core already fills the second accumulator stage.
+//     hand bf16 blocks to TMA stores (epilogue.cuh), while the tensor core already fills the second accumulator.
 //
 // Tiles are visited in the reference's windowed serpentine order; each CTA takes tile ids
 // blockIdx.x, blockIdx.x + gridDim.x, ...
 #pragma once
 
+#include "epilogue.cuh"
 #include "ptx.cuh"
 
 namespace blaze {
@@ -51,7 +52,8 @@ struct MxGemmSmem {
     // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
     static constexpr int kNumBars = 2 * kStages + 4;
     static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
-    static constexpr int kTotal = kMiscOffset + 16;
+    static constexpr int kEpiOffset = (kMiscOffset + 16 + 1023) / 1024 * 1024;     // bf16 staging blocks of the epilogue
+    static constexpr int kTotal = kEpiOffset + kEpiStageBytes;
     static constexpr int kDynamicBytes = kTotal + 1024;      // slack for manual 1024-byte alignment
     static constexpr uint32_t kTxBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
 };
@@ -69,7 +71,7 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
 template <int kBN, int kStages, int kAct>
 __global__ void __launch_bounds__(192, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const MxGemmParams p) {
+               const __grid_constant__ CUtensorMap tmap_d, const MxGemmParams p) {
     using L = MxGemmSmem<kBN, kStages>;
     static_assert(kBN % 32 == 0 && kBN >= 32 && kBN <= 256, "tile N");
     constexpr int kAccStages = 2;
@@ -109,6 +111,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (warp == 4 && lane == 0) {
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_d);
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -191,8 +194,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // ------------------------------------------------------------------ epilogue warps 0..3
         int acc = 0;
         uint32_t acc_phase = 0;
+        uint32_t chunk_counter = 0;
         bool ok = true;
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        uint8_t* stage_buf = smem + L::kEpiOffset + warp * kEpiStageBytesPerWarp;
+        const EpilogueArgs ea{p.M, p.N, p.bias, p.residual, p.ldr};
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             int mt, nt;
             tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);
@@ -200,59 +206,16 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tcgen05_fence_after();
-            const int row = mt * L::kBM + warp * 32 + lane;
-            const bool row_ok = row < p.M;
-            __nv_bfloat16* d_row = p.D + (long long)row * p.ldd;
-            const __nv_bfloat16* r_row = p.residual ? p.residual + (long long)row * p.ldr : nullptr;
-#pragma unroll 1
-            for (int c = 0; c < kBN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_base + lane_base + acc * kBN + c * 32, v);
-                tmem_ld_wait();
-                const int n0 = nt * kBN + c * 32;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int n = n0 + q * 8;
-                    if (n < p.N) {                       // N is a multiple of 8
-                        float x[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[q * 8 + e]);
-                        if (p.bias) {
-                            const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
-                            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                x[2 * e] += __uint_as_float(bw[e] << 16);
-                                x[2 * e + 1] += __uint_as_float(bw[e] & 0xFFFF0000u);
-                            }
-                        }
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) x[e] = apply_act<kAct>(x[e]);
-                        if (row_ok) {
-                            if (r_row) {
-                                const uint4 rv = *reinterpret_cast<const uint4*>(r_row + n);
-                                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    x[2 * e] += __uint_as_float(rw[e] << 16);
-                                    x[2 * e + 1] += __uint_as_float(rw[e] & 0xFFFF0000u);
-                                }
-                            }
-                            uint4 o;
-                            o.x = pack_bf16(x[0], x[1]);
-                            o.y = pack_bf16(x[2], x[3]);
-                            o.z = pack_bf16(x[4], x[5]);
-                            o.w = pack_bf16(x[6], x[7]);
-                            *reinterpret_cast<uint4*>(d_row + n) = o;
-                        }
-                    }
-                }
-            }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+            uint64_t* release_bar = &tmem_empty_bar[acc];
+            epilogue_store_tile<kBN, kAct>(tmem_base + lane_base + acc * kBN, ea, &tmap_d, stage_buf,
+                                           mt * L::kBM + warp * 32, nt * kBN, lane, chunk_counter, [&]() {
+                                               tcgen05_fence_before();
+                                               __syncwarp();
+                                               if (lane == 0) mbar_arrive(release_bar);
+                                           });
             if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
         }
+        if (lane == 0) epilogue_drain_stores();
     }
 
     // ---------------------------------------------------------------------- teardown

@@ -1,0 +1,230 @@
+// G1, paired form: the MX block-scaled GEMM of gemm_mx.cuh on 256 x kBN tiles computed by two CTAs on neighbouring
+// SMs (a cluster of 2, tcgen05 cta_group::2).
+//
+// Each CTA of a pair stages its own 128 rows of A and its own kBN/2 rows of B; the tensor cores of both SMs read the
+// two B halves from both shared memories, so every SM loads (128 + kBN/2) x 128 bytes per K step instead of
+// (128 + kBN) x 128, which is what bounds the single-CTA kernel (traffic through L2 and time to refill a stage).
+// Only the even ("leader") CTA issues tcgen05.cp / tcgen05.mma; its commits arrive on the barriers of both CTAs.
+// Every load is an ordinary per-CTA TMA load (no cluster multicast); the odd CTA's loads credit their bytes to the
+// leader's "full" barrier.  The role of the reference code it replaces is the same as in gemm_mx.cuh
+// (include/blaze/gemm/kernel/kernel_qbmm_mx.h:379-454, include/blaze/gemm/block/block_mmad_qbmm_mx.h:398-480).
+#pragma once
+
+#include "gemm_mx.cuh"
+
+namespace blaze {
+
+template <int kBN, int kStages>
+struct MxPairSmem {
+    static constexpr int kBM = 128;                       // rows of A per CTA (256 per pair)
+    static constexpr int kBK = 128;
+    static constexpr int kABytes = kBM * kBK;
+    static constexpr int kBHalfBytes = (kBN / 2) * kBK;
+    static constexpr int kStageBytes = kABytes + kBHalfBytes;
+    static constexpr int kSfaBytes = 512;
+    static constexpr int kSfbAtoms = (kBN + 127) / 128;
+    static constexpr int kSfbBytes = kSfbAtoms * 512;
+    static constexpr int kSfOffset = kStages * kStageBytes;
+    static constexpr int kBarOffset = kSfOffset + kStages * (kSfaBytes + kSfbBytes);
+    static constexpr int kNumBars = 2 * kStages + 4;
+    static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
+    static constexpr int kEpiOffset = (kMiscOffset + 16 + 1023) / 1024 * 1024;
+    static constexpr int kTotal = kEpiOffset + kEpiStageBytes;
+    static constexpr int kDynamicBytes = kTotal + 1024;
+    static constexpr uint32_t kTxBytesPerCta = kABytes + kBHalfBytes + kSfaBytes + kSfbBytes;
+    static_assert(kStageBytes % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+};
+
+__device__ __forceinline__ uint32_t map_to_cta(const void* smem_ptr, uint32_t cta_rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(smem_ptr)), "r"(cta_rank));
+    return remote;
+}
+
+// TMA load issued by either CTA of the pair; `bar_cluster_addr` is the shared::cluster address of the barrier that
+// receives the byte count (the leader's).
+__device__ __forceinline__ void tma_load_2d_to_pair_bar(void* smem_dst, const CUtensorMap* tmap,
+                                                        uint32_t bar_cluster_addr, int x, int y, uint64_t hint) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y), "l"(hint)
+        : "memory");
+}
+
+template <int kBN, int kStages, int kAct>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                    const __grid_constant__ CUtensorMap tmap_d, const MxGemmParams p) {
+    using L = MxPairSmem<kBN, kStages>;
+    static_assert(kBN % 32 == 0 && kBN >= 32 && kBN <= 256, "tile N");
+    constexpr int kAccStages = 2;
+    constexpr int kSfaCol = kAccStages * kBN;
+    constexpr int kSfbCol = kSfaCol + 4;
+    static_assert(kSfbCol + 4 * L::kSfbAtoms <= 512, "TMEM budget");
+    constexpr uint32_t kTmemCols = 512;
+
+    extern __shared__ uint8_t smem_unaligned[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+    uint64_t* full_bar = bars;                       // used in the leader only
+    uint64_t* empty_bar = bars + kStages;            // one per CTA, released by the leader's commits
+    uint64_t* tmem_full_bar = bars + 2 * kStages;    // one per CTA
+    uint64_t* tmem_empty_bar = bars + 2 * kStages + 2;   // used in the leader only: 8 epilogue warps arrive
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tmem_full_bar[s], 1);
+            mbar_init(&tmem_empty_bar[s], 8);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 5) {
+        tmem_alloc<2>(tmem_base_slot, kTmemCols);
+    }
+    if (warp == 4 && lane == 0) {
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_sfa);
+        tma_prefetch_desc(&tmap_sfb);
+        tma_prefetch_desc(&tmap_d);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();                                  // both CTAs' barriers exist before anyone signals across
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    const int num_tiles = p.m_tiles * p.n_tiles;     // m_tiles counts 256-row tiles here
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+                int mt, nt;
+                tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);
+                const int a_row = mt * 256 + (int)cta_rank * 128;
+                const int b_row = nt * kBN + (int)cta_rank * (kBN / 2);
+                const int sfa_row = (mt * 2 + (int)cta_rank) * p.k_steps;
+                const int sfb_row = nt * p.k_steps * L::kSfbAtoms;
+                for (int ks = 0; ks < p.k_steps; ++ks) {
+                    ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
+                    if (!ok) break;
+                    uint8_t* a_dst = smem + stage * L::kStageBytes;
+                    uint8_t* b_dst = a_dst + L::kABytes;
+                    uint8_t* sfa_dst = smem + L::kSfOffset + stage * (L::kSfaBytes + L::kSfbBytes);
+                    uint8_t* sfb_dst = sfa_dst + L::kSfaBytes;
+                    if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * L::kTxBytesPerCta);
+                    const uint32_t bar = map_to_cta(&full_bar[stage], 0);
+                    tma_load_2d_to_pair_bar(a_dst, &tmap_a, bar, ks * L::kBK, a_row, kEvictNormal);
+                    tma_load_2d_to_pair_bar(b_dst, &tmap_b, bar, ks * L::kBK, b_row, kEvictNormal);
+                    tma_load_2d_to_pair_bar(sfa_dst, &tmap_sfa, bar, 0, sfa_row + ks, kEvictNormal);
+                    tma_load_2d_to_pair_bar(sfb_dst, &tmap_sfb, bar, 0, sfb_row + ks * L::kSfbAtoms, kEvictNormal);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && cta_rank == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+                ok = mbar_wait<true>(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * kBN;
+                for (int ks = 0; ks < p.k_steps; ++ks) {
+                    ok = mbar_wait<true>(&full_bar[stage], phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
+                    const uint32_t b_addr = a_addr + L::kABytes;
+                    const uint32_t sfa_addr = smem_u32(smem + L::kSfOffset + stage * (L::kSfaBytes + L::kSfbBytes));
+                    const uint32_t sfb_addr = sfa_addr + L::kSfaBytes;
+                    utccp_sf<2>(tmem_base + kSfaCol, umma_desc_sf(sfa_addr));
+#pragma unroll
+                    for (int i = 0; i < L::kSfbAtoms; ++i) {
+                        utccp_sf<2>(tmem_base + kSfbCol + 4 * i, umma_desc_sf(sfb_addr + 512 * i));
+                    }
+                    const uint64_t a_desc = umma_desc_sw128(a_addr);
+                    const uint64_t b_desc = umma_desc_sw128(b_addr);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        umma_mx<2>(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
+                                   umma_idesc_mx(FMT_E4M3, FMT_E4M3, 256, kBN, j, j), (ks | j) != 0 ? 1u : 0u,
+                                   tmem_base + kSfaCol, tmem_base + kSfbCol);
+                    }
+                    umma_commit_pair(&empty_bar[stage], 0x3);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(&tmem_full_bar[acc], 0x3);
+                if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps 0..3 (both CTAs)
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        uint32_t chunk_counter = 0;
+        bool ok = true;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        uint8_t* stage_buf = smem + L::kEpiOffset + warp * kEpiStageBytesPerWarp;
+        const EpilogueArgs ea{p.M, p.N, p.bias, p.residual, p.ldr};
+        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+            int mt, nt;
+            tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);
+            ok = mbar_wait<true>(&tmem_full_bar[acc], acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
+            uint64_t* release_bar = &tmem_empty_bar[acc];          // owned by the leader CTA
+            epilogue_store_tile<kBN, kAct>(tmem_base + lane_base + acc * kBN, ea, &tmap_d, stage_buf,
+                                           mt * 256 + (int)cta_rank * 128 + warp * 32, nt * kBN, lane, chunk_counter,
+                                           [&]() {
+                                               tcgen05_fence_before();
+                                               __syncwarp();
+                                               if (lane == 0) mbar_arrive_cluster(release_bar, 0);
+                                           });
+            if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+        }
+        if (lane == 0) epilogue_drain_stores();
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    __syncthreads();
+    if (*abort_flag != 0) {
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();          // neither CTA leaves while its partner may still signal its barriers or read its tiles
+    if (warp == 5) {
+        __syncwarp();
+        tcgen05_fence_after();
+        tmem_dealloc<2>(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace blaze

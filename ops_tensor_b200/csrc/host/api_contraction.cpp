@@ -58,6 +58,7 @@ void fill_mx_args(const acltensorOperationDescriptor& op, blazeMxGemmArgs* a) {
     a->activation = activation_of(op.epilogueAct);
     a->tile_n = op.tileN;
     a->sm_limit = op.smLimit;
+    a->cta_pair = op.ctaPair;
 }
 
 acltensorStatus_t MxWorkspace(const acltensorOperationDescriptor& op, int32_t, uint64_t* bytes) {
@@ -240,6 +241,7 @@ int32_t* attribute_slot(acltensorOperationDescriptor* d, acltensorOperationDescr
         case ACLTENSOR_OPERATION_DESCRIPTOR_TILE_N: return &d->tileN;
         case ACLTENSOR_OPERATION_DESCRIPTOR_SM_LIMIT: return &d->smLimit;
         case ACLTENSOR_OPERATION_DESCRIPTOR_B_IS_STATIC: return &d->bIsStatic;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_CTA_PAIR: return &d->ctaPair;
         default: return nullptr;
     }
 }
@@ -281,6 +283,9 @@ acltensorStatus_t acltensorOperationDescriptorSetAttribute(const acltensorHandle
             break;
         case ACLTENSOR_OPERATION_DESCRIPTOR_SM_LIMIT:
             if (v < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
+            break;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_CTA_PAIR:
+            if (v < 0 || v > 2) return ACLTENSOR_STATUS_INVALID_VALUE;
             break;
         default:
             break;

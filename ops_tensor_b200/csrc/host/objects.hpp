@@ -94,6 +94,7 @@ struct acltensorOperationDescriptor {
     int32_t tileN = 0;
     int32_t smLimit = 0;
     int32_t bIsStatic = 0;
+    int32_t ctaPair = 0;
 
     // contraction geometry, resolved at creation
     int64_t M = 0, N = 0, K = 0;

@@ -12,6 +12,7 @@
 #include "cann_ops_tensor_types.h"
 #include "gemm_fp8.cuh"
 #include "gemm_mx.cuh"
+#include "gemm_mx_pair.cuh"
 #include "launch.h"
 
 namespace blaze {
@@ -85,6 +86,20 @@ static bool make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t row_byt
     return r == CUDA_SUCCESS;
 }
 
+// bf16 output matrix [rows][cols valid, ld elements apart] written in 32 x 32 blocks staged with the 64-byte swizzle.
+static bool make_tmap_bf16_store(CUtensorMap* map, void* base, uint64_t cols, uint64_t rows, uint64_t ld_elems) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld_elems * 2};
+    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, elem_strides,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 static inline size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
 
@@ -97,6 +112,7 @@ static int status_of(cudaError_t e) {
 // ------------------------------------------------------------------------------------------------ MX GEMM
 
 struct MxPlan {
+    bool pair;          // 256 x 224 tiles on 2-CTA clusters
     int tile_n;
     int m_tiles, n_tiles, k_steps;
     size_t sfa_bytes, sfb_bytes, b_expand_bytes;
@@ -122,8 +138,13 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl) {
     if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_GELU_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->tile_n != 0 && a->tile_n != 128 && a->tile_n != 224) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if ((a->K % 16) != 0 || (a->N % 8) != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    pl->tile_n = choose_tile_n(a->M, a->N, sms, a->tile_n);
-    pl->m_tiles = (a->M + 127) / 128;
+    if (a->cta_pair < 0 || a->cta_pair > 2) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->cta_pair == 2 && a->tile_n == 128) return ACLTENSOR_STATUS_NOT_SUPPORTED;    // paired tiles are 256 x 224
+    // 256 x 224 tiles on CTA pairs once there are at least two 128-row blocks and more than one 128-column block
+    // (an explicit tile_n without cta_pair = 2 keeps the single-CTA kernel of that width)
+    pl->pair = a->cta_pair == 2 || (a->cta_pair == 0 && a->tile_n == 0 && a->M > 128 && a->N > 128 && sms >= 2);
+    pl->tile_n = pl->pair ? 224 : choose_tile_n(a->M, a->N, sms, a->tile_n);
+    pl->m_tiles = pl->pair ? (a->M + 255) / 256 : (a->M + 127) / 128;
     pl->n_tiles = (a->N + pl->tile_n - 1) / pl->tile_n;
     pl->k_steps = (a->K + 127) / 128;
     pl->sfa_bytes = (size_t)sf_tiled_bytes(a->M, a->K, 128);
@@ -137,8 +158,8 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl) {
 }
 
 template <int kBN, int kAct>
-static cudaError_t launch_mx_instance(const CUtensorMap& ta, const CUtensorMap& tb, const MxGemmParams& p, int grid,
-                                      cudaStream_t stream) {
+static cudaError_t launch_mx_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                                      const MxGemmParams& p, int grid, cudaStream_t stream) {
     constexpr int kStages = 4;
     using L = MxGemmSmem<kBN, kStages>;
     auto kernel = mx_gemm_kernel<kBN, kStages, kAct>;
@@ -150,18 +171,105 @@ static cudaError_t launch_mx_instance(const CUtensorMap& ta, const CUtensorMap& 
         if (e != cudaSuccess) return e;
         attr_done[dev & 63] = true;
     }
-    kernel<<<grid, 192, L::kDynamicBytes, stream>>>(ta, tb, p);
+    kernel<<<grid, 192, L::kDynamicBytes, stream>>>(ta, tb, td, p);
     return cudaGetLastError();
 }
 
 template <int kBN>
-static cudaError_t launch_mx_act(int act, const CUtensorMap& ta, const CUtensorMap& tb, const MxGemmParams& p, int grid,
-                                 cudaStream_t stream) {
+static cudaError_t launch_mx_act(int act, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                                 const MxGemmParams& p, int grid, cudaStream_t stream) {
     switch (act) {
-        case BLAZE_ACT_RELU: return launch_mx_instance<kBN, ACT_RELU>(ta, tb, p, grid, stream);
-        case BLAZE_ACT_GELU_TANH: return launch_mx_instance<kBN, ACT_GELU_TANH>(ta, tb, p, grid, stream);
-        default: return launch_mx_instance<kBN, ACT_IDENTITY>(ta, tb, p, grid, stream);
+        case BLAZE_ACT_RELU: return launch_mx_instance<kBN, ACT_RELU>(ta, tb, td, p, grid, stream);
+        case BLAZE_ACT_GELU_TANH: return launch_mx_instance<kBN, ACT_GELU_TANH>(ta, tb, td, p, grid, stream);
+        default: return launch_mx_instance<kBN, ACT_IDENTITY>(ta, tb, td, p, grid, stream);
     }
+}
+
+// Row-major matrix of 512-byte scale-factor blocks, loaded `box_rows` blocks at a time, no swizzle.
+static bool make_tmap_sf_blocks(CUtensorMap* map, const void* base, uint64_t blocks, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {128, blocks};                 // 128 x 4-byte words per block
+    const cuuint64_t strides[1] = {512};
+    const cuuint32_t box[2] = {128, box_rows};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box,
+                          elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int kAct>
+static cudaError_t launch_mx_pair_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
+                                           const CUtensorMap& tsb, const CUtensorMap& td, const MxGemmParams& p,
+                                           int pairs, cudaStream_t stream) {
+    constexpr int kBN = 224, kStages = 6;
+    using L = MxPairSmem<kBN, kStages>;
+    auto kernel = mx_gemm_pair_kernel<kBN, kStages, kAct>;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+        if (e != cudaSuccess) return e;
+        attr_done[dev & 63] = true;
+    }
+    kernel<<<2 * pairs, 192, L::kDynamicBytes, stream>>>(ta, tb, tsa, tsb, td, p);     // cluster of 2 set on the kernel
+    return cudaGetLastError();
+}
+
+// Encodes the tensor maps and launches the GEMM kernel the plan chose.  `sfa_tiled` / `sfb_tiled` hold the re-tiled
+// scales, `b_codes` the 8-bit B operand (the caller's, or the expansion of a packed E2M1 one).
+static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8_t* sfa_tiled, const uint8_t* sfb_tiled,
+                         const uint8_t* b_codes, int64_t b_pitch, int* status_word, int sm_count,
+                         cudaStream_t stream) {
+    MxGemmParams p;
+    p.M = a->M; p.N = a->N; p.K = a->K;
+    p.m_tiles = pl.m_tiles; p.n_tiles = pl.n_tiles; p.k_steps = pl.k_steps;
+    p.window = pl.pair ? (pl.m_tiles < 8 ? pl.m_tiles : 8) : (pl.m_tiles < 16 ? pl.m_tiles : 16);
+    p.sfa_tiled = sfa_tiled;
+    p.sfb_tiled = sfb_tiled;
+    p.bias = static_cast<const __nv_bfloat16*>(a->bias);
+    p.residual = static_cast<const __nv_bfloat16*>(a->residual);
+    p.ldr = a->ldr;
+    p.D = static_cast<__nv_bfloat16*>(a->D);
+    p.ldd = a->ldd;
+    p.status = status_word;
+
+    const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
+    int sms = sm_count;
+    if (a->sm_limit > 0 && a->sm_limit < sms) sms = a->sm_limit;
+    CUtensorMap ta, tb, td;
+    cudaError_t e;
+    if (!make_tmap_bf16_store(&td, a->D, (uint64_t)a->N, (uint64_t)a->M, (uint64_t)a->ldd))
+        return ACLTENSOR_STATUS_INTERNAL_ERROR;
+    if (pl.pair) {
+        CUtensorMap tsa, tsb;
+        const uint64_t sfa_blocks = (uint64_t)((a->M + 127) / 128) * pl.k_steps;
+        const uint64_t sfb_blocks = (uint64_t)pl.n_tiles * pl.k_steps * 2;
+        if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
+            !make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, 112) ||
+            !make_tmap_sf_blocks(&tsa, sfa_tiled, sfa_blocks, 1) || !make_tmap_sf_blocks(&tsb, sfb_tiled, sfb_blocks, 2))
+            return ACLTENSOR_STATUS_INTERNAL_ERROR;
+        int pairs = sms / 2;
+        if (pairs < 1) pairs = 1;
+        if (tiles < pairs) pairs = (int)tiles;
+        switch (a->activation) {
+            case BLAZE_ACT_RELU: e = launch_mx_pair_instance<ACT_RELU>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
+            case BLAZE_ACT_GELU_TANH: e = launch_mx_pair_instance<ACT_GELU_TANH>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
+            default: e = launch_mx_pair_instance<ACT_IDENTITY>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
+        }
+        return status_of(e);
+    }
+    if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
+        !make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n))
+        return ACLTENSOR_STATUS_INTERNAL_ERROR;
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    if (pl.tile_n == 224)
+        e = launch_mx_act<224>(a->activation, ta, tb, td, p, grid, stream);
+    else
+        e = launch_mx_act<128>(a->activation, ta, tb, td, p, grid, stream);
+    return status_of(e);
 }
 
 }  // namespace blaze
@@ -225,33 +333,7 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
         }
     }
 
-    CUtensorMap ta, tb;
-    if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
-        !make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n))
-        return ACLTENSOR_STATUS_INTERNAL_ERROR;
-
-    MxGemmParams p;
-    p.M = a->M; p.N = a->N; p.K = a->K;
-    p.m_tiles = pl.m_tiles; p.n_tiles = pl.n_tiles; p.k_steps = pl.k_steps;
-    p.window = pl.m_tiles < 16 ? pl.m_tiles : 16;
-    p.sfa_tiled = sfa_tiled;
-    p.sfb_tiled = sfb_tiled;
-    p.bias = static_cast<const __nv_bfloat16*>(a->bias);
-    p.residual = static_cast<const __nv_bfloat16*>(a->residual);
-    p.ldr = a->ldr;
-    p.D = static_cast<__nv_bfloat16*>(a->D);
-    p.ldd = a->ldd;
-    p.status = ctx->status_word;
-
-    const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
-    int sms = ctx->sm_count;
-    if (a->sm_limit > 0 && a->sm_limit < sms) sms = a->sm_limit;
-    const int grid = (int)(tiles < sms ? tiles : sms);
-    if (pl.tile_n == 224)
-        e = launch_mx_act<224>(a->activation, ta, tb, p, grid, stream);
-    else
-        e = launch_mx_act<128>(a->activation, ta, tb, p, grid, stream);
-    return status_of(e);
+    return run_mx_kernel(a, pl, sfa_tiled, sfb_tiled, b_codes, b_pitch, ctx->status_word, ctx->sm_count, stream);
 }
 
 // ------------------------------------------------------------------------------------------------ FP8 GEMM
@@ -566,31 +648,6 @@ extern "C" int blazeMxGemmNoAlloc(const blazeMxGemmArgs* a, int32_t* device_stat
     e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleB), a->N, a->K, pl.tile_n, sfb_tiled, nd->sm_count, stream);
     if (e != cudaSuccess) return status_of(e);
 
-    CUtensorMap ta, tb;
-    if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
-        !make_tmap_bytes(&tb, a->B, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->ldb, (uint32_t)pl.tile_n))
-        return ACLTENSOR_STATUS_INTERNAL_ERROR;
-
-    MxGemmParams p;
-    p.M = a->M; p.N = a->N; p.K = a->K;
-    p.m_tiles = pl.m_tiles; p.n_tiles = pl.n_tiles; p.k_steps = pl.k_steps;
-    p.window = pl.m_tiles < 16 ? pl.m_tiles : 16;
-    p.sfa_tiled = sfa_tiled;
-    p.sfb_tiled = sfb_tiled;
-    p.bias = static_cast<const __nv_bfloat16*>(a->bias);
-    p.residual = static_cast<const __nv_bfloat16*>(a->residual);
-    p.ldr = a->ldr;
-    p.D = static_cast<__nv_bfloat16*>(a->D);
-    p.ldd = a->ldd;
-    p.status = device_status ? reinterpret_cast<int*>(device_status) : nd->status;
-
-    const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
-    int sms = nd->sm_count;
-    if (a->sm_limit > 0 && a->sm_limit < sms) sms = a->sm_limit;
-    const int grid = (int)(tiles < sms ? tiles : sms);
-    if (pl.tile_n == 224)
-        e = launch_mx_act<224>(a->activation, ta, tb, p, grid, stream);
-    else
-        e = launch_mx_act<128>(a->activation, ta, tb, p, grid, stream);
-    return status_of(e);
+    return run_mx_kernel(a, pl, sfa_tiled, sfb_tiled, static_cast<const uint8_t*>(a->B), a->ldb,
+                         device_status ? reinterpret_cast<int*>(device_status) : nd->status, nd->sm_count, stream);
 }

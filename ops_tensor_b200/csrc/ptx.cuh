@@ -369,10 +369,16 @@ __device__ __forceinline__ void cluster_sync() {
 
 enum Activation : int { ACT_IDENTITY = 0, ACT_RELU = 1, ACT_GELU_TANH = 2 };
 
+// GELU, tanh form: 0.5 x (1 + tanh(u)), u = sqrt(2/pi) (x + 0.044715 x^3).  Since 0.5 (1 + tanh(u)) = 1 / (1 + e^(-2u)),
+// it is evaluated as x / (1 + 2^w) with w = -2 u log2(e): one ex2 and one reciprocal, relative error ~1e-6, and the
+// tails are exact limits (x -> +inf gives x, x -> -inf gives -0).
 __device__ __forceinline__ float gelu_tanh_f32(float x) {
-    const float c = 0.7978845608028654f;      // sqrt(2/pi)
-    const float inner = c * (x + 0.044715f * x * x * x);
-    return 0.5f * x * (1.0f + tanhf(inner));
+    const float k0 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
+    const float k1 = k0 * 0.044715f;
+    const float w = x * fmaf(x * x, k1, k0);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(w));
+    return __fdividef(x, 1.0f + e);
 }
 
 template <int kAct>

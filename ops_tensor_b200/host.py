@@ -21,7 +21,7 @@ WORKSPACE_MIN, WORKSPACE_DEFAULT, WORKSPACE_MAX = 1, 2, 3
 SCALE_NONE, SCALE_MX_E8M0_VEC32, SCALE_FP32_1X128, SCALE_FP32_128X128 = 0, 1, 2, 3
 SPLIT_AUTO, SPLIT_DATA_PARALLEL, SPLIT_STREAM_K = 0, 1, 2
 (ATTR_SCALE_MODE_A, ATTR_SCALE_MODE_B, ATTR_EPILOGUE_ACT, ATTR_BIAS_TYPE, ATTR_GROUP_COUNT, ATTR_SPLIT_POLICY,
- ATTR_TILE_N, ATTR_SM_LIMIT, ATTR_B_IS_STATIC) = range(1, 10)
+ ATTR_TILE_N, ATTR_SM_LIMIT, ATTR_B_IS_STATIC, ATTR_CTA_PAIR) = range(1, 11)
 
 STATUS_SUCCESS = 0
 STATUS_NOT_INITIALIZED = 1
@@ -181,7 +181,7 @@ class Contraction:
     """
 
     def __init__(self, M, N, K, *, scale_mode_a, scale_mode_b, b_dtype=R_8F_E4M3, groups=0, activation=OP_IDENTITY,
-                 bias=False, residual=False, split=SPLIT_AUTO, tile_n=0, sm_limit=0, b_is_static=False,
+                 bias=False, residual=False, split=SPLIT_AUTO, tile_n=0, sm_limit=0, b_is_static=False, cta_pair=0,
                  lda=None, ldb=None, ldd=None, ldc=None, workspace_limit=2 ** 62):
         self.M, self.N, self.K, self.groups = M, N, K, groups
         self.handle = create_handle()
@@ -216,6 +216,8 @@ class Contraction:
             set_attribute(self.handle, self.op, ATTR_SM_LIMIT, sm_limit)
         if b_is_static:
             set_attribute(self.handle, self.op, ATTR_B_IS_STATIC, 1)
+        if cta_pair:
+            set_attribute(self.handle, self.op, ATTR_CTA_PAIR, cta_pair)
         check(api.acltensorCreatePlanPreference(self.handle, C.byref(self.pref), ALGO_DEFAULT),
               "acltensorCreatePlanPreference")
         check(api.acltensorCreatePlan(self.handle, C.byref(self.plan), self.op, self.pref, workspace_limit),
