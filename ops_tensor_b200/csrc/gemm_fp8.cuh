@@ -13,8 +13,9 @@
 //  include/blaze/epilogue/block/block_epilogue_matmul_streamk.h:123-184).
 //
 // float32 scales cannot ride on the hardware block-scale path, so every 128-deep K block is multiplied into a
-// fresh TMEM accumulator (4 stages of 128 columns) and promoted into registers by the epilogue warps:
-// acc += (sa * sb) * block, while the tensor core works on the next blocks.
+// fresh TMEM accumulator (4 stages of 128 columns) and promoted into registers by eight epilogue warps (two per
+// TMEM lane quadrant, 64 columns each): acc += (sa * sb) * block, while the tensor core works on the next blocks.
+// Warps 0-7: promotion + epilogue, warp 8: TMA producer, warp 9: MMA issuer.
 #pragma once
 
 #include "ptx.cuh"
@@ -158,7 +159,7 @@ __device__ __forceinline__ void st_release_gpu(int* ptr, int v) {
 }
 
 template <int kStages, int kAct>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const Fp8GemmParams p) {
     using L = Fp8GemmSmem<kStages>;
@@ -188,13 +189,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
         for (int s = 0; s < kAccStages; ++s) {
             mbar_init(&tmem_full_bar[s], 1);
-            mbar_init(&tmem_empty_bar[s], 4);
+            mbar_init(&tmem_empty_bar[s], 8);
         }
-        mbar_init(fix_bar, 128);
+        mbar_init(fix_bar, 256);
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (threadIdx.x == 32 && p.groups > 0) {
+    if (threadIdx.x == 288 && p.groups > 0) {
         // prefix sums of rows and of 128-row tiles over the group list
         int rows = 0, tiles = 0;
         for (int g = 0; g < p.groups; ++g) {
@@ -209,10 +210,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         row_start[p.groups] = rows;
         mtile_start[p.groups] = tiles;
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tmem_alloc<1>(tmem_base_slot, kTmemCols);
     }
-    if (warp == 4 && lane == 0) {
+    if (warp == 8 && lane == 0) {
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
     }
@@ -221,12 +222,21 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
 
-    if (warp == 4) {
+    // The two single-thread loops below run once per 128-deep K block, i.e. every 256 tensor-core cycles: they are
+    // written with precomputed shared-memory addresses and descriptor words so that their instruction count, not
+    // the tensor core, does not set the pace.
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t full0 = smem_u32(&full_bar[0]);
+    const uint32_t empty0 = smem_u32(&empty_bar[0]);
+    const uint32_t tfull0 = smem_u32(&tmem_full_bar[0]);
+    const uint32_t tempty0 = smem_u32(&tmem_empty_bar[0]);
+
+    if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             Fp8WorkWalker walk(p, row_start, mtile_start);
             Fp8Segment seg;
-            int stage = 0;
+            uint32_t stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             // B is streamed once when there is a single row of tiles; keep A (re-read by every N tile) instead
@@ -234,95 +244,112 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             while (ok && walk.next(seg)) {
                 const int b_row = seg.group * p.N + seg.nt * 128;
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
-                    ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
+                    ok = mbar_wait_addr(empty0 + stage * 8, phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
-                    uint8_t* a_dst = smem + stage * L::kStageBytes;
-                    uint8_t* b_dst = a_dst + L::kABytes;
-                    mbar_arrive_expect_tx(&full_bar[stage], L::kTxBytes);
-                    tma_load_2d(a_dst, &tmap_a, &full_bar[stage], kb * 128, seg.m0, kEvictNormal);
-                    tma_load_2d(b_dst, &tmap_b, &full_bar[stage], kb * 128, b_row, b_hint);
+                    const uint32_t a_dst = smem_base + stage * L::kStageBytes;
+                    const uint32_t bar = full0 + stage * 8;
+                    mbar_arrive_expect_tx_addr(bar, L::kTxBytes);
+                    tma_load_2d_addr(a_dst, &tmap_a, bar, kb * 128, seg.m0, kEvictNormal);
+                    tma_load_2d_addr(a_dst + L::kABytes, &tmap_b, bar, kb * 128, b_row, b_hint);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             Fp8WorkWalker walk(p, row_start, mtile_start);
             Fp8Segment seg;
-            int stage = 0;
+            uint32_t stage = 0;
             uint32_t phase = 0;
-            int acc = 0;
+            uint32_t acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
             constexpr uint32_t idesc = umma_idesc_f8(FMT_E4M3, FMT_E4M3, 128, 128);
+            const uint64_t desc0 = umma_desc_sw128(0);
+            const uint32_t desc_hi = (uint32_t)(desc0 >> 32);
+            const uint32_t desc_lo0 = (uint32_t)desc0 + (smem_base >> 4);          // start-address field of stage 0's A tile
             while (ok && walk.next(seg)) {
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
-                    ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                    ok = mbar_wait_addr(tempty0 + acc * 8, acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
                     if (!ok) break;
-                    ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
+                    ok = mbar_wait_addr(full0 + stage * 8, phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
                     tcgen05_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
-                    const uint64_t a_desc = umma_desc_sw128(a_addr);
-                    const uint64_t b_desc = umma_desc_sw128(a_addr + L::kABytes);
-                    const uint32_t d_tmem = tmem_base + acc * 128;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        umma_f8<1>(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, j != 0 ? 1u : 0u);
-                    }
-                    umma_commit(&empty_bar[stage]);
-                    umma_commit(&tmem_full_bar[acc]);
+                    const uint32_t a_lo = desc_lo0 + stage * (L::kStageBytes >> 4);
+                    umma_f8_kblock(tmem_base + acc * 128, a_lo, a_lo + (L::kABytes >> 4), desc_hi, idesc);
+                    umma_commit_addr(empty0 + stage * 8);
+                    umma_commit_addr(tfull0 + acc * 8);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
-                    if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+                    if (++acc == (uint32_t)kAccStages) { acc = 0; acc_phase ^= 1; }
                 }
             }
         }
     } else {
-        // ------------------------------------------------------------------ promotion + epilogue warps 0..3
+        // ------------------------------------------------------------------ promotion + epilogue warps 0..7
         Fp8WorkWalker walk(p, row_start, mtile_start);
         Fp8Segment seg;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-        const int r_in_tile = warp * 32 + lane;
+        const int quad = warp & 3;                      // TMEM lane quadrant this warp may read
+        const int half = warp >> 2;                     // which 64 of the tile's 128 columns
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        const int r_in_tile = quad * 32 + lane;
+        const int c0 = half * 64;
         while (ok && walk.next(seg)) {
             const int row = seg.m0 + r_in_tile;
             const bool row_ok = row < seg.row_end;
-            const bool warp_has_rows = seg.m0 + warp * 32 < seg.row_end;      // warp-uniform
+            const bool warp_has_rows = seg.m0 + quad * 32 < seg.row_end;      // warp-uniform
             const float* sa_row = p.sa + (long long)(row_ok ? row : 0) * p.k_blocks;
             const float* sb_col = p.sb + (long long)seg.group * p.k_blocks * p.n_blocks + seg.nt;
-            float accum[128];
+            float accum[64];
 #pragma unroll
-            for (int j = 0; j < 128; ++j) accum[j] = 0.0f;
+            for (int j = 0; j < 64; ++j) accum[j] = 0.0f;
 
-            float s_next = row_ok ? __ldg(sa_row + seg.kb0) * __ldg(sb_col + (long long)seg.kb0 * p.n_blocks) : 0.0f;
-            for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
-                const float s = s_next;
-                if (kb + 1 < seg.kb1 && row_ok) {
-                    s_next = __ldg(sa_row + kb + 1) * __ldg(sb_col + (long long)(kb + 1) * p.n_blocks);
-                }
-                ok = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tcgen05_fence_after();
-                if (warp_has_rows) {
+            // The two scale factors of a K block come from global memory (L2 latency); they are fetched kScaleAhead
+            // blocks ahead into a register ring so that the promotion never waits for them.
+            constexpr int kScaleAhead = 4;
+            float sa_q[kScaleAhead], sb_q[kScaleAhead];
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t v[32];
-                        tmem_ld_32x32(tmem_base + lane_base + acc * 128 + c * 32, v);
-                        tmem_ld_wait();
+            for (int u = 0; u < kScaleAhead; ++u) {
+                const int kq = seg.kb0 + u;
+                const bool in = row_ok && kq < seg.kb1;
+                sa_q[u] = in ? __ldg(sa_row + kq) : 0.0f;
+                sb_q[u] = in ? __ldg(sb_col + (long long)kq * p.n_blocks) : 0.0f;
+            }
+            for (int kb0 = seg.kb0; kb0 < seg.kb1 && ok; kb0 += kScaleAhead) {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            accum[c * 32 + e] = fmaf(__uint_as_float(v[e]), s, accum[c * 32 + e]);
-                        }
+                for (int u = 0; u < kScaleAhead; ++u) {
+                    const int kb = kb0 + u;
+                    if (kb >= seg.kb1) break;                                   // uniform across the CTA
+                    const float s = sa_q[u] * sb_q[u];
+                    {
+                        const int kq = kb + kScaleAhead;
+                        const bool in = row_ok && kq < seg.kb1;
+                        sa_q[u] = in ? __ldg(sa_row + kq) : 0.0f;
+                        sb_q[u] = in ? __ldg(sb_col + (long long)kq * p.n_blocks) : 0.0f;
                     }
+                    ok = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    if (warp_has_rows) {
+                        uint32_t v[64];
+                        tmem_ld_32x64(tmem_base + lane_base + acc * 128 + c0, v);
+                        tmem_ld_wait();
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);    // the block is in registers: free the stage
+#pragma unroll
+                        for (int e = 0; e < 64; ++e) accum[e] = fmaf(__uint_as_float(v[e]), s, accum[e]);
+                    } else {
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+                    }
+                    if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
                 }
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
-                if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
             }
             if (!ok) break;
 
@@ -332,7 +359,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 float* slot = p.partials + (size_t)blockIdx.x * (128 * 128);
                 if (row_ok) {
 #pragma unroll
-                    for (int j = 0; j < 128; ++j) __stcg(slot + j * 128 + r_in_tile, accum[j]);
+                    for (int j = 0; j < 64; ++j) __stcg(slot + (c0 + j) * 128 + r_in_tile, accum[j]);
                 }
                 __threadfence();
                 mbar_arrive(fix_bar);
@@ -366,20 +393,20 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     const float* slot = p.partials + (size_t)j * (128 * 128);
                     if (row_ok) {
 #pragma unroll
-                        for (int c = 0; c < 128; ++c) accum[c] += __ldcg(slot + c * 128 + r_in_tile);
+                        for (int c = 0; c < 64; ++c) accum[c] += __ldcg(slot + (c0 + c) * 128 + r_in_tile);
                     }
                 }
                 ok = __all_sync(0xffffffffu, ok);      // also re-converges the warp after the per-thread polling
                 if (!ok) break;
             }
 
-            // -------- fused epilogue: bias, activation, residual, bf16
+            // -------- fused epilogue: bias, activation, residual, bf16; 128 contiguous bytes per thread
             if (row_ok) {
                 __nv_bfloat16* d_row = p.D + (long long)row * p.ldd;
                 const __nv_bfloat16* r_row = p.residual ? p.residual + (long long)row * p.ldr : nullptr;
 #pragma unroll
-                for (int q = 0; q < 16; ++q) {
-                    const int n = seg.nt * 128 + q * 8;
+                for (int q = 0; q < 8; ++q) {
+                    const int n = seg.nt * 128 + c0 + q * 8;
                     if (n < p.N) {
                         float x[8];
 #pragma unroll
@@ -422,7 +449,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         for (int i = 0; i < 64; ++i) __nanosleep(2000);
         __syncthreads();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         __syncwarp();
         tcgen05_fence_after();
         tmem_dealloc<1>(tmem_base, kTmemCols);

@@ -399,7 +399,7 @@ static cudaError_t launch_fp8_instance(const CUtensorMap& ta, const CUtensorMap&
         if (e != cudaSuccess) return e;
         attr_done[dev & 63] = true;
     }
-    kernel<<<grid, 192, L::kDynamicBytes, stream>>>(ta, tb, p);
+    kernel<<<grid, 320, L::kDynamicBytes, stream>>>(ta, tb, p);
     return cudaGetLastError();
 }
 

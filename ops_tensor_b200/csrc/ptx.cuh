@@ -130,6 +130,57 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+// Lean forms for the single-thread issue loops, which pay for every instruction: barriers are named by their
+// precomputed 32-bit shared-memory address.
+__device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                               int code) {
+    if (mbar_try_wait_addr(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i) {
+            if (mbar_try_wait_addr(bar, parity)) return true;
+        }
+        if (*abort_flag != 0) return false;
+        if (clock64() - t0 > BLAZE_WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx_addr(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_addr(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_addr(uint32_t smem_dst, const CUtensorMap* tmap, uint32_t bar, int x, int y,
+                                                 uint64_t hint) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(smem_dst),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "l"(hint)
+        : "memory");
+}
+
 // ------------------------------------------------------------------------------------------------ TMA
 
 // L2 eviction-priority hints for TMA loads (opaque 64-bit policy words the hardware defines).
@@ -301,6 +352,41 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t a_desc, uint64
     }
 }
 
+// Four K=32 steps of one 128-byte-swizzled K block with kind::f8f6f4: the operand descriptors are given as the low
+// word of the first step (start address in 16-byte units plus the constant fields) and the shared high word; each
+// further step starts 32 bytes (2 units) later.  The first instruction overwrites the accumulator.
+__device__ __forceinline__ void umma_f8_kblock(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                               uint32_t idesc) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p0, p1;\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .b32 la, lb;\n\t"
+        "setp.ne.b32 p0, 0, 0;\n\t"
+        "setp.eq.b32 p1, 0, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p0;\n\t"
+        "add.u32 la, %1, 2;\n\t"
+        "add.u32 lb, %2, 2;\n\t"
+        "mov.b64 da, {la, %3};\n\t"
+        "mov.b64 db, {lb, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p1;\n\t"
+        "add.u32 la, %1, 4;\n\t"
+        "add.u32 lb, %2, 4;\n\t"
+        "mov.b64 da, {la, %3};\n\t"
+        "mov.b64 db, {lb, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p1;\n\t"
+        "add.u32 la, %1, 6;\n\t"
+        "add.u32 lb, %2, 6;\n\t"
+        "mov.b64 da, {la, %3};\n\t"
+        "mov.b64 db, {lb, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p1;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc)
+        : "memory");
+}
+
 template <int kCtaGroup>
 __device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                         uint32_t accumulate, uint32_t tmem_sfa, uint32_t tmem_sfb) {
@@ -346,6 +432,25 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+// Same for 64 consecutive columns.
+__device__ __forceinline__ void tmem_ld_32x64(uint32_t taddr, uint32_t (&r)[64]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+        "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+        "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]),
+          "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]),
+          "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
+          "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]),
+          "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
         : "r"(taddr)
         : "memory");
 }
