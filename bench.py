@@ -139,6 +139,12 @@ def make_cpu_golden(workload):
     workload: the first rows of A against the first rows of B, full K.  Returns (run, flops, description)."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import blaze_oracle as o
+    try:
+        # the launcher of multi-process runs pins OMP_NUM_THREADS to 1; the CPU golden is allowed every host core
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=len(os.sched_getaffinity(0)))
+    except Exception:
+        pass
     kind, M, N, K, desc = WORKLOADS[workload]
     rows, cols = CPU_SAMPLE["mx" if kind == "mx" else "fp8"]
     rows, cols = min(rows, M), min(cols, N)
