@@ -150,12 +150,12 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t acc_phase = 0;
             bool ok = true;
             for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-                ok = mbar_wait<true>(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kBN;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
-                    ok = mbar_wait<true>(&full_bar[stage], phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
+                    ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
@@ -195,7 +195,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int t = pair; t < num_tiles && ok; t += num_pairs) {
             int mt, nt;
             tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);
-            ok = mbar_wait<true>(&tmem_full_bar[acc], acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
+            ok = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tcgen05_fence_after();
