@@ -161,6 +161,11 @@ BLAZE_API int blazeAddF32(const void* A, const void* C, void* D, int64_t n, void
  * wait that gave up (see DeviceStatus in csrc/ptx.cuh).  Synchronises the device.  reset != 0 clears it. */
 BLAZE_API int blazeDeviceStatus(int32_t* value, int32_t reset);
 
+/* Diagnostic of the failure-reporting path (no counterpart in the reference): launches one CTA that waits, for at most
+ * `limit_cycles` SM cycles (<= 2^31), on a barrier nothing signals.  The wait expires, the kernel returns normally, and
+ * the next blazeDeviceStatus / acltensorGetDeviceStatus reports code 7.  Nothing hangs or faults. */
+BLAZE_API int blazeSelfTestWaitTimeout(int64_t limit_cycles, void* stream);
+
 /* SM count and compute capability of the current device (the handle's device query). */
 BLAZE_API int blazeDeviceInfo(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor);
 

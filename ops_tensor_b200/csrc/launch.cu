@@ -550,6 +550,32 @@ extern "C" int blazeDeviceStatus(int32_t* value, int32_t reset) {
     return ACLTENSOR_STATUS_SUCCESS;
 }
 
+// Diagnostic: one CTA waits, with the given cycle budget, on a barrier that nothing ever signals.  The wait gives
+// up, records DEV_TIMEOUT_SELFTEST in the status word and the kernel returns normally: the path a real
+// synchronisation failure would take, exercised without hanging or faulting anything.
+__global__ void wait_timeout_selftest_kernel(int* status, long long limit_cycles) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        blaze::mbar_init(&bar, 1);
+        abort_flag = 0;
+        blaze::fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        blaze::mbar_wait(&bar, 0, &abort_flag, status, blaze::DEV_TIMEOUT_SELFTEST, limit_cycles);
+    }
+    __syncthreads();
+}
+
+extern "C" int blazeSelfTestWaitTimeout(int64_t limit_cycles, void* stream) {
+    if (limit_cycles < 0 || limit_cycles > (1LL << 31)) return ACLTENSOR_STATUS_INVALID_VALUE;    // at most ~1 s
+    DeviceContext* ctx = current_context();
+    if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ctx->status_word, limit_cycles);
+    return status_of(cudaGetLastError());
+}
+
 extern "C" int blazeDeviceInfo(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor) {
     DeviceContext* ctx = current_context();
     if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;

@@ -22,6 +22,7 @@ enum DeviceStatus : int {
     DEV_TIMEOUT_TMEM_EMPTY = 4,   // MMA warp waited for an accumulator that was never drained
     DEV_TIMEOUT_FIXUP_FLAG = 5,   // stream-K owner waited for a partial tile that was never published
     DEV_TIMEOUT_PEER = 6,         // 2-CTA pair: waited for the partner CTA
+    DEV_TIMEOUT_SELFTEST = 7,     // the diagnostic kernel's wait on a barrier nobody signals (expected to expire)
 };
 
 #ifndef BLAZE_WAIT_LIMIT_CYCLES
@@ -112,7 +113,7 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 // global status word.  Returns false when the wait was abandoned.
 template <bool kClusterScope = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code) {
+                                          int code, long long limit_cycles = BLAZE_WAIT_LIMIT_CYCLES) {
     auto probe = [&]() { return kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
     if (probe()) return true;
     const long long t0 = clock64();
@@ -122,7 +123,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             if (probe()) return true;
         }
         if (*abort_flag != 0) return false;
-        if (clock64() - t0 > BLAZE_WAIT_LIMIT_CYCLES) {
+        if (clock64() - t0 > limit_cycles) {
             *abort_flag = 1;
             atomicCAS(status, 0, code);
             return false;

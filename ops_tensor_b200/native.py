@@ -103,6 +103,8 @@ def _declare(l: C.CDLL) -> None:
     l.blazeQuantizeFp8Blocks.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_int64,
                                          C.c_void_p, C.c_void_p]
     l.blazeAddF32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
+    l.blazeSelfTestWaitTimeout.argtypes = [C.c_int64, C.c_void_p]
+    l.blazeSelfTestWaitTimeout.restype = C.c_int
     l.blazeDeviceStatus.argtypes = [C.POINTER(C.c_int32), C.c_int32]
     l.blazeDeviceInfo.argtypes = [C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     for name in ("blazeMxGemmWorkspaceSize", "blazeMxGemm", "blazeFp8GemmWorkspaceSize", "blazeFp8Gemm",

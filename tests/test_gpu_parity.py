@@ -56,6 +56,26 @@ def test_elementwise_add_call_sequence(cuda_device, n):
     assert np.array_equal(to_np(d), a + c)
 
 
+def test_abandoned_wait_is_reported_and_context_survives(cuda_device):
+    """A kernel wait that runs out of its budget returns an error status to the host; nothing hangs, nothing faults,
+    and the next GEMM on the same context is still right."""
+    import ctypes as C
+    import torch
+    from ops_tensor_b200 import native
+    assert H.device_status() == 0
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert native.lib().blazeSelfTestWaitTimeout(1 << 20, stream) == H.STATUS_SUCCESS      # ~0.5 ms budget
+    code = C.c_int32(0)
+    assert H.api.acltensorGetDeviceStatus(None, C.byref(code)) == H.STATUS_EXECUTION_FAILED
+    assert code.value == 7
+    assert H.api.acltensorGetDeviceStatus(None, C.byref(code)) == H.STATUS_SUCCESS and code.value == 0
+    assert native.lib().blazeSelfTestWaitTimeout(-1, stream) == H.STATUS_INVALID_VALUE
+    a = np.full((128, 32), 1.0, dtype=np.float32)
+    w = np.full((8, 32), 0.5, dtype=np.float32)
+    got, *_ = run_mx(cuda_device, a, w)
+    assert np.all(got == 16.0) and H.device_status() == 0
+
+
 # ------------------------------------------------------------------------------------------------ quantisers
 
 @pytest.mark.parametrize("rows,K", [(1, 32), (4, 128), (37, 96), (256, 1024), (130, 4160), (515, 2048)])
