@@ -234,13 +234,29 @@ def gpu_arm(args):
     native.lib()                                     # fails loudly if the CUDA library is missing
 
     kind, M, N, K, desc = WORKLOADS[args.workload]
-    flops = 2.0 * M * N * K
     steps, warmup = args.steps, max(args.warmup, 3)
-
-    # ---- inputs (seeded, generated on the host once) -----------------------------------------------------------
     cfg_id = int(args.workload[1])
     G = 128
     group_rows = None
+    group_rows_host = None
+    strong = args.shard == "strong" and world > 1
+    flops_job = 2.0 * M * N * K * (1 if strong or world == 1 else world)     # whole-job flops per step
+    sharding = f"N-sharded over {world} GPU(s), A replicated, no collective"
+    if strong and kind == "grouped":
+        # experts (or row ranges of oversized experts) dealt to ranks by token count; every rank computes its share
+        pieces = shard.plan_experts(o.moe_group_rows(), world)[rank]
+        group_rows_host = np.array([pc.rows for pc in pieces], dtype=np.int64)
+        G = len(pieces)
+        M = int(group_rows_host.sum())
+        sharding = f"experts partitioned over {world} GPUs by token count (longest first), no collective"
+    elif strong:
+        n0, n1 = shard.n_shard(N, world, rank)
+        N = n1 - n0
+    elif kind == "grouped":
+        group_rows_host = o.moe_group_rows()
+    flops = 2.0 * M * N * K                                                  # this rank's flops per step
+
+    # ---- inputs (seeded, generated on the host once) -----------------------------------------------------------
     a_host = torch.from_numpy(o.normal_f32(cfg_id, 0, (M, K), 1.0)).pin_memory()
     a_dev = a_host.to(dev, non_blocking=True)
     sigma_b = 1.0 if kind == "mx" else 0.02
@@ -263,7 +279,7 @@ def gpu_arm(args):
     else:
         mode_a, mode_b = H.SCALE_FP32_1X128, H.SCALE_FP32_128X128
         if kind == "grouped":
-            group_rows = torch.from_numpy(o.moe_group_rows()).to(dev)
+            group_rows = torch.from_numpy(group_rows_host).to(dev)
             qb = torch.empty((G, N, K), dtype=torch.uint8, device=dev)
             sb = torch.empty((G, K // 128, N // 128), dtype=torch.float32, device=dev)
             for g in range(G):
@@ -324,8 +340,8 @@ def gpu_arm(args):
 
     if rank == 0:
         peaks = measured_peaks()
-        value = world * flops / (ms_per_step * 1e-3) / 1e12
-        abytes = algorithmic_bytes(kind, M, N, K)
+        value = flops_job / (ms_per_step * 1e-3) / 1e12
+        abytes = algorithmic_bytes(kind, M, N, K, G)
         tensor_bound = kind in ("mx", "mx4")
         if tensor_bound:
             # FP8 operands run at twice the bf16 MMA rate; the loop is timed back to back, so the burst figure
@@ -345,16 +361,17 @@ def gpu_arm(args):
                 traffic = json.load(f).get(args.workload)
         line = {
             "metric": "quantized GEMM TFLOPS", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": steps,
-            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
-            "config": {"workload": desc, "M": M, "N_per_gpu": N, "N_global": N * world, "K": K,
-                       "sharding": f"N-sharded over {world} GPU(s), A replicated, no collective",
+            "config": {"workload": desc, "M_rank0": M, "N_rank0": N, "K": K, "groups_rank0": G if kind == "grouped" else 0,
+                       "job_flops_per_step": flops_job, "sharding": sharding,
                        "l2": "operands + output exceed the 126 MB L2" if abytes > 126e6 else "fits in L2 (latency config)",
                        "pct_of_published_dense_fp8_peak": round(100.0 * value / world / 4500.0, 2)},
             "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak, "unit": unit,
                          "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
                          "algorithmic_bytes": abytes, "flops": flops},
-            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
+            "e2e": {"value": flops_job / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
                     "h2d_bytes_per_step": a_host.numel() * 4, "d2h_bytes_per_step": out_host.numel() * 2,
                     "ms_per_step": e2e_ms},
             "gpu_launches": launches_per_step * steps,
@@ -380,6 +397,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--shard", default="weak", choices=["weak", "strong"],
+                    help="with N GPUs: weak = every GPU runs the whole single-GPU problem on its own shard of a "
+                         "gpus-times larger N (default); strong = the single-GPU problem itself is split (along N, or by "
+                         "expert for the grouped workload)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (used for profiler captures)")
     args = ap.parse_args()

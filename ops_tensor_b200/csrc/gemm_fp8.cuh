@@ -40,7 +40,7 @@ struct Fp8GemmParams {
     __nv_bfloat16* D;
     long long ldd;
     int stream_k;                   // 1: split the (tile, k-block) units evenly over the grid
-    float* partials;                // [gridDim.x][128 cols][128 rows] fp32 (stream-K only)
+    float* partials;                // [gridDim.x][32 column quads][128 rows][4] fp32 (stream-K only)
     int* flags;                     // [gridDim.x], zeroed before the launch (stream-K only)
     int* status;
 };
@@ -355,11 +355,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
             const bool full_tile = (seg.kb0 == 0 && seg.kb1 == p.k_blocks);
             if (!full_tile && seg.kb0 > 0) {
-                // -------- contributor: publish the partial tile, column-major so that a warp writes 128 contiguous bytes
+                // -------- contributor: publish the partial tile
                 float* slot = p.partials + (size_t)blockIdx.x * (128 * 128);
                 if (row_ok) {
+                    // layout [column quad][row][4]: a warp writes 512 contiguous bytes per instruction
+                    float4* slot4 = reinterpret_cast<float4*>(slot) + (size_t)(c0 >> 2) * 128 + r_in_tile;
 #pragma unroll
-                    for (int j = 0; j < 64; ++j) __stcg(slot + (c0 + j) * 128 + r_in_tile, accum[j]);
+                    for (int j = 0; j < 16; ++j) {
+                        __stcg(slot4 + j * 128, make_float4(accum[4 * j], accum[4 * j + 1], accum[4 * j + 2], accum[4 * j + 3]));
+                    }
                 }
                 __threadfence();
                 mbar_arrive(fix_bar);
@@ -392,8 +396,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     if (!ok) break;
                     const float* slot = p.partials + (size_t)j * (128 * 128);
                     if (row_ok) {
+                        const float4* slot4 = reinterpret_cast<const float4*>(slot) + (size_t)(c0 >> 2) * 128 + r_in_tile;
 #pragma unroll
-                        for (int c = 0; c < 64; ++c) accum[c] += __ldcg(slot + (c0 + c) * 128 + r_in_tile);
+                        for (int c = 0; c < 16; ++c) {
+                            const float4 v4 = __ldcg(slot4 + c * 128);
+                            accum[4 * c] += v4.x;
+                            accum[4 * c + 1] += v4.y;
+                            accum[4 * c + 2] += v4.z;
+                            accum[4 * c + 3] += v4.w;
+                        }
                     }
                 }
                 ok = __all_sync(0xffffffffu, ok);      // also re-converges the warp after the per-thread polling
