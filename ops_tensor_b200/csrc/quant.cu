@@ -32,6 +32,10 @@ __device__ __forceinline__ uint8_t cvt_e2m1(float x) {
 
 // ---------------------------------------------------------------------------------------------------- MX
 
+// Work items a warp loads before it starts converting: four 16-byte loads in flight per lane keep enough bytes
+// outstanding per SM to cover HBM latency at full bandwidth.
+constexpr int kQuantUnroll = 4;
+
 // One warp handles 128 consecutive K of one row (4 groups of 32); 8 lanes share a group, 4 floats per lane.
 template <bool kE2M1>
 __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__ x, long long ldx, int rows, int K,
@@ -42,41 +46,60 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
     const int lane = threadIdx.x & 31;
     const int emax = kE2M1 ? 2 : 8;
     const int n_groups = (K + 31) >> 5;
-    for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < total;
-         w += (long long)gridDim.x * (blockDim.x >> 5)) {
-        const int row = (int)(w / chunks_per_row);
-        const int chunk = (int)(w - (long long)row * chunks_per_row);
-        const int k = chunk * 128 + lane * 4;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (k < K) v = *reinterpret_cast<const float4*>(x + (long long)row * ldx + k);     // K is a multiple of 4
-        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-        int has_nan = (v.x != v.x) | (v.y != v.y) | (v.z != v.z) | (v.w != v.w);
+    const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long w0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w0 < total;
+         w0 += stride * kQuantUnroll) {
+        float4 vals[kQuantUnroll];
+        int row_of[kQuantUnroll], chunk_of[kQuantUnroll];
 #pragma unroll
-        for (int o = 1; o < 8; o <<= 1) {
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            has_nan |= __shfl_xor_sync(0xffffffffu, has_nan, o);
-        }
-        const int field = (__float_as_uint(amax) >> 23) & 0xFF;
-        int byte = min(max(field - emax, 0), 254);
-        if (amax == 0.0f) byte = 127;
-        const int eff = byte;
-        if (has_nan) byte = 255;
-        const float inv = (eff == 254) ? __uint_as_float(0x00400000u) : __uint_as_float((uint32_t)(254 - eff) << 23);
-        const float q0 = v.x * inv, q1 = v.y * inv, q2 = v.z * inv, q3 = v.w * inv;
-        if (k < K) {
-            if (kE2M1) {
-                const uint16_t packed = (uint16_t)(cvt_e2m1(q0) | (cvt_e2m1(q1) << 4) | (cvt_e2m1(q2) << 8) |
-                                                   (cvt_e2m1(q3) << 12));
-                *reinterpret_cast<uint16_t*>(codes + (long long)row * ldc_bytes + (k >> 1)) = packed;
-            } else {
-                const uint32_t packed = (uint32_t)cvt_e4m3(q0) | ((uint32_t)cvt_e4m3(q1) << 8) |
-                                        ((uint32_t)cvt_e4m3(q2) << 16) | ((uint32_t)cvt_e4m3(q3) << 24);
-                *reinterpret_cast<uint32_t*>(codes + (long long)row * ldc_bytes + k) = packed;
+        for (int u = 0; u < kQuantUnroll; ++u) {
+            const long long w = w0 + u * stride;
+            vals[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            row_of[u] = -1;
+            chunk_of[u] = 0;
+            if (w < total) {
+                row_of[u] = (int)(w / chunks_per_row);
+                chunk_of[u] = (int)(w - (long long)row_of[u] * chunks_per_row);
+                const int k = chunk_of[u] * 128 + lane * 4;
+                if (k < K) vals[u] = __ldcs(reinterpret_cast<const float4*>(x + (long long)row_of[u] * ldx + k));
             }
         }
-        const int g = chunk * 4 + (lane >> 3);
-        if ((lane & 7) == 0 && g < scale_cols) {
-            scales[(long long)row * scale_cols + g] = (g < n_groups) ? (uint8_t)byte : (uint8_t)127;
+#pragma unroll
+        for (int u = 0; u < kQuantUnroll; ++u) {
+            if (row_of[u] < 0) continue;                                   // uniform over the warp
+            const int row = row_of[u], chunk = chunk_of[u];
+            const int k = chunk * 128 + lane * 4;
+            const float4 v = vals[u];
+            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+            int has_nan = (v.x != v.x) | (v.y != v.y) | (v.z != v.z) | (v.w != v.w);
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                has_nan |= __shfl_xor_sync(0xffffffffu, has_nan, o);
+            }
+            const int field = (__float_as_uint(amax) >> 23) & 0xFF;
+            int byte = min(max(field - emax, 0), 254);
+            if (amax == 0.0f) byte = 127;
+            const int eff = byte;
+            if (has_nan) byte = 255;
+            const float inv =
+                (eff == 254) ? __uint_as_float(0x00400000u) : __uint_as_float((uint32_t)(254 - eff) << 23);
+            const float q0 = v.x * inv, q1 = v.y * inv, q2 = v.z * inv, q3 = v.w * inv;
+            if (k < K) {
+                if (kE2M1) {
+                    const uint16_t packed = (uint16_t)(cvt_e2m1(q0) | (cvt_e2m1(q1) << 4) | (cvt_e2m1(q2) << 8) |
+                                                       (cvt_e2m1(q3) << 12));
+                    *reinterpret_cast<uint16_t*>(codes + (long long)row * ldc_bytes + (k >> 1)) = packed;
+                } else {
+                    const uint32_t packed = (uint32_t)cvt_e4m3(q0) | ((uint32_t)cvt_e4m3(q1) << 8) |
+                                            ((uint32_t)cvt_e4m3(q2) << 16) | ((uint32_t)cvt_e4m3(q3) << 24);
+                    *reinterpret_cast<uint32_t*>(codes + (long long)row * ldc_bytes + k) = packed;
+                }
+            }
+            const int g = chunk * 4 + (lane >> 3);
+            if ((lane & 7) == 0 && g < scale_cols) {
+                scales[(long long)row * scale_cols + g] = (g < n_groups) ? (uint8_t)byte : (uint8_t)127;
+            }
         }
     }
 }
@@ -89,24 +112,43 @@ __global__ void __launch_bounds__(256) quant_fp8_1x128_kernel(const float* __res
                                                               float* __restrict__ scales, int k_blocks) {
     const long long total = (long long)rows * k_blocks;
     const int lane = threadIdx.x & 31;
-    for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < total;
-         w += (long long)gridDim.x * (blockDim.x >> 5)) {
-        const int row = (int)(w / k_blocks);
-        const int kb = (int)(w - (long long)row * k_blocks);
-        const int k = kb * 128 + lane * 4;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (k < K) v = *reinterpret_cast<const float4*>(x + (long long)row * ldx + k);
-        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long w0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w0 < total;
+         w0 += stride * kQuantUnroll) {
+        float4 vals[kQuantUnroll];
+        int row_of[kQuantUnroll], kb_of[kQuantUnroll];
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 448.0f);
-        if (k < K) {
-            const uint32_t packed = (uint32_t)cvt_e4m3(__fdiv_rn(v.x, scale)) | ((uint32_t)cvt_e4m3(__fdiv_rn(v.y, scale)) << 8) |
-                                    ((uint32_t)cvt_e4m3(__fdiv_rn(v.z, scale)) << 16) |
-                                    ((uint32_t)cvt_e4m3(__fdiv_rn(v.w, scale)) << 24);
-            *reinterpret_cast<uint32_t*>(codes + (long long)row * ldc + k) = packed;
+        for (int u = 0; u < kQuantUnroll; ++u) {
+            const long long w = w0 + u * stride;
+            vals[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            row_of[u] = -1;
+            kb_of[u] = 0;
+            if (w < total) {
+                row_of[u] = (int)(w / k_blocks);
+                kb_of[u] = (int)(w - (long long)row_of[u] * k_blocks);
+                const int k = kb_of[u] * 128 + lane * 4;
+                if (k < K) vals[u] = __ldcs(reinterpret_cast<const float4*>(x + (long long)row_of[u] * ldx + k));
+            }
         }
-        if (lane == 0) scales[(long long)row * k_blocks + kb] = scale;
+#pragma unroll
+        for (int u = 0; u < kQuantUnroll; ++u) {
+            if (row_of[u] < 0) continue;                                   // uniform over the warp
+            const int row = row_of[u], kb = kb_of[u];
+            const int k = kb * 128 + lane * 4;
+            const float4 v = vals[u];
+            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 448.0f);
+            if (k < K) {
+                const uint32_t packed = (uint32_t)cvt_e4m3(__fdiv_rn(v.x, scale)) |
+                                        ((uint32_t)cvt_e4m3(__fdiv_rn(v.y, scale)) << 8) |
+                                        ((uint32_t)cvt_e4m3(__fdiv_rn(v.z, scale)) << 16) |
+                                        ((uint32_t)cvt_e4m3(__fdiv_rn(v.w, scale)) << 24);
+                *reinterpret_cast<uint32_t*>(codes + (long long)row * ldc + k) = packed;
+            }
+            if (lane == 0) scales[(long long)row * k_blocks + kb] = scale;
+        }
     }
 }
 
