@@ -22,60 +22,84 @@
 
 namespace blaze {
 
-__device__ __forceinline__ uint8_t cvt_e4m3(float x) {
-    return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+// Four floats -> four E4M3 bytes (x in the low byte), two conversions of a pair each.
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float x, float y, float z, float w) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(x, y), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(z, w), __NV_SATFINITE, __NV_E4M3);
+    return (lo & 0xFFFFu) | (hi << 16);
 }
 
-__device__ __forceinline__ uint8_t cvt_e2m1(float x) {
-    return (uint8_t)(__nv_cvt_float_to_fp4(x, __NV_E2M1, cudaRoundNearest) & 0xF);
+// Four floats -> four E2M1 nibbles (x in the lowest).
+__device__ __forceinline__ uint16_t cvt_e2m1x4(float x, float y, float z, float w) {
+    const uint32_t lo = __nv_cvt_float2_to_fp4x2(make_float2(x, y), __NV_E2M1, cudaRoundNearest);
+    const uint32_t hi = __nv_cvt_float2_to_fp4x2(make_float2(z, w), __NV_E2M1, cudaRoundNearest);
+    return (uint16_t)((lo & 0xFFu) | ((hi & 0xFFu) << 8));
+}
+
+// w = q * d + r.  Work-item counts almost always fit 32 bits, where the division is a handful of instructions
+// instead of the 64-bit software routine.
+__device__ __forceinline__ void split_index(long long w, int d, int& q, int& r) {
+    if ((unsigned long long)w <= 0xFFFFFFFFull) {
+        const uint32_t w32 = (uint32_t)w;
+        q = (int)(w32 / (uint32_t)d);
+        r = (int)(w32 - (uint32_t)q * (uint32_t)d);
+    } else {
+        q = (int)(w / d);
+        r = (int)(w - (long long)q * d);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------- MX
 
-// Work items a warp loads before it starts converting: four 16-byte loads in flight per lane keep enough bytes
-// outstanding per SM to cover HBM latency at full bandwidth.
+// A warp's work item is kQuantUnroll consecutive 128-wide chunks of one row (2 KB of fp32): all of its 16-byte loads
+// are issued before the first conversion, which keeps enough bytes in flight per SM to cover HBM latency, and the
+// row/column split of the item index is paid once per item.
 constexpr int kQuantUnroll = 4;
 
-// One warp handles 128 consecutive K of one row (4 groups of 32); 8 lanes share a group, 4 floats per lane.
+// Within a chunk 8 lanes share a group of 32, 4 floats per lane.
 template <bool kE2M1>
 __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__ x, long long ldx, int rows, int K,
                                                        uint8_t* __restrict__ codes, long long ldc_bytes,
                                                        uint8_t* __restrict__ scales, int scale_cols) {
     const int chunks_per_row = (K + 127) >> 7;
-    const long long total = (long long)rows * chunks_per_row;
+    const int items_per_row = (chunks_per_row + kQuantUnroll - 1) / kQuantUnroll;
+    const long long total = (long long)rows * items_per_row;
     const int lane = threadIdx.x & 31;
     const int emax = kE2M1 ? 2 : 8;
     const int n_groups = (K + 31) >> 5;
     const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
-    for (long long w0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w0 < total;
-         w0 += stride * kQuantUnroll) {
+    for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < total; w += stride) {
+        int row, item;
+        split_index(w, items_per_row, row, item);
+        const int k0 = item * (128 * kQuantUnroll) + lane * 4;
+        const float* src = x + (long long)row * ldx + k0;
         float4 vals[kQuantUnroll];
-        int row_of[kQuantUnroll], chunk_of[kQuantUnroll];
 #pragma unroll
         for (int u = 0; u < kQuantUnroll; ++u) {
-            const long long w = w0 + u * stride;
             vals[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            row_of[u] = -1;
-            chunk_of[u] = 0;
-            if (w < total) {
-                row_of[u] = (int)(w / chunks_per_row);
-                chunk_of[u] = (int)(w - (long long)row_of[u] * chunks_per_row);
-                const int k = chunk_of[u] * 128 + lane * 4;
-                if (k < K) vals[u] = __ldcs(reinterpret_cast<const float4*>(x + (long long)row_of[u] * ldx + k));
-            }
+            if (k0 + u * 128 < K) vals[u] = __ldcs(reinterpret_cast<const float4*>(src + u * 128));   // K % 4 == 0
         }
+        uint8_t* code_row = codes + (long long)row * ldc_bytes;
+        uint8_t* scale_row = scales + (long long)row * scale_cols;
 #pragma unroll
         for (int u = 0; u < kQuantUnroll; ++u) {
-            if (row_of[u] < 0) continue;                                   // uniform over the warp
-            const int row = row_of[u], chunk = chunk_of[u];
-            const int k = chunk * 128 + lane * 4;
+            const int chunk = item * kQuantUnroll + u;
+            if (chunk >= chunks_per_row) break;                            // uniform over the warp
+            const int k = k0 + u * 128;
             const float4 v = vals[u];
-            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-            int has_nan = (v.x != v.x) | (v.y != v.y) | (v.z != v.z) | (v.w != v.w);
+            // |x| as integers order like the floats, with every NaN above infinity: one max finds both the largest
+            // magnitude and whether the group holds a NaN
+            uint32_t m = max(max(__float_as_uint(v.x) & 0x7FFFFFFFu, __float_as_uint(v.y) & 0x7FFFFFFFu),
+                             max(__float_as_uint(v.z) & 0x7FFFFFFFu, __float_as_uint(v.w) & 0x7FFFFFFFu));
 #pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                has_nan |= __shfl_xor_sync(0xffffffffu, has_nan, o);
+            for (int o = 1; o < 8; o <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+            const bool has_nan = m > 0x7F800000u;
+            float amax = __uint_as_float(m);
+            if (__any_sync(0xffffffffu, has_nan)) {
+                // rare: the scale of a group with NaNs comes from its largest finite magnitude (fmaxf drops NaNs)
+                amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             }
             const int field = (__float_as_uint(amax) >> 23) & 0xFF;
             int byte = min(max(field - emax, 0), 254);
@@ -87,67 +111,56 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
             const float q0 = v.x * inv, q1 = v.y * inv, q2 = v.z * inv, q3 = v.w * inv;
             if (k < K) {
                 if (kE2M1) {
-                    const uint16_t packed = (uint16_t)(cvt_e2m1(q0) | (cvt_e2m1(q1) << 4) | (cvt_e2m1(q2) << 8) |
-                                                       (cvt_e2m1(q3) << 12));
-                    *reinterpret_cast<uint16_t*>(codes + (long long)row * ldc_bytes + (k >> 1)) = packed;
+                    *reinterpret_cast<uint16_t*>(code_row + (k >> 1)) = cvt_e2m1x4(q0, q1, q2, q3);
                 } else {
-                    const uint32_t packed = (uint32_t)cvt_e4m3(q0) | ((uint32_t)cvt_e4m3(q1) << 8) |
-                                            ((uint32_t)cvt_e4m3(q2) << 16) | ((uint32_t)cvt_e4m3(q3) << 24);
-                    *reinterpret_cast<uint32_t*>(codes + (long long)row * ldc_bytes + k) = packed;
+                    *reinterpret_cast<uint32_t*>(code_row + k) = cvt_e4m3x4(q0, q1, q2, q3);
                 }
             }
             const int g = chunk * 4 + (lane >> 3);
-            if ((lane & 7) == 0 && g < scale_cols) {
-                scales[(long long)row * scale_cols + g] = (g < n_groups) ? (uint8_t)byte : (uint8_t)127;
-            }
+            if ((lane & 7) == 0 && g < scale_cols) scale_row[g] = (g < n_groups) ? (uint8_t)byte : (uint8_t)127;
         }
     }
 }
 
 // ---------------------------------------------------------------------------------------------------- FP8, fp32 scales
 
-// One warp per (row, 128-wide K group).
+// One warp per (row, 128-wide K group), kQuantUnroll consecutive groups per work item.
 __global__ void __launch_bounds__(256) quant_fp8_1x128_kernel(const float* __restrict__ x, long long ldx, int rows, int K,
                                                               uint8_t* __restrict__ codes, long long ldc,
                                                               float* __restrict__ scales, int k_blocks) {
-    const long long total = (long long)rows * k_blocks;
+    const int items_per_row = (k_blocks + kQuantUnroll - 1) / kQuantUnroll;
+    const long long total = (long long)rows * items_per_row;
     const int lane = threadIdx.x & 31;
     const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
-    for (long long w0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w0 < total;
-         w0 += stride * kQuantUnroll) {
+    for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < total; w += stride) {
+        int row, item;
+        split_index(w, items_per_row, row, item);
+        const int k0 = item * (128 * kQuantUnroll) + lane * 4;
+        const float* src = x + (long long)row * ldx + k0;
         float4 vals[kQuantUnroll];
-        int row_of[kQuantUnroll], kb_of[kQuantUnroll];
 #pragma unroll
         for (int u = 0; u < kQuantUnroll; ++u) {
-            const long long w = w0 + u * stride;
             vals[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            row_of[u] = -1;
-            kb_of[u] = 0;
-            if (w < total) {
-                row_of[u] = (int)(w / k_blocks);
-                kb_of[u] = (int)(w - (long long)row_of[u] * k_blocks);
-                const int k = kb_of[u] * 128 + lane * 4;
-                if (k < K) vals[u] = __ldcs(reinterpret_cast<const float4*>(x + (long long)row_of[u] * ldx + k));
-            }
+            if (k0 + u * 128 < K) vals[u] = __ldcs(reinterpret_cast<const float4*>(src + u * 128));
         }
+        uint8_t* code_row = codes + (long long)row * ldc;
+        float* scale_row = scales + (long long)row * k_blocks;
 #pragma unroll
         for (int u = 0; u < kQuantUnroll; ++u) {
-            if (row_of[u] < 0) continue;                                   // uniform over the warp
-            const int row = row_of[u], kb = kb_of[u];
-            const int k = kb * 128 + lane * 4;
+            const int kb = item * kQuantUnroll + u;
+            if (kb >= k_blocks) break;                                     // uniform over the warp
+            const int k = k0 + u * 128;
             const float4 v = vals[u];
             float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 448.0f);
             if (k < K) {
-                const uint32_t packed = (uint32_t)cvt_e4m3(__fdiv_rn(v.x, scale)) |
-                                        ((uint32_t)cvt_e4m3(__fdiv_rn(v.y, scale)) << 8) |
-                                        ((uint32_t)cvt_e4m3(__fdiv_rn(v.z, scale)) << 16) |
-                                        ((uint32_t)cvt_e4m3(__fdiv_rn(v.w, scale)) << 24);
-                *reinterpret_cast<uint32_t*>(codes + (long long)row * ldc + k) = packed;
+                *reinterpret_cast<uint32_t*>(code_row + k) =
+                    cvt_e4m3x4(__fdiv_rn(v.x, scale), __fdiv_rn(v.y, scale), __fdiv_rn(v.z, scale),
+                               __fdiv_rn(v.w, scale));
             }
-            if (lane == 0) scales[(long long)row * k_blocks + kb] = scale;
+            if (lane == 0) scale_row[kb] = scale;
         }
     }
 }
@@ -189,11 +202,9 @@ __global__ void __launch_bounds__(256) quant_fp8_128x128_kernel(const float* __r
             const int n = nb * 128 + r;
             if (n < N && k < K) {
                 const float4 v = *reinterpret_cast<const float4*>(w + (long long)n * ldw + k);
-                const uint32_t packed = (uint32_t)cvt_e4m3(__fdiv_rn(v.x, scale)) |
-                                        ((uint32_t)cvt_e4m3(__fdiv_rn(v.y, scale)) << 8) |
-                                        ((uint32_t)cvt_e4m3(__fdiv_rn(v.z, scale)) << 16) |
-                                        ((uint32_t)cvt_e4m3(__fdiv_rn(v.w, scale)) << 24);
-                *reinterpret_cast<uint32_t*>(codes + (long long)n * ldc + k) = packed;
+                *reinterpret_cast<uint32_t*>(codes + (long long)n * ldc + k) =
+                    cvt_e4m3x4(__fdiv_rn(v.x, scale), __fdiv_rn(v.y, scale), __fdiv_rn(v.z, scale),
+                               __fdiv_rn(v.w, scale));
             }
         }
         __syncthreads();
@@ -295,7 +306,7 @@ static int grid_for(long long work_items, int per_block, int sm_count) {
 cudaError_t launch_quant_mx(const float* x, long long ldx, int rows, int K, bool e2m1, uint8_t* codes,
                             long long ldc_bytes, uint8_t* scales, int sm_count, cudaStream_t stream) {
     if (rows <= 0 || K <= 0) return cudaSuccess;
-    const long long warps = (long long)rows * ((K + 127) / 128);
+    const long long warps = (long long)rows * (((K + 127) / 128 + kQuantUnroll - 1) / kQuantUnroll);
     const int grid = grid_for(warps, 8, sm_count);
     const int scale_cols = ((K + 63) / 64) * 2;
     if (e2m1)
@@ -309,7 +320,7 @@ cudaError_t launch_quant_fp8_1x128(const float* x, long long ldx, int rows, int 
                                    float* scales, int sm_count, cudaStream_t stream) {
     if (rows <= 0 || K <= 0) return cudaSuccess;
     const int k_blocks = (K + 127) / 128;
-    const int grid = grid_for((long long)rows * k_blocks, 8, sm_count);
+    const int grid = grid_for((long long)rows * ((k_blocks + kQuantUnroll - 1) / kQuantUnroll), 8, sm_count);
     quant_fp8_1x128_kernel<<<grid, 256, 0, stream>>>(x, ldx, rows, K, codes, ldc, scales, k_blocks);
     return cudaGetLastError();
 }
