@@ -131,12 +131,10 @@ class ClockSampler:
 
 # ---------------------------------------------------------------------------------------------------- CPU golden
 
-CPU_SAMPLE = {"mx": (2048, 4096), "fp8": (256, 512)}        # (rows of A, rows of B) the CPU golden is timed on
-
-
 def make_cpu_golden(workload):
     """Reference-style CPU golden (de-quantise to float32, np.matmul, epilogue, bf16) on a bounded sample of the
-    workload: the first rows of A against the first rows of B, full K.  Returns (run, flops, description)."""
+    workload: the first rows of A against the first rows of B (the first experts for the grouped workload), full K.
+    Returns (run, flops, description)."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import blaze_oracle as o
     try:
@@ -146,30 +144,53 @@ def make_cpu_golden(workload):
     except Exception:
         pass
     kind, M, N, K, desc = WORKLOADS[workload]
-    rows, cols = CPU_SAMPLE["mx" if kind == "mx" else "fp8"]
-    rows, cols = min(rows, M), min(cols, N)
-    if kind == "mx":
-        a = o.normal_f32(2, 0, (rows, K), 1.0)
-        w = o.normal_f32(2, 1, (cols, K), 1.0)
-        bias = o.bf16_round(o.normal_f32(2, 2, (cols,), 0.1))
+    cfg = int(workload[1:])
+    if kind in ("mx", "mx4"):
+        rows, cols = min(2048, M), min(4096, N)
+        name = "e2m1" if kind == "mx4" else "e4m3"
+        a = o.normal_f32(cfg, 0, (rows, K), 1.0)
+        w = o.normal_f32(cfg, 1, (cols, K), 1.0 if kind == "mx" else 0.02)
+        bias = o.bf16_round(o.normal_f32(cfg, 2, (cols,), 0.1)) if kind == "mx" else None
+        act = o.ACT_GELU_TANH if kind == "mx" else o.ACT_IDENTITY
         qa, sa = o.quant_mx(a)
-        qb, sb = o.quant_mx(w)
+        qb, sb = o.quant_mx(w, name)
 
         def run():
             da = o.dequant_mx(qa, sa, K, "e4m3", np.float32)
-            db = o.dequant_mx(qb, sb, K, "e4m3", np.float32)
-            return o.matmul_golden32(da, db, bias, o.ACT_GELU_TANH)
+            db = o.dequant_mx(qb, sb, K, name, np.float32)
+            return o.matmul_golden32(da, db, bias, act)
+        what = f"{rows} rows of A x {cols} rows of B x K={K}"
+        flops = 2.0 * rows * cols * K
+    elif kind == "grouped":
+        experts = 32
+        group_rows = o.moe_group_rows()[:experts]
+        rows = int(group_rows.sum())
+        a = o.normal_f32(cfg, 0, (rows, K), 1.0)
+        w = o.normal_f32(cfg, 1, (experts * N, K), 0.02)
+        qa, sa = o.quant_fp8_1x128(a)
+        qw = [o.quant_fp8_128x128(w[g * N:(g + 1) * N]) for g in range(experts)]
+
+        def run():
+            da = o.dequant_fp8_1x128(qa, sa, np.float32)
+            db = np.stack([o.dequant_fp8_128x128(c, s, np.float32) for c, s in qw])
+            return o.bf16_round(o.grouped_matmul_ref(da, db, group_rows, np.float32))
+        what = f"the first {experts} experts ({rows} tokens) x N={N} x K={K}"
+        flops = 2.0 * rows * N * K
     else:
-        a = o.normal_f32(1, 0, (rows, K), 1.0)
-        w = o.normal_f32(1, 1, (cols, K), 0.02)
+        rows, cols = min(256, M), min(1024, N)
+        a = o.normal_f32(cfg, 0, (rows, K), 1.0)
+        w = o.normal_f32(cfg, 1, (cols, K), 0.02)
+        residual = o.bf16_round(o.normal_f32(cfg, 3, (rows, cols), 1.0)) if kind == "fp8sk" else None
         qa, sa = o.quant_fp8_1x128(a)
         qb, sb = o.quant_fp8_128x128(w)
 
         def run():
-            return o.matmul_golden32(o.dequant_fp8_1x128(qa, sa, np.float32), o.dequant_fp8_128x128(qb, sb, np.float32))
-    sample = (f"{rows} rows of A x {cols} rows of B x K={K} of '{desc}' per step: de-quantise to float32, np.matmul, "
-              f"epilogue, bf16")
-    return run, 2.0 * rows * cols * K, sample
+            return o.matmul_golden32(o.dequant_fp8_1x128(qa, sa, np.float32), o.dequant_fp8_128x128(qb, sb, np.float32),
+                                     None, o.ACT_IDENTITY, residual)
+        what = f"{rows} rows of A x {cols} rows of B x K={K}"
+        flops = 2.0 * rows * cols * K
+    sample = f"{what} of '{desc}' per step: de-quantise to float32, np.matmul, epilogue, bf16"
+    return run, flops, sample
 
 
 def time_cpu_golden(run, repeats):
@@ -187,7 +208,7 @@ def reference_arm(args):
     if rank != 0:
         return
     kind, M, N, K, desc = WORKLOADS[args.workload]
-    wl = args.workload if kind in ("mx", "fp8") else "c1"
+    wl = args.workload
     cores = len(os.sched_getaffinity(0))
     run, flops, sample = make_cpu_golden(wl)
     for _ in range(max(1, min(args.warmup, 3))):
@@ -221,8 +242,7 @@ def gpu_arm(args):
     import torch.distributed as dist
     from ops_tensor_b200 import host as H
     from ops_tensor_b200 import native, shard
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import blaze_oracle as o
+    from ops_tensor_b200 import synthetic as o           # seeded input generators; the CPU oracle is not used here
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -264,9 +284,9 @@ def gpu_arm(args):
     w_dev = torch.from_numpy(o.normal_f32(cfg_id, 1 + 16 * rank, (b_rows, K), sigma_b)).to(dev)
     bias = residual = None
     if kind == "mx":
-        bias = torch.from_numpy(o.bf16_round(o.normal_f32(cfg_id, 2, (N,), 0.1))).to(dev).to(torch.bfloat16)
+        bias = torch.from_numpy(o.normal_f32(cfg_id, 2, (N,), 0.1)).to(dev).to(torch.bfloat16)   # nearest-even
     if kind == "fp8sk":
-        residual = torch.from_numpy(o.bf16_round(o.normal_f32(cfg_id, 3, (M, N), 1.0))).to(dev).to(torch.bfloat16)
+        residual = torch.from_numpy(o.normal_f32(cfg_id, 3, (M, N), 1.0)).to(dev).to(torch.bfloat16)
 
     if kind in ("mx", "mx4"):
         b_dtype = H.R_4F_E2M1 if kind == "mx4" else H.R_8F_E4M3
@@ -464,8 +484,7 @@ def gpu_arm(args):
             "device_status": status,
         }
         if world == 1 and not args.kernel_only:
-            cpu_wl = args.workload if kind in ("mx", "fp8") else "c1"
-            run, cpu_flops, sample = make_cpu_golden(cpu_wl)
+            run, cpu_flops, sample = make_cpu_golden(args.workload)
             times = time_cpu_golden(run, 3)
             line["cpu_baseline"] = {"value": cpu_flops / float(np.mean(times)) / 1e12, "unit": "TFLOPS",
                                     "cores": len(os.sched_getaffinity(0)), "kind": "port",

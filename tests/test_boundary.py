@@ -292,3 +292,14 @@ def test_kernel_abi_argument_checks(built_library):
     assert l.blazeQuantizeMx(None, 0, 4, 32, 0, None, 0, None, None) == H.STATUS_INVALID_VALUE
     assert l.blazeAddF32(None, None, None, 0, None) == H.STATUS_SUCCESS
     assert l.blazeAddF32(None, None, None, -1, None) == H.STATUS_INVALID_VALUE
+
+
+def test_benchmark_generators_match_the_oracle():
+    """bench.py draws its inputs from ops_tensor_b200.synthetic; the parity tests draw theirs from the oracle.  Both
+    must produce the same tensors for the same (config, tensor id)."""
+    import numpy as np
+    import blaze_oracle as o
+    from ops_tensor_b200 import synthetic as s
+    assert np.array_equal(s.normal_f32(2, 0, (5, 64), 1.0), o.normal_f32(2, 0, (5, 64), 1.0))
+    assert np.array_equal(s.normal_f32(5, 1, (3, 128), 0.02), o.normal_f32(5, 1, (3, 128), 0.02))
+    assert np.array_equal(s.moe_group_rows(), o.moe_group_rows())
