@@ -67,10 +67,10 @@ typedef struct {
     void* D;                 /* device bf16 [M][ldd] */
     int64_t ldd;             /* elements */
     int32_t activation;      /* blazeActivation_t */
-    int32_t tile_n;          /* 0 = choose; else 128 or 224 */
+    int32_t tile_n;          /* 0 = choose; else 128, 224 or 256 (256 only with 2-CTA tiles) */
     int32_t reuse_b_prepass; /* 1: workspace still holds B's re-tiled scales / expanded codes from the previous call */
     int32_t sm_limit;        /* 0 = all SMs; else cap on the persistent grid */
-    int32_t cta_pair;        /* 0 = choose; 1 = 128-row tiles, one CTA each; 2 = 256 x 224 tiles on 2-CTA clusters */
+    int32_t cta_pair;        /* 0 = choose; 1 = 128-row tiles, one CTA each; 2 = 256-row tiles on 2-CTA clusters */
     int32_t reserved;
     void* workspace;         /* device, 256-byte aligned */
     size_t workspace_bytes;

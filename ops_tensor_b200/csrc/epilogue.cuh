@@ -28,26 +28,33 @@ struct EpilogueArgs {
 // Drains one accumulator tile.  `tmem_tile` = TMEM address of column 0 of the accumulator, lane field already set to
 // this warp's quadrant.  `row0` = global row of lane 0, `col0` = global column of accumulator column 0.  `stage` =
 // this warp's staging area (kEpiStageBytesPerWarp bytes, 512-byte aligned).  `chunk_counter` persists across tiles.
-// Calls `release()` once the last TMEM read of the tile has completed, before the remaining math and stores.
-template <int kBN, int kAct, class Release>
-__device__ __forceinline__ void epilogue_store_tile(uint32_t tmem_tile, const EpilogueArgs& ea,
-                                                    const CUtensorMap* tmap_d, uint8_t* stage, int row0, int col0,
-                                                    int lane, uint32_t& chunk_counter, Release release) {
+// The 32-column chunks are visited in the order first_chunk, first_chunk + 1, ... (wrapping).  `early()` is called
+// once the TMEM read of the first visited chunk has completed, `release()` once the last TMEM read of the tile has
+// completed; both run before the remaining math and stores.
+template <int kBN, int kAct, class Early, class Release>
+__device__ __forceinline__ void epilogue_store_tile_from(uint32_t tmem_tile, const EpilogueArgs& ea,
+                                                         const CUtensorMap* tmap_d, uint8_t* stage, int row0, int col0,
+                                                         int lane, uint32_t& chunk_counter, int first_chunk,
+                                                         Early early, Release release) {
     const int row = row0 + lane;
     const bool row_ok = row < ea.M;
     const __nv_bfloat16* r_row = (ea.residual && row_ok) ? ea.residual + (long long)row * ea.ldr : nullptr;
     constexpr int kChunks = kBN / 32;
 #pragma unroll 1
-    for (int c = 0; c < kChunks; ++c) {
+    for (int i = 0; i < kChunks; ++i) {
+        int c = first_chunk + i;
+        if (c >= kChunks) c -= kChunks;
         const int n0 = col0 + c * 32;
         if (n0 >= ea.N) {                       // whole chunk beyond the matrix: nothing to store
-            if (c == kChunks - 1) release();
+            if (i == 0) early();
+            if (i == kChunks - 1) release();
             continue;
         }
         uint32_t v[32];
         tmem_ld_32x32(tmem_tile + c * 32, v);
         tmem_ld_wait();
-        if (c == kChunks - 1) release();
+        if (i == 0) early();
+        if (i == kChunks - 1) release();
 
         uint32_t packed[16];
 #pragma unroll
@@ -100,6 +107,15 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t tmem_tile, const Ep
         }
         ++chunk_counter;
     }
+}
+
+// The common case: chunks in ascending order, one release at the end.
+template <int kBN, int kAct, class Release>
+__device__ __forceinline__ void epilogue_store_tile(uint32_t tmem_tile, const EpilogueArgs& ea,
+                                                    const CUtensorMap* tmap_d, uint8_t* stage, int row0, int col0,
+                                                    int lane, uint32_t& chunk_counter, Release release) {
+    epilogue_store_tile_from<kBN, kAct>(tmem_tile, ea, tmap_d, stage, row0, col0, lane, chunk_counter, 0, []() {},
+                                        release);
 }
 
 // To be called by lane 0 of every epilogue warp before the kernel ends.

@@ -5,6 +5,13 @@
 // two B halves from both shared memories, so every SM loads (128 + kBN/2) x 128 bytes per K step instead of
 // (128 + kBN) x 128, which is what bounds the single-CTA kernel (traffic through L2 and time to refill a stage).
 // Only the even ("leader") CTA issues tcgen05.cp / tcgen05.mma; its commits arrive on the barriers of both CTAs.
+//
+// kBN = 224: two disjoint accumulators (2 x 224 columns) + 12 scale columns fit the 512 TMEM columns.
+// kBN = 256: the two accumulators cannot both fit beside the scale columns, so they overlap by 16 columns
+// (accumulator 0 = columns [0, 256), accumulator 1 = [240, 496), scales at 496).  The epilogue of a tile reads the 32
+// columns that contain the shared ones first and signals "overlap read"; the first MMA of the next tile (which uses
+// the other accumulator) waits for that signal, a bubble of one barrier round trip per tile.  In exchange a K step
+// carries 14 % more MMA work per scale copy and per operand byte loaded.
 // Every load is an ordinary per-CTA TMA load (no cluster multicast); the odd CTA's loads credit their bytes to the
 // leader's "full" barrier.  The role of the reference code it replaces is the same as in gemm_mx.cuh
 // (include/blaze/gemm/kernel/kernel_qbmm_mx.h:379-454, include/blaze/gemm/block/block_mmad_qbmm_mx.h:398-480).
@@ -26,7 +33,7 @@ struct MxPairSmem {
     static constexpr int kSfbBytes = kSfbAtoms * 512;
     static constexpr int kSfOffset = kStages * kStageBytes;
     static constexpr int kBarOffset = kSfOffset + kStages * (kSfaBytes + kSfbBytes);
-    static constexpr int kNumBars = 2 * kStages + 4;
+    static constexpr int kNumBars = 2 * kStages + 5;
     static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
     static constexpr int kEpiOffset = (kMiscOffset + 16 + 1023) / 1024 * 1024;
     static constexpr int kTotal = kEpiOffset + kEpiStageBytes;
@@ -60,9 +67,14 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     using L = MxPairSmem<kBN, kStages>;
     static_assert(kBN % 32 == 0 && kBN >= 32 && kBN <= 256, "tile N");
     constexpr int kAccStages = 2;
-    constexpr int kSfaCol = kAccStages * kBN;
+    constexpr int kSfCols = 4 + 4 * L::kSfbAtoms;
+    constexpr bool kOverlap = kAccStages * kBN + kSfCols > 512;         // accumulators share their edge columns
+    constexpr int kSfaCol = kOverlap ? 512 - 16 : kAccStages * kBN;
     constexpr int kSfbCol = kSfaCol + 4;
+    constexpr int kAccStride = kOverlap ? kSfaCol - kBN : kBN;           // column of accumulator 1
     static_assert(kSfbCol + 4 * L::kSfbAtoms <= 512, "TMEM budget");
+    static_assert(!kOverlap || (kBN - kAccStride <= 32 && kAccStride % 16 == 0), "shared columns fit one chunk");
+    constexpr int kChunks = kBN / 32;
     constexpr uint32_t kTmemCols = 512;
 
     extern __shared__ uint8_t smem_unaligned[];
@@ -72,6 +84,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint64_t* empty_bar = bars + kStages;            // one per CTA, released by the leader's commits
     uint64_t* tmem_full_bar = bars + 2 * kStages;    // one per CTA
     uint64_t* tmem_empty_bar = bars + 2 * kStages + 2;   // used in the leader only: 8 epilogue warps arrive
+    uint64_t* overlap_bar = bars + 2 * kStages + 4;      // leader only: the shared accumulator columns were read
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
 
@@ -90,6 +103,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             mbar_init(&tmem_full_bar[s], 1);
             mbar_init(&tmem_empty_bar[s], 8);
         }
+        mbar_init(overlap_bar, 8);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -148,12 +162,19 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
+            uint32_t tiles_done = 0;
             bool ok = true;
             for (int t = pair; t < num_tiles && ok; t += num_pairs) {
                 ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
                 if (!ok) break;
+                if (kOverlap && tiles_done != 0) {
+                    // the previous tile's epilogue must have read the columns this accumulator shares with it
+                    ok = mbar_wait(overlap_bar, (tiles_done - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                    if (!ok) break;
+                }
+                ++tiles_done;
                 tcgen05_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * kBN;
+                const uint32_t d_tmem = tmem_base + acc * kAccStride;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
@@ -200,13 +221,23 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (!ok) break;
             tcgen05_fence_after();
             uint64_t* release_bar = &tmem_empty_bar[acc];          // owned by the leader CTA
-            epilogue_store_tile<kBN, kAct>(tmem_base + lane_base + acc * kBN, ea, &tmap_d, stage_buf,
-                                           mt * 256 + (int)cta_rank * 128 + warp * 32, nt * kBN, lane, chunk_counter,
-                                           [&]() {
-                                               tcgen05_fence_before();
-                                               __syncwarp();
-                                               if (lane == 0) mbar_arrive_cluster(release_bar, 0);
-                                           });
+            // accumulator 0 shares its last columns, accumulator 1 its first: start with the chunk that holds them
+            const int first_chunk = (kOverlap && acc == 0) ? kChunks - 1 : 0;
+            epilogue_store_tile_from<kBN, kAct>(
+                tmem_base + lane_base + acc * kAccStride, ea, &tmap_d, stage_buf,
+                mt * 256 + (int)cta_rank * 128 + warp * 32, nt * kBN, lane, chunk_counter, first_chunk,
+                [&]() {
+                    if (kOverlap) {
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(overlap_bar, 0);
+                    }
+                },
+                [&]() {
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(release_bar, 0);
+                });
             if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
         }
         if (lane == 0) epilogue_drain_stores();

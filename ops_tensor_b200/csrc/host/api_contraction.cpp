@@ -279,7 +279,7 @@ acltensorStatus_t acltensorOperationDescriptorSetAttribute(const acltensorHandle
             if (v < ACLTENSOR_SPLIT_AUTO || v > ACLTENSOR_SPLIT_STREAM_K) return ACLTENSOR_STATUS_INVALID_VALUE;
             break;
         case ACLTENSOR_OPERATION_DESCRIPTOR_TILE_N:
-            if (v != 0 && v != 128 && v != 224) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+            if (v != 0 && v != 128 && v != 224 && v != 256) return ACLTENSOR_STATUS_NOT_SUPPORTED;
             break;
         case ACLTENSOR_OPERATION_DESCRIPTOR_SM_LIMIT:
             if (v < 0) return ACLTENSOR_STATUS_INVALID_VALUE;

@@ -131,19 +131,43 @@ static int choose_tile_n(int M, int N, int sms, int requested) {
     return cost(224) <= cost(128) ? 224 : 128;
 }
 
+// Width of the 256-row paired tiles: the one whose last wave wastes less, 256 on a tie (a K step then carries more MMA
+// work per scale copy and per operand byte).
+static int choose_pair_tile_n(int M, int N, int sms) {
+    const long long pairs = sms / 2 > 0 ? sms / 2 : 1;
+    const long long m_tiles = (M + 255) / 256;
+    long long best_cost = 0;
+    int best = 256;
+    for (int w : {256, 224}) {
+        const long long tiles = m_tiles * ((N + w - 1) / w);
+        const long long cost = ((tiles + pairs - 1) / pairs) * w;
+        if (best_cost == 0 || cost < best_cost) {
+            best_cost = cost;
+            best = w;
+        }
+    }
+    return best;
+}
+
 static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl) {
     if (!a || a->struct_size != sizeof(blazeMxGemmArgs)) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->M < 0 || a->N < 0 || a->K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->b_elem != BLAZE_ELEM_E4M3 && a->b_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_GELU_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    if (a->tile_n != 0 && a->tile_n != 128 && a->tile_n != 224) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->tile_n != 0 && a->tile_n != 128 && a->tile_n != 224 && a->tile_n != 256) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if ((a->K % 16) != 0 || (a->N % 8) != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->cta_pair < 0 || a->cta_pair > 2) return ACLTENSOR_STATUS_INVALID_VALUE;
-    if (a->cta_pair == 2 && a->tile_n == 128) return ACLTENSOR_STATUS_NOT_SUPPORTED;    // paired tiles are 256 x 224
-    // 256 x 224 tiles on CTA pairs once there are at least two 128-row blocks and more than one 128-column block
-    // (an explicit tile_n without cta_pair = 2 keeps the single-CTA kernel of that width)
-    pl->pair = a->cta_pair == 2 || (a->cta_pair == 0 && a->tile_n == 0 && a->M > 128 && a->N > 128 && sms >= 2);
-    pl->tile_n = pl->pair ? 224 : choose_tile_n(a->M, a->N, sms, a->tile_n);
+    if (a->cta_pair == 2 && a->tile_n == 128) return ACLTENSOR_STATUS_NOT_SUPPORTED;    // paired tiles: 256 x 224 / 256
+    if (a->cta_pair == 1 && a->tile_n == 256) return ACLTENSOR_STATUS_NOT_SUPPORTED;    // 256 wide only on pairs
+    // 256-row tiles on CTA pairs once there are at least two 128-row blocks and more than one 128-column block
+    // (an explicit tile_n of 128 or 224 without cta_pair = 2 keeps the single-CTA kernel of that width)
+    pl->pair = a->cta_pair == 2 || a->tile_n == 256 ||
+               (a->cta_pair == 0 && a->tile_n == 0 && a->M > 128 && a->N > 128 && sms >= 2);
+    if (pl->pair) {
+        pl->tile_n = a->tile_n ? a->tile_n : choose_pair_tile_n(a->M, a->N, sms);
+    } else {
+        pl->tile_n = choose_tile_n(a->M, a->N, sms, a->tile_n);
+    }
     pl->m_tiles = pl->pair ? (a->M + 255) / 256 : (a->M + 127) / 128;
     pl->n_tiles = (a->N + pl->tile_n - 1) / pl->tile_n;
     pl->k_steps = (a->K + 127) / 128;
@@ -199,11 +223,11 @@ static bool make_tmap_sf_blocks(CUtensorMap* map, const void* base, uint64_t blo
     return r == CUDA_SUCCESS;
 }
 
-template <int kAct>
+template <int kBN, int kAct>
 static cudaError_t launch_mx_pair_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
                                            const CUtensorMap& tsb, const CUtensorMap& td, const MxGemmParams& p,
                                            int pairs, cudaStream_t stream) {
-    constexpr int kBN = 224, kStages = 6;
+    constexpr int kStages = 6;
     using L = MxPairSmem<kBN, kStages>;
     auto kernel = mx_gemm_pair_kernel<kBN, kStages, kAct>;
     static bool attr_done[64] = {};
@@ -248,16 +272,24 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
         const uint64_t sfa_blocks = (uint64_t)((a->M + 127) / 128) * pl.k_steps;
         const uint64_t sfb_blocks = (uint64_t)pl.n_tiles * pl.k_steps * 2;
         if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
-            !make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, 112) ||
+            !make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n / 2) ||
             !make_tmap_sf_blocks(&tsa, sfa_tiled, sfa_blocks, 1) || !make_tmap_sf_blocks(&tsb, sfb_tiled, sfb_blocks, 2))
             return ACLTENSOR_STATUS_INTERNAL_ERROR;
         int pairs = sms / 2;
         if (pairs < 1) pairs = 1;
         if (tiles < pairs) pairs = (int)tiles;
-        switch (a->activation) {
-            case BLAZE_ACT_RELU: e = launch_mx_pair_instance<ACT_RELU>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
-            case BLAZE_ACT_GELU_TANH: e = launch_mx_pair_instance<ACT_GELU_TANH>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
-            default: e = launch_mx_pair_instance<ACT_IDENTITY>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
+        if (pl.tile_n == 256) {
+            switch (a->activation) {
+                case BLAZE_ACT_RELU: e = launch_mx_pair_instance<256, ACT_RELU>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
+                case BLAZE_ACT_GELU_TANH: e = launch_mx_pair_instance<256, ACT_GELU_TANH>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
+                default: e = launch_mx_pair_instance<256, ACT_IDENTITY>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
+            }
+        } else {
+            switch (a->activation) {
+                case BLAZE_ACT_RELU: e = launch_mx_pair_instance<224, ACT_RELU>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
+                case BLAZE_ACT_GELU_TANH: e = launch_mx_pair_instance<224, ACT_GELU_TANH>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
+                default: e = launch_mx_pair_instance<224, ACT_IDENTITY>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
+            }
         }
         return status_of(e);
     }

@@ -243,7 +243,7 @@ def test_config4_moe_grouped(cuda_device):
 # ------------------------------------------------------------------------------------------------ MX
 
 def run_mx(device, a, w, *, b_dtype=H.R_8F_E4M3, act=H.OP_IDENTITY, bias=None, residual=None, tile_n=0,
-           check_quant=True, static_b=False, cta_pair=0):
+           check_quant=True, static_b=False, cta_pair=0, sm_limit=0):
     import torch
     M, K = a.shape
     N = w.shape[0]
@@ -260,7 +260,7 @@ def run_mx(device, a, w, *, b_dtype=H.R_8F_E4M3, act=H.OP_IDENTITY, bias=None, r
     res_t = bf16_tensor(residual, device) if residual is not None else None
     with H.Contraction(M, N, K, scale_mode_a=H.SCALE_MX_E8M0_VEC32, scale_mode_b=H.SCALE_MX_E8M0_VEC32, b_dtype=b_dtype,
                        activation=act, bias=bias is not None, residual=residual is not None, tile_n=tile_n,
-                       b_is_static=static_b, cta_pair=cta_pair) as c:
+                       b_is_static=static_b, cta_pair=cta_pair, sm_limit=sm_limit) as c:
         c(qa, sa, qb, sb, out, bias=bias_t, residual=res_t)
         first = to_np(out).copy()
         out.fill_(float("nan"))
@@ -283,9 +283,9 @@ def mx_reference(qa, sa, qb, sb, K, name="e4m3", act=o.ACT_IDENTITY, bias=None, 
 
 @pytest.mark.parametrize("M,N,K", [(1, 8, 32), (128, 128, 128), (128, 224, 256), (300, 520, 1040), (129, 232, 96),
                                    (256, 512, 1024), (77, 456, 2064)])
-@pytest.mark.parametrize("tile_n,cta_pair", [(128, 1), (224, 1), (0, 2)])
+@pytest.mark.parametrize("tile_n,cta_pair", [(128, 1), (224, 1), (0, 2), (256, 2)])
 def test_mx_shapes_and_tails(cuda_device, M, N, K, tile_n, cta_pair):
-    """Single-CTA tiles of both widths and the 2-CTA 256 x 224 tiles, on aligned and ragged shapes."""
+    """Single-CTA tiles of both widths and the 2-CTA 256 x 224 / 256 x 256 tiles, on aligned and ragged shapes."""
     a = o.normal_f32(21, 0, (M, K), 1.0)
     w = o.normal_f32(21, 1, (N, K), 1.0)
     got, qa, sa, qb, sb = run_mx(cuda_device, a, w, tile_n=tile_n, cta_pair=cta_pair)
@@ -314,7 +314,7 @@ def test_mx_scale_extremes(cuda_device):
     assert_gemm_ok(got, ref, gold)
 
 
-@pytest.mark.parametrize("cta_pair", [1, 2])
+@pytest.mark.parametrize("cta_pair", [1, 2, 256])
 @pytest.mark.parametrize("act", [H.OP_IDENTITY, H.OP_RELU, H.OP_GELU])
 def test_mx_fused_epilogue(cuda_device, act, cta_pair):
     M, N, K = 260, 456, 512
@@ -322,7 +322,8 @@ def test_mx_fused_epilogue(cuda_device, act, cta_pair):
     w = o.normal_f32(22, 1, (N, K), 0.05)
     bias = o.normal_f32(22, 2, (N,), 0.5)
     residual = o.normal_f32(22, 3, (M, N), 1.0)
-    got, qa, sa, qb, sb = run_mx(cuda_device, a, w, act=act, bias=bias, residual=residual, cta_pair=cta_pair)
+    got, qa, sa, qb, sb = run_mx(cuda_device, a, w, act=act, bias=bias, residual=residual,
+                                 cta_pair=min(cta_pair, 2), tile_n=256 if cta_pair == 256 else 0)
     ref, gold = mx_reference(qa, sa, qb, sb, K, "e4m3", ACT[act], bias, residual)
     assert_gemm_ok(got, ref, gold)
 
@@ -333,6 +334,19 @@ def test_w4a8_mx(cuda_device, M, N, K):
     w = o.normal_f32(23, 1, (N, K), 0.02)
     got, qa, sa, qb, sb = run_mx(cuda_device, a, w, b_dtype=H.R_4F_E2M1, static_b=True)
     ref, gold = mx_reference(qa, sa, qb, sb, K, "e2m1")
+    assert_gemm_ok(got, ref, gold)
+
+
+@pytest.mark.parametrize("tile_n", [224, 256])
+def test_mx_pair_many_tiles_per_pair(cuda_device, tile_n):
+    """Two CTA pairs walk 24-28 tiles each, so both accumulators (and, for 256-wide tiles, the columns they share)
+    are handed back and forth many times; every element is checked."""
+    M, N, K = 1000, 1544, 384
+    a = o.normal_f32(23, 0, (M, K), 1.0)
+    w = o.normal_f32(23, 1, (N, K), 1.0)
+    bias = o.normal_f32(23, 2, (N,), 0.5)
+    got, qa, sa, qb, sb = run_mx(cuda_device, a, w, act=H.OP_RELU, bias=bias, tile_n=tile_n, cta_pair=2, sm_limit=4)
+    ref, gold = mx_reference(qa, sa, qb, sb, K, "e4m3", o.ACT_RELU, bias)
     assert_gemm_ok(got, ref, gold)
 
 
