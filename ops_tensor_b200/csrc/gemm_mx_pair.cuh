@@ -21,7 +21,7 @@
 
 namespace blaze {
 
-template <int kBN, int kStages>
+template <int kBN, int kStages, bool kWide = (kBN == 256)>
 struct MxPairSmem {
     static constexpr int kBM = 128;                       // rows of A per CTA (256 per pair)
     static constexpr int kBK = 128;
@@ -30,7 +30,12 @@ struct MxPairSmem {
     static constexpr int kStageBytes = kABytes + kBHalfBytes;
     static constexpr int kSfaBytes = 512;
     static constexpr int kSfbAtoms = (kBN + 127) / 128;
-    static constexpr int kSfbBytes = kSfbAtoms * 512;
+    // 256-wide tiles copy both scale atoms of B into TMEM with one 128x256b tcgen05.cp (a scale copy costs tensor-pipe
+    // time per instruction, not per byte).  That shape has no lane broadcast, so the re-tiled scale array holds each
+    // 512-byte atom four times, once per 32-lane quadrant: [atom][quadrant][32 lanes][16 B] per K step.
+    static constexpr bool kWideSfb = kWide;
+    static constexpr int kSfbBlocks = kWideSfb ? kSfbAtoms * 4 : kSfbAtoms;     // 512-byte blocks per K step
+    static constexpr int kSfbBytes = kSfbBlocks * 512;
     static constexpr int kSfOffset = kStages * kStageBytes;
     static constexpr int kBarOffset = kSfOffset + kStages * (kSfaBytes + kSfbBytes);
     static constexpr int kNumBars = 2 * kStages + 5;
@@ -59,12 +64,12 @@ __device__ __forceinline__ void tma_load_2d_to_pair_bar(void* smem_dst, const CU
         : "memory");
 }
 
-template <int kBN, int kStages, int kAct>
+template <int kBN, int kStages, int kAct, bool kWide = (kBN == 256)>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                     const __grid_constant__ CUtensorMap tmap_d, const MxGemmParams p) {
-    using L = MxPairSmem<kBN, kStages>;
+    using L = MxPairSmem<kBN, kStages, kWide>;
     static_assert(kBN % 32 == 0 && kBN >= 32 && kBN <= 256, "tile N");
     constexpr int kAccStages = 2;
     constexpr int kSfCols = 4 + 4 * L::kSfbAtoms;
@@ -137,7 +142,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 const int a_row = mt * 256 + (int)cta_rank * 128;
                 const int b_row = nt * kBN + (int)cta_rank * (kBN / 2);
                 const int sfa_row = (mt * 2 + (int)cta_rank) * p.k_steps;
-                const int sfb_row = nt * p.k_steps * L::kSfbAtoms;
+                const int sfb_row = nt * p.k_steps * L::kSfbBlocks;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
@@ -150,7 +155,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     tma_load_2d_to_pair_bar(a_dst, &tmap_a, bar, ks * L::kBK, a_row, kEvictNormal);
                     tma_load_2d_to_pair_bar(b_dst, &tmap_b, bar, ks * L::kBK, b_row, kEvictNormal);
                     tma_load_2d_to_pair_bar(sfa_dst, &tmap_sfa, bar, 0, sfa_row + ks, kEvictNormal);
-                    tma_load_2d_to_pair_bar(sfb_dst, &tmap_sfb, bar, 0, sfb_row + ks * L::kSfbAtoms, kEvictNormal);
+                    tma_load_2d_to_pair_bar(sfb_dst, &tmap_sfb, bar, 0, sfb_row + ks * L::kSfbBlocks, kEvictNormal);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -184,9 +189,13 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t sfa_addr = smem_u32(smem + L::kSfOffset + stage * (L::kSfaBytes + L::kSfbBytes));
                     const uint32_t sfb_addr = sfa_addr + L::kSfaBytes;
                     utccp_sf<2>(tmem_base + kSfaCol, umma_desc_sf(sfa_addr));
+                    if constexpr (L::kWideSfb) {
+                        utccp_sf_wide<2>(tmem_base + kSfbCol, umma_desc_sf_wide(sfb_addr, 4 * 512));
+                    } else {
 #pragma unroll
-                    for (int i = 0; i < L::kSfbAtoms; ++i) {
-                        utccp_sf<2>(tmem_base + kSfbCol + 4 * i, umma_desc_sf(sfb_addr + 512 * i));
+                        for (int i = 0; i < L::kSfbAtoms; ++i) {
+                            utccp_sf<2>(tmem_base + kSfbCol + 4 * i, umma_desc_sf(sfb_addr + 512 * i));
+                        }
                     }
                     const uint64_t a_desc = umma_desc_sw128(a_addr);
                     const uint64_t b_desc = umma_desc_sw128(b_addr);

@@ -112,8 +112,9 @@ static int status_of(cudaError_t e) {
 // ------------------------------------------------------------------------------------------------ MX GEMM
 
 struct MxPlan {
-    bool pair;          // 256 x 224 tiles on 2-CTA clusters
+    bool pair;          // 256-row tiles on 2-CTA clusters
     int tile_n;
+    int sfb_replicas;   // copies of every 512-byte scale block of B in the re-tiled array
     int m_tiles, n_tiles, k_steps;
     size_t sfa_bytes, sfb_bytes, b_expand_bytes;
     size_t sfa_off, sfb_off, b_expand_off, total;
@@ -172,7 +173,8 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl) {
     pl->n_tiles = (a->N + pl->tile_n - 1) / pl->tile_n;
     pl->k_steps = (a->K + 127) / 128;
     pl->sfa_bytes = (size_t)sf_tiled_bytes(a->M, a->K, 128);
-    pl->sfb_bytes = (size_t)sf_tiled_bytes(a->N, a->K, pl->tile_n);
+    pl->sfb_replicas = (pl->pair && pl->tile_n == 256) ? 4 : 1;      // the 256-wide kernel copies B's scales unbroadcast
+    pl->sfb_bytes = (size_t)sf_tiled_bytes(a->N, a->K, pl->tile_n, pl->sfb_replicas);
     pl->b_expand_bytes = a->b_elem == BLAZE_ELEM_E2M1 ? (size_t)a->N * (size_t)a->K : 0;
     pl->sfa_off = 0;
     pl->sfb_off = round256(pl->sfa_bytes);
@@ -227,7 +229,7 @@ template <int kBN, int kAct>
 static cudaError_t launch_mx_pair_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
                                            const CUtensorMap& tsb, const CUtensorMap& td, const MxGemmParams& p,
                                            int pairs, cudaStream_t stream) {
-    constexpr int kStages = 6;
+    constexpr int kStages = kBN == 256 ? 5 : 6;      // the replicated scale block of the wide tile costs a stage
     using L = MxPairSmem<kBN, kStages>;
     auto kernel = mx_gemm_pair_kernel<kBN, kStages, kAct>;
     static bool attr_done[64] = {};
@@ -270,10 +272,10 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
     if (pl.pair) {
         CUtensorMap tsa, tsb;
         const uint64_t sfa_blocks = (uint64_t)((a->M + 127) / 128) * pl.k_steps;
-        const uint64_t sfb_blocks = (uint64_t)pl.n_tiles * pl.k_steps * 2;
+        const uint64_t sfb_blocks = (uint64_t)pl.n_tiles * pl.k_steps * 2 * pl.sfb_replicas;
         if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
             !make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n / 2) ||
-            !make_tmap_sf_blocks(&tsa, sfa_tiled, sfa_blocks, 1) || !make_tmap_sf_blocks(&tsb, sfb_tiled, sfb_blocks, 2))
+            !make_tmap_sf_blocks(&tsa, sfa_tiled, sfa_blocks, 1) || !make_tmap_sf_blocks(&tsb, sfb_tiled, sfb_blocks, 2 * pl.sfb_replicas))
             return ACLTENSOR_STATUS_INTERNAL_ERROR;
         int pairs = sms / 2;
         if (pairs < 1) pairs = 1;
@@ -347,7 +349,7 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
     const uint8_t* b_codes = static_cast<const uint8_t*>(a->B);
     int64_t b_pitch = a->ldb;
 
-    cudaError_t e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleA), a->M, a->K, 128, sfa_tiled, ctx->sm_count,
+    cudaError_t e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleA), a->M, a->K, 128, 1, sfa_tiled, ctx->sm_count,
                                      stream);
     if (e != cudaSuccess) return status_of(e);
     if (a->b_elem == BLAZE_ELEM_E2M1) {
@@ -355,7 +357,7 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
         b_pitch = a->K;
     }
     if (!a->reuse_b_prepass) {
-        e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleB), a->N, a->K, pl.tile_n, sfb_tiled, ctx->sm_count,
+        e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleB), a->N, a->K, pl.tile_n, pl.sfb_replicas, sfb_tiled, ctx->sm_count,
                              stream);
         if (e != cudaSuccess) return status_of(e);
         if (a->b_elem == BLAZE_ELEM_E2M1) {
@@ -685,6 +687,16 @@ extern "C" int blazeMxGemmNoAlloc(const blazeMxGemmArgs* a, int32_t* device_stat
     MxPlan pl;
     st = plan_mx(a, nd->sm_count, &pl);
     if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    blazeMxGemmArgs narrow;
+    if (pl.total > kNoAllocScratchBytes && a->tile_n == 0 && pl.tile_n == 256) {
+        // the 256-wide tiles keep four copies of B's scale blocks; the 224-wide ones need a quarter of that
+        narrow = *a;
+        narrow.tile_n = 224;
+        narrow.cta_pair = 2;
+        a = &narrow;
+        st = plan_mx(a, nd->sm_count, &pl);
+        if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    }
     if (a->b_elem != BLAZE_ELEM_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;      // packed E2M1 needs an N x K expansion buffer
     if (pl.total > kNoAllocScratchBytes) return ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE;   // problem too large for the fixed array
     if (a->M == 0 || a->N == 0) return ACLTENSOR_STATUS_SUCCESS;
@@ -700,10 +712,10 @@ extern "C" int blazeMxGemmNoAlloc(const blazeMxGemmArgs* a, int32_t* device_stat
     uint8_t* sfa_tiled = nd->scratch + pl.sfa_off;
     uint8_t* sfb_tiled = nd->scratch + pl.sfb_off;
     // the array still holds the previous call's tiles: both scale arrays are rebuilt in full on every call
-    cudaError_t e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleA), a->M, a->K, 128, sfa_tiled, nd->sm_count,
+    cudaError_t e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleA), a->M, a->K, 128, 1, sfa_tiled, nd->sm_count,
                                      stream);
     if (e != cudaSuccess) return status_of(e);
-    e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleB), a->N, a->K, pl.tile_n, sfb_tiled, nd->sm_count, stream);
+    e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleB), a->N, a->K, pl.tile_n, pl.sfb_replicas, sfb_tiled, nd->sm_count, stream);
     if (e != cudaSuccess) return status_of(e);
 
     return run_mx_kernel(a, pl, sfa_tiled, sfb_tiled, static_cast<const uint8_t*>(a->B), a->ldb,

@@ -17,12 +17,13 @@ struct DeviceContext {
 // Per-device context of the current device (created on first use; thread-safe).  nullptr if no usable device.
 DeviceContext* current_context();
 
-// Bytes of the re-tiled scale-factor array for `rows` x K with tiles of `tile_rows` rows.
-inline long long sf_tiled_bytes(int rows, int K, int tile_rows) {
+// Bytes of the re-tiled scale-factor array for `rows` x K with tiles of `tile_rows` rows, every 512-byte block
+// stored `replicas` times in a row.
+inline long long sf_tiled_bytes(int rows, int K, int tile_rows, int replicas = 1) {
     const long long tiles = (rows + tile_rows - 1) / tile_rows;
     const long long k_steps = (K + 127) / 128;
     const long long atoms = (tile_rows + 127) / 128;
-    return tiles * k_steps * atoms * 512;
+    return tiles * k_steps * atoms * replicas * 512;
 }
 
 cudaError_t launch_quant_mx(const float* x, long long ldx, int rows, int K, bool e2m1, uint8_t* codes,
@@ -31,8 +32,8 @@ cudaError_t launch_quant_fp8_1x128(const float* x, long long ldx, int rows, int 
                                    float* scales, int sm_count, cudaStream_t stream);
 cudaError_t launch_quant_fp8_128x128(const float* w, long long ldw, int N, int K, uint8_t* codes, long long ldc,
                                      float* scales, int sm_count, cudaStream_t stream);
-cudaError_t launch_sf_retile(const uint8_t* in, int rows, int K, int tile_rows, uint8_t* out, int sm_count,
-                             cudaStream_t stream);
+cudaError_t launch_sf_retile(const uint8_t* in, int rows, int K, int tile_rows, int replicas, uint8_t* out,
+                             int sm_count, cudaStream_t stream);
 cudaError_t launch_e2m1_expand(const uint8_t* in, long long ld_in, int rows, int K, uint8_t* out, long long ld_out,
                                int sm_count, cudaStream_t stream);
 cudaError_t launch_add_f32(const float* a, const float* c, float* d, long long n, int sm_count, cudaStream_t stream);

@@ -313,6 +313,17 @@ __device__ __forceinline__ uint64_t umma_desc_sf(uint32_t smem_addr) {
     return d;
 }
 
+// Descriptor for a 128-row x 32-byte block copied by tcgen05.cp.128x256b: rows 16 bytes apart in groups of eight
+// (128 bytes per group), the second 16-byte half of every row `half_stride` bytes after the first.
+__device__ __forceinline__ uint64_t umma_desc_sf_wide(uint32_t smem_addr, uint32_t half_stride) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(half_stride >> 4) << 16;        // leading byte offset between the two 16-byte halves
+    d |= static_cast<uint64_t>(128 >> 4) << 32;                // stride byte offset between 8-row groups
+    d |= static_cast<uint64_t>(1) << 46;
+    return d;
+}
+
 enum UmmaFormat : uint32_t { FMT_E4M3 = 0, FMT_E5M2 = 1, FMT_E2M1 = 5 };
 
 // Instruction descriptor for kind::f8f6f4 (fp32 accumulate, both operands K-major).
@@ -420,6 +431,16 @@ __device__ __forceinline__ void utccp_sf(uint32_t tmem_dst, uint64_t sf_desc) {
         asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(sf_desc) : "memory");
     } else {
         asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(sf_desc) : "memory");
+    }
+}
+
+// Copy a 128-row x 32-byte block from shared memory into 8 TMEM columns of all 128 lanes (no broadcast).
+template <int kCtaGroup>
+__device__ __forceinline__ void utccp_sf_wide(uint32_t tmem_dst, uint64_t desc) {
+    if constexpr (kCtaGroup == 1) {
+        asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(tmem_dst), "l"(desc) : "memory");
+    } else {
+        asm volatile("tcgen05.cp.cta_group::2.128x256b [%0], %1;" ::"r"(tmem_dst), "l"(desc) : "memory");
     }
 }
 

@@ -213,10 +213,11 @@ __global__ void __launch_bounds__(256) quant_fp8_128x128_kernel(const float* __r
 
 // ---------------------------------------------------------------------------------------------------- layout helpers
 
-// out[tile][k_step][atom][lane 0..31][quarter 0..3][kk 0..3] = scale[row][k_step*4 + kk],
-// row = tile*tile_rows + atom*128 + quarter*32 + lane; anything outside the matrix is 127 (2^0).
+// out[tile][k_step][atom][replica][lane 0..31][quarter 0..3][kk 0..3] = scale[row][k_step*4 + kk],
+// row = tile*tile_rows + atom*128 + quarter*32 + lane; anything outside the matrix is 127 (2^0).  `replicas` is 1,
+// or 4 where the kernel copies the block into TMEM without the lane broadcast (one copy per 32-lane quadrant).
 __global__ void __launch_bounds__(256) sf_retile_kernel(const uint8_t* __restrict__ in, int rows, int scale_cols,
-                                                        int valid_groups, int tile_rows, int k_steps,
+                                                        int valid_groups, int tile_rows, int k_steps, int replicas,
                                                         uint32_t* __restrict__ out, long long out_words) {
     const int atoms = (tile_rows + 127) >> 7;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < out_words;
@@ -224,6 +225,7 @@ __global__ void __launch_bounds__(256) sf_retile_kernel(const uint8_t* __restric
         long long r = i;
         const int quarter = (int)(r & 3); r >>= 2;
         const int lane = (int)(r & 31); r >>= 5;
+        r /= replicas;
         const int atom = (int)(r % atoms); r /= atoms;
         const int ks = (int)(r % k_steps);
         const int tile = (int)(r / k_steps);
@@ -334,15 +336,15 @@ cudaError_t launch_quant_fp8_128x128(const float* w, long long ldw, int N, int K
     return cudaGetLastError();
 }
 
-cudaError_t launch_sf_retile(const uint8_t* in, int rows, int K, int tile_rows, uint8_t* out, int sm_count,
-                             cudaStream_t stream) {
+cudaError_t launch_sf_retile(const uint8_t* in, int rows, int K, int tile_rows, int replicas, uint8_t* out,
+                             int sm_count, cudaStream_t stream) {
     const int scale_cols = ((K + 63) / 64) * 2;
     const int valid_groups = (K + 31) / 32;
     const int k_steps = (K + 127) / 128;
-    const long long words = sf_tiled_bytes(rows, K, tile_rows) / 4;
+    const long long words = sf_tiled_bytes(rows, K, tile_rows, replicas) / 4;
     if (words <= 0) return cudaSuccess;
     const int grid = grid_for(words, 256, sm_count);
-    sf_retile_kernel<<<grid, 256, 0, stream>>>(in, rows, scale_cols, valid_groups, tile_rows, k_steps,
+    sf_retile_kernel<<<grid, 256, 0, stream>>>(in, rows, scale_cols, valid_groups, tile_rows, k_steps, replicas,
                                                reinterpret_cast<uint32_t*>(out), words);
     return cudaGetLastError();
 }
