@@ -90,8 +90,8 @@ BLAZE_API int blazeMxGemm(const blazeMxGemmArgs* args, void* stream);
  *   - B must be BLAZE_ELEM_E4M3 (packed E2M1 would need an N x K expansion buffer): NOT_SUPPORTED otherwise;
  *   - a problem whose re-tiled scales exceed 8 MiB - about 512*(ceil(M/128) + 2*ceil(N/224))*ceil(K/128) bytes, e.g.
  *     M = N = K = 8192 needs 4.4 MiB - is refused with ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE before anything runs
- *     (the 256-wide tiles blazeMxGemm may pick keep four copies of B's scale blocks; when only the 224-wide form
- *     fits the array, this call uses that form);
+ *     (blazeMxGemm keeps four copies of B's scale blocks on 2-CTA tiles to save a tensor-pipe copy per K step; this
+ *     call does the same while that fits the array and keeps a single copy otherwise);
  *   - the first call on a device looks up the array's device address (one-time set-up, with that device current);
  *     make that first call outside any stream capture;
  *   - all calls share the one array, which still holds the previous call's tiles; each call rewrites the part it

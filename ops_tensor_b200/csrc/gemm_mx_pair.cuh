@@ -21,7 +21,7 @@
 
 namespace blaze {
 
-template <int kBN, int kStages, bool kWide = (kBN == 256)>
+template <int kBN, int kStages, bool kWide = true>
 struct MxPairSmem {
     static constexpr int kBM = 128;                       // rows of A per CTA (256 per pair)
     static constexpr int kBK = 128;
@@ -30,8 +30,8 @@ struct MxPairSmem {
     static constexpr int kStageBytes = kABytes + kBHalfBytes;
     static constexpr int kSfaBytes = 512;
     static constexpr int kSfbAtoms = (kBN + 127) / 128;
-    // 256-wide tiles copy both scale atoms of B into TMEM with one 128x256b tcgen05.cp (a scale copy costs tensor-pipe
-    // time per instruction, not per byte).  That shape has no lane broadcast, so the re-tiled scale array holds each
+    // kWide: both scale atoms of B go into TMEM with one 128x256b tcgen05.cp (a scale copy costs tensor-pipe time per
+    // instruction, not per byte).  That shape has no lane broadcast, so the re-tiled scale array holds each
     // 512-byte atom four times, once per 32-lane quadrant: [atom][quadrant][32 lanes][16 B] per K step.
     static constexpr bool kWideSfb = kWide;
     static constexpr int kSfbBlocks = kWideSfb ? kSfbAtoms * 4 : kSfbAtoms;     // 512-byte blocks per K step
@@ -64,7 +64,7 @@ __device__ __forceinline__ void tma_load_2d_to_pair_bar(void* smem_dst, const CU
         : "memory");
 }
 
-template <int kBN, int kStages, int kAct, bool kWide = (kBN == 256)>
+template <int kBN, int kStages, int kAct, bool kWide = true>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,

@@ -150,7 +150,9 @@ static int choose_pair_tile_n(int M, int N, int sms) {
     return best;
 }
 
-static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl) {
+// `wide_scale_copy` = false keeps one copy of B's scale blocks (a quarter of the workspace, one more tensor-pipe copy
+// per K step); the allocation-free entry uses it when the replicated form does not fit its fixed array.
+static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scale_copy = true) {
     if (!a || a->struct_size != sizeof(blazeMxGemmArgs)) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->M < 0 || a->N < 0 || a->K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->b_elem != BLAZE_ELEM_E4M3 && a->b_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
@@ -173,7 +175,7 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl) {
     pl->n_tiles = (a->N + pl->tile_n - 1) / pl->tile_n;
     pl->k_steps = (a->K + 127) / 128;
     pl->sfa_bytes = (size_t)sf_tiled_bytes(a->M, a->K, 128);
-    pl->sfb_replicas = (pl->pair && pl->tile_n == 256) ? 4 : 1;      // the 256-wide kernel copies B's scales unbroadcast
+    pl->sfb_replicas = (pl->pair && wide_scale_copy) ? 4 : 1;        // the wide copy has no lane broadcast
     pl->sfb_bytes = (size_t)sf_tiled_bytes(a->N, a->K, pl->tile_n, pl->sfb_replicas);
     pl->b_expand_bytes = a->b_elem == BLAZE_ELEM_E2M1 ? (size_t)a->N * (size_t)a->K : 0;
     pl->sfa_off = 0;
@@ -225,13 +227,13 @@ static bool make_tmap_sf_blocks(CUtensorMap* map, const void* base, uint64_t blo
     return r == CUDA_SUCCESS;
 }
 
-template <int kBN, int kAct>
+template <int kBN, int kAct, bool kWide>
 static cudaError_t launch_mx_pair_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
                                            const CUtensorMap& tsb, const CUtensorMap& td, const MxGemmParams& p,
                                            int pairs, cudaStream_t stream) {
-    constexpr int kStages = kBN == 256 ? 5 : 6;      // the replicated scale block of the wide tile costs a stage
-    using L = MxPairSmem<kBN, kStages>;
-    auto kernel = mx_gemm_pair_kernel<kBN, kStages, kAct>;
+    constexpr int kStages = kWide ? 5 : 6;           // the replicated scale block costs a stage of shared memory
+    using L = MxPairSmem<kBN, kStages, kWide>;
+    auto kernel = mx_gemm_pair_kernel<kBN, kStages, kAct, kWide>;
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -242,6 +244,17 @@ static cudaError_t launch_mx_pair_instance(const CUtensorMap& ta, const CUtensor
     }
     kernel<<<2 * pairs, 192, L::kDynamicBytes, stream>>>(ta, tb, tsa, tsb, td, p);     // cluster of 2 set on the kernel
     return cudaGetLastError();
+}
+
+template <int kBN, bool kWide>
+static cudaError_t launch_mx_pair_act(int act, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
+                                      const CUtensorMap& tsb, const CUtensorMap& td, const MxGemmParams& p, int pairs,
+                                      cudaStream_t stream) {
+    switch (act) {
+        case BLAZE_ACT_RELU: return launch_mx_pair_instance<kBN, ACT_RELU, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
+        case BLAZE_ACT_GELU_TANH: return launch_mx_pair_instance<kBN, ACT_GELU_TANH, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
+        default: return launch_mx_pair_instance<kBN, ACT_IDENTITY, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
+    }
 }
 
 // Encodes the tensor maps and launches the GEMM kernel the plan chose.  `sfa_tiled` / `sfb_tiled` hold the re-tiled
@@ -280,18 +293,13 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
         int pairs = sms / 2;
         if (pairs < 1) pairs = 1;
         if (tiles < pairs) pairs = (int)tiles;
+        const bool wide = pl.sfb_replicas == 4;
         if (pl.tile_n == 256) {
-            switch (a->activation) {
-                case BLAZE_ACT_RELU: e = launch_mx_pair_instance<256, ACT_RELU>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
-                case BLAZE_ACT_GELU_TANH: e = launch_mx_pair_instance<256, ACT_GELU_TANH>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
-                default: e = launch_mx_pair_instance<256, ACT_IDENTITY>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
-            }
+            e = wide ? launch_mx_pair_act<256, true>(a->activation, ta, tb, tsa, tsb, td, p, pairs, stream)
+                     : launch_mx_pair_act<256, false>(a->activation, ta, tb, tsa, tsb, td, p, pairs, stream);
         } else {
-            switch (a->activation) {
-                case BLAZE_ACT_RELU: e = launch_mx_pair_instance<224, ACT_RELU>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
-                case BLAZE_ACT_GELU_TANH: e = launch_mx_pair_instance<224, ACT_GELU_TANH>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
-                default: e = launch_mx_pair_instance<224, ACT_IDENTITY>(ta, tb, tsa, tsb, td, p, pairs, stream); break;
-            }
+            e = wide ? launch_mx_pair_act<224, true>(a->activation, ta, tb, tsa, tsb, td, p, pairs, stream)
+                     : launch_mx_pair_act<224, false>(a->activation, ta, tb, tsa, tsb, td, p, pairs, stream);
         }
         return status_of(e);
     }
@@ -687,14 +695,9 @@ extern "C" int blazeMxGemmNoAlloc(const blazeMxGemmArgs* a, int32_t* device_stat
     MxPlan pl;
     st = plan_mx(a, nd->sm_count, &pl);
     if (st != ACLTENSOR_STATUS_SUCCESS) return st;
-    blazeMxGemmArgs narrow;
-    if (pl.total > kNoAllocScratchBytes && a->tile_n == 0 && pl.tile_n == 256) {
-        // the 256-wide tiles keep four copies of B's scale blocks; the 224-wide ones need a quarter of that
-        narrow = *a;
-        narrow.tile_n = 224;
-        narrow.cta_pair = 2;
-        a = &narrow;
-        st = plan_mx(a, nd->sm_count, &pl);
+    if (pl.total > kNoAllocScratchBytes) {
+        // four copies of B's scale blocks do not fit the array: keep one copy (one more scale copy per K step)
+        st = plan_mx(a, nd->sm_count, &pl, false);
         if (st != ACLTENSOR_STATUS_SUCCESS) return st;
     }
     if (a->b_elem != BLAZE_ELEM_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;      // packed E2M1 needs an N x K expansion buffer

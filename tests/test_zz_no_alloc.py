@@ -68,6 +68,14 @@ def test_no_alloc_entry_matches_regular_entry_twice(cuda_device):
     assert torch.cuda.memory_allocated() <= allocated + (1 << 20)
 
 
+def test_no_alloc_entry_keeps_one_scale_copy_when_four_do_not_fit(cuda_device):
+    """M=256, N=K=8192: four copies of the weight's re-tiled scale blocks (what the regular entry uses on 2-CTA tiles)
+    need over 8 MiB, one copy needs 2 MiB; the allocation-free entry takes the second form and returns the same bits."""
+    problem = _problem(cuda_device, 33, 256, 8192, 8192, with_bias=True)
+    out = _run_both(cuda_device, *problem, activation=native.ACT_RELU)
+    assert bool((out.float() >= 0).all())
+
+
 def test_no_alloc_entry_refuses_what_does_not_fit(cuda_device):
     """Too large for the 8 MiB array, or needing an expansion buffer: refused before any launch."""
     a = native.MxGemmArgs()
