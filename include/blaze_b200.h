@@ -102,6 +102,27 @@ BLAZE_API int blazeMxGemm(const blazeMxGemmArgs* args, void* stream);
  */
 BLAZE_API int blazeMxGemmNoAlloc(const blazeMxGemmArgs* args, int32_t* device_status, void* stream);
 
+/*
+ * Batched MX GEMM with broadcast: D[b] = act(A[ia(b)] x B[ib(b)]^T + bias) + residual[b] over up to four batch
+ * dimensions, the loop nest of GemmUniversal<...>::ProcessWithBatch (include/blaze/gemm/kernel/kernel_qbmm_mx.h:282-338)
+ * with the per-batch offsets of AddBatchOffset (:340-377).  c[] are the batch extents of D (outermost first, 1 for an
+ * unused dimension); a[i] and b[i] are c[i], or 1 when that operand is broadcast along dimension i.  Every operand is
+ * packed batch after batch: A[prod(a)][M][lda], scaleA[prod(a)][M][ceil(K/64)*2], B[prod(b)][N][ldb], scaleB likewise,
+ * D and residual [prod(c)][M][ldd / ldr], bias [N] or, with bias_per_batch, [prod(c)][N].  `args` describes one
+ * batch.  When B is the same for every batch and A is not broadcast, the batches are rows of one tall GEMM and run as
+ * a single launch; otherwise one launch per batch on `stream`, sharing the workspace.
+ */
+typedef struct {
+    int32_t c[4];
+    int32_t a[4];
+    int32_t b[4];
+    int32_t bias_per_batch;
+    int32_t reserved;
+} blazeBatchDims;
+
+BLAZE_API int blazeMxGemmBatchedWorkspaceSize(const blazeMxGemmArgs* args, const blazeBatchDims* batch, size_t* bytes);
+BLAZE_API int blazeMxGemmBatched(const blazeMxGemmArgs* args, const blazeBatchDims* batch, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------------
  * FP8 GEMM with float32 scales (1x128 groups of A, 128x128 blocks of B), dense or grouped, data-parallel or
  * stream-K.  D = act(sum_kb sa*sb*(A_kb x B_kb^T) + bias) + residual, bf16 output.

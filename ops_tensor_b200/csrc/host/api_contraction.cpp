@@ -61,11 +61,23 @@ void fill_mx_args(const acltensorOperationDescriptor& op, blazeMxGemmArgs* a) {
     a->cta_pair = op.ctaPair;
 }
 
+void fill_batch(const acltensorOperationDescriptor& op, blazeBatchDims* b) {
+    std::memset(b, 0, sizeof(*b));
+    for (int i = 0; i < 4; ++i) {
+        b->c[i] = op.batchC[i];
+        b->a[i] = op.batchA[i];
+        b->b[i] = op.batchB[i];
+    }
+    b->bias_per_batch = op.biasPerBatch;
+}
+
 acltensorStatus_t MxWorkspace(const acltensorOperationDescriptor& op, int32_t, uint64_t* bytes) {
     blazeMxGemmArgs a;
     fill_mx_args(op, &a);
     size_t n = 0;
-    const int st = blazeMxGemmWorkspaceSize(&a, &n);
+    blazeBatchDims bd;
+    fill_batch(op, &bd);
+    const int st = op.batchModes > 0 ? blazeMxGemmBatchedWorkspaceSize(&a, &bd, &n) : blazeMxGemmWorkspaceSize(&a, &n);
     *bytes = n;
     return static_cast<acltensorStatus_t>(st);
 }
@@ -83,6 +95,11 @@ acltensorStatus_t MxExecute(const ContractionArgs& c) {
     a.reuse_b_prepass = c.reuseBPrepass ? 1 : 0;
     a.workspace = c.workspace;
     a.workspace_bytes = c.workspaceSize;
+    if (c.op->batchModes > 0) {
+        blazeBatchDims bd;
+        fill_batch(*c.op, &bd);
+        return static_cast<acltensorStatus_t>(blazeMxGemmBatched(&a, &bd, c.stream));
+    }
     return static_cast<acltensorStatus_t>(blazeMxGemm(&a, c.stream));
 }
 
@@ -105,6 +122,7 @@ void fill_fp8_args(const acltensorOperationDescriptor& op, int32_t splitPolicy, 
 }
 
 acltensorStatus_t Fp8Workspace(const acltensorOperationDescriptor& op, int32_t splitPolicy, uint64_t* bytes) {
+    if (op.batchModes > 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;          // batch broadcast is an MX feature
     blazeFp8GemmArgs a;
     fill_fp8_args(op, splitPolicy, &a);
     size_t n = 0;
@@ -159,12 +177,28 @@ acltensorStatus_t acltensorCreateContraction(const acltensorHandle_t handle, acl
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (descD->dataType != ACLTENSOR_R_16BF) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (descC != nullptr && descC->dataType != ACLTENSOR_R_16BF) return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    if (descA->numModes != 2 || descD->numModes != 2 || (descB->numModes != 2 && descB->numModes != 3))
+    // D = [batch..., m, n] with up to four batch modes; A = [its batch modes..., m, k]; B = [its batch modes..., n, k]
+    // or, without batch modes in D, [group, n, k].  A batch mode missing from an operand is a broadcast.
+    if (descD->numModes < 2 || descD->numModes > 6 || descA->numModes < 2 || descB->numModes < 2)
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    if (descC != nullptr && descC->numModes != 2) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    const uint32_t nBatch = descD->numModes - 2;
+    std::vector<int32_t> fullA(modeA, modeA + descA->numModes), fullB(modeB, modeB + descB->numModes),
+        fullD(modeD, modeD + descD->numModes);
+    const std::vector<int32_t> batchLabels(fullD.begin(), fullD.begin() + nBatch);
+    const bool groupedB = nBatch == 0 && descB->numModes == 3;
+    const uint32_t leadA = descA->numModes - 2, leadB = groupedB ? 0 : descB->numModes - 2;
+    if (leadA > nBatch || leadB > nBatch) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (descC != nullptr && descC->numModes != descD->numModes) return ACLTENSOR_STATUS_NOT_SUPPORTED;
 
-    std::vector<int32_t> mA(modeA, modeA + descA->numModes), mB(modeB, modeB + descB->numModes),
-        mD(modeD, modeD + descD->numModes);
+    // the two innermost modes of every tensor are the matrix modes
+    std::vector<int32_t> mA(fullA.begin() + leadA, fullA.end()), mB(fullB.begin() + leadB, fullB.end()),
+        mD(fullD.begin() + nBatch, fullD.end());
+    const int64_t* lensA = descA->lens.data() + leadA;
+    const int64_t* stridesA = descA->strides.data() + leadA;
+    const int64_t* lensB = descB->lens.data() + leadB;
+    const int64_t* stridesB = descB->strides.data() + leadB;
+    const int64_t* lensD = descD->lens.data() + nBatch;
+    const int64_t* stridesD = descD->strides.data() + nBatch;
     const int32_t mLabel = mD[0], nLabel = mD[1];
     if (mLabel == nLabel) return ACLTENSOR_STATUS_INVALID_VALUE;
     const int aM = find_mode(mA, mLabel);
@@ -175,29 +209,61 @@ acltensorStatus_t acltensorCreateContraction(const acltensorHandle_t handle, acl
     const int bN = find_mode(mB, nLabel), bK = find_mode(mB, kLabel);
     if (bN < 0 || bK < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
     int bG = -1;
-    if (descB->numModes == 3) {
+    if (groupedB) {
         bG = 3 - bN - bK;
         if (mB[bG] == mLabel || mB[bG] == nLabel || mB[bG] == kLabel) return ACLTENSOR_STATUS_INVALID_VALUE;
     }
-    const int64_t M = descD->lens[0], N = descD->lens[1], K = descA->lens[aK];
-    if (descA->lens[aM] != M || descB->lens[bN] != N || descB->lens[bK] != K) return ACLTENSOR_STATUS_INVALID_VALUE;
+    const int64_t M = lensD[0], N = lensD[1], K = lensA[aK];
+    if (lensA[aM] != M || lensB[bN] != N || lensB[bK] != K) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (!fits_int32(M) || !fits_int32(N) || !fits_int32(K)) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     // K must be the contiguous mode of both operands, n the contiguous mode of the output
-    if (descA->strides[aK] != 1 || descB->strides[bK] != 1 || descD->strides[1] != 1)
-        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (stridesA[aK] != 1 || stridesB[bK] != 1 || stridesD[1] != 1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (descC != nullptr) {
-        if (modeC[0] != mLabel || modeC[1] != nLabel) return ACLTENSOR_STATUS_INVALID_VALUE;
-        if (descC->lens[0] != M || descC->lens[1] != N) return ACLTENSOR_STATUS_INVALID_VALUE;
-        if (descC->strides[1] != 1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+        for (uint32_t i = 0; i < descD->numModes; ++i) {
+            if (modeC[i] != fullD[i] || descC->lens[i] != descD->lens[i]) return ACLTENSOR_STATUS_INVALID_VALUE;
+        }
+        if (descC->strides[nBatch + 1] != 1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     }
     int64_t groupStride = 0;
     int32_t groups = 0;
     if (bG >= 0) {
         if (bG != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;                 // group must be the outermost mode
-        groups = static_cast<int32_t>(descB->lens[bG]);
-        groupStride = descB->strides[bG];
-        if (groupStride != N * descB->strides[bN]) return ACLTENSOR_STATUS_NOT_SUPPORTED;   // groups back to back
+        groups = static_cast<int32_t>(lensB[bG]);
+        groupStride = stridesB[bG];
+        if (groupStride != N * stridesB[bN]) return ACLTENSOR_STATUS_NOT_SUPPORTED;   // groups back to back
         if (descB->dataType != ACLTENSOR_R_8F_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    }
+
+    // batch extents, right-aligned in four slots; every tensor must be packed batch after batch
+    int32_t batchC[4] = {1, 1, 1, 1}, batchA[4] = {1, 1, 1, 1}, batchB[4] = {1, 1, 1, 1};
+    if (nBatch > 0) {
+        if (aM != 0 || bN != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;      // [.., m, k] and [.., n, k] only
+        auto walk = [&](const acltensorTensorDescriptor_t t, const std::vector<int32_t>& modes, uint32_t lead,
+                        int32_t* out) -> acltensorStatus_t {
+            int64_t expect = t->lens[lead] * t->strides[lead];              // rows x row pitch of one matrix
+            uint32_t next = nBatch;                                         // batch labels must keep D's order
+            for (int i = static_cast<int>(lead) - 1; i >= 0; --i) {
+                int pos = -1;
+                for (uint32_t j = 0; j < next; ++j)
+                    if (batchLabels[j] == modes[i]) pos = static_cast<int>(j);
+                if (pos < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
+                if (t->lens[i] != descD->lens[pos]) return ACLTENSOR_STATUS_INVALID_VALUE;
+                if (t->strides[i] != expect) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+                if (!fits_int32(t->lens[i])) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+                expect *= t->lens[i];
+                out[4 - nBatch + pos] = static_cast<int32_t>(t->lens[i]);
+                next = static_cast<uint32_t>(pos);
+            }
+            return ACLTENSOR_STATUS_SUCCESS;
+        };
+        acltensorStatus_t st = walk(descD, fullD, nBatch, batchC);
+        if (st == ACLTENSOR_STATUS_SUCCESS) st = walk(descA, fullA, leadA, batchA);
+        if (st == ACLTENSOR_STATUS_SUCCESS) st = walk(descB, fullB, leadB, batchB);
+        if (st == ACLTENSOR_STATUS_SUCCESS && descC != nullptr) {
+            int32_t batchR[4] = {1, 1, 1, 1};
+            st = walk(descC, fullD, nBatch, batchR);
+        }
+        if (st != ACLTENSOR_STATUS_SUCCESS) return st;
     }
 
     acltensorOperationDescriptor* d = new (std::nothrow) acltensorOperationDescriptor();
@@ -207,10 +273,16 @@ acltensorStatus_t acltensorCreateContraction(const acltensorHandle_t handle, acl
     d->descB = descB;
     d->descC = descC;
     d->descD = descD;
-    d->modeA = mA;
-    d->modeB = mB;
-    d->modeD = mD;
-    if (descC != nullptr) d->modeC.assign(modeC, modeC + 2);
+    d->modeA = fullA;
+    d->modeB = fullB;
+    d->modeD = fullD;
+    if (descC != nullptr) d->modeC.assign(modeC, modeC + descC->numModes);
+    d->batchModes = static_cast<int32_t>(nBatch);
+    for (int i = 0; i < 4; ++i) {
+        d->batchC[i] = batchC[i];
+        d->batchA[i] = batchA[i];
+        d->batchB[i] = batchB[i];
+    }
     d->opA = opA;
     d->opB = opB;
     d->opC = opC;
@@ -218,10 +290,10 @@ acltensorStatus_t acltensorCreateContraction(const acltensorHandle_t handle, acl
     d->M = M;
     d->N = N;
     d->K = K;
-    d->lda = descA->strides[aM];
-    d->ldb = descB->strides[bN];
-    d->ldc = descC ? descC->strides[0] : 0;
-    d->ldd = descD->strides[0];
+    d->lda = stridesA[aM];
+    d->ldb = stridesB[bN];
+    d->ldc = descC ? descC->strides[nBatch] : 0;
+    d->ldd = stridesD[0];
     d->groupStrideB = groupStride;
     d->groupCount = groups;
     *desc = d;
@@ -242,6 +314,7 @@ int32_t* attribute_slot(acltensorOperationDescriptor* d, acltensorOperationDescr
         case ACLTENSOR_OPERATION_DESCRIPTOR_SM_LIMIT: return &d->smLimit;
         case ACLTENSOR_OPERATION_DESCRIPTOR_B_IS_STATIC: return &d->bIsStatic;
         case ACLTENSOR_OPERATION_DESCRIPTOR_CTA_PAIR: return &d->ctaPair;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_BIAS_PER_BATCH: return &d->biasPerBatch;
         default: return nullptr;
     }
 }
@@ -287,6 +360,9 @@ acltensorStatus_t acltensorOperationDescriptorSetAttribute(const acltensorHandle
         case ACLTENSOR_OPERATION_DESCRIPTOR_CTA_PAIR:
             if (v < 0 || v > 2) return ACLTENSOR_STATUS_INVALID_VALUE;
             break;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_BIAS_PER_BATCH:
+            if (v < 0 || v > 1) return ACLTENSOR_STATUS_INVALID_VALUE;
+            break;
         default:
             break;
     }
@@ -313,7 +389,9 @@ acltensorStatus_t acltensorOperationDescriptorGetAttribute(const acltensorHandle
 namespace {
 
 std::shared_ptr<ContractionSolution> solution_for(const acltensorOperationDescriptor& op) {
-    ContractionUid uid{op.descA->dataType, op.descB->dataType, op.scaleModeA, op.scaleModeB, op.descB->numModes};
+    // the registry keys on "B carries a group mode" (3) or not (2); batch modes do not change the solution
+    ContractionUid uid{op.descA->dataType, op.descB->dataType, op.scaleModeA, op.scaleModeB,
+                       op.groupCount > 0 ? 3u : 2u};
     return ContractionSolutionRegistry::instance().getSolution(uid);
 }
 

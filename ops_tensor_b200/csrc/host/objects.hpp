@@ -100,6 +100,9 @@ struct acltensorOperationDescriptor {
     int64_t M = 0, N = 0, K = 0;
     int64_t lda = 0, ldb = 0, ldc = 0, ldd = 0;       // elements
     int64_t groupStrideB = 0;                         // elements between consecutive groups of B
+    int32_t batchModes = 0;                           // leading batch modes of D (0..4)
+    int32_t batchC[4] = {1, 1, 1, 1}, batchA[4] = {1, 1, 1, 1}, batchB[4] = {1, 1, 1, 1};   // right-aligned extents
+    int32_t biasPerBatch = 0;                         // bias is [batches][N] instead of [N]
 
     size_t getTotalElements() const { return descD ? descD->totalElements : 0; }
     acltensorDataType_t getDataType() const { return descD ? descD->dataType : ACLTENSOR_R_32F; }

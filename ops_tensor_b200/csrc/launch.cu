@@ -378,6 +378,94 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
     return run_mx_kernel(a, pl, sfa_tiled, sfb_tiled, b_codes, b_pitch, ctx->status_word, ctx->sm_count, stream);
 }
 
+// ------------------------------------------------------------------------------------------------ batched MX GEMM
+
+namespace blaze {
+
+struct BatchWalk {
+    long long count_c, count_a, count_b;
+    bool folds;          // all batches are rows of one GEMM
+};
+
+static int check_batch(const blazeMxGemmArgs* a, const blazeBatchDims* bd, BatchWalk* w) {
+    if (!a || !bd || a->struct_size != sizeof(blazeMxGemmArgs)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    w->count_c = w->count_a = w->count_b = 1;
+    bool a_full = true, b_one = true;
+    for (int i = 0; i < 4; ++i) {
+        if (bd->c[i] < 1 || bd->a[i] < 1 || bd->b[i] < 1) return ACLTENSOR_STATUS_INVALID_VALUE;
+        if ((bd->a[i] != bd->c[i] && bd->a[i] != 1) || (bd->b[i] != bd->c[i] && bd->b[i] != 1))
+            return ACLTENSOR_STATUS_INVALID_VALUE;
+        w->count_c *= bd->c[i];
+        w->count_a *= bd->a[i];
+        w->count_b *= bd->b[i];
+        a_full = a_full && bd->a[i] == bd->c[i];
+        b_one = b_one && bd->b[i] == 1;
+    }
+    if (w->count_c > 0x7fffffffLL) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    // one tall GEMM: same weight for every batch, one A per batch, one bias, rows of consecutive batches adjacent
+    w->folds = a_full && b_one && !bd->bias_per_batch && w->count_c * (long long)a->M <= 0x7fffffffLL;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+}  // namespace blaze
+
+extern "C" int blazeMxGemmBatchedWorkspaceSize(const blazeMxGemmArgs* args, const blazeBatchDims* batch, size_t* bytes) {
+    if (!bytes) return ACLTENSOR_STATUS_INVALID_VALUE;
+    BatchWalk w;
+    const int st = check_batch(args, batch, &w);
+    if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    blazeMxGemmArgs one = *args;
+    if (w.folds) one.M = (int32_t)(w.count_c * args->M);
+    return blazeMxGemmWorkspaceSize(&one, bytes);
+}
+
+extern "C" int blazeMxGemmBatched(const blazeMxGemmArgs* args, const blazeBatchDims* bd, void* stream) {
+    BatchWalk w;
+    int st = check_batch(args, bd, &w);
+    if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    blazeMxGemmArgs one = *args;
+    if (w.folds) {
+        one.M = (int32_t)(w.count_c * args->M);
+        return blazeMxGemm(&one, stream);
+    }
+    const int64_t scale_cols = ((int64_t)(args->K + 63) / 64) * 2;
+    const int64_t a_bytes = (int64_t)args->M * args->lda, sa_bytes = (int64_t)args->M * scale_cols;
+    const int64_t b_bytes = (int64_t)args->N * args->ldb, sb_bytes = (int64_t)args->N * scale_cols;
+    const int64_t d_bytes = (int64_t)args->M * args->ldd * 2, r_bytes = (int64_t)args->M * args->ldr * 2;
+    // strides of the operands' own batch spaces, innermost dimension last
+    long long stride_a[4], stride_b[4];
+    long long sa = 1, sb = 1;
+    for (int i = 3; i >= 0; --i) {
+        stride_a[i] = bd->a[i] == 1 ? 0 : sa;
+        stride_b[i] = bd->b[i] == 1 ? 0 : sb;
+        sa *= bd->a[i];
+        sb *= bd->b[i];
+    }
+    long long last_ib = -1;
+    long long ic = 0;
+    for (int i0 = 0; i0 < bd->c[0]; ++i0)
+        for (int i1 = 0; i1 < bd->c[1]; ++i1)
+            for (int i2 = 0; i2 < bd->c[2]; ++i2)
+                for (int i3 = 0; i3 < bd->c[3]; ++i3, ++ic) {
+                    const long long ia = i0 * stride_a[0] + i1 * stride_a[1] + i2 * stride_a[2] + i3 * stride_a[3];
+                    const long long ib = i0 * stride_b[0] + i1 * stride_b[1] + i2 * stride_b[2] + i3 * stride_b[3];
+                    one.A = static_cast<const uint8_t*>(args->A) + ia * a_bytes;
+                    one.scaleA = static_cast<const uint8_t*>(args->scaleA) + ia * sa_bytes;
+                    one.B = static_cast<const uint8_t*>(args->B) + ib * b_bytes;
+                    one.scaleB = static_cast<const uint8_t*>(args->scaleB) + ib * sb_bytes;
+                    one.D = static_cast<uint8_t*>(args->D) + ic * d_bytes;
+                    if (args->residual) one.residual = static_cast<const uint8_t*>(args->residual) + ic * r_bytes;
+                    if (args->bias && bd->bias_per_batch)
+                        one.bias = static_cast<const uint8_t*>(args->bias) + ic * (int64_t)args->N * 2;
+                    // the workspace keeps the weight's pre-pass of the batch before: reuse it while B stays the same
+                    one.reuse_b_prepass = (ib == last_ib || (ic == 0 && args->reuse_b_prepass)) ? 1 : 0;
+                    st = blazeMxGemm(&one, stream);
+                    if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+                    last_ib = ib;
+                }
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
 // ------------------------------------------------------------------------------------------------ FP8 GEMM
 
 namespace blaze {

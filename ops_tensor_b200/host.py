@@ -21,7 +21,7 @@ WORKSPACE_MIN, WORKSPACE_DEFAULT, WORKSPACE_MAX = 1, 2, 3
 SCALE_NONE, SCALE_MX_E8M0_VEC32, SCALE_FP32_1X128, SCALE_FP32_128X128 = 0, 1, 2, 3
 SPLIT_AUTO, SPLIT_DATA_PARALLEL, SPLIT_STREAM_K = 0, 1, 2
 (ATTR_SCALE_MODE_A, ATTR_SCALE_MODE_B, ATTR_EPILOGUE_ACT, ATTR_BIAS_TYPE, ATTR_GROUP_COUNT, ATTR_SPLIT_POLICY,
- ATTR_TILE_N, ATTR_SM_LIMIT, ATTR_B_IS_STATIC, ATTR_CTA_PAIR) = range(1, 11)
+ ATTR_TILE_N, ATTR_SM_LIMIT, ATTR_B_IS_STATIC, ATTR_CTA_PAIR, ATTR_BIAS_PER_BATCH) = range(1, 12)
 
 STATUS_SUCCESS = 0
 STATUS_NOT_INITIALIZED = 1
@@ -178,11 +178,14 @@ class Contraction:
 
     a_shape = (M, K); b_shape = (N, K) or (G, N, K); scale modes choose the kernel family:
     (MX, MX) -> block-scaled MX GEMM; (FP32_1X128, FP32_128X128) -> FP8 GEMM (dense, stream-K or grouped).
+    `batch` = extents of up to four leading batch modes of D; `batch_a` / `batch_b` say which of them A and B carry
+    (True) or broadcast over (False); all tensors are packed batch after batch (MX only).
     """
 
     def __init__(self, M, N, K, *, scale_mode_a, scale_mode_b, b_dtype=R_8F_E4M3, groups=0, activation=OP_IDENTITY,
                  bias=False, residual=False, split=SPLIT_AUTO, tile_n=0, sm_limit=0, b_is_static=False, cta_pair=0,
-                 lda=None, ldb=None, ldd=None, ldc=None, workspace_limit=2 ** 62):
+                 lda=None, ldb=None, ldd=None, ldc=None, workspace_limit=2 ** 62, batch=(), batch_a=None, batch_b=None,
+                 bias_per_batch=False):
         self.M, self.N, self.K, self.groups = M, N, K, groups
         self.handle = create_handle()
         self._descs = []
@@ -190,20 +193,45 @@ class Contraction:
         lda = lda or K
         ldb = ldb or K
         ldd = ldd or N
-        self.dA = create_tensor_descriptor(self.handle, [M, K], [lda, 1], R_8F_E4M3)
+        ldc = ldc or N
+        batch = list(batch)
+        labels = [10 + i for i in range(len(batch))]
+        batch_a = [True] * len(batch) if batch_a is None else list(batch_a)
+        batch_b = [False] * len(batch) if batch_b is None else list(batch_b)
+
+        def packed(dims, keep, rows, pitch):
+            """lens, strides and modes of [kept batch dims..., rows, cols] packed batch after batch."""
+            lens = [d for d, kp in zip(dims, keep) if kp]
+            modes = [l for l, kp in zip(labels, keep) if kp]
+            strides, step = [], rows * pitch
+            for d in reversed(lens):
+                strides.insert(0, step)
+                step *= d
+            return lens, strides, modes
+
+        la, sa, ma = packed(batch, batch_a, M, lda)
+        self.dA = create_tensor_descriptor(self.handle, la + [M, K], sa + [lda, 1], R_8F_E4M3)
         if groups:
             self.dB = create_tensor_descriptor(self.handle, [groups, N, K], [N * ldb, ldb, 1], b_dtype)
             mode_b = i32([g, n, k])
         else:
-            self.dB = create_tensor_descriptor(self.handle, [N, K], [ldb, 1], b_dtype)
-            mode_b = i32([n, k])
-        self.dD = create_tensor_descriptor(self.handle, [M, N], [ldd, 1], R_16BF)
-        self.dC = create_tensor_descriptor(self.handle, [M, N], [ldc or N, 1], R_16BF) if residual else None
+            lb, sb, mb = packed(batch, batch_b, N, ldb)
+            self.dB = create_tensor_descriptor(self.handle, lb + [N, K], sb + [ldb, 1], b_dtype)
+            mode_b = i32(mb + [n, k])
+        ld_, sd, md = packed(batch, [True] * len(batch), M, ldd)
+        self.dD = create_tensor_descriptor(self.handle, ld_ + [M, N], sd + [ldd, 1], R_16BF)
+        self.dC = None
+        if residual:
+            lc, sc, _ = packed(batch, [True] * len(batch), M, ldc)
+            self.dC = create_tensor_descriptor(self.handle, lc + [M, N], sc + [ldc, 1], R_16BF)
         self.op, self.pref, self.plan = C.c_void_p(), C.c_void_p(), C.c_void_p()
-        check(api.acltensorCreateContraction(self.handle, C.byref(self.op), self.dA, i32([m, k]), OP_IDENTITY, self.dB,
-                                             mode_b, OP_IDENTITY, self.dC, i32([m, n]) if residual else None,
-                                             OP_IDENTITY, self.dD, i32([m, n]), COMPUTE_DESC_32F),
+        check(api.acltensorCreateContraction(self.handle, C.byref(self.op), self.dA, i32(ma + [m, k]), OP_IDENTITY,
+                                             self.dB, mode_b, OP_IDENTITY, self.dC,
+                                             i32(md + [m, n]) if residual else None, OP_IDENTITY, self.dD,
+                                             i32(md + [m, n]), COMPUTE_DESC_32F),
               "acltensorCreateContraction")
+        if bias_per_batch:
+            set_attribute(self.handle, self.op, ATTR_BIAS_PER_BATCH, 1)
         set_attribute(self.handle, self.op, ATTR_SCALE_MODE_A, scale_mode_a)
         set_attribute(self.handle, self.op, ATTR_SCALE_MODE_B, scale_mode_b)
         set_attribute(self.handle, self.op, ATTR_EPILOGUE_ACT, activation)

@@ -47,6 +47,12 @@ class MxGemmArgs(C.Structure):
     ]
 
 
+class BatchDims(C.Structure):
+    """blazeBatchDims: batch extents of D, A and B (outermost first, 1 = unused or broadcast)."""
+    _fields_ = [("c", C.c_int32 * 4), ("a", C.c_int32 * 4), ("b", C.c_int32 * 4), ("bias_per_batch", C.c_int32),
+                ("reserved", C.c_int32)]
+
+
 class Fp8GemmArgs(C.Structure):
     _fields_ = [
         ("struct_size", C.c_size_t),
@@ -94,6 +100,10 @@ def _declare(l: C.CDLL) -> None:
     l.blazeMxGemm.argtypes = [C.POINTER(MxGemmArgs), C.c_void_p]
     l.blazeMxGemmNoAlloc.argtypes = [C.POINTER(MxGemmArgs), C.c_void_p, C.c_void_p]
     l.blazeMxGemmNoAlloc.restype = C.c_int
+    l.blazeMxGemmBatchedWorkspaceSize.argtypes = [C.POINTER(MxGemmArgs), C.POINTER(BatchDims), C.POINTER(C.c_size_t)]
+    l.blazeMxGemmBatchedWorkspaceSize.restype = C.c_int
+    l.blazeMxGemmBatched.argtypes = [C.POINTER(MxGemmArgs), C.POINTER(BatchDims), C.c_void_p]
+    l.blazeMxGemmBatched.restype = C.c_int
     l.blazeFp8GemmWorkspaceSize.argtypes = [C.POINTER(Fp8GemmArgs), C.POINTER(C.c_size_t)]
     l.blazeFp8Gemm.argtypes = [C.POINTER(Fp8GemmArgs), C.c_void_p]
     l.blazeQuantizeMx.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int64,

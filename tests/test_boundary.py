@@ -303,3 +303,44 @@ def test_benchmark_generators_match_the_oracle():
     assert np.array_equal(s.normal_f32(2, 0, (5, 64), 1.0), o.normal_f32(2, 0, (5, 64), 1.0))
     assert np.array_equal(s.normal_f32(5, 1, (3, 128), 0.02), o.normal_f32(5, 1, (3, 128), 0.02))
     assert np.array_equal(s.moe_group_rows(), o.moe_group_rows())
+
+
+def test_batched_contraction_descriptor_rules(built_library):
+    """Batch modes of D with broadcast operands (the loop nest of kernel_qbmm_mx.h:282-338): accepted when every tensor
+    is packed batch after batch; a batch mode D does not have, a wrong extent or a gap between batches is refused."""
+    MX = H.SCALE_MX_E8M0_VEC32
+    # A per batch, B broadcast; A broadcast over the outer batch dim, B batched over the inner one
+    for kw in (dict(batch=(3,)), dict(batch=(2, 3), batch_a=(False, True), batch_b=(False, True)),
+               dict(batch=(2, 1, 2, 2), batch_a=(True, True, True, True), batch_b=(True, False, False, True))):
+        with H.Contraction(64, 72, 128, scale_mode_a=MX, scale_mode_b=MX, **kw) as c:
+            assert c.workspace_bytes > 0
+    h = H.create_handle()
+    dA = H.create_tensor_descriptor(h, [3, 64, 128], [64 * 128, 128, 1], H.R_8F_E4M3)
+    dB = H.create_tensor_descriptor(h, [72, 128], [128, 1], H.R_8F_E4M3)
+    dD = H.create_tensor_descriptor(h, [3, 64, 72], [64 * 72, 72, 1], H.R_16BF)
+    dD_gap = H.create_tensor_descriptor(h, [3, 64, 72], [64 * 72 + 8, 72, 1], H.R_16BF)
+    dA_bad = H.create_tensor_descriptor(h, [4, 64, 128], [64 * 128, 128, 1], H.R_8F_E4M3)
+    op = C.c_void_p()
+    args = lambda a, ma, d, md: (h, C.byref(op), a, H.i32(ma), H.OP_IDENTITY, dB, H.i32([1, 2]), H.OP_IDENTITY, None,
+                                 None, H.OP_IDENTITY, d, H.i32(md), H.COMPUTE_DESC_32F)
+    assert H.api.acltensorCreateContraction(*args(dA, [10, 0, 2], dD, [10, 0, 1])) == H.STATUS_SUCCESS
+    H.api.acltensorDestroyOperationDescriptor(op)
+    assert H.api.acltensorCreateContraction(*args(dA, [11, 0, 2], dD, [10, 0, 1])) == H.STATUS_INVALID_VALUE
+    assert H.api.acltensorCreateContraction(*args(dA_bad, [10, 0, 2], dD, [10, 0, 1])) == H.STATUS_INVALID_VALUE
+    assert H.api.acltensorCreateContraction(*args(dA, [10, 0, 2], dD_gap, [10, 0, 1])) == H.STATUS_NOT_SUPPORTED
+    for d in (dA, dB, dD, dD_gap, dA_bad):
+        H.api.acltensorDestroyTensorDescriptor(d)
+    H.api.acltensorDestroy(h)
+    # the C ABI refuses batch extents that are neither the output's nor 1
+    bd = native.BatchDims()
+    for i in range(4):
+        bd.c[i], bd.a[i], bd.b[i] = 1, 1, 1
+    bd.c[3], bd.a[3], bd.b[3] = 4, 2, 1
+    a = native.MxGemmArgs()
+    a.struct_size = C.sizeof(a)
+    a.M = a.N = a.K = 128
+    n = C.c_size_t(0)
+    assert native.lib().blazeMxGemmBatchedWorkspaceSize(C.byref(a), C.byref(bd), C.byref(n)) == H.STATUS_INVALID_VALUE
+    bd.a[3] = 4
+    assert native.lib().blazeMxGemmBatchedWorkspaceSize(C.byref(a), C.byref(bd), C.byref(n)) == H.STATUS_SUCCESS
+    assert n.value > 0

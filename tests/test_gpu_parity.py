@@ -337,6 +337,40 @@ def test_w4a8_mx(cuda_device, M, N, K):
     assert_gemm_ok(got, ref, gold)
 
 
+@pytest.mark.parametrize("batch,batch_a,batch_b,per_batch_bias", [
+    ((3,), (True,), (False,), False),                      # one weight for all batches: runs as one tall GEMM
+    ((2, 3), (False, True), (True, False), True),          # A broadcast over the outer, B over the inner dimension
+    ((2, 1, 2, 2), (True, True, True, True), (True, False, False, True), False),
+])
+def test_mx_batched_broadcast(cuda_device, batch, batch_a, batch_b, per_batch_bias):
+    """Batched MX GEMM with numpy-style broadcast of either operand over up to four batch dimensions
+    (include/blaze/gemm/kernel/kernel_qbmm_mx.h:282-377)."""
+    import torch
+    M, N, K = 136, 264, 160
+    dims_a = [d if k else 1 for d, k in zip(batch, batch_a)]
+    dims_b = [d if k else 1 for d, k in zip(batch, batch_b)]
+    na, nb, nc = int(np.prod(dims_a)), int(np.prod(dims_b)), int(np.prod(batch))
+    a = o.normal_f32(24, 0, (na * M, K), 1.0)
+    w = o.normal_f32(24, 1, (nb * N, K), 1.0)
+    bias = o.normal_f32(24, 2, (nc if per_batch_bias else 1, N), 0.5)
+    residual = o.normal_f32(24, 3, (nc * M, N), 1.0)
+    qa, sa = H.quantize(dev_tensor(a, cuda_device), H.SCALE_MX_E8M0_VEC32)
+    qb, sb = H.quantize(dev_tensor(w, cuda_device), H.SCALE_MX_E8M0_VEC32)
+    out = torch.full((nc * M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    with H.Contraction(M, N, K, scale_mode_a=H.SCALE_MX_E8M0_VEC32, scale_mode_b=H.SCALE_MX_E8M0_VEC32,
+                       activation=H.OP_RELU, bias=True, residual=True, batch=batch, batch_a=batch_a, batch_b=batch_b,
+                       bias_per_batch=per_batch_bias) as c:
+        c(qa, sa, qb, sb, out, bias=bf16_tensor(bias, cuda_device), residual=bf16_tensor(residual, cuda_device))
+    got = to_np(out).reshape(*batch, M, N)
+    da = o.dequant_mx(to_np(qa), to_np(sa), K).reshape(*dims_a, M, K)
+    db = o.dequant_mx(to_np(qb), to_np(sb), K).reshape(*dims_b, N, K)
+    acc = np.matmul(da, np.swapaxes(db, -1, -2))                       # float64, numpy broadcasting over the batch
+    b16 = o.bf16_round(bias).astype(np.float64).reshape(*(batch if per_batch_bias else [1] * len(batch)), 1, N)
+    r16 = o.bf16_round(residual).astype(np.float64).reshape(*batch, M, N)
+    ref = np.maximum(acc + b16, 0.0) + r16
+    assert_gemm_ok(got.reshape(-1, N), ref.reshape(-1, N))
+
+
 @pytest.mark.parametrize("tile_n", [224, 256])
 def test_mx_pair_many_tiles_per_pair(cuda_device, tile_n):
     """Two CTA pairs walk 24-28 tiles each, so both accumulators (and, for 256-wide tiles, the columns they share)
