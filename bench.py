@@ -410,12 +410,27 @@ def gpu_arm(args):
             dist.barrier()
         return shard.max_over_ranks(e0.elapsed_time(e1), dev)
 
-    for _ in range(warmup):
-        step()
     sampler = ClockSampler(local_rank)
     if rank == 0 and not args.kernel_only:
         sampler.start()
         time.sleep(0.05)
+    step()                                           # first call: module load, workspace allocation
+    torch.cuda.synchronize()
+    w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0.record()
+    for _ in range(warmup):
+        step()
+    w1.record()
+    torch.cuda.synchronize()
+    # A short step (tens of microseconds) finishes its warm-up before the SM clock has left its idle state: keep
+    # stepping, untimed, until the GPU has been busy for about 20 ms.  Long steps (C2) get exactly `warmup` steps.
+    ramp_steps = 0
+    warm_ms = w0.elapsed_time(w1)
+    if warmup > 0 and warm_ms < 1.0:
+        ramp_steps = min(5000, int(20.0 / max(warm_ms / warmup, 1e-3)))
+        for _ in range(ramp_steps):
+            step()
+        torch.cuda.synchronize()
     total_ms = timed(step, steps)
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = total_ms / steps
@@ -464,6 +479,7 @@ def gpu_arm(args):
             "config": {"workload": desc, "M_rank0": M, "N_rank0": N, "K": K, "groups_rank0": G if kind == "grouped" else 0,
                        "job_flops_per_step": flops_job, "sharding": sharding,
                        "l2": "operands + output exceed the 126 MB L2" if abytes > 126e6 else "fits in L2 (latency config)",
+                       "clock_ramp_steps": ramp_steps,
                        "pct_of_published_dense_fp8_peak": round(100.0 * value / world / 4500.0, 2)},
             "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak, "unit": unit,
                          "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
