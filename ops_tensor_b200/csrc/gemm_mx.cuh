@@ -126,6 +126,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            grid_dependency_wait();        // the re-tiled scales come from the kernel launched just before this one
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 int mt, nt;
                 tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);

@@ -136,6 +136,9 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // the re-tiled scales come from the kernel launched just before this one; everything above (barriers,
+            // TMEM, descriptor prefetch) may overlap its tail
+            grid_dependency_wait();
             for (int t = pair; t < num_tiles && ok; t += num_pairs) {
                 int mt, nt;
                 tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);

@@ -185,6 +185,25 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scal
     return ACLTENSOR_STATUS_SUCCESS;
 }
 
+// Launch of a GEMM kernel that follows its scale re-tile pre-pass in the stream: programmatic stream serialisation
+// lets the GEMM's blocks set themselves up while the pre-pass is still running; the kernel's producer thread waits for
+// the pre-pass (griddepcontrol.wait) before its first load.
+template <class... KArgs, class... Args>
+static cudaError_t launch_after_prepass(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t stream,
+                                        const Args&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <int kBN, int kAct>
 static cudaError_t launch_mx_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
                                       const MxGemmParams& p, int grid, cudaStream_t stream) {
@@ -199,8 +218,7 @@ static cudaError_t launch_mx_instance(const CUtensorMap& ta, const CUtensorMap& 
         if (e != cudaSuccess) return e;
         attr_done[dev & 63] = true;
     }
-    kernel<<<grid, 192, L::kDynamicBytes, stream>>>(ta, tb, td, p);
-    return cudaGetLastError();
+    return launch_after_prepass(kernel, grid, 192, L::kDynamicBytes, stream, ta, tb, td, p);
 }
 
 template <int kBN>
@@ -242,8 +260,8 @@ static cudaError_t launch_mx_pair_instance(const CUtensorMap& ta, const CUtensor
         if (e != cudaSuccess) return e;
         attr_done[dev & 63] = true;
     }
-    kernel<<<2 * pairs, 192, L::kDynamicBytes, stream>>>(ta, tb, tsa, tsb, td, p);     // cluster of 2 set on the kernel
-    return cudaGetLastError();
+    // cluster of 2 set on the kernel
+    return launch_after_prepass(kernel, 2 * pairs, 192, L::kDynamicBytes, stream, ta, tb, tsa, tsb, td, p);
 }
 
 template <int kBN, bool kWide>

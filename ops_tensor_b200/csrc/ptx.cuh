@@ -182,6 +182,15 @@ __device__ __forceinline__ void tma_load_2d_addr(uint32_t smem_dst, const CUtens
         : "memory");
 }
 
+// ------------------------------------------------------------------------------------------------ dependent launch
+
+// A kernel launched with programmatic stream serialisation may start while its predecessor in the stream is still
+// running.  `grid_dependency_wait` blocks the calling thread until the predecessor grid has finished and its writes
+// are visible; `grid_launch_dependents` lets the successor's blocks start being scheduled.  Both are no-ops for a
+// plain launch.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ------------------------------------------------------------------------------------------------ TMA
 
 // L2 eviction-priority hints for TMA loads (opaque 64-bit policy words the hardware defines).

@@ -220,6 +220,9 @@ __global__ void __launch_bounds__(256) sf_retile_kernel(const uint8_t* __restric
                                                         int valid_groups, int tile_rows, int k_steps, int replicas,
                                                         uint32_t* __restrict__ out, long long out_words) {
     const int atoms = (tile_rows + 127) >> 7;
+    // the GEMM that follows may set itself up (barriers, TMEM, descriptors) while this kernel runs; it waits for this
+    // grid to finish before it loads the first scale block
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < out_words;
          i += (long long)gridDim.x * blockDim.x) {
         long long r = i;
@@ -250,6 +253,7 @@ __global__ void __launch_bounds__(256) e2m1_expand_kernel(const uint8_t* __restr
                                                           int K, uint8_t* __restrict__ out, long long ld_out) {
     const int vec_per_row = K >> 4;           // K is a multiple of 16
     const long long total = (long long)rows * vec_per_row;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // see sf_retile_kernel
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const int row = (int)(i / vec_per_row);
