@@ -221,6 +221,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
+    if (p.stream_k) grid_dependency_wait();      // the fix-up flags are zeroed by the kernel launched just before
 
     // The two single-thread loops below run once per 128-deep K block, i.e. every 256 tensor-core cycles: they are
     // written with precomputed shared-memory addresses and descriptor words so that their instruction count, not

@@ -547,6 +547,11 @@ static cudaError_t launch_fp8_instance(const CUtensorMap& ta, const CUtensorMap&
         if (e != cudaSuccess) return e;
         attr_done[dev & 63] = true;
     }
+    if (p.stream_k) {
+        // behind the kernel that zeroes the fix-up flags: set-up overlaps it, every thread waits for it before the
+        // role loops start
+        return launch_after_prepass(kernel, grid, 320, L::kDynamicBytes, stream, ta, tb, p);
+    }
     kernel<<<grid, 320, L::kDynamicBytes, stream>>>(ta, tb, p);
     return cudaGetLastError();
 }
@@ -614,7 +619,7 @@ extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
     if (pl.stream_k) {
         p.flags = static_cast<int*>(a->workspace);
         p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + pl.flags_bytes);
-        cudaError_t e = cudaMemsetAsync(p.flags, 0, pl.flags_bytes, stream);
+        cudaError_t e = launch_zero_words(p.flags, (int)(pl.flags_bytes / 4), stream);
         if (e != cudaSuccess) return status_of(e);
     }
     cudaError_t e;

@@ -299,7 +299,18 @@ __global__ void __launch_bounds__(256) add_f32_kernel(const float* __restrict__ 
     }
 }
 
+__global__ void __launch_bounds__(256) zero_words_kernel(int* __restrict__ p, int words) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the GEMM behind may start setting up
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < words; i += gridDim.x * blockDim.x) p[i] = 0;
+}
+
 // ---------------------------------------------------------------------------------------------------- launchers
+
+cudaError_t launch_zero_words(int* p, int words, cudaStream_t stream) {
+    if (words <= 0) return cudaSuccess;
+    zero_words_kernel<<<(words + 255) / 256, 256, 0, stream>>>(p, words);
+    return cudaGetLastError();
+}
 
 static int grid_for(long long work_items, int per_block, int sm_count) {
     long long blocks = (work_items + per_block - 1) / per_block;
