@@ -337,6 +337,39 @@ def test_w4a8_mx(cuda_device, M, N, K):
     assert_gemm_ok(got, ref, gold)
 
 
+def test_mx_agrees_with_vendor_mxfp8_gemm(cuda_device):
+    """An independent implementation of the same format: the vendor library's MXFP8 GEMM (torch._scaled_mm with E8M0
+    scales per 32 K) on the same codes and scales.  Both accumulate in float32 and round once to bf16, so they may
+    differ by the order of the additions only: at most one bf16 ulp, and bit-equal almost everywhere."""
+    import torch
+    if not hasattr(torch, "float8_e8m0fnu"):
+        pytest.skip("this torch has no E8M0 dtype")
+    M, N, K = 512, 768, 1024
+    a = o.normal_f32(25, 0, (M, K), 1.0) * np.exp2(o.rng_for(25, 5).integers(-6, 7, size=(M, 1))).astype(np.float32)
+    w = o.normal_f32(25, 1, (N, K), 1.0)
+    got, qa, sa, qb, sb = run_mx(cuda_device, a, w)
+
+    def library_layout(scales):
+        # [rows][K/32] -> 128-row x 4-group blocks of 512 bytes: byte (r % 32) * 16 + (r // 32) * 4 + g
+        rows, groups = scales.shape
+        t = torch.from_numpy(scales).to(cuda_device).view(rows // 128, 4, 32, groups // 4, 4)
+        return t.permute(0, 3, 2, 1, 4).contiguous().view(-1).view(torch.float8_e8m0fnu)
+
+    qa_t = torch.from_numpy(qa).to(cuda_device).view(torch.float8_e4m3fn)
+    qb_t = torch.from_numpy(qb).to(cuda_device).view(torch.float8_e4m3fn)
+    try:
+        lib = torch._scaled_mm(qa_t, qb_t.t(), scale_a=library_layout(sa), scale_b=library_layout(sb),
+                               out_dtype=torch.bfloat16)
+    except (RuntimeError, ValueError) as exc:
+        pytest.skip(f"vendor MXFP8 GEMM unavailable here: {exc}")
+    lib = to_np(lib)
+    assert np.all(np.isfinite(lib))
+    same = np.mean(lib.view(np.uint32) == got.view(np.uint32))
+    ulp = np.abs(lib - got) / np.maximum(np.abs(lib), 1e-30)
+    assert same > 0.97, f"only {same:.4f} of the outputs are bit-equal"
+    assert float(ulp.max()) <= 2.0 ** -7, f"largest relative difference {float(ulp.max())}"
+
+
 @pytest.mark.parametrize("batch,batch_a,batch_b,per_batch_bias", [
     ((3,), (True,), (False,), False),                      # one weight for all batches: runs as one tall GEMM
     ((2, 3), (False, True), (True, False), True),          # A broadcast over the outer, B over the inner dimension
