@@ -49,7 +49,8 @@ typedef enum {
  * (include/blaze/gemm/kernel/kernel_qbmm_mx.h:80-115, :154-176) with the scale layouts of
  * include/tensor_api/impl/tensor_api/tensor/layout_pattern.h:180-226.
  * Constraints: K % 16 == 0, N % 8 == 0, lda/ldb multiples of 16 bytes, ldd/ldr multiples of 8 elements, all base
- * pointers 16-byte aligned.
+ * pointers 16-byte aligned.  A packed E2M1 B with K % 128 == 0, ldb % 32 == 0 and a 32-byte aligned base is read as it
+ * is; any other packed B is first expanded to one-byte codes in the workspace (same results, N x K more bytes).
  * ------------------------------------------------------------------------------------------------------------ */
 typedef struct {
     size_t struct_size; /* sizeof(blazeMxGemmArgs), for forward compatibility */

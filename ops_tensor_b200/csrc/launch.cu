@@ -86,6 +86,25 @@ static bool make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t row_byt
     return r == CUDA_SUCCESS;
 }
 
+// Packed 4-bit operand [rows][pitch bytes], K elements per row, two per byte: TMA unpacks every 16 codes (8 bytes) into
+// a 16-byte slot of shared memory, the form the f8f6f4 tensor-core kinds read 4-bit operands in, so a row of 128
+// codes fills the same 128 swizzled bytes as a row of 128 one-byte codes.  The driver wants the base 32-byte aligned,
+// the pitch a multiple of 32 bytes and whole 128-code boxes along K; the caller checks those and falls back to the
+// expansion pre-pass when the encoder refuses.
+static bool make_tmap_packed4(CUtensorMap* map, const void* base, uint64_t k_elems, uint64_t rows, uint64_t pitch_bytes,
+                              uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {k_elems, rows};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {128, box_rows};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void*>(base), dims, strides, box,
+                          elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 // bf16 output matrix [rows][cols valid, ld elements apart] written in 32 x 32 blocks staged with the 64-byte swizzle.
 static bool make_tmap_bf16_store(CUtensorMap* map, void* base, uint64_t cols, uint64_t rows, uint64_t ld_elems) {
     EncodeTiledFn fn = encode_tiled_fn();
@@ -277,9 +296,11 @@ static cudaError_t launch_mx_pair_act(int act, const CUtensorMap& ta, const CUte
 
 // Encodes the tensor maps and launches the GEMM kernel the plan chose.  `sfa_tiled` / `sfb_tiled` hold the re-tiled
 // scales, `b_codes` the 8-bit B operand (the caller's, or the expansion of a packed E2M1 one).
+// `b_packed4`: b_codes is the caller's packed E2M1 operand and `tb_packed` its tensor map (built by the caller, who
+// had to know whether the encoder accepts it before choosing between this and the expansion pre-pass).
 static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8_t* sfa_tiled, const uint8_t* sfb_tiled,
                          const uint8_t* b_codes, int64_t b_pitch, int* status_word, int sm_count,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const CUtensorMap* tb_packed = nullptr) {
     MxGemmParams p;
     p.M = a->M; p.N = a->N; p.K = a->K;
     p.m_tiles = pl.m_tiles; p.n_tiles = pl.n_tiles; p.k_steps = pl.k_steps;
@@ -292,6 +313,8 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
     p.D = static_cast<__nv_bfloat16*>(a->D);
     p.ldd = a->ldd;
     p.status = status_word;
+    p.b_format = tb_packed ? FMT_E2M1 : FMT_E4M3;
+    p.b_tx_shift = tb_packed ? 1 : 0;        // a 4-bit load reports the bytes it read, not the bytes it wrote
 
     const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
     int sms = sm_count;
@@ -305,9 +328,10 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
         const uint64_t sfa_blocks = (uint64_t)((a->M + 127) / 128) * pl.k_steps;
         const uint64_t sfb_blocks = (uint64_t)pl.n_tiles * pl.k_steps * 2 * pl.sfb_replicas;
         if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
-            !make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n / 2) ||
+            !(tb_packed || make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n / 2)) ||
             !make_tmap_sf_blocks(&tsa, sfa_tiled, sfa_blocks, 1) || !make_tmap_sf_blocks(&tsb, sfb_tiled, sfb_blocks, 2 * pl.sfb_replicas))
             return ACLTENSOR_STATUS_INTERNAL_ERROR;
+        if (tb_packed) tb = *tb_packed;
         int pairs = sms / 2;
         if (pairs < 1) pairs = 1;
         if (tiles < pairs) pairs = (int)tiles;
@@ -322,8 +346,9 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
         return status_of(e);
     }
     if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
-        !make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n))
+        !(tb_packed || make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n)))
         return ACLTENSOR_STATUS_INTERNAL_ERROR;
+    if (tb_packed) tb = *tb_packed;
     const int grid = (int)(tiles < sms ? tiles : sms);
     if (pl.tile_n == 224)
         e = launch_mx_act<224>(a->activation, ta, tb, td, p, grid, stream);
@@ -378,7 +403,16 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
     cudaError_t e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleA), a->M, a->K, 128, 1, sfa_tiled, ctx->sm_count,
                                      stream);
     if (e != cudaSuccess) return status_of(e);
-    if (a->b_elem == BLAZE_ELEM_E2M1) {
+    // A packed E2M1 weight is fed to the tensor core as it is when TMA can unpack it (whole 128-code boxes along K,
+    // 32-byte aligned rows); otherwise it is expanded once to one-byte E4M3 codes of the same values.
+    CUtensorMap tb_packed;
+    bool native4 = false;
+    if (a->b_elem == BLAZE_ELEM_E2M1 && (a->K % 128) == 0 && (a->ldb % 32) == 0 &&
+        (reinterpret_cast<uintptr_t>(a->B) & 31) == 0) {
+        native4 = make_tmap_packed4(&tb_packed, a->B, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->ldb,
+                                    (uint32_t)(pl.pair ? pl.tile_n / 2 : pl.tile_n));
+    }
+    if (a->b_elem == BLAZE_ELEM_E2M1 && !native4) {
         b_codes = ws + pl.b_expand_off;
         b_pitch = a->K;
     }
@@ -386,14 +420,15 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
         e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleB), a->N, a->K, pl.tile_n, pl.sfb_replicas, sfb_tiled, ctx->sm_count,
                              stream);
         if (e != cudaSuccess) return status_of(e);
-        if (a->b_elem == BLAZE_ELEM_E2M1) {
+        if (a->b_elem == BLAZE_ELEM_E2M1 && !native4) {
             e = launch_e2m1_expand(static_cast<const uint8_t*>(a->B), a->ldb, a->N, a->K, ws + pl.b_expand_off, a->K,
                                    ctx->sm_count, stream);
             if (e != cudaSuccess) return status_of(e);
         }
     }
 
-    return run_mx_kernel(a, pl, sfa_tiled, sfb_tiled, b_codes, b_pitch, ctx->status_word, ctx->sm_count, stream);
+    return run_mx_kernel(a, pl, sfa_tiled, sfb_tiled, b_codes, b_pitch, ctx->status_word, ctx->sm_count, stream,
+                         native4 ? &tb_packed : nullptr);
 }
 
 // ------------------------------------------------------------------------------------------------ batched MX GEMM

@@ -328,7 +328,28 @@ def test_mx_fused_epilogue(cuda_device, act, cta_pair):
     assert_gemm_ok(got, ref, gold)
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 224, 128), (200, 448, 1024), (64, 1000, 4096)])
+def test_w4a8_native_and_expanded_weights_agree(cuda_device):
+    """A packed E2M1 weight goes to the tensor core as it is (TMA unpacks the nibbles) when its rows are 32-byte
+    aligned, and through the one-time expansion to E4M3 codes otherwise; both must give the same bits."""
+    import torch
+    from ops_tensor_b200 import native
+    M, N, K = 300, 520, 1024
+    a = o.normal_f32(26, 0, (M, K), 1.0)
+    w = o.normal_f32(26, 1, (N, K), 0.02)
+    qa, sa = H.quantize(dev_tensor(a, cuda_device), H.SCALE_MX_E8M0_VEC32)
+    qb, sb = H.quantize(dev_tensor(w, cuda_device), H.SCALE_MX_E8M0_VEC32, H.R_4F_E2M1)
+    assert qb.data_ptr() % 32 == 0
+    direct = native.mx_gemm(qa, sa, qb, sb, b_elem=native.ELEM_E2M1)
+    shifted = torch.empty(qb.numel() + 16, dtype=torch.uint8, device=cuda_device)[16:].view(N, K // 2)
+    shifted.copy_(qb)
+    assert shifted.data_ptr() % 32 == 16
+    expanded = native.mx_gemm(qa, sa, shifted, sb, b_elem=native.ELEM_E2M1)
+    assert torch.equal(direct.view(torch.int16), expanded.view(torch.int16))
+    ref, gold = mx_reference(to_np(qa), to_np(sa), to_np(qb), to_np(sb), K, "e2m1")
+    assert_gemm_ok(to_np(direct), ref, gold)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 224, 128), (200, 448, 1024), (64, 1000, 4096), (150, 264, 96), (300, 520, 1056)])
 def test_w4a8_mx(cuda_device, M, N, K):
     a = o.normal_f32(23, 0, (M, K), 1.0)
     w = o.normal_f32(23, 1, (N, K), 0.02)
