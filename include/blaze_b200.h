@@ -43,7 +43,7 @@ typedef enum {
 
 /* ------------------------------------------------------------------------------------------------------------
  * MX block-scaled GEMM:  D = act(A x B^T + bias) + residual, bf16 output, fp32 accumulation.
- *   A  [M][lda] codes, K-contiguous (E4M3)                 scaleA [M][ceil(K/64)*2] E8M0 bytes, one per 32 K
+ *   A  [M][lda] codes, K-contiguous (E4M3 or packed E2M1)  scaleA [M][ceil(K/64)*2] E8M0 bytes, one per 32 K
  *   B  [N][ldb] codes, K-contiguous (E4M3 or packed E2M1)  scaleB [N][ceil(K/64)*2]
  * Stands in for GemmUniversal<KernelMmadWithScaleMx>::operator() and its Params
  * (include/blaze/gemm/kernel/kernel_qbmm_mx.h:80-115, :154-176) with the scale layouts of
@@ -55,7 +55,7 @@ typedef enum {
 typedef struct {
     size_t struct_size; /* sizeof(blazeMxGemmArgs), for forward compatibility */
     int32_t M, N, K;
-    int32_t b_elem;          /* blazeElem_t of B; A is always E4M3 */
+    int32_t b_elem;          /* blazeElem_t of B */
     const void* A;           /* device */
     int64_t lda;             /* bytes between rows of A */
     const void* B;           /* device */
@@ -72,7 +72,9 @@ typedef struct {
     int32_t reuse_b_prepass; /* 1: workspace still holds B's re-tiled scales / expanded codes from the previous call */
     int32_t sm_limit;        /* 0 = all SMs; else cap on the persistent grid */
     int32_t cta_pair;        /* 0 = choose; 1 = 128-row tiles, one CTA each; 2 = 256-row tiles on 2-CTA clusters */
-    int32_t reserved;
+    int32_t a_elem;          /* blazeElem_t of A: 0 = E4M3; BLAZE_ELEM_E2M1 = packed 4-bit A (the FP4 x FP4 pair of
+                                include/tensor_api/impl/tensor_api/arch/cube/mmad/check_data_type.h:41-50); needs
+                                K % 128 == 0, lda % 32 == 0, a 32-byte aligned A, and an E2M1 B */
     void* workspace;         /* device, 256-byte aligned */
     size_t workspace_bytes;
 } blazeMxGemmArgs;

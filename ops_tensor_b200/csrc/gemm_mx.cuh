@@ -38,6 +38,7 @@ struct MxGemmParams {
     int* status;
     uint32_t b_format;             // UmmaFormat of B in shared memory: FMT_E4M3, or FMT_E2M1 when TMA unpacks 4-bit codes
     uint32_t b_tx_shift;           // 1 when the B loads credit the barrier with the packed (half) byte count, else 0
+    uint32_t a_format, a_tx_shift; // the same two for A
 };
 
 template <int kBN, int kStages>
@@ -141,7 +142,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     uint8_t* b_dst = a_dst + L::kABytes;
                     uint8_t* sfa_dst = smem + L::kSfOffset + stage * (L::kSfaBytes + L::kSfbBytes);
                     uint8_t* sfb_dst = sfa_dst + L::kSfaBytes;
-                    mbar_arrive_expect_tx(&full_bar[stage], L::kTxBytes - L::kBBytes + (L::kBBytes >> p.b_tx_shift));
+                    mbar_arrive_expect_tx(&full_bar[stage], L::kTxBytes - L::kBBytes - L::kABytes + (L::kBBytes >> p.b_tx_shift) +
+                                                                 (L::kABytes >> p.a_tx_shift));
                     tma_load_2d(a_dst, &tmap_a, &full_bar[stage], ks * L::kBK, mt * L::kBM, kEvictNormal);
                     tma_load_2d(b_dst, &tmap_b, &full_bar[stage], ks * L::kBK, nt * kBN, kEvictNormal);
                     bulk_load(sfa_dst, sfa_src + (size_t)ks * L::kSfaBytes, L::kSfaBytes, &full_bar[stage]);
@@ -182,7 +184,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     for (int j = 0; j < 4; ++j) {
                         // 32 bytes further along K inside the swizzled row = 2 units of 16 bytes
                         umma_mx<1>(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
-                                   umma_idesc_mx(FMT_E4M3, p.b_format, 128, kBN, j, j), (ks | j) != 0 ? 1u : 0u,
+                                   umma_idesc_mx(p.a_format, p.b_format, 128, kBN, j, j), (ks | j) != 0 ? 1u : 0u,
                                    tmem_base + kSfaCol, tmem_base + kSfbCol);
                     }
                     umma_commit(&empty_bar[stage]);

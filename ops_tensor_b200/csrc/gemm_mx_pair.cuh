@@ -154,8 +154,9 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     uint8_t* sfa_dst = smem + L::kSfOffset + stage * (L::kSfaBytes + L::kSfbBytes);
                     uint8_t* sfb_dst = sfa_dst + L::kSfaBytes;
                     if (cta_rank == 0) {
-                        mbar_arrive_expect_tx(&full_bar[stage], 2 * (L::kTxBytesPerCta - L::kBHalfBytes +
-                                                                     (L::kBHalfBytes >> p.b_tx_shift)));
+                        mbar_arrive_expect_tx(&full_bar[stage], 2 * (L::kTxBytesPerCta - L::kBHalfBytes - L::kABytes +
+                                                                     (L::kBHalfBytes >> p.b_tx_shift) +
+                                                                     (L::kABytes >> p.a_tx_shift)));
                     }
                     const uint32_t bar = map_to_cta(&full_bar[stage], 0);
                     tma_load_2d_to_pair_bar(a_dst, &tmap_a, bar, ks * L::kBK, a_row, kEvictNormal);
@@ -208,7 +209,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         umma_mx<2>(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
-                                   umma_idesc_mx(FMT_E4M3, p.b_format, 256, kBN, j, j), (ks | j) != 0 ? 1u : 0u,
+                                   umma_idesc_mx(p.a_format, p.b_format, 256, kBN, j, j), (ks | j) != 0 ? 1u : 0u,
                                    tmem_base + kSfaCol, tmem_base + kSfbCol);
                     }
                     umma_commit_pair(&empty_bar[stage], 0x3);

@@ -51,7 +51,8 @@ void fill_mx_args(const acltensorOperationDescriptor& op, blazeMxGemmArgs* a) {
     a->N = static_cast<int32_t>(op.N);
     a->K = static_cast<int32_t>(op.K);
     a->b_elem = op.descB->dataType == ACLTENSOR_R_4F_E2M1 ? BLAZE_ELEM_E2M1 : BLAZE_ELEM_E4M3;
-    a->lda = op.lda;                                                  // one byte per element
+    a->a_elem = op.descA->dataType == ACLTENSOR_R_4F_E2M1 ? BLAZE_ELEM_E2M1 : BLAZE_ELEM_E4M3;
+    a->lda = a->a_elem == BLAZE_ELEM_E2M1 ? op.lda / 2 : op.lda;      // bytes
     a->ldb = a->b_elem == BLAZE_ELEM_E2M1 ? op.ldb / 2 : op.ldb;      // bytes
     a->ldr = op.ldc;
     a->ldd = op.ldd;
@@ -151,6 +152,7 @@ acltensorStatus_t Fp8Execute(const ContractionArgs& c) {
 
 REGISTER_CONTRACTION_SOLUTION(MxFp8, R_8F_E4M3, R_8F_E4M3, MX_E8M0_VEC32, MX_E8M0_VEC32, 2, MxWorkspace, MxExecute);
 REGISTER_CONTRACTION_SOLUTION(MxW4A8, R_8F_E4M3, R_4F_E2M1, MX_E8M0_VEC32, MX_E8M0_VEC32, 2, MxWorkspace, MxExecute);
+REGISTER_CONTRACTION_SOLUTION(MxFp4, R_4F_E2M1, R_4F_E2M1, MX_E8M0_VEC32, MX_E8M0_VEC32, 2, MxWorkspace, MxExecute);
 REGISTER_CONTRACTION_SOLUTION(Fp8Block, R_8F_E4M3, R_8F_E4M3, FP32_1X128, FP32_128X128, 0, Fp8Workspace, Fp8Execute);
 
 // ------------------------------------------------------------------------------------------------ descriptor
@@ -172,7 +174,11 @@ acltensorStatus_t acltensorCreateContraction(const acltensorHandle_t handle, acl
     const acltensorStatus_t cst = CheckComputeDescriptor(descCompute);
     if (cst != ACLTENSOR_STATUS_SUCCESS) return cst;
 
-    if (descA->dataType != ACLTENSOR_R_8F_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (descA->dataType != ACLTENSOR_R_8F_E4M3 && descA->dataType != ACLTENSOR_R_4F_E2M1)
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    // operand pairs of the reference (check_data_type.h:41-50) plus the mixed W4A8 pair: no FP4 A with an FP8 B
+    if (descA->dataType == ACLTENSOR_R_4F_E2M1 && descB->dataType != ACLTENSOR_R_4F_E2M1)
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (descB->dataType != ACLTENSOR_R_8F_E4M3 && descB->dataType != ACLTENSOR_R_4F_E2M1)
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (descD->dataType != ACLTENSOR_R_16BF) return ACLTENSOR_STATUS_NOT_SUPPORTED;

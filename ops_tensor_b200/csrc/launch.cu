@@ -175,6 +175,10 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scal
     if (!a || a->struct_size != sizeof(blazeMxGemmArgs)) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->M < 0 || a->N < 0 || a->K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->b_elem != BLAZE_ELEM_E4M3 && a->b_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->a_elem != BLAZE_ELEM_E4M3 && a->a_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    // legal operand pairs: FP8 x FP8, FP8 x FP4 (W4A8) and FP4 x FP4; a 4-bit A is only read natively
+    if (a->a_elem == BLAZE_ELEM_E2M1 && (a->b_elem != BLAZE_ELEM_E2M1 || (a->K % 128) != 0))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_GELU_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->tile_n != 0 && a->tile_n != 128 && a->tile_n != 224 && a->tile_n != 256) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if ((a->K % 16) != 0 || (a->N % 8) != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
@@ -300,7 +304,8 @@ static cudaError_t launch_mx_pair_act(int act, const CUtensorMap& ta, const CUte
 // had to know whether the encoder accepts it before choosing between this and the expansion pre-pass).
 static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8_t* sfa_tiled, const uint8_t* sfb_tiled,
                          const uint8_t* b_codes, int64_t b_pitch, int* status_word, int sm_count,
-                         cudaStream_t stream, const CUtensorMap* tb_packed = nullptr) {
+                         cudaStream_t stream, const CUtensorMap* tb_packed = nullptr,
+                         const CUtensorMap* ta_packed = nullptr) {
     MxGemmParams p;
     p.M = a->M; p.N = a->N; p.K = a->K;
     p.m_tiles = pl.m_tiles; p.n_tiles = pl.n_tiles; p.k_steps = pl.k_steps;
@@ -315,6 +320,8 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
     p.status = status_word;
     p.b_format = tb_packed ? FMT_E2M1 : FMT_E4M3;
     p.b_tx_shift = tb_packed ? 1 : 0;        // a 4-bit load reports the bytes it read, not the bytes it wrote
+    p.a_format = ta_packed ? FMT_E2M1 : FMT_E4M3;
+    p.a_tx_shift = ta_packed ? 1 : 0;
 
     const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
     int sms = sm_count;
@@ -327,11 +334,12 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
         CUtensorMap tsa, tsb;
         const uint64_t sfa_blocks = (uint64_t)((a->M + 127) / 128) * pl.k_steps;
         const uint64_t sfb_blocks = (uint64_t)pl.n_tiles * pl.k_steps * 2 * pl.sfb_replicas;
-        if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
+        if (!(ta_packed || make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128)) ||
             !(tb_packed || make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n / 2)) ||
             !make_tmap_sf_blocks(&tsa, sfa_tiled, sfa_blocks, 1) || !make_tmap_sf_blocks(&tsb, sfb_tiled, sfb_blocks, 2 * pl.sfb_replicas))
             return ACLTENSOR_STATUS_INTERNAL_ERROR;
         if (tb_packed) tb = *tb_packed;
+        if (ta_packed) ta = *ta_packed;
         int pairs = sms / 2;
         if (pairs < 1) pairs = 1;
         if (tiles < pairs) pairs = (int)tiles;
@@ -345,10 +353,11 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
         }
         return status_of(e);
     }
-    if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
+    if (!(ta_packed || make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128)) ||
         !(tb_packed || make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n)))
         return ACLTENSOR_STATUS_INTERNAL_ERROR;
     if (tb_packed) tb = *tb_packed;
+    if (ta_packed) ta = *ta_packed;
     const int grid = (int)(tiles < sms ? tiles : sms);
     if (pl.tile_n == 224)
         e = launch_mx_act<224>(a->activation, ta, tb, td, p, grid, stream);
@@ -384,7 +393,8 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
     if (!a->A || !a->B || !a->scaleA || !a->scaleB || !a->D) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->K == 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     const int64_t min_ldb = a->b_elem == BLAZE_ELEM_E2M1 ? a->K / 2 : a->K;
-    if (a->lda < a->K || a->ldb < min_ldb || a->ldd < a->N || (a->residual && a->ldr < a->N))
+    const int64_t min_lda = a->a_elem == BLAZE_ELEM_E2M1 ? a->K / 2 : a->K;
+    if (a->lda < min_lda || a->ldb < min_ldb || a->ldd < a->N || (a->residual && a->ldr < a->N))
         return ACLTENSOR_STATUS_INVALID_VALUE;
     if ((a->lda % 16) || (a->ldb % 16) || (a->ldd % 8) || (a->residual && (a->ldr % 8)))
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
@@ -412,6 +422,13 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
         native4 = make_tmap_packed4(&tb_packed, a->B, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->ldb,
                                     (uint32_t)(pl.pair ? pl.tile_n / 2 : pl.tile_n));
     }
+    CUtensorMap ta_packed;
+    if (a->a_elem == BLAZE_ELEM_E2M1) {
+        // FP4 x FP4: both operands must take the native route
+        if (!native4 || (a->lda % 32) != 0 || (reinterpret_cast<uintptr_t>(a->A) & 31) != 0 ||
+            !make_tmap_packed4(&ta_packed, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128))
+            return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    }
     if (a->b_elem == BLAZE_ELEM_E2M1 && !native4) {
         b_codes = ws + pl.b_expand_off;
         b_pitch = a->K;
@@ -428,7 +445,7 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
     }
 
     return run_mx_kernel(a, pl, sfa_tiled, sfb_tiled, b_codes, b_pitch, ctx->status_word, ctx->sm_count, stream,
-                         native4 ? &tb_packed : nullptr);
+                         native4 ? &tb_packed : nullptr, a->a_elem == BLAZE_ELEM_E2M1 ? &ta_packed : nullptr);
 }
 
 // ------------------------------------------------------------------------------------------------ batched MX GEMM

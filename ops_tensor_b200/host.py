@@ -185,7 +185,7 @@ class Contraction:
     def __init__(self, M, N, K, *, scale_mode_a, scale_mode_b, b_dtype=R_8F_E4M3, groups=0, activation=OP_IDENTITY,
                  bias=False, residual=False, split=SPLIT_AUTO, tile_n=0, sm_limit=0, b_is_static=False, cta_pair=0,
                  lda=None, ldb=None, ldd=None, ldc=None, workspace_limit=2 ** 62, batch=(), batch_a=None, batch_b=None,
-                 bias_per_batch=False):
+                 bias_per_batch=False, a_dtype=R_8F_E4M3):
         self.M, self.N, self.K, self.groups = M, N, K, groups
         self.handle = create_handle()
         self._descs = []
@@ -210,7 +210,7 @@ class Contraction:
             return lens, strides, modes
 
         la, sa, ma = packed(batch, batch_a, M, lda)
-        self.dA = create_tensor_descriptor(self.handle, la + [M, K], sa + [lda, 1], R_8F_E4M3)
+        self.dA = create_tensor_descriptor(self.handle, la + [M, K], sa + [lda, 1], a_dtype)
         if groups:
             self.dB = create_tensor_descriptor(self.handle, [groups, N, K], [N * ldb, ldb, 1], b_dtype)
             mode_b = i32([g, n, k])

@@ -42,7 +42,7 @@ class MxGemmArgs(C.Structure):
         ("reuse_b_prepass", C.c_int32),
         ("sm_limit", C.c_int32),
         ("cta_pair", C.c_int32),
-        ("reserved", C.c_int32),
+        ("a_elem", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
@@ -192,8 +192,10 @@ def quantize_fp8_blocks(w):
 # ------------------------------------------------------------------------------------------------ GEMMs
 
 def mx_gemm_args(a, sa, b, sb, out, *, b_elem=ELEM_E4M3, bias=None, residual=None, activation=ACT_IDENTITY,
-                 tile_n=0, reuse_b_prepass=False, sm_limit=0, cta_pair=0, workspace=None) -> MxGemmArgs:
+                 tile_n=0, reuse_b_prepass=False, sm_limit=0, cta_pair=0, workspace=None, a_elem=ELEM_E4M3) -> MxGemmArgs:
     M, K = a.shape
+    if a_elem == ELEM_E2M1:
+        K *= 2                       # two codes per byte
     N = b.shape[0]
     args = MxGemmArgs()
     args.struct_size = C.sizeof(MxGemmArgs)
@@ -211,6 +213,7 @@ def mx_gemm_args(a, sa, b, sb, out, *, b_elem=ELEM_E4M3, bias=None, residual=Non
     args.reuse_b_prepass = 1 if reuse_b_prepass else 0
     args.sm_limit = sm_limit
     args.cta_pair = cta_pair
+    args.a_elem = a_elem
     if workspace is not None:
         args.workspace, args.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
     return args

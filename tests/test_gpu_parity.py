@@ -349,6 +349,28 @@ def test_w4a8_native_and_expanded_weights_agree(cuda_device):
     assert_gemm_ok(to_np(direct), ref, gold)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 224, 128), (300, 520, 1024), (64, 1000, 4096)])
+def test_mxfp4_both_operands(cuda_device, M, N, K):
+    """FP4 x FP4 (the reference's other legal operand pair): A and B packed E2M1 with E8M0 scales per 32 K."""
+    import torch
+    a = o.normal_f32(27, 0, (M, K), 1.0)
+    w = o.normal_f32(27, 1, (N, K), 0.05)
+    MX = H.SCALE_MX_E8M0_VEC32
+    qa, sa = H.quantize(dev_tensor(a, cuda_device), MX, H.R_4F_E2M1)
+    qb, sb = H.quantize(dev_tensor(w, cuda_device), MX, H.R_4F_E2M1)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    with H.Contraction(M, N, K, scale_mode_a=MX, scale_mode_b=MX, a_dtype=H.R_4F_E2M1, b_dtype=H.R_4F_E2M1) as c:
+        c(qa, sa, qb, sb, out)
+    da = o.dequant_mx(to_np(qa), to_np(sa), K, "e2m1")
+    db = o.dequant_mx(to_np(qb), to_np(sb), K, "e2m1")
+    ref = o.matmul_ref64(da, db)
+    gold = o.matmul_golden32(da.astype(np.float32), db.astype(np.float32))
+    assert_gemm_ok(to_np(out), ref, gold)
+    # an FP4 A against an FP8 B is not an operand pair
+    with pytest.raises(Exception):
+        H.Contraction(M, N, K, scale_mode_a=MX, scale_mode_b=MX, a_dtype=H.R_4F_E2M1)
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 224, 128), (200, 448, 1024), (64, 1000, 4096), (150, 264, 96), (300, 520, 1056)])
 def test_w4a8_mx(cuda_device, M, N, K):
     a = o.normal_f32(23, 0, (M, K), 1.0)
