@@ -31,6 +31,10 @@ typedef enum {
                             (include/blaze/gemm/tile/arch35/shift_w4_to_w8.h:88-99) */
 } blazeElem_t;
 
+/* Element type of the output D: the cast-on-store modes of the reference's fix pipe
+ * (include/tensor_api/impl/tensor_api/arch/cube/utils/l0c2out_utils.h:122-132). */
+typedef enum { BLAZE_OUT_BF16 = 0, BLAZE_OUT_F16 = 1, BLAZE_OUT_F32 = 2 } blazeOutType_t;
+
 /* Fused activation, applied after bias and before the residual add. */
 typedef enum { BLAZE_ACT_IDENTITY = 0, BLAZE_ACT_RELU = 1, BLAZE_ACT_GELU_TANH = 2 } blazeActivation_t;
 
@@ -42,7 +46,7 @@ typedef enum {
 } blazeSched_t;
 
 /* ------------------------------------------------------------------------------------------------------------
- * MX block-scaled GEMM:  D = act(A x B^T + bias) + residual, bf16 output, fp32 accumulation.
+ * MX block-scaled GEMM:  D = act(A x B^T + bias) + residual, fp32 accumulation, bf16 / half / float32 output.
  *   A  [M][lda] codes, K-contiguous (E4M3 or packed E2M1)  scaleA [M][ceil(K/64)*2] E8M0 bytes, one per 32 K
  *   B  [N][ldb] codes, K-contiguous (E4M3 or packed E2M1)  scaleB [N][ceil(K/64)*2]
  * Stands in for GemmUniversal<KernelMmadWithScaleMx>::operator() and its Params
@@ -65,7 +69,7 @@ typedef struct {
     const void* bias;        /* device bf16[N] or NULL */
     const void* residual;    /* device bf16 [M][ldr] or NULL */
     int64_t ldr;             /* elements */
-    void* D;                 /* device bf16 [M][ldd] */
+    void* D;                 /* device [M][ldd], bf16 unless d_type says otherwise */
     int64_t ldd;             /* elements */
     int32_t activation;      /* blazeActivation_t */
     int32_t tile_n;          /* 0 = choose; else 128, 224 or 256 (256 only with 2-CTA tiles) */
@@ -77,6 +81,8 @@ typedef struct {
                                 K % 128 == 0, lda % 32 == 0, a 32-byte aligned A, and an E2M1 B */
     void* workspace;         /* device, 256-byte aligned */
     size_t workspace_bytes;
+    int32_t d_type;          /* blazeOutType_t of D (ldd counts elements of that type) */
+    int32_t reserved;
 } blazeMxGemmArgs;
 
 BLAZE_API int blazeMxGemmWorkspaceSize(const blazeMxGemmArgs* args, size_t* bytes);
@@ -157,7 +163,7 @@ typedef struct {
     int32_t activation;
     int32_t sched;    /* blazeSched_t */
     int32_t sm_limit; /* 0 = all SMs */
-    int32_t reserved;
+    int32_t d_type;   /* blazeOutType_t of D */
     void* workspace;
     size_t workspace_bytes;
 } blazeFp8GemmArgs;

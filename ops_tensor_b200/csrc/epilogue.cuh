@@ -1,5 +1,5 @@
-// Fused epilogue of the MX GEMM kernels: TMEM -> registers -> (bias, activation, residual, bf16) -> shared memory
-// -> TMA store.
+// Fused epilogue of the MX GEMM kernels: TMEM -> registers -> (bias, activation, residual, cast to bf16 / half /
+// float32) -> shared memory -> TMA store.
 //
 // One warp owns 32 accumulator rows (its TMEM lane quadrant); each thread holds one row.  The tile is drained in
 // chunks of 32 columns: tcgen05.ld brings 32 fp32 values per thread, the fused ops run in registers, the bf16
@@ -23,6 +23,7 @@ struct EpilogueArgs {
     const __nv_bfloat16* bias;
     const __nv_bfloat16* residual;
     long long ldr;
+    int out_type;       // OutType of D; the tensor map handed to the store has the matching element size and box
 };
 
 // Drains one accumulator tile.  `tmem_tile` = TMEM address of column 0 of the accumulator, lane field already set to
@@ -56,7 +57,7 @@ __device__ __forceinline__ void epilogue_store_tile_from(uint32_t tmem_tile, con
         if (i == 0) early();
         if (i == kChunks - 1) release();
 
-        uint32_t packed[16];
+        // fused ops in place: v[] holds the finished float32 values afterwards
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int n = n0 + q * 8;
@@ -85,7 +86,42 @@ __device__ __forceinline__ void epilogue_store_tile_from(uint32_t tmem_tile, con
                 }
             }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) packed[q * 4 + e] = pack_bf16(x[2 * e], x[2 * e + 1]);
+            for (int e = 0; e < 8; ++e) v[q * 8 + e] = __float_as_uint(x[e]);
+        }
+
+        const int sw = (lane >> 1) & 3;                // 64-byte swizzle: 16-byte slot ^= (row / 2) % 4
+        if (ea.out_type == OUT_F32) {
+            // 4-byte outputs: the chunk leaves as two 32 x 16 blocks (64-byte rows, like the 16-bit case)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (n0 + 16 * h >= ea.N) break;
+                uint8_t* block = stage + (chunk_counter & 1) * (32 * 64);
+                if (lane == 0) tma_store_wait_read<1>();
+                __syncwarp();
+                uint8_t* my_row = block + lane * 64;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    *reinterpret_cast<uint4*>(my_row + ((q ^ sw) << 4)) =
+                        make_uint4(v[h * 16 + q * 4], v[h * 16 + q * 4 + 1], v[h * 16 + q * 4 + 2], v[h * 16 + q * 4 + 3]);
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(tmap_d, block, n0 + 16 * h, row0);
+                    tma_store_commit();
+                }
+                ++chunk_counter;
+            }
+            continue;
+        }
+
+        uint32_t packed[16];
+        if (ea.out_type == OUT_F16) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) packed[e] = pack_f16(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
+        } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) packed[e] = pack_bf16(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
         }
 
         // staging block: make sure TMA has finished reading it (at most one younger store may still be in flight)
@@ -93,7 +129,6 @@ __device__ __forceinline__ void epilogue_store_tile_from(uint32_t tmem_tile, con
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
         uint8_t* my_row = block + lane * 64;
-        const int sw = (lane >> 1) & 3;                // 64-byte swizzle: 16-byte slot ^= (row / 2) % 4
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             *reinterpret_cast<uint4*>(my_row + ((q ^ sw) << 4)) =

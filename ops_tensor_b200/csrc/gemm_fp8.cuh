@@ -41,6 +41,7 @@ struct Fp8GemmParams {
     long long ldd;
     int stream_k;                   // 1: split the (tile, k-block) units evenly over the grid
     float* partials;                // [gridDim.x][32 column quads][128 rows][4] fp32 (stream-K only)
+    int out_type;                   // OutType of D (ldd counts elements of that type)
     int* flags;                     // [gridDim.x], zeroed before the launch (stream-K only)
     int* status;
 };
@@ -414,7 +415,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
             // -------- fused epilogue: bias, activation, residual, bf16; 128 contiguous bytes per thread
             if (row_ok) {
-                __nv_bfloat16* d_row = p.D + (long long)row * p.ldd;
+                const int elem_bytes = p.out_type == OUT_F32 ? 4 : 2;
+                uint8_t* d_row = reinterpret_cast<uint8_t*>(p.D) + (long long)row * p.ldd * elem_bytes;
                 const __nv_bfloat16* r_row = p.residual ? p.residual + (long long)row * p.ldr : nullptr;
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
@@ -443,12 +445,21 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                                 x[2 * e + 1] += __uint_as_float(rw[e] & 0xFFFF0000u);
                             }
                         }
-                        uint4 o;
-                        o.x = pack_bf16(x[0], x[1]);
-                        o.y = pack_bf16(x[2], x[3]);
-                        o.z = pack_bf16(x[4], x[5]);
-                        o.w = pack_bf16(x[6], x[7]);
-                        *reinterpret_cast<uint4*>(d_row + n) = o;
+                        if (p.out_type == OUT_F32) {
+                            float4* dst = reinterpret_cast<float4*>(d_row + (long long)n * 4);
+                            dst[0] = make_float4(x[0], x[1], x[2], x[3]);
+                            dst[1] = make_float4(x[4], x[5], x[6], x[7]);
+                        } else {
+                            uint4 o;
+                            if (p.out_type == OUT_F16) {
+                                o = make_uint4(pack_f16(x[0], x[1]), pack_f16(x[2], x[3]), pack_f16(x[4], x[5]),
+                                               pack_f16(x[6], x[7]));
+                            } else {
+                                o = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]),
+                                               pack_bf16(x[6], x[7]));
+                            }
+                            *reinterpret_cast<uint4*>(d_row + (long long)n * 2) = o;
+                        }
                     }
                 }
             }

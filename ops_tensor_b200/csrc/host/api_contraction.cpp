@@ -32,6 +32,14 @@ int activation_of(int32_t op) {
     }
 }
 
+int out_type_of(acltensorDataType_t t) {
+    switch (t) {
+        case ACLTENSOR_R_16F: return BLAZE_OUT_F16;
+        case ACLTENSOR_R_32F: return BLAZE_OUT_F32;
+        default: return BLAZE_OUT_BF16;
+    }
+}
+
 int sched_of(int32_t policy) {
     switch (policy) {
         case ACLTENSOR_SPLIT_DATA_PARALLEL: return BLAZE_SCHED_DATA_PARALLEL;
@@ -57,6 +65,7 @@ void fill_mx_args(const acltensorOperationDescriptor& op, blazeMxGemmArgs* a) {
     a->ldr = op.ldc;
     a->ldd = op.ldd;
     a->activation = activation_of(op.epilogueAct);
+    a->d_type = out_type_of(op.descD->dataType);
     a->tile_n = op.tileN;
     a->sm_limit = op.smLimit;
     a->cta_pair = op.ctaPair;
@@ -118,6 +127,7 @@ void fill_fp8_args(const acltensorOperationDescriptor& op, int32_t splitPolicy, 
     a->ldr = op.ldc;
     a->ldd = op.ldd;
     a->activation = activation_of(op.epilogueAct);
+    a->d_type = out_type_of(op.descD->dataType);
     a->sched = sched_of(splitPolicy);
     a->sm_limit = op.smLimit;
 }
@@ -181,7 +191,9 @@ acltensorStatus_t acltensorCreateContraction(const acltensorHandle_t handle, acl
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (descB->dataType != ACLTENSOR_R_8F_E4M3 && descB->dataType != ACLTENSOR_R_4F_E2M1)
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    if (descD->dataType != ACLTENSOR_R_16BF) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    // output: the three cast-on-store modes (bf16, half, float32)
+    if (descD->dataType != ACLTENSOR_R_16BF && descD->dataType != ACLTENSOR_R_16F && descD->dataType != ACLTENSOR_R_32F)
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (descC != nullptr && descC->dataType != ACLTENSOR_R_16BF) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     // D = [batch..., m, n] with up to four batch modes; A = [its batch modes..., m, k]; B = [its batch modes..., n, k]
     // or, without batch modes in D, [group, n, k].  A batch mode missing from an operand is a broadcast.

@@ -42,7 +42,8 @@ inline size_t GetDataTypeSize(acltensorDataType_t t) { return DataTypeBits(t) / 
 // (lib/core/tensor_descriptor.cpp:43-45); the contraction path adds its operand, scale, output and index types.
 inline bool IsDescriptorTypeSupported(acltensorDataType_t t) {
     switch (t) {
-        case ACLTENSOR_R_32F: case ACLTENSOR_R_16BF: case ACLTENSOR_R_8F_E4M3: case ACLTENSOR_R_4F_E2M1:
+        case ACLTENSOR_R_32F: case ACLTENSOR_R_16BF: case ACLTENSOR_R_16F: case ACLTENSOR_R_8F_E4M3:
+        case ACLTENSOR_R_4F_E2M1:
         case ACLTENSOR_R_8F_UE8M0: case ACLTENSOR_R_8U: case ACLTENSOR_R_64I:
             return true;
         default:

@@ -106,14 +106,20 @@ static bool make_tmap_packed4(CUtensorMap* map, const void* base, uint64_t k_ele
 }
 
 // bf16 output matrix [rows][cols valid, ld elements apart] written in 32 x 32 blocks staged with the 64-byte swizzle.
-static bool make_tmap_bf16_store(CUtensorMap* map, void* base, uint64_t cols, uint64_t rows, uint64_t ld_elems) {
+// (Half outputs use the same shape; float32 outputs leave as 32 x 16 blocks, again 64 bytes per row.)
+static bool make_tmap_store(CUtensorMap* map, void* base, uint64_t cols, uint64_t rows, uint64_t ld_elems,
+                            int out_type) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
+    const bool f32 = out_type == BLAZE_OUT_F32;
     const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {ld_elems * 2};
-    const cuuint32_t box[2] = {32, 32};
+    const cuuint64_t strides[1] = {ld_elems * (f32 ? 4 : 2)};
+    const cuuint32_t box[2] = {f32 ? 16u : 32u, 32};
     const cuuint32_t elem_strides[2] = {1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, elem_strides,
+    const CUtensorMapDataType dt = f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                       : (out_type == BLAZE_OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                    : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+    const CUresult r = fn(map, dt, 2, base, dims, strides, box, elem_strides,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
@@ -176,6 +182,7 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scal
     if (a->M < 0 || a->N < 0 || a->K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->b_elem != BLAZE_ELEM_E4M3 && a->b_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->a_elem != BLAZE_ELEM_E4M3 && a->a_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->d_type < BLAZE_OUT_BF16 || a->d_type > BLAZE_OUT_F32) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     // legal operand pairs: FP8 x FP8, FP8 x FP4 (W4A8) and FP4 x FP4; a 4-bit A is only read natively
     if (a->a_elem == BLAZE_ELEM_E2M1 && (a->b_elem != BLAZE_ELEM_E2M1 || (a->K % 128) != 0))
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
@@ -320,6 +327,7 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
     p.status = status_word;
     p.b_format = tb_packed ? FMT_E2M1 : FMT_E4M3;
     p.b_tx_shift = tb_packed ? 1 : 0;        // a 4-bit load reports the bytes it read, not the bytes it wrote
+    p.out_type = a->d_type;
     p.a_format = ta_packed ? FMT_E2M1 : FMT_E4M3;
     p.a_tx_shift = ta_packed ? 1 : 0;
 
@@ -328,7 +336,7 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
     if (a->sm_limit > 0 && a->sm_limit < sms) sms = a->sm_limit;
     CUtensorMap ta, tb, td;
     cudaError_t e;
-    if (!make_tmap_bf16_store(&td, a->D, (uint64_t)a->N, (uint64_t)a->M, (uint64_t)a->ldd))
+    if (!make_tmap_store(&td, a->D, (uint64_t)a->N, (uint64_t)a->M, (uint64_t)a->ldd, a->d_type))
         return ACLTENSOR_STATUS_INTERNAL_ERROR;
     if (pl.pair) {
         CUtensorMap tsa, tsb;
@@ -553,6 +561,7 @@ static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
     if (a->groups > kFp8MaxGroups) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_GELU_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->sched < BLAZE_SCHED_AUTO || a->sched > BLAZE_SCHED_STREAM_K) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->d_type < BLAZE_OUT_BF16 || a->d_type > BLAZE_OUT_F32) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if ((a->K % 16) != 0 || (a->N % 8) != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->groups > 0 && a->sched == BLAZE_SCHED_STREAM_K) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     int sms = sm_count;
@@ -664,6 +673,7 @@ extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
     p.ldr = a->ldr;
     p.D = static_cast<__nv_bfloat16*>(a->D);
     p.ldd = a->ldd;
+    p.out_type = a->d_type;
     p.stream_k = pl.stream_k;
     p.flags = nullptr;
     p.partials = nullptr;

@@ -9,6 +9,7 @@
 #include <cstdint>
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace blaze {
 
@@ -540,5 +541,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Output element types of the fused epilogues: the cast-on-store modes of the reference's fix pipe (float32 ->
+// bf16 / half / float32: include/tensor_api/impl/tensor_api/arch/cube/utils/l0c2out_utils.h:122-132).
+enum OutType : int { OUT_BF16 = 0, OUT_F16 = 1, OUT_F32 = 2 };
 
 }  // namespace blaze

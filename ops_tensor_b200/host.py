@@ -185,7 +185,7 @@ class Contraction:
     def __init__(self, M, N, K, *, scale_mode_a, scale_mode_b, b_dtype=R_8F_E4M3, groups=0, activation=OP_IDENTITY,
                  bias=False, residual=False, split=SPLIT_AUTO, tile_n=0, sm_limit=0, b_is_static=False, cta_pair=0,
                  lda=None, ldb=None, ldd=None, ldc=None, workspace_limit=2 ** 62, batch=(), batch_a=None, batch_b=None,
-                 bias_per_batch=False, a_dtype=R_8F_E4M3):
+                 bias_per_batch=False, a_dtype=R_8F_E4M3, d_dtype=R_16BF):
         self.M, self.N, self.K, self.groups = M, N, K, groups
         self.handle = create_handle()
         self._descs = []
@@ -219,7 +219,7 @@ class Contraction:
             self.dB = create_tensor_descriptor(self.handle, lb + [N, K], sb + [ldb, 1], b_dtype)
             mode_b = i32(mb + [n, k])
         ld_, sd, md = packed(batch, [True] * len(batch), M, ldd)
-        self.dD = create_tensor_descriptor(self.handle, ld_ + [M, N], sd + [ldd, 1], R_16BF)
+        self.dD = create_tensor_descriptor(self.handle, ld_ + [M, N], sd + [ldd, 1], d_dtype)
         self.dC = None
         if residual:
             lc, sc, _ = packed(batch, [True] * len(batch), M, ldc)

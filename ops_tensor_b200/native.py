@@ -24,6 +24,13 @@ STATUS_INSUFFICIENT_WORKSPACE = 19
 ELEM_E4M3, ELEM_E2M1 = 0, 1
 ACT_IDENTITY, ACT_RELU, ACT_GELU_TANH = 0, 1, 2
 SCHED_AUTO, SCHED_DATA_PARALLEL, SCHED_STREAM_K = 0, 1, 2
+OUT_BF16, OUT_F16, OUT_F32 = 0, 1, 2
+
+
+def out_type_of(tensor) -> int:
+    """blazeOutType_t of a torch output tensor (bf16, half or float32)."""
+    import torch
+    return {torch.bfloat16: OUT_BF16, torch.float16: OUT_F16, torch.float32: OUT_F32}[tensor.dtype]
 
 
 class MxGemmArgs(C.Structure):
@@ -44,6 +51,7 @@ class MxGemmArgs(C.Structure):
         ("cta_pair", C.c_int32),
         ("a_elem", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("d_type", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -68,7 +76,7 @@ class Fp8GemmArgs(C.Structure):
         ("activation", C.c_int32),
         ("sched", C.c_int32),
         ("sm_limit", C.c_int32),
-        ("reserved", C.c_int32),
+        ("d_type", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
@@ -208,6 +216,7 @@ def mx_gemm_args(a, sa, b, sb, out, *, b_elem=ELEM_E4M3, bias=None, residual=Non
     args.residual = residual.data_ptr() if residual is not None else None
     args.ldr = residual.stride(0) if residual is not None else 0
     args.D, args.ldd = out.data_ptr(), out.stride(0)
+    args.d_type = out_type_of(out)
     args.activation = activation
     args.tile_n = tile_n
     args.reuse_b_prepass = 1 if reuse_b_prepass else 0
@@ -262,6 +271,7 @@ def fp8_gemm_args(a, sa, b, sb, out, *, group_rows=None, bias=None, residual=Non
     args.residual = residual.data_ptr() if residual is not None else None
     args.ldr = residual.stride(0) if residual is not None else 0
     args.D, args.ldd = out.data_ptr(), out.stride(0)
+    args.d_type = out_type_of(out)
     args.activation = activation
     args.sched = sched
     args.sm_limit = sm_limit

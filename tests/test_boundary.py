@@ -60,9 +60,9 @@ def test_handle_and_tensor_descriptor_checks(api):
     assert api.acltensorCreateTensorDescriptor(h, None, 2, lens, None, H.R_32F, 0) == H.STATUS_INVALID_VALUE
     assert api.acltensorCreateTensorDescriptor(h, C.byref(d), 2, None, None, H.R_32F, 0) == H.STATUS_INVALID_VALUE
     assert api.acltensorCreateTensorDescriptor(h, C.byref(d), 0, lens, None, H.R_32F, 0) == H.STATUS_INVALID_VALUE
-    for unsupported in (H.R_16F, H.R_64F, H.R_8I, H.C_32F, H.R_8F_E5M2):
+    for unsupported in (H.R_64F, H.R_8I, H.C_32F, H.R_8F_E5M2):
         assert api.acltensorCreateTensorDescriptor(h, C.byref(d), 2, lens, None, unsupported, 0) == H.STATUS_NOT_SUPPORTED
-    for ok in (H.R_32F, H.R_16BF, H.R_8F_E4M3, H.R_4F_E2M1, H.R_8F_UE8M0, H.R_64I):
+    for ok in (H.R_32F, H.R_16BF, H.R_16F, H.R_8F_E4M3, H.R_4F_E2M1, H.R_8F_UE8M0, H.R_64I):
         assert api.acltensorCreateTensorDescriptor(h, C.byref(d), 2, lens, None, ok, 0) == H.STATUS_SUCCESS
         assert api.acltensorDestroyTensorDescriptor(d) == H.STATUS_SUCCESS
     assert api.acltensorDestroy(h) == H.STATUS_SUCCESS
@@ -142,9 +142,13 @@ def test_contraction_descriptor_checks(api):
     dBbad = H.create_tensor_descriptor(h, [512, 512], None, H.R_8F_E4M3)
     assert f(h, C.byref(op), dA, mA, H.OP_IDENTITY, dBbad, mB, H.OP_IDENTITY, None, None, H.OP_IDENTITY, dD, mD,
              H.COMPUTE_DESC_32F) == H.STATUS_INVALID_VALUE
-    # output must be bf16; A must be E4M3
+    # output may be bf16, half or float32 (the reference's cast-on-store modes), nothing else
     dD32 = H.create_tensor_descriptor(h, [256, 512], None, H.R_32F)
     assert f(h, C.byref(op), dA, mA, H.OP_IDENTITY, dB, mB, H.OP_IDENTITY, None, None, H.OP_IDENTITY, dD32, mD,
+             H.COMPUTE_DESC_32F) == H.STATUS_SUCCESS
+    api.acltensorDestroyOperationDescriptor(op)
+    dD8 = H.create_tensor_descriptor(h, [256, 512], None, H.R_8F_E4M3)
+    assert f(h, C.byref(op), dA, mA, H.OP_IDENTITY, dB, mB, H.OP_IDENTITY, None, None, H.OP_IDENTITY, dD8, mD,
              H.COMPUTE_DESC_32F) == H.STATUS_NOT_SUPPORTED
     # K must be the contiguous mode of A
     dAt = H.create_tensor_descriptor(h, [256, 1024], [1, 256], H.R_8F_E4M3)

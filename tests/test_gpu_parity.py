@@ -380,6 +380,47 @@ def test_w4a8_mx(cuda_device, M, N, K):
     assert_gemm_ok(got, ref, gold)
 
 
+@pytest.mark.parametrize("kind", ["mx", "mx_pair256", "fp8", "fp8_streamk"])
+@pytest.mark.parametrize("d_dtype", ["float16", "float32"])
+def test_half_and_float32_outputs(cuda_device, kind, d_dtype):
+    """The other two cast-on-store modes of the reference (float32 -> half, float32 -> float32:
+    include/tensor_api/impl/tensor_api/arch/cube/utils/l0c2out_utils.h:122-132) on ragged shapes, with bias, ReLU and
+    a bf16 residual."""
+    import torch
+    M, N, K = (300, 520, 1040) if kind.startswith("mx") else (200, 392, 640)
+    tdt = getattr(torch, d_dtype)
+    code = H.R_16F if d_dtype == "float16" else H.R_32F
+    a = o.normal_f32(28, 0, (M, K), 1.0)
+    w = o.normal_f32(28, 1, (N, K), 1.0 if kind.startswith("mx") else 0.05)
+    bias = o.normal_f32(28, 2, (N,), 0.5)
+    residual = o.normal_f32(28, 3, (M, N), 1.0)
+    out = torch.full((M, N), float("nan"), dtype=tdt, device=cuda_device)
+    if kind.startswith("mx"):
+        MX = H.SCALE_MX_E8M0_VEC32
+        qa, sa = H.quantize(dev_tensor(a, cuda_device), MX)
+        qb, sb = H.quantize(dev_tensor(w, cuda_device), MX)
+        extra = dict(cta_pair=2, tile_n=256) if kind == "mx_pair256" else dict(cta_pair=1)
+        plan = H.Contraction(M, N, K, scale_mode_a=MX, scale_mode_b=MX, activation=H.OP_RELU, bias=True, residual=True,
+                             d_dtype=code, **extra)
+        da, db = o.dequant_mx(to_np(qa), to_np(sa), K), o.dequant_mx(to_np(qb), to_np(sb), K)
+    else:
+        qa, sa = H.quantize(dev_tensor(a, cuda_device), H.SCALE_FP32_1X128)
+        qb, sb = H.quantize(dev_tensor(w, cuda_device), H.SCALE_FP32_128X128)
+        plan = H.Contraction(M, N, K, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128,
+                             activation=H.OP_RELU, bias=True, residual=True, d_dtype=code,
+                             split=H.SPLIT_STREAM_K if kind == "fp8_streamk" else H.SPLIT_DATA_PARALLEL)
+        da, db = o.dequant_fp8_1x128(to_np(qa), to_np(sa)), o.dequant_fp8_128x128(to_np(qb), to_np(sb))
+    with plan as c:
+        c(qa, sa, qb, sb, out, bias=bf16_tensor(bias, cuda_device), residual=bf16_tensor(residual, cuda_device))
+    got = out.float().cpu().numpy().astype(np.float64)
+    ref = o.matmul_ref64(da, db, o.bf16_round(bias), o.ACT_RELU, o.bf16_round(residual))
+    assert np.all(np.isfinite(got))
+    # half keeps 11 significant bits, float32 24: far tighter than the bf16 bound
+    bound = 2.0 ** -10 if d_dtype == "float16" else 2.0 ** -13
+    assert o.maxrel(got, ref) <= bound, o.maxrel(got, ref)
+    assert H.device_status() == 0
+
+
 def test_mx_agrees_with_vendor_mxfp8_gemm(cuda_device):
     """An independent implementation of the same format: the vendor library's MXFP8 GEMM (torch._scaled_mm with E8M0
     scales per 32 K) on the same codes and scales.  Both accumulate in float32 and round once to bf16, so they may
