@@ -344,7 +344,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);    // the block is in registers: free the stage
 #pragma unroll
-                        for (int e = 0; e < 64; ++e) accum[e] = fmaf(__uint_as_float(v[e]), s, accum[e]);
+                        for (int e = 0; e < 64; e += 2) fma_f32x2(accum[e], accum[e + 1], v[e], v[e + 1], s);
                     } else {
                         tcgen05_fence_before();
                         __syncwarp();

@@ -537,6 +537,16 @@ __device__ __forceinline__ float apply_act(float x) {
     return x;
 }
 
+// (a0, a1) += (v0, v1) * s with one packed float32x2 FMA (two IEEE fused multiply-adds, same bits as two fmaf).
+__device__ __forceinline__ void fma_f32x2(float& a0, float& a1, uint32_t v0, uint32_t v1, float s) {
+    unsigned long long acc, v, sc;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(acc) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(v0), "r"(v1));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(sc) : "f"(s));
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(v), "l"(sc));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(acc));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
