@@ -486,18 +486,6 @@ __device__ __forceinline__ void tmem_ld_32x64(uint32_t taddr, uint32_t (&r)[64])
         : "r"(taddr)
         : "memory");
 }
-// Store 4 / 8 consecutive 32-bit columns of this thread's TMEM lane from registers.
-__device__ __forceinline__ void tmem_st_32x4(uint32_t taddr, const uint4& v) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v.x), "r"(v.y),
-                 "r"(v.z), "r"(v.w)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint4& lo, const uint4& hi) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(lo.x),
-                 "r"(lo.y), "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------------------------ cluster
