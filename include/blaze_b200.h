@@ -33,7 +33,14 @@ typedef enum {
 
 /* Element type of the output D: the cast-on-store modes of the reference's fix pipe
  * (include/tensor_api/impl/tensor_api/arch/cube/utils/l0c2out_utils.h:122-132). */
-typedef enum { BLAZE_OUT_BF16 = 0, BLAZE_OUT_F16 = 1, BLAZE_OUT_F32 = 2 } blazeOutType_t;
+typedef enum {
+    BLAZE_OUT_BF16 = 0,
+    BLAZE_OUT_F16 = 1,
+    BLAZE_OUT_F32 = 2,
+    BLAZE_OUT_MX_E4M3 = 3 /* MX GEMM only: D leaves quantised - E4M3 codes [M][ldd bytes] plus E8M0 scales
+                             scaleD [M][ceil(N/64)*2], one per 32 columns: the A operand of the next MX GEMM, bit-equal
+                             to blazeQuantizeMx applied to the float32 result */
+} blazeOutType_t;
 
 /* Fused activation, applied after bias and before the residual add. */
 typedef enum { BLAZE_ACT_IDENTITY = 0, BLAZE_ACT_RELU = 1, BLAZE_ACT_GELU_TANH = 2 } blazeActivation_t;
@@ -83,6 +90,7 @@ typedef struct {
     size_t workspace_bytes;
     int32_t d_type;          /* blazeOutType_t of D (ldd counts elements of that type) */
     int32_t reserved;
+    void* scaleD;            /* device, E8M0 scales of D when d_type is BLAZE_OUT_MX_E4M3, else NULL */
 } blazeMxGemmArgs;
 
 BLAZE_API int blazeMxGemmWorkspaceSize(const blazeMxGemmArgs* args, size_t* bytes);

@@ -24,6 +24,8 @@ struct EpilogueArgs {
     const __nv_bfloat16* residual;
     long long ldr;
     int out_type;       // OutType of D; the tensor map handed to the store has the matching element size and box
+    uint8_t* scale_d;   // OUT_MX_E4M3: E8M0 scales of D, [M][scale_cols_d]
+    int scale_cols_d;   // ceil(N / 64) * 2
 };
 
 // Drains one accumulator tile.  `tmem_tile` = TMEM address of column 0 of the accumulator, lane field already set to
@@ -112,6 +114,57 @@ __device__ __forceinline__ void epilogue_store_tile_from(uint32_t tmem_tile, con
                 }
                 ++chunk_counter;
             }
+            continue;
+        }
+
+        if (ea.out_type == OUT_MX_E4M3) {
+            // this thread's 32 columns are one MX group of its row: scale from the largest magnitude, then the codes,
+            // by the rules of the stand-alone quantiser (quant_mx_kernel)
+            uint32_t m = 0;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                if (n0 + (e & ~7) >= ea.N) v[e] = 0;                  // columns beyond the matrix do not exist
+                m = max(m, v[e] & 0x7FFFFFFFu);
+            }
+            const bool has_nan = m > 0x7F800000u;
+            float amax = __uint_as_float(m);
+            if (has_nan) {
+                amax = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) amax = fmaxf(amax, fabsf(__uint_as_float(v[e])));
+            }
+            const int field = (__float_as_uint(amax) >> 23) & 0xFF;
+            int byte = min(max(field - 8, 0), 254);
+            if (amax == 0.0f) byte = 127;
+            const int eff = byte;
+            if (has_nan) byte = 255;
+            const float inv =
+                (eff == 254) ? __uint_as_float(0x00400000u) : __uint_as_float((uint32_t)(254 - eff) << 23);
+            uint32_t codes[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                codes[e] = cvt_e4m3x4_sat(__uint_as_float(v[4 * e]) * inv, __uint_as_float(v[4 * e + 1]) * inv,
+                                          __uint_as_float(v[4 * e + 2]) * inv, __uint_as_float(v[4 * e + 3]) * inv);
+            }
+            if (row_ok) {
+                const int g = n0 >> 5;
+                uint8_t* srow = ea.scale_d + (long long)row * ea.scale_cols_d;
+                srow[g] = (uint8_t)byte;
+                if (n0 + 32 >= ea.N && g + 1 < ea.scale_cols_d) srow[g + 1] = 127;      // pad column of an odd count
+            }
+            uint8_t* block = stage + (chunk_counter & 1) * (32 * 64);
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+            uint8_t* my_row = block + lane * 32;                      // 32 rows x 32 bytes, no swizzle
+            *reinterpret_cast<uint4*>(my_row) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+            *reinterpret_cast<uint4*>(my_row + 16) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(tmap_d, block, n0, row0);
+                tma_store_commit();
+            }
+            ++chunk_counter;
             continue;
         }
 

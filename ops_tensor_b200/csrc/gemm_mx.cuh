@@ -40,6 +40,8 @@ struct MxGemmParams {
     uint32_t b_tx_shift;           // 1 when the B loads credit the barrier with the packed (half) byte count, else 0
     uint32_t a_format, a_tx_shift; // the same two for A
     int out_type;                  // OutType of D
+    uint8_t* scale_d;              // OUT_MX_E4M3: [M][scale_cols_d] E8M0 scales of D
+    int scale_cols_d;
 };
 
 template <int kBN, int kStages>
@@ -204,7 +206,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         bool ok = true;
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         uint8_t* stage_buf = smem + L::kEpiOffset + warp * kEpiStageBytesPerWarp;
-        const EpilogueArgs ea{p.M, p.N, p.bias, p.residual, p.ldr, p.out_type};
+        const EpilogueArgs ea{p.M, p.N, p.bias, p.residual, p.ldr, p.out_type, p.scale_d, p.scale_cols_d};
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             int mt, nt;
             tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);

@@ -36,6 +36,7 @@ int out_type_of(acltensorDataType_t t) {
     switch (t) {
         case ACLTENSOR_R_16F: return BLAZE_OUT_F16;
         case ACLTENSOR_R_32F: return BLAZE_OUT_F32;
+        case ACLTENSOR_R_8F_E4M3: return BLAZE_OUT_MX_E4M3;
         default: return BLAZE_OUT_BF16;
     }
 }
@@ -102,6 +103,7 @@ acltensorStatus_t MxExecute(const ContractionArgs& c) {
     a.bias = c.bias;
     a.residual = c.C;
     a.D = c.D;
+    a.scaleD = c.scaleD;
     a.reuse_b_prepass = c.reuseBPrepass ? 1 : 0;
     a.workspace = c.workspace;
     a.workspace_bytes = c.workspaceSize;
@@ -134,6 +136,7 @@ void fill_fp8_args(const acltensorOperationDescriptor& op, int32_t splitPolicy, 
 
 acltensorStatus_t Fp8Workspace(const acltensorOperationDescriptor& op, int32_t splitPolicy, uint64_t* bytes) {
     if (op.batchModes > 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;          // batch broadcast is an MX feature
+    if (op.descD->dataType == ACLTENSOR_R_8F_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;   // so is the quantised output
     blazeFp8GemmArgs a;
     fill_fp8_args(op, splitPolicy, &a);
     size_t n = 0;
@@ -191,8 +194,9 @@ acltensorStatus_t acltensorCreateContraction(const acltensorHandle_t handle, acl
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (descB->dataType != ACLTENSOR_R_8F_E4M3 && descB->dataType != ACLTENSOR_R_4F_E2M1)
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    // output: the three cast-on-store modes (bf16, half, float32)
-    if (descD->dataType != ACLTENSOR_R_16BF && descD->dataType != ACLTENSOR_R_16F && descD->dataType != ACLTENSOR_R_32F)
+    // output: the three cast-on-store modes (bf16, half, float32), or E4M3 codes for the quantising epilogue
+    if (descD->dataType != ACLTENSOR_R_16BF && descD->dataType != ACLTENSOR_R_16F && descD->dataType != ACLTENSOR_R_32F &&
+        descD->dataType != ACLTENSOR_R_8F_E4M3)
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (descC != nullptr && descC->dataType != ACLTENSOR_R_16BF) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     // D = [batch..., m, n] with up to four batch modes; A = [its batch modes..., m, k]; B = [its batch modes..., n, k]
@@ -333,6 +337,7 @@ int32_t* attribute_slot(acltensorOperationDescriptor* d, acltensorOperationDescr
         case ACLTENSOR_OPERATION_DESCRIPTOR_B_IS_STATIC: return &d->bIsStatic;
         case ACLTENSOR_OPERATION_DESCRIPTOR_CTA_PAIR: return &d->ctaPair;
         case ACLTENSOR_OPERATION_DESCRIPTOR_BIAS_PER_BATCH: return &d->biasPerBatch;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_SCALE_MODE_D: return &d->scaleModeD;
         default: return nullptr;
     }
 }
@@ -380,6 +385,9 @@ acltensorStatus_t acltensorOperationDescriptorSetAttribute(const acltensorHandle
             break;
         case ACLTENSOR_OPERATION_DESCRIPTOR_BIAS_PER_BATCH:
             if (v < 0 || v > 1) return ACLTENSOR_STATUS_INVALID_VALUE;
+            break;
+        case ACLTENSOR_OPERATION_DESCRIPTOR_SCALE_MODE_D:
+            if (v != ACLTENSOR_SCALE_NONE && v != ACLTENSOR_SCALE_MX_E8M0_VEC32) return ACLTENSOR_STATUS_NOT_SUPPORTED;
             break;
         default:
             break;
@@ -493,6 +501,10 @@ acltensorStatus_t acltensorContract(const acltensorHandle_t handle, const aclten
     if (aux->scaleA == nullptr || aux->scaleB == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (op->biasType >= 0 && aux->bias == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (op->groupCount > 0 && aux->groupList == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    // a quantised D needs its scale mode declared and somewhere to put the scales, and nothing else may ask for them
+    const bool quantD = op->descD->dataType == ACLTENSOR_R_8F_E4M3;
+    if (quantD != (op->scaleModeD == ACLTENSOR_SCALE_MX_E8M0_VEC32)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (quantD && aux->scaleD == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (workspaceSize < plan->requiredWorkspace) return ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE;
     if (plan->requiredWorkspace > 0 && workspace == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
 
@@ -507,6 +519,7 @@ acltensorStatus_t acltensorContract(const acltensorHandle_t handle, const aclten
     args.scaleB = aux->scaleB;
     args.bias = op->biasType >= 0 ? aux->bias : nullptr;
     args.groupList = op->groupCount > 0 ? aux->groupList : nullptr;
+    args.scaleD = quantD ? aux->scaleD : nullptr;
     args.workspace = workspace;
     args.workspaceSize = workspaceSize;
     args.stream = stream;

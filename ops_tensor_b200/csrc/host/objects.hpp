@@ -104,6 +104,7 @@ struct acltensorOperationDescriptor {
     int32_t batchModes = 0;                           // leading batch modes of D (0..4)
     int32_t batchC[4] = {1, 1, 1, 1}, batchA[4] = {1, 1, 1, 1}, batchB[4] = {1, 1, 1, 1};   // right-aligned extents
     int32_t biasPerBatch = 0;                         // bias is [batches][N] instead of [N]
+    int32_t scaleModeD = ACLTENSOR_SCALE_NONE;        // MX_E8M0_VEC32: the epilogue quantises D
 
     size_t getTotalElements() const { return descD ? descD->totalElements : 0; }
     acltensorDataType_t getDataType() const { return descD ? descD->dataType : ACLTENSOR_R_32F; }

@@ -177,6 +177,7 @@ struct ContractionArgs {
     const void* scaleB = nullptr;
     const void* bias = nullptr;
     const void* groupList = nullptr;
+    void* scaleD = nullptr;
     void* workspace = nullptr;
     uint64_t workspaceSize = 0;
     bool reuseBPrepass = false;

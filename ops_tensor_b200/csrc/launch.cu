@@ -113,9 +113,16 @@ static bool make_tmap_store(CUtensorMap* map, void* base, uint64_t cols, uint64_
     if (!fn) return false;
     const bool f32 = out_type == BLAZE_OUT_F32;
     const cuuint64_t dims[2] = {cols, rows};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    if (out_type == BLAZE_OUT_MX_E4M3) {                    // one-byte codes: 32 x 32-byte blocks, no swizzle
+        const cuuint64_t strides8[1] = {ld_elems};
+        const cuuint32_t box8[2] = {32, 32};
+        return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides8, box8, elem_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
     const cuuint64_t strides[1] = {ld_elems * (f32 ? 4 : 2)};
     const cuuint32_t box[2] = {f32 ? 16u : 32u, 32};
-    const cuuint32_t elem_strides[2] = {1, 1};
     const CUtensorMapDataType dt = f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                        : (out_type == BLAZE_OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
@@ -182,7 +189,7 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scal
     if (a->M < 0 || a->N < 0 || a->K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->b_elem != BLAZE_ELEM_E4M3 && a->b_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->a_elem != BLAZE_ELEM_E4M3 && a->a_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    if (a->d_type < BLAZE_OUT_BF16 || a->d_type > BLAZE_OUT_F32) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->d_type < BLAZE_OUT_BF16 || a->d_type > BLAZE_OUT_MX_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     // legal operand pairs: FP8 x FP8, FP8 x FP4 (W4A8) and FP4 x FP4; a 4-bit A is only read natively
     if (a->a_elem == BLAZE_ELEM_E2M1 && (a->b_elem != BLAZE_ELEM_E2M1 || (a->K % 128) != 0))
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
@@ -328,6 +335,9 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
     p.b_format = tb_packed ? FMT_E2M1 : FMT_E4M3;
     p.b_tx_shift = tb_packed ? 1 : 0;        // a 4-bit load reports the bytes it read, not the bytes it wrote
     p.out_type = a->d_type;
+    p.scale_d = static_cast<uint8_t*>(a->scaleD);
+    p.scale_cols_d = ((a->N + 63) / 64) * 2;
+    if (a->d_type == BLAZE_OUT_MX_E4M3 && (!a->scaleD || (a->ldd % 16) != 0)) return ACLTENSOR_STATUS_INVALID_VALUE;
     p.a_format = ta_packed ? FMT_E2M1 : FMT_E4M3;
     p.a_tx_shift = ta_packed ? 1 : 0;
 

@@ -10,6 +10,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 namespace blaze {
 
@@ -547,6 +548,16 @@ __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
 
 // Output element types of the fused epilogues: the cast-on-store modes of the reference's fix pipe (float32 ->
 // bf16 / half / float32: include/tensor_api/impl/tensor_api/arch/cube/utils/l0c2out_utils.h:122-132).
-enum OutType : int { OUT_BF16 = 0, OUT_F16 = 1, OUT_F32 = 2 };
+// OUT_MX_E4M3 is the fused quantising output: E4M3 codes plus one E8M0 scale byte per 32 consecutive columns of a row,
+// the operand format of the next MX GEMM (the reference plans this as its epilogue extension:
+// docs/API/epilogue/block/block_epilogue.md:133; fix-pipe FP8 quant modes l0c2out_utils.h:75-76).
+enum OutType : int { OUT_BF16 = 0, OUT_F16 = 1, OUT_F32 = 2, OUT_MX_E4M3 = 3 };
+
+// Four floats -> four E4M3 bytes (x in the low byte), round-to-nearest-even, saturating.
+__device__ __forceinline__ uint32_t cvt_e4m3x4_sat(float x, float y, float z, float w) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(x, y), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(z, w), __NV_SATFINITE, __NV_E4M3);
+    return (lo & 0xFFFFu) | (hi << 16);
+}
 
 }  // namespace blaze

@@ -21,7 +21,7 @@ WORKSPACE_MIN, WORKSPACE_DEFAULT, WORKSPACE_MAX = 1, 2, 3
 SCALE_NONE, SCALE_MX_E8M0_VEC32, SCALE_FP32_1X128, SCALE_FP32_128X128 = 0, 1, 2, 3
 SPLIT_AUTO, SPLIT_DATA_PARALLEL, SPLIT_STREAM_K = 0, 1, 2
 (ATTR_SCALE_MODE_A, ATTR_SCALE_MODE_B, ATTR_EPILOGUE_ACT, ATTR_BIAS_TYPE, ATTR_GROUP_COUNT, ATTR_SPLIT_POLICY,
- ATTR_TILE_N, ATTR_SM_LIMIT, ATTR_B_IS_STATIC, ATTR_CTA_PAIR, ATTR_BIAS_PER_BATCH) = range(1, 12)
+ ATTR_TILE_N, ATTR_SM_LIMIT, ATTR_B_IS_STATIC, ATTR_CTA_PAIR, ATTR_BIAS_PER_BATCH, ATTR_SCALE_MODE_D) = range(1, 13)
 
 STATUS_SUCCESS = 0
 STATUS_NOT_INITIALIZED = 1
@@ -35,7 +35,8 @@ STATUS_INSUFFICIENT_WORKSPACE = 19
 
 
 class ContractionAux(C.Structure):
-    _fields_ = [("scaleA", C.c_void_p), ("scaleB", C.c_void_p), ("bias", C.c_void_p), ("groupList", C.c_void_p)]
+    _fields_ = [("scaleA", C.c_void_p), ("scaleB", C.c_void_p), ("bias", C.c_void_p), ("groupList", C.c_void_p),
+                ("scaleD", C.c_void_p)]
 
 
 _PROTOTYPES = {
@@ -232,6 +233,8 @@ class Contraction:
               "acltensorCreateContraction")
         if bias_per_batch:
             set_attribute(self.handle, self.op, ATTR_BIAS_PER_BATCH, 1)
+        if d_dtype == R_8F_E4M3:
+            set_attribute(self.handle, self.op, ATTR_SCALE_MODE_D, SCALE_MX_E8M0_VEC32)
         set_attribute(self.handle, self.op, ATTR_SCALE_MODE_A, scale_mode_a)
         set_attribute(self.handle, self.op, ATTR_SCALE_MODE_B, scale_mode_b)
         set_attribute(self.handle, self.op, ATTR_EPILOGUE_ACT, activation)
@@ -256,14 +259,15 @@ class Contraction:
         self._workspace = None
 
     def __call__(self, a, scale_a, b, scale_b, out, *, bias=None, residual=None, group_rows=None, workspace=None,
-                 stream=None):
+                 stream=None, scale_out=None):
         import torch
         if workspace is None:
             if self._workspace is None and self.workspace_bytes:
                 self._workspace = torch.empty(self.workspace_bytes, dtype=torch.uint8, device=a.device)
             workspace = self._workspace
         aux = ContractionAux(scale_a.data_ptr(), scale_b.data_ptr(), bias.data_ptr() if bias is not None else None,
-                             group_rows.data_ptr() if group_rows is not None else None)
+                             group_rows.data_ptr() if group_rows is not None else None,
+                             scale_out.data_ptr() if scale_out is not None else None)
         if stream is None:
             stream = torch.cuda.current_stream().cuda_stream
         check(api.acltensorContract(self.handle, self.plan, None, a.data_ptr(), b.data_ptr(), None,

@@ -24,13 +24,14 @@ STATUS_INSUFFICIENT_WORKSPACE = 19
 ELEM_E4M3, ELEM_E2M1 = 0, 1
 ACT_IDENTITY, ACT_RELU, ACT_GELU_TANH = 0, 1, 2
 SCHED_AUTO, SCHED_DATA_PARALLEL, SCHED_STREAM_K = 0, 1, 2
-OUT_BF16, OUT_F16, OUT_F32 = 0, 1, 2
+OUT_BF16, OUT_F16, OUT_F32, OUT_MX_E4M3 = 0, 1, 2, 3
 
 
 def out_type_of(tensor) -> int:
     """blazeOutType_t of a torch output tensor (bf16, half or float32)."""
     import torch
-    return {torch.bfloat16: OUT_BF16, torch.float16: OUT_F16, torch.float32: OUT_F32}[tensor.dtype]
+    return {torch.bfloat16: OUT_BF16, torch.float16: OUT_F16, torch.float32: OUT_F32,
+            torch.uint8: OUT_MX_E4M3}[tensor.dtype]
 
 
 class MxGemmArgs(C.Structure):
@@ -52,6 +53,7 @@ class MxGemmArgs(C.Structure):
         ("a_elem", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("d_type", C.c_int32), ("reserved", C.c_int32),
+        ("scaleD", C.c_void_p),
     ]
 
 
@@ -200,7 +202,8 @@ def quantize_fp8_blocks(w):
 # ------------------------------------------------------------------------------------------------ GEMMs
 
 def mx_gemm_args(a, sa, b, sb, out, *, b_elem=ELEM_E4M3, bias=None, residual=None, activation=ACT_IDENTITY,
-                 tile_n=0, reuse_b_prepass=False, sm_limit=0, cta_pair=0, workspace=None, a_elem=ELEM_E4M3) -> MxGemmArgs:
+                 tile_n=0, reuse_b_prepass=False, sm_limit=0, cta_pair=0, workspace=None, a_elem=ELEM_E4M3,
+                 scale_out=None) -> MxGemmArgs:
     M, K = a.shape
     if a_elem == ELEM_E2M1:
         K *= 2                       # two codes per byte
@@ -223,6 +226,7 @@ def mx_gemm_args(a, sa, b, sb, out, *, b_elem=ELEM_E4M3, bias=None, residual=Non
     args.sm_limit = sm_limit
     args.cta_pair = cta_pair
     args.a_elem = a_elem
+    args.scaleD = scale_out.data_ptr() if scale_out is not None else None
     if workspace is not None:
         args.workspace, args.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
     return args

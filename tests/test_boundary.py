@@ -147,7 +147,7 @@ def test_contraction_descriptor_checks(api):
     assert f(h, C.byref(op), dA, mA, H.OP_IDENTITY, dB, mB, H.OP_IDENTITY, None, None, H.OP_IDENTITY, dD32, mD,
              H.COMPUTE_DESC_32F) == H.STATUS_SUCCESS
     api.acltensorDestroyOperationDescriptor(op)
-    dD8 = H.create_tensor_descriptor(h, [256, 512], None, H.R_8F_E4M3)
+    dD8 = H.create_tensor_descriptor(h, [256, 512], None, H.R_64I)
     assert f(h, C.byref(op), dA, mA, H.OP_IDENTITY, dB, mB, H.OP_IDENTITY, None, None, H.OP_IDENTITY, dD8, mD,
              H.COMPUTE_DESC_32F) == H.STATUS_NOT_SUPPORTED
     # K must be the contiguous mode of A

@@ -421,6 +421,49 @@ def test_half_and_float32_outputs(cuda_device, kind, d_dtype):
     assert H.device_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K,pair", [(300, 520, 1040, 1), (300, 520, 1040, 2), (136, 96, 256, 1), (512, 1024, 512, 2)])
+def test_mx_quantised_output_feeds_the_next_gemm(cuda_device, M, N, K, pair):
+    """Fused quantising epilogue: D leaves as E4M3 codes + one E8M0 byte per 32 columns.  The float32-output run of
+    the same call holds the very values the epilogue quantises, so the codes and scales must be bit-equal to the
+    oracle's quantiser applied to it (including the pad byte of an odd group count); then the pair is used, as it is,
+    as the A operand of a second MX GEMM."""
+    import torch
+    from ops_tensor_b200 import native
+    a = o.normal_f32(29, 0, (M, K), 1.0)
+    w1 = o.normal_f32(29, 1, (N, K), 1.0)
+    bias = bf16_tensor(o.normal_f32(29, 2, (N,), 0.5), cuda_device)
+    qa, sa = H.quantize(dev_tensor(a, cuda_device), H.SCALE_MX_E8M0_VEC32)
+    qb, sb = H.quantize(dev_tensor(w1, cuda_device), H.SCALE_MX_E8M0_VEC32)
+    kw = dict(bias=bias, activation=native.ACT_GELU_TANH, cta_pair=pair)
+    f32 = native.mx_gemm(qa, sa, qb, sb, out=torch.empty((M, N), dtype=torch.float32, device=cuda_device), **kw)
+    pitch = -(-N // 16) * 16                               # rows of one-byte codes must start 16 bytes apart
+    codes = torch.full((M, pitch), 0xAA, dtype=torch.uint8, device=cuda_device)[:, :N]
+    scales = torch.full((M, native.mx_scale_cols(N)), 0xAA, dtype=torch.uint8, device=cuda_device)
+    native.mx_gemm(qa, sa, qb, sb, out=codes, scale_out=scales, **kw)
+    want_codes, want_scales = o.quant_mx(to_np(f32))
+    assert np.array_equal(to_np(scales), want_scales)
+    assert np.array_equal(to_np(codes.contiguous()), want_codes)
+    if N % 16 == 0:
+        # the same through the host API: D described as E4M3 with SCALE_MODE_D = MX
+        codes2 = torch.zeros((M, N), dtype=torch.uint8, device=cuda_device)
+        scales2 = torch.zeros_like(scales)
+        with H.Contraction(M, N, K, scale_mode_a=H.SCALE_MX_E8M0_VEC32, scale_mode_b=H.SCALE_MX_E8M0_VEC32,
+                           activation=H.OP_GELU, bias=True, cta_pair=pair, d_dtype=H.R_8F_E4M3) as c:
+            c(qa, sa, qb, sb, codes2, bias=bias, scale_out=scales2)
+            with pytest.raises(Exception):
+                c(qa, sa, qb, sb, codes2, bias=bias)                   # nowhere to put the scales
+        assert torch.equal(codes2, codes.contiguous()) and torch.equal(scales2, scales)
+    # second layer: D (quantised) x W2^T
+    N2 = 264
+    w2 = o.normal_f32(29, 3, (N2, N), 0.1)
+    if N % 16 == 0:
+        qb2, sb2 = H.quantize(dev_tensor(w2, cuda_device), H.SCALE_MX_E8M0_VEC32)
+        out2 = native.mx_gemm(codes, scales, qb2, sb2)
+        ref = o.matmul_ref64(o.dequant_mx(want_codes, want_scales, N), o.dequant_mx(to_np(qb2), to_np(sb2), N))
+        assert_gemm_ok(to_np(out2), ref)
+    assert H.device_status() == 0
+
+
 def test_mx_agrees_with_vendor_mxfp8_gemm(cuda_device):
     """An independent implementation of the same format: the vendor library's MXFP8 GEMM (torch._scaled_mm with E8M0
     scales per 32 K) on the same codes and scales.  Both accumulate in float32 and round once to bf16, so they may
