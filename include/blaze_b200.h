@@ -37,9 +37,12 @@ typedef enum {
     BLAZE_OUT_BF16 = 0,
     BLAZE_OUT_F16 = 1,
     BLAZE_OUT_F32 = 2,
-    BLAZE_OUT_MX_E4M3 = 3 /* MX GEMM only: D leaves quantised - E4M3 codes [M][ldd bytes] plus E8M0 scales
-                             scaleD [M][ceil(N/64)*2], one per 32 columns: the A operand of the next MX GEMM, bit-equal
-                             to blazeQuantizeMx applied to the float32 result */
+    BLAZE_OUT_MX_E4M3 = 3, /* MX GEMM only: D leaves quantised - E4M3 codes [M][ldd bytes] plus E8M0 scales
+                              scaleD [M][ceil(N/64)*2], one per 32 columns: the A operand of the next MX GEMM, bit-equal
+                              to blazeQuantizeMx applied to the float32 result */
+    BLAZE_OUT_FP8_128 = 4  /* FP8 GEMM only: E4M3 codes [M][ldd bytes] plus float32 scales scaleD [M][ceil(N/128)]
+                              (amax / 448 per 128 columns): the A operand of the next FP8 GEMM, bit-equal to
+                              blazeQuantizeFp8RowGroups applied to the float32 result */
 } blazeOutType_t;
 
 /* Fused activation, applied after bias and before the residual add. */
@@ -174,6 +177,7 @@ typedef struct {
     int32_t d_type;   /* blazeOutType_t of D */
     void* workspace;
     size_t workspace_bytes;
+    void* scaleD;     /* device float32 scales of D when d_type is BLAZE_OUT_FP8_128, else NULL */
 } blazeFp8GemmArgs;
 
 BLAZE_API int blazeFp8GemmWorkspaceSize(const blazeFp8GemmArgs* args, size_t* bytes);

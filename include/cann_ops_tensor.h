@@ -120,7 +120,7 @@ typedef struct {
     const void* scaleB;    /* scales of B, layout given by SCALE_MODE_B */
     const void* bias;      /* bf16[n], when BIAS_TYPE is set */
     const void* groupList; /* int64[groups]: rows of A per group, when GROUP_COUNT > 0 */
-    void* scaleD;          /* output: E8M0 scales of D [m][ceil(n/64)*2], when SCALE_MODE_D is MX_E8M0_VEC32 */
+    void* scaleD;          /* output, when SCALE_MODE_D is set: E8M0 [m][ceil(n/64)*2] or float32 [m][ceil(n/128)] */
 } acltensorContractionAux_t;
 
 /*

@@ -42,6 +42,7 @@ struct Fp8GemmParams {
     int stream_k;                   // 1: split the (tile, k-block) units evenly over the grid
     float* partials;                // [gridDim.x][32 column quads][128 rows][4] fp32 (stream-K only)
     int out_type;                   // OutType of D (ldd counts elements of that type)
+    float* scale_d;                 // OUT_FP8_128: [M][n_blocks] float32 scales of D
     int* flags;                     // [gridDim.x], zeroed before the launch (stream-K only)
     int* status;
 };
@@ -54,11 +55,12 @@ struct Fp8GemmSmem {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarOffset = kStages * kStageBytes;
     static constexpr int kAccStages = 4;
-    // full[kStages], empty[kStages], tmem_full[4], tmem_empty[4], fixup
-    static constexpr int kNumBars = 2 * kStages + 2 * kAccStages + 1;
+    // full[kStages], empty[kStages], tmem_full[4], tmem_empty[4], fixup, amax exchange
+    static constexpr int kNumBars = 2 * kStages + 2 * kAccStages + 2;
     static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
     static constexpr int kGroupOffset = kMiscOffset + 16;       // int row_start[G+1], int mtile_start[G+1]
-    static constexpr int kTotal = kGroupOffset + 2 * (kFp8MaxGroups + 1) * 4;
+    static constexpr int kAmaxOffset = kGroupOffset + 2 * (kFp8MaxGroups + 1) * 4;   // float amax[2 tiles][2 halves][128]
+    static constexpr int kTotal = kAmaxOffset + 2 * 2 * 128 * 4;
     static constexpr int kDynamicBytes = kTotal + 1024;
     static constexpr uint32_t kTxBytes = kABytes + kBBytes;
 };
@@ -175,6 +177,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     uint64_t* tmem_full_bar = bars + 2 * kStages;
     uint64_t* tmem_empty_bar = tmem_full_bar + kAccStages;
     uint64_t* fix_bar = tmem_empty_bar + kAccStages;
+    uint64_t* amax_bar = fix_bar + 1;              // the 256 promotion threads, once per quantised output tile
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
     int* row_start = reinterpret_cast<int*>(smem + L::kGroupOffset);
@@ -193,6 +196,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             mbar_init(&tmem_empty_bar[s], 8);
         }
         mbar_init(fix_bar, 256);
+        mbar_init(amax_bar, 256);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -294,6 +298,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
+        float* amax_smem = reinterpret_cast<float*>(smem + L::kAmaxOffset);
+        int tile_parity = 0;
         const int quad = warp & 3;                      // TMEM lane quadrant this warp may read
         const int half = warp >> 2;                     // which 64 of the tile's 128 columns
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
@@ -413,38 +419,88 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 if (!ok) break;
             }
 
-            // -------- fused epilogue: bias, activation, residual, bf16; 128 contiguous bytes per thread
-            if (row_ok) {
+            // -------- fused epilogue: bias, activation, residual, cast; 64 consecutive outputs per thread
+            const __nv_bfloat16* r_row = (p.residual && row_ok) ? p.residual + (long long)row * p.ldr : nullptr;
+            float row_amax = 0.0f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int n = seg.nt * 128 + c0 + q * 8;
+                if (row_ok && n < p.N) {
+                    float x[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) x[e] = accum[q * 8 + e];
+                    if (p.bias) {
+                        const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
+                        const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            x[2 * e] += __uint_as_float(bw[e] << 16);
+                            x[2 * e + 1] += __uint_as_float(bw[e] & 0xFFFF0000u);
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) x[e] = apply_act<kAct>(x[e]);
+                    if (r_row) {
+                        const uint4 rv = *reinterpret_cast<const uint4*>(r_row + n);
+                        const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            x[2 * e] += __uint_as_float(rw[e] << 16);
+                            x[2 * e + 1] += __uint_as_float(rw[e] & 0xFFFF0000u);
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        accum[q * 8 + e] = x[e];
+                        row_amax = fmaxf(row_amax, fabsf(x[e]));
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) accum[q * 8 + e] = 0.0f;
+                }
+            }
+            if (p.out_type == OUT_FP8_128) {
+                // Quantising output: one float32 scale per row per 128 columns (this tile's width), amax / 448, and
+                // E4M3 codes of x / scale - the A operand of the next FP8 GEMM, by the rules of quant_fp8_1x128_kernel.
+                // The two warps that share a row (column halves) exchange their maxima through shared memory.
+                float* amax_buf = amax_smem + (tile_parity * 2) * 128;
+                amax_buf[half * 128 + r_in_tile] = row_amax;
+                mbar_arrive(amax_bar);                                     // all eight promotion warps
+                ok = mbar_wait(amax_bar, (uint32_t)tile_parity, abort_flag, p.status, DEV_TIMEOUT_FIXUP_FLAG);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const float amax = fmaxf(row_amax, amax_buf[(half ^ 1) * 128 + r_in_tile]);
+                tile_parity ^= 1;
+                const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 448.0f);
+                if (row_ok) {
+                    uint8_t* d_row = reinterpret_cast<uint8_t*>(p.D) + (long long)row * p.ldd;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int n = seg.nt * 128 + c0 + q * 16;
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            w[e] = cvt_e4m3x4_sat(__fdiv_rn(accum[q * 16 + 4 * e], scale),
+                                                  __fdiv_rn(accum[q * 16 + 4 * e + 1], scale),
+                                                  __fdiv_rn(accum[q * 16 + 4 * e + 2], scale),
+                                                  __fdiv_rn(accum[q * 16 + 4 * e + 3], scale));
+                        }
+                        if (n + 8 < p.N) {
+                            *reinterpret_cast<uint4*>(d_row + n) = make_uint4(w[0], w[1], w[2], w[3]);
+                        } else if (n < p.N) {
+                            *reinterpret_cast<uint2*>(d_row + n) = make_uint2(w[0], w[1]);
+                        }
+                    }
+                    if (half == 0 && seg.nt * 128 < p.N) p.scale_d[(long long)row * p.n_blocks + seg.nt] = scale;
+                }
+            } else if (row_ok) {
                 const int elem_bytes = p.out_type == OUT_F32 ? 4 : 2;
                 uint8_t* d_row = reinterpret_cast<uint8_t*>(p.D) + (long long)row * p.ldd * elem_bytes;
-                const __nv_bfloat16* r_row = p.residual ? p.residual + (long long)row * p.ldr : nullptr;
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     const int n = seg.nt * 128 + c0 + q * 8;
                     if (n < p.N) {
-                        float x[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) x[e] = accum[q * 8 + e];
-                        if (p.bias) {
-                            const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + n));
-                            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                x[2 * e] += __uint_as_float(bw[e] << 16);
-                                x[2 * e + 1] += __uint_as_float(bw[e] & 0xFFFF0000u);
-                            }
-                        }
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) x[e] = apply_act<kAct>(x[e]);
-                        if (r_row) {
-                            const uint4 rv = *reinterpret_cast<const uint4*>(r_row + n);
-                            const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                x[2 * e] += __uint_as_float(rw[e] << 16);
-                                x[2 * e + 1] += __uint_as_float(rw[e] & 0xFFFF0000u);
-                            }
-                        }
+                        const float* x = accum + q * 8;
                         if (p.out_type == OUT_F32) {
                             float4* dst = reinterpret_cast<float4*>(d_row + (long long)n * 4);
                             dst[0] = make_float4(x[0], x[1], x[2], x[3]);

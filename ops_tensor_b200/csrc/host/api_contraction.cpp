@@ -129,14 +129,13 @@ void fill_fp8_args(const acltensorOperationDescriptor& op, int32_t splitPolicy, 
     a->ldr = op.ldc;
     a->ldd = op.ldd;
     a->activation = activation_of(op.epilogueAct);
-    a->d_type = out_type_of(op.descD->dataType);
+    a->d_type = op.descD->dataType == ACLTENSOR_R_8F_E4M3 ? BLAZE_OUT_FP8_128 : out_type_of(op.descD->dataType);
     a->sched = sched_of(splitPolicy);
     a->sm_limit = op.smLimit;
 }
 
 acltensorStatus_t Fp8Workspace(const acltensorOperationDescriptor& op, int32_t splitPolicy, uint64_t* bytes) {
     if (op.batchModes > 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;          // batch broadcast is an MX feature
-    if (op.descD->dataType == ACLTENSOR_R_8F_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;   // so is the quantised output
     blazeFp8GemmArgs a;
     fill_fp8_args(op, splitPolicy, &a);
     size_t n = 0;
@@ -156,6 +155,7 @@ acltensorStatus_t Fp8Execute(const ContractionArgs& c) {
     a.bias = c.bias;
     a.residual = c.C;
     a.D = c.D;
+    a.scaleD = c.scaleD;
     a.workspace = c.workspace;
     a.workspace_bytes = c.workspaceSize;
     return static_cast<acltensorStatus_t>(blazeFp8Gemm(&a, c.stream));
@@ -387,7 +387,8 @@ acltensorStatus_t acltensorOperationDescriptorSetAttribute(const acltensorHandle
             if (v < 0 || v > 1) return ACLTENSOR_STATUS_INVALID_VALUE;
             break;
         case ACLTENSOR_OPERATION_DESCRIPTOR_SCALE_MODE_D:
-            if (v != ACLTENSOR_SCALE_NONE && v != ACLTENSOR_SCALE_MX_E8M0_VEC32) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+            if (v != ACLTENSOR_SCALE_NONE && v != ACLTENSOR_SCALE_MX_E8M0_VEC32 && v != ACLTENSOR_SCALE_FP32_1X128)
+                return ACLTENSOR_STATUS_NOT_SUPPORTED;
             break;
         default:
             break;
@@ -503,7 +504,9 @@ acltensorStatus_t acltensorContract(const acltensorHandle_t handle, const aclten
     if (op->groupCount > 0 && aux->groupList == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     // a quantised D needs its scale mode declared and somewhere to put the scales, and nothing else may ask for them
     const bool quantD = op->descD->dataType == ACLTENSOR_R_8F_E4M3;
-    if (quantD != (op->scaleModeD == ACLTENSOR_SCALE_MX_E8M0_VEC32)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    // the output is quantised the way the A operand is: MX kernels emit MX scales, the FP8 kernel 1x128 scales
+    const int32_t wantModeD = quantD ? op->scaleModeA : ACLTENSOR_SCALE_NONE;
+    if (op->scaleModeD != wantModeD) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (quantD && aux->scaleD == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (workspaceSize < plan->requiredWorkspace) return ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE;
     if (plan->requiredWorkspace > 0 && workspace == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;

@@ -571,7 +571,8 @@ static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
     if (a->groups > kFp8MaxGroups) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_GELU_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->sched < BLAZE_SCHED_AUTO || a->sched > BLAZE_SCHED_STREAM_K) return ACLTENSOR_STATUS_INVALID_VALUE;
-    if (a->d_type < BLAZE_OUT_BF16 || a->d_type > BLAZE_OUT_F32) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->d_type != BLAZE_OUT_FP8_128 && (a->d_type < BLAZE_OUT_BF16 || a->d_type > BLAZE_OUT_F32))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if ((a->K % 16) != 0 || (a->N % 8) != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->groups > 0 && a->sched == BLAZE_SCHED_STREAM_K) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     int sms = sm_count;
@@ -684,6 +685,8 @@ extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
     p.D = static_cast<__nv_bfloat16*>(a->D);
     p.ldd = a->ldd;
     p.out_type = a->d_type;
+    p.scale_d = static_cast<float*>(a->scaleD);
+    if (a->d_type == BLAZE_OUT_FP8_128 && (!a->scaleD || (a->ldd % 16) != 0)) return ACLTENSOR_STATUS_INVALID_VALUE;
     p.stream_k = pl.stream_k;
     p.flags = nullptr;
     p.partials = nullptr;

@@ -551,7 +551,8 @@ __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
 // OUT_MX_E4M3 is the fused quantising output: E4M3 codes plus one E8M0 scale byte per 32 consecutive columns of a row,
 // the operand format of the next MX GEMM (the reference plans this as its epilogue extension:
 // docs/API/epilogue/block/block_epilogue.md:133; fix-pipe FP8 quant modes l0c2out_utils.h:75-76).
-enum OutType : int { OUT_BF16 = 0, OUT_F16 = 1, OUT_F32 = 2, OUT_MX_E4M3 = 3 };
+// OUT_FP8_128 is its counterpart in the FP8 kernel: E4M3 codes plus one float32 scale (amax / 448) per 128 columns.
+enum OutType : int { OUT_BF16 = 0, OUT_F16 = 1, OUT_F32 = 2, OUT_MX_E4M3 = 3, OUT_FP8_128 = 4 };
 
 // Four floats -> four E4M3 bytes (x in the low byte), round-to-nearest-even, saturating.
 __device__ __forceinline__ uint32_t cvt_e4m3x4_sat(float x, float y, float z, float w) {

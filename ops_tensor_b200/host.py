@@ -233,8 +233,8 @@ class Contraction:
               "acltensorCreateContraction")
         if bias_per_batch:
             set_attribute(self.handle, self.op, ATTR_BIAS_PER_BATCH, 1)
-        if d_dtype == R_8F_E4M3:
-            set_attribute(self.handle, self.op, ATTR_SCALE_MODE_D, SCALE_MX_E8M0_VEC32)
+        if d_dtype == R_8F_E4M3:          # quantising epilogue: D gets the scale mode of A (it is the next layer's A)
+            set_attribute(self.handle, self.op, ATTR_SCALE_MODE_D, scale_mode_a)
         set_attribute(self.handle, self.op, ATTR_SCALE_MODE_A, scale_mode_a)
         set_attribute(self.handle, self.op, ATTR_SCALE_MODE_B, scale_mode_b)
         set_attribute(self.handle, self.op, ATTR_EPILOGUE_ACT, activation)

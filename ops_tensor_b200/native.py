@@ -24,7 +24,7 @@ STATUS_INSUFFICIENT_WORKSPACE = 19
 ELEM_E4M3, ELEM_E2M1 = 0, 1
 ACT_IDENTITY, ACT_RELU, ACT_GELU_TANH = 0, 1, 2
 SCHED_AUTO, SCHED_DATA_PARALLEL, SCHED_STREAM_K = 0, 1, 2
-OUT_BF16, OUT_F16, OUT_F32, OUT_MX_E4M3 = 0, 1, 2, 3
+OUT_BF16, OUT_F16, OUT_F32, OUT_MX_E4M3, OUT_FP8_128 = 0, 1, 2, 3, 4
 
 
 def out_type_of(tensor) -> int:
@@ -80,6 +80,7 @@ class Fp8GemmArgs(C.Structure):
         ("sm_limit", C.c_int32),
         ("d_type", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("scaleD", C.c_void_p),
     ]
 
 
@@ -255,7 +256,7 @@ def mx_gemm(a, sa, b, sb, *, out=None, workspace=None, **kw):
 
 
 def fp8_gemm_args(a, sa, b, sb, out, *, group_rows=None, bias=None, residual=None, activation=ACT_IDENTITY,
-                  sched=SCHED_AUTO, sm_limit=0, workspace=None) -> Fp8GemmArgs:
+                  sched=SCHED_AUTO, sm_limit=0, workspace=None, scale_out=None) -> Fp8GemmArgs:
     M, K = a.shape
     if b.dim() == 3:
         G, N, _ = b.shape
@@ -275,7 +276,8 @@ def fp8_gemm_args(a, sa, b, sb, out, *, group_rows=None, bias=None, residual=Non
     args.residual = residual.data_ptr() if residual is not None else None
     args.ldr = residual.stride(0) if residual is not None else 0
     args.D, args.ldd = out.data_ptr(), out.stride(0)
-    args.d_type = out_type_of(out)
+    args.d_type = OUT_FP8_128 if scale_out is not None else out_type_of(out)
+    args.scaleD = scale_out.data_ptr() if scale_out is not None else None
     args.activation = activation
     args.sched = sched
     args.sm_limit = sm_limit

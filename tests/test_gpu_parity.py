@@ -464,6 +464,42 @@ def test_mx_quantised_output_feeds_the_next_gemm(cuda_device, M, N, K, pair):
     assert H.device_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K,split", [(200, 392, 640, H.SPLIT_DATA_PARALLEL), (200, 392, 640, H.SPLIT_STREAM_K),
+                                         (128, 1024, 2048, H.SPLIT_AUTO)])
+def test_fp8_quantised_output_feeds_the_next_gemm(cuda_device, M, N, K, split):
+    """FP8 kernel, quantising epilogue: E4M3 codes + one float32 scale per row per 128 columns, bit-equal to the
+    oracle's 1x128 quantiser applied to the float32-output run of the same call, then used as the next GEMM's A."""
+    import torch
+    a = o.normal_f32(30, 0, (M, K), 1.0)
+    w1 = o.normal_f32(30, 1, (N, K), 0.05)
+    bias = bf16_tensor(o.normal_f32(30, 2, (N,), 0.5), cuda_device)
+    A_MODE, B_MODE = H.SCALE_FP32_1X128, H.SCALE_FP32_128X128
+    qa, sa = H.quantize(dev_tensor(a, cuda_device), A_MODE)
+    qb, sb = H.quantize(dev_tensor(w1, cuda_device), B_MODE)
+    kw = dict(scale_mode_a=A_MODE, scale_mode_b=B_MODE, activation=H.OP_RELU, bias=True, split=split)
+    f32 = torch.empty((M, N), dtype=torch.float32, device=cuda_device)
+    with H.Contraction(M, N, K, d_dtype=H.R_32F, **kw) as c:
+        c(qa, sa, qb, sb, f32, bias=bias)
+    pitch = -(-N // 16) * 16
+    codes = torch.full((M, pitch), 0xAA, dtype=torch.uint8, device=cuda_device)[:, :N]
+    scales = torch.full((M, -(-N // 128)), float("nan"), dtype=torch.float32, device=cuda_device)
+    with H.Contraction(M, N, K, d_dtype=H.R_8F_E4M3, ldd=pitch, **kw) as c:
+        c(qa, sa, qb, sb, codes, bias=bias, scale_out=scales)
+    want_codes, want_scales = o.quant_fp8_1x128(to_np(f32))
+    assert np.array_equal(to_np(scales).view(np.uint32), want_scales.view(np.uint32))
+    assert np.array_equal(to_np(codes.contiguous()), want_codes)
+    if N % 16 == 0:
+        N2 = 264
+        w2 = o.normal_f32(30, 3, (N2, N), 0.1)
+        qb2, sb2 = H.quantize(dev_tensor(w2, cuda_device), B_MODE)
+        out2 = torch.empty((M, N2), dtype=torch.bfloat16, device=cuda_device)
+        with H.Contraction(M, N2, N, scale_mode_a=A_MODE, scale_mode_b=B_MODE, lda=pitch) as c:
+            c(codes, scales, qb2, sb2, out2)
+        ref = o.matmul_ref64(o.dequant_fp8_1x128(want_codes, want_scales), o.dequant_fp8_128x128(to_np(qb2), to_np(sb2)))
+        assert_gemm_ok(to_np(out2), ref)
+    assert H.device_status() == 0
+
+
 def test_mx_agrees_with_vendor_mxfp8_gemm(cuda_device):
     """An independent implementation of the same format: the vendor library's MXFP8 GEMM (torch._scaled_mm with E8M0
     scales per 32 K) on the same codes and scales.  Both accumulate in float32 and round once to bf16, so they may
