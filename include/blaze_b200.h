@@ -46,7 +46,14 @@ typedef enum {
 } blazeOutType_t;
 
 /* Fused activation, applied after bias and before the residual add. */
-typedef enum { BLAZE_ACT_IDENTITY = 0, BLAZE_ACT_RELU = 1, BLAZE_ACT_GELU_TANH = 2 } blazeActivation_t;
+typedef enum {
+    BLAZE_ACT_IDENTITY = 0,
+    BLAZE_ACT_RELU = 1,
+    BLAZE_ACT_GELU_TANH = 2,
+    BLAZE_ACT_SILU = 3,     /* x * sigmoid(x) */
+    BLAZE_ACT_SIGMOID = 4,
+    BLAZE_ACT_TANH = 5
+} blazeActivation_t;
 
 /* How the output tiles are scheduled over the SMs. */
 typedef enum {

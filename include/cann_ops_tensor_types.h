@@ -127,7 +127,7 @@ typedef enum {
 typedef enum {
     ACLTENSOR_OPERATION_DESCRIPTOR_SCALE_MODE_A = 1,     /* int32: acltensorScaleMode_t */
     ACLTENSOR_OPERATION_DESCRIPTOR_SCALE_MODE_B = 2,     /* int32 */
-    ACLTENSOR_OPERATION_DESCRIPTOR_EPILOGUE_ACT = 3,     /* int32: ACLTENSOR_OP_IDENTITY / RELU / GELU */
+    ACLTENSOR_OPERATION_DESCRIPTOR_EPILOGUE_ACT = 3,     /* int32: ACLTENSOR_OP_IDENTITY / RELU / GELU / SILU / SIGMOID / TANH */
     ACLTENSOR_OPERATION_DESCRIPTOR_BIAS_TYPE = 4,        /* int32: acltensorDataType_t of the bias (16BF) or -1 for none */
     ACLTENSOR_OPERATION_DESCRIPTOR_GROUP_COUNT = 5,      /* int32: number of groups (0 = dense) */
     ACLTENSOR_OPERATION_DESCRIPTOR_SPLIT_POLICY = 6,     /* int32: acltensorSplitPolicy_t */

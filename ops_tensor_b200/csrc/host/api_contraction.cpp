@@ -28,6 +28,9 @@ int activation_of(int32_t op) {
         case ACLTENSOR_OP_IDENTITY: return BLAZE_ACT_IDENTITY;
         case ACLTENSOR_OP_RELU: return BLAZE_ACT_RELU;
         case ACLTENSOR_OP_GELU: return BLAZE_ACT_GELU_TANH;
+        case ACLTENSOR_OP_SILU: return BLAZE_ACT_SILU;
+        case ACLTENSOR_OP_SIGMOID: return BLAZE_ACT_SIGMOID;
+        case ACLTENSOR_OP_TANH: return BLAZE_ACT_TANH;
         default: return -1;
     }
 }

@@ -193,7 +193,7 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scal
     // legal operand pairs: FP8 x FP8, FP8 x FP4 (W4A8) and FP4 x FP4; a 4-bit A is only read natively
     if (a->a_elem == BLAZE_ELEM_E2M1 && (a->b_elem != BLAZE_ELEM_E2M1 || (a->K % 128) != 0))
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_GELU_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->tile_n != 0 && a->tile_n != 128 && a->tile_n != 224 && a->tile_n != 256) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if ((a->K % 16) != 0 || (a->N % 8) != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->cta_pair < 0 || a->cta_pair > 2) return ACLTENSOR_STATUS_INVALID_VALUE;
@@ -264,6 +264,9 @@ static cudaError_t launch_mx_act(int act, const CUtensorMap& ta, const CUtensorM
     switch (act) {
         case BLAZE_ACT_RELU: return launch_mx_instance<kBN, ACT_RELU>(ta, tb, td, p, grid, stream);
         case BLAZE_ACT_GELU_TANH: return launch_mx_instance<kBN, ACT_GELU_TANH>(ta, tb, td, p, grid, stream);
+        case BLAZE_ACT_SILU: return launch_mx_instance<kBN, ACT_SILU>(ta, tb, td, p, grid, stream);
+        case BLAZE_ACT_SIGMOID: return launch_mx_instance<kBN, ACT_SIGMOID>(ta, tb, td, p, grid, stream);
+        case BLAZE_ACT_TANH: return launch_mx_instance<kBN, ACT_TANH>(ta, tb, td, p, grid, stream);
         default: return launch_mx_instance<kBN, ACT_IDENTITY>(ta, tb, td, p, grid, stream);
     }
 }
@@ -308,6 +311,9 @@ static cudaError_t launch_mx_pair_act(int act, const CUtensorMap& ta, const CUte
     switch (act) {
         case BLAZE_ACT_RELU: return launch_mx_pair_instance<kBN, ACT_RELU, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
         case BLAZE_ACT_GELU_TANH: return launch_mx_pair_instance<kBN, ACT_GELU_TANH, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
+        case BLAZE_ACT_SILU: return launch_mx_pair_instance<kBN, ACT_SILU, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
+        case BLAZE_ACT_SIGMOID: return launch_mx_pair_instance<kBN, ACT_SIGMOID, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
+        case BLAZE_ACT_TANH: return launch_mx_pair_instance<kBN, ACT_TANH, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
         default: return launch_mx_pair_instance<kBN, ACT_IDENTITY, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
     }
 }
@@ -569,7 +575,7 @@ static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
     if (!a || a->struct_size != sizeof(blazeFp8GemmArgs)) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->M < 0 || a->N < 0 || a->K < 0 || a->groups < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->groups > kFp8MaxGroups) return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_GELU_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->sched < BLAZE_SCHED_AUTO || a->sched > BLAZE_SCHED_STREAM_K) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->d_type != BLAZE_OUT_FP8_128 && (a->d_type < BLAZE_OUT_BF16 || a->d_type > BLAZE_OUT_F32))
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
@@ -701,6 +707,9 @@ extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
     switch (a->activation) {
         case BLAZE_ACT_RELU: e = launch_fp8_instance<ACT_RELU>(ta, tb, p, pl.grid, stream); break;
         case BLAZE_ACT_GELU_TANH: e = launch_fp8_instance<ACT_GELU_TANH>(ta, tb, p, pl.grid, stream); break;
+        case BLAZE_ACT_SILU: e = launch_fp8_instance<ACT_SILU>(ta, tb, p, pl.grid, stream); break;
+        case BLAZE_ACT_SIGMOID: e = launch_fp8_instance<ACT_SIGMOID>(ta, tb, p, pl.grid, stream); break;
+        case BLAZE_ACT_TANH: e = launch_fp8_instance<ACT_TANH>(ta, tb, p, pl.grid, stream); break;
         default: e = launch_fp8_instance<ACT_IDENTITY>(ta, tb, p, pl.grid, stream); break;
     }
     return status_of(e);

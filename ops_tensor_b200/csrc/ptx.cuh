@@ -505,7 +505,7 @@ __device__ __forceinline__ void cluster_sync() {
 
 // ------------------------------------------------------------------------------------------------ epilogue math
 
-enum Activation : int { ACT_IDENTITY = 0, ACT_RELU = 1, ACT_GELU_TANH = 2 };
+enum Activation : int { ACT_IDENTITY = 0, ACT_RELU = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_SIGMOID = 4, ACT_TANH = 5 };
 
 // GELU, tanh form: 0.5 x (1 + tanh(u)), u = sqrt(2/pi) (x + 0.044715 x^3).  Since 0.5 (1 + tanh(u)) = 1 / (1 + e^(-2u)),
 // it is evaluated as x / (1 + 2^w) with w = -2 u log2(e): one ex2 and one reciprocal, relative error ~1e-6, and the
@@ -519,10 +519,20 @@ __device__ __forceinline__ float gelu_tanh_f32(float x) {
     return __fdividef(x, 1.0f + e);
 }
 
+// 1 / (1 + 2^(-x log2 e)): one ex2 and one reciprocal; exact limits 0 and 1 at the tails.
+__device__ __forceinline__ float sigmoid_f32(float x) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+    return __fdividef(1.0f, 1.0f + e);
+}
+
 template <int kAct>
 __device__ __forceinline__ float apply_act(float x) {
     if constexpr (kAct == ACT_RELU) return fmaxf(x, 0.0f);
     if constexpr (kAct == ACT_GELU_TANH) return gelu_tanh_f32(x);
+    if constexpr (kAct == ACT_SILU) return x * sigmoid_f32(x);
+    if constexpr (kAct == ACT_SIGMOID) return sigmoid_f32(x);
+    if constexpr (kAct == ACT_TANH) return fmaf(2.0f, sigmoid_f32(2.0f * x), -1.0f);
     return x;
 }
 

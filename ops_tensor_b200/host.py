@@ -16,6 +16,7 @@ R_16F, R_32F, R_64F, R_16BF, R_8I, R_8U, R_32I, R_32U, C_32F, C_64F = range(10)
 R_8F_E4M3, R_8F_E5M2, R_4F_E2M1, R_8F_UE8M0, R_64I = 32, 33, 34, 35, 36
 COMPUTE_DESC_NONE, COMPUTE_DESC_16F, COMPUTE_DESC_32F, COMPUTE_DESC_64F, COMPUTE_DESC_16BF = 0, 1, 4, 16, 1024
 OP_IDENTITY, OP_SQRT, OP_ADD, OP_MUL, OP_RELU, OP_GELU, OP_SILU = 1, 2, 3, 5, 8, 39, 40
+OP_SIGMOID, OP_TANH = 11, 12
 ALGO_DEFAULT, ALGO_DEFAULT_PATIENT = -1, -6
 WORKSPACE_MIN, WORKSPACE_DEFAULT, WORKSPACE_MAX = 1, 2, 3
 SCALE_NONE, SCALE_MX_E8M0_VEC32, SCALE_FP32_1X128, SCALE_FP32_128X128 = 0, 1, 2, 3

@@ -22,7 +22,7 @@ STATUS_NOT_SUPPORTED = 15
 STATUS_INSUFFICIENT_WORKSPACE = 19
 
 ELEM_E4M3, ELEM_E2M1 = 0, 1
-ACT_IDENTITY, ACT_RELU, ACT_GELU_TANH = 0, 1, 2
+ACT_IDENTITY, ACT_RELU, ACT_GELU_TANH, ACT_SILU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3, 4, 5
 SCHED_AUTO, SCHED_DATA_PARALLEL, SCHED_STREAM_K = 0, 1, 2
 OUT_BF16, OUT_F16, OUT_F32, OUT_MX_E4M3, OUT_FP8_128 = 0, 1, 2, 3, 4
 

@@ -298,7 +298,7 @@ def dequant_fp8_128x128(codes_nk, scale_kn, dtype=np.float64):
 # Epilogues and matmul references
 # ----------------------------------------------------------------------------------------------------------
 
-ACT_IDENTITY, ACT_RELU, ACT_GELU_TANH = 0, 1, 2
+ACT_IDENTITY, ACT_RELU, ACT_GELU_TANH, ACT_SILU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3, 4, 5
 
 
 def gelu_tanh(x):
@@ -317,6 +317,12 @@ def epilogue(acc, bias=None, act=ACT_IDENTITY, residual=None):
         y = np.maximum(y, 0)
     elif act == ACT_GELU_TANH:
         y = gelu_tanh(y)
+    elif act == ACT_SILU:
+        y = y / (1 + np.exp(-y))
+    elif act == ACT_SIGMOID:
+        y = 1 / (1 + np.exp(-y))
+    elif act == ACT_TANH:
+        y = np.tanh(y)
     if residual is not None:
         y = y + np.asarray(residual, dtype=acc.dtype)
     return y

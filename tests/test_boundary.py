@@ -169,7 +169,7 @@ def test_contraction_descriptor_checks(api):
     assert sa(h, op, H.ATTR_SCALE_MODE_A, C.byref(v), 8) == H.STATUS_INVALID_VALUE
     assert sa(h, op, 77, C.byref(v), 4) == H.STATUS_INVALID_VALUE
     assert sa(h, op, H.ATTR_SCALE_MODE_A, C.byref(C.c_int32(9)), 4) == H.STATUS_INVALID_VALUE
-    assert sa(h, op, H.ATTR_EPILOGUE_ACT, C.byref(C.c_int32(H.OP_SILU)), 4) == H.STATUS_NOT_SUPPORTED
+    assert sa(h, op, H.ATTR_EPILOGUE_ACT, C.byref(C.c_int32(H.OP_SQRT)), 4) == H.STATUS_NOT_SUPPORTED
     assert sa(h, op, H.ATTR_TILE_N, C.byref(C.c_int32(96)), 4) == H.STATUS_NOT_SUPPORTED
     assert sa(h, op, H.ATTR_GROUP_COUNT, C.byref(C.c_int32(4)), 4) == H.STATUS_INVALID_VALUE
     H.set_attribute(h, op, H.ATTR_EPILOGUE_ACT, H.OP_GELU)

@@ -156,7 +156,8 @@ def fp8_reference(qa, sa, qb, sb, act=o.ACT_IDENTITY, bias=None, residual=None, 
     return ref, gold
 
 
-ACT = {H.OP_IDENTITY: o.ACT_IDENTITY, H.OP_RELU: o.ACT_RELU, H.OP_GELU: o.ACT_GELU_TANH}
+ACT = {H.OP_IDENTITY: o.ACT_IDENTITY, H.OP_RELU: o.ACT_RELU, H.OP_GELU: o.ACT_GELU_TANH, H.OP_SILU: o.ACT_SILU,
+       H.OP_SIGMOID: o.ACT_SIGMOID, H.OP_TANH: o.ACT_TANH}
 
 
 @pytest.mark.parametrize("split", [H.SPLIT_DATA_PARALLEL, H.SPLIT_STREAM_K, H.SPLIT_AUTO])
@@ -177,7 +178,7 @@ def test_fp8_ragged_shapes(cuda_device, M, N, K, split):
     assert_gemm_ok(got, ref, gold)
 
 
-@pytest.mark.parametrize("act", [H.OP_IDENTITY, H.OP_RELU, H.OP_GELU])
+@pytest.mark.parametrize("act", [H.OP_IDENTITY, H.OP_RELU, H.OP_GELU, H.OP_SILU, H.OP_SIGMOID, H.OP_TANH])
 def test_fp8_fused_epilogue(cuda_device, act):
     M, N, K = 200, 392, 640
     a, w = fp8_problem(12, M, N, K, sigma_b=0.05)
@@ -315,7 +316,7 @@ def test_mx_scale_extremes(cuda_device):
 
 
 @pytest.mark.parametrize("cta_pair", [1, 2, 256])
-@pytest.mark.parametrize("act", [H.OP_IDENTITY, H.OP_RELU, H.OP_GELU])
+@pytest.mark.parametrize("act", [H.OP_IDENTITY, H.OP_RELU, H.OP_GELU, H.OP_SILU, H.OP_SIGMOID, H.OP_TANH])
 def test_mx_fused_epilogue(cuda_device, act, cta_pair):
     M, N, K = 260, 456, 512
     a = o.normal_f32(22, 0, (M, K), 1.0)
