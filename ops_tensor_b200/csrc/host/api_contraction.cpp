@@ -547,8 +547,9 @@ acltensorStatus_t acltensorQuantize(const acltensorHandle_t handle, const void* 
                                     int64_t cols, acltensorScaleMode_t scaleMode, acltensorDataType_t dType,
                                     void* codes, int64_t ldCodesBytes, void* scales, aclrtStream stream) {
     (void)handle;
-    if (src == nullptr || codes == nullptr || scales == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (!fits_int32(rows) || !fits_int32(cols)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (rows == 0 || cols == 0) return ACLTENSOR_STATUS_SUCCESS;            // nothing to quantise, pointers may be null
+    if (src == nullptr || codes == nullptr || scales == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     const int32_t r = static_cast<int32_t>(rows), c = static_cast<int32_t>(cols);
     switch (scaleMode) {
         case ACLTENSOR_SCALE_MX_E8M0_VEC32:

@@ -76,6 +76,65 @@ def test_abandoned_wait_is_reported_and_context_survives(cuda_device):
     assert np.all(got == 16.0) and H.device_status() == 0
 
 
+def test_empty_and_invalid_calls(cuda_device):
+    """Edge cases of the C ABI on a live device: empty problems succeed without touching memory, a problem without K
+    or with a missing / misaligned / too-small buffer is refused with the documented status, and nothing is left in
+    the device status word."""
+    import ctypes as C
+    import torch
+    from ops_tensor_b200 import native
+    dev = cuda_device
+    u8 = lambda *shape: torch.zeros(shape, dtype=torch.uint8, device=dev)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    lib = native.lib()
+    # MX: M = 0 and N = 0 are no-ops (null pointers are fine), K = 0 is not a GEMM
+    for M, N in ((0, 64), (64, 0)):
+        args = native.MxGemmArgs()
+        args.struct_size = C.sizeof(args)
+        args.M, args.N, args.K = M, N, 128
+        args.lda = args.ldb = 128
+        args.ldd = max(N, 8)
+        assert lib.blazeMxGemm(C.byref(args), stream) == native.STATUS_SUCCESS
+    a, sa, b, sb = u8(64, 128), u8(64, 4), u8(64, 128), u8(64, 4)
+    out = torch.zeros((64, 64), dtype=torch.bfloat16, device=dev)
+    good = native.mx_gemm_args(a, sa, b, sb, out)
+    ws = u8(native.mx_gemm_workspace_bytes(good) + 256)
+    good.workspace, good.workspace_bytes = ws.data_ptr(), ws.numel()
+    assert lib.blazeMxGemm(C.byref(good), stream) == native.STATUS_SUCCESS
+
+    def variant(**kw):
+        v = native.MxGemmArgs.from_buffer_copy(good)
+        for k, val in kw.items():
+            setattr(v, k, val)
+        return lib.blazeMxGemm(C.byref(v), stream)
+
+    assert variant(K=0) == native.STATUS_NOT_SUPPORTED
+    assert variant(A=None) == native.STATUS_INVALID_VALUE
+    assert variant(scaleB=None) == native.STATUS_INVALID_VALUE
+    assert variant(lda=64) == native.STATUS_INVALID_VALUE                       # shorter than a row
+    assert variant(lda=136) == native.STATUS_NOT_SUPPORTED                      # rows not 16-byte aligned
+    assert variant(A=a.data_ptr() + 8) == native.STATUS_NOT_SUPPORTED
+    assert variant(K=72) == native.STATUS_NOT_SUPPORTED                         # K % 16
+    assert variant(N=60, ldd=64) == native.STATUS_NOT_SUPPORTED                 # N % 8
+    assert variant(workspace_bytes=16) == native.STATUS_INSUFFICIENT_WORKSPACE
+    assert variant(workspace=ws.data_ptr() + 16) == native.STATUS_INVALID_VALUE  # workspace must be 256-byte aligned
+    assert variant(activation=17) == native.STATUS_NOT_SUPPORTED
+    assert variant(struct_size=8) == native.STATUS_INVALID_VALUE
+    # FP8: all groups empty, and a dense problem with no rows
+    sa32 = torch.zeros((0, 1), dtype=torch.float32, device=dev)
+    sb32 = torch.ones((3, 1, 1), dtype=torch.float32, device=dev)
+    empty_rows = torch.zeros(3, dtype=torch.int64, device=dev)
+    out0 = torch.zeros((0, 128), dtype=torch.bfloat16, device=dev)
+    native.fp8_gemm(u8(0, 128), sa32, u8(3, 128, 128), sb32, out=out0, group_rows=empty_rows)
+    native.fp8_gemm(u8(0, 128), sa32, u8(128, 128), sb32[0], out=out0)
+    # quantisers: nothing to do for zero rows
+    x0 = torch.zeros((0, 64), dtype=torch.float32, device=dev)
+    codes, scales = H.quantize(x0, H.SCALE_MX_E8M0_VEC32)
+    assert codes.shape == (0, 64) and scales.shape == (0, 2)
+    torch.cuda.synchronize()
+    assert H.device_status() == 0
+
+
 # ------------------------------------------------------------------------------------------------ quantisers
 
 @pytest.mark.parametrize("rows,K", [(1, 32), (4, 128), (37, 96), (256, 1024), (130, 4160), (515, 2048)])
