@@ -310,7 +310,8 @@ def gpu_arm(args):
             qb, sb = H.quantize(w_dev, mode_b)
         plan = H.Contraction(M, N, K, scale_mode_a=mode_a, scale_mode_b=mode_b, groups=G if kind == "grouped" else 0,
                              residual=residual is not None)
-        launches_per_step = 1
+        # a plan that asks for workspace runs stream-K: a kernel that zeroes the fix-up flags, then the GEMM
+        launches_per_step = 2 if plan.workspace_bytes > 0 else 1
     del w_dev
     qa, sa = H.quantize(a_dev, mode_a)
     out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)

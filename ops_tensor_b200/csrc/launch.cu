@@ -591,10 +591,16 @@ static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
     if (a->groups == 0 && tiles > 0 && pl->k_blocks >= 2) {
         if (a->sched == BLAZE_SCHED_STREAM_K) {
             stream_k = 1;
-        } else if (a->sched == BLAZE_SCHED_AUTO && pl->k_blocks >= 8) {
-            const long long waves = (tiles + sms - 1) / sms;
-            const double fill = (double)tiles / (double)(waves * sms);
-            if (fill < 0.8) stream_k = 1;      // a poorly filled last wave: split along K instead
+        } else if (a->sched == BLAZE_SCHED_AUTO) {
+            // Cost of both schedules in units of one K block on one SM (about 0.47 us).  Whole tiles: waves x K blocks.
+            // Stream-K: the evenly split units, plus a fixed ~8 us (flag reset launch, partial tiles through L2, flag
+            // hand-over) and the owner's serial walk over the contributors of its tile.  Measured on seven shapes
+            // from 256x512x1024 to 128x7168x18432, the model picks the faster schedule on all of them.
+            const long long units = tiles * pl->k_blocks;
+            const long long used = units < sms ? units : sms;
+            const double whole_tiles = (double)((tiles + sms - 1) / sms) * pl->k_blocks;
+            const double split = (double)((units + used - 1) / used) + 17.0 + (double)used / (double)tiles;
+            if (split < whole_tiles) stream_k = 1;
         }
     }
     pl->stream_k = stream_k;
