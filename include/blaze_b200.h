@@ -45,6 +45,12 @@ typedef enum {
                               blazeQuantizeFp8RowGroups applied to the float32 result */
 } blazeOutType_t;
 
+/* Storage order of B.  K-major: [N][ldb], K contiguous, scales [N][ceil(K/64)*2] (what every config uses).  N-major:
+ * [K][ldb], N contiguous, with the scale layout the reference pairs with it: [ceil(K/64)][N][2]
+ * (include/tensor_api/impl/tensor_api/tensor/layout_pattern.h:204-215); E4M3 only.  An N-major B is transposed once
+ * into the workspace (reused across calls like the other weight pre-passes). */
+typedef enum { BLAZE_B_K_MAJOR = 0, BLAZE_B_N_MAJOR = 1 } blazeBLayout_t;
+
 /* Fused activation, applied after bias and before the residual add. */
 typedef enum {
     BLAZE_ACT_IDENTITY = 0,
@@ -99,7 +105,7 @@ typedef struct {
     void* workspace;         /* device, 256-byte aligned */
     size_t workspace_bytes;
     int32_t d_type;          /* blazeOutType_t of D (ldd counts elements of that type) */
-    int32_t reserved;
+    int32_t b_layout;        /* blazeBLayout_t */
     void* scaleD;            /* device, E8M0 scales of D when d_type is BLAZE_OUT_MX_E4M3, else NULL */
 } blazeMxGemmArgs;
 

@@ -70,6 +70,7 @@ void fill_mx_args(const acltensorOperationDescriptor& op, blazeMxGemmArgs* a) {
     a->ldd = op.ldd;
     a->activation = activation_of(op.epilogueAct);
     a->d_type = out_type_of(op.descD->dataType);
+    a->b_layout = op.bNMajor ? BLAZE_B_N_MAJOR : BLAZE_B_K_MAJOR;
     a->tile_n = op.tileN;
     a->sm_limit = op.smLimit;
     a->cta_pair = op.ctaPair;
@@ -139,6 +140,7 @@ void fill_fp8_args(const acltensorOperationDescriptor& op, int32_t splitPolicy, 
 
 acltensorStatus_t Fp8Workspace(const acltensorOperationDescriptor& op, int32_t splitPolicy, uint64_t* bytes) {
     if (op.batchModes > 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;          // batch broadcast is an MX feature
+    if (op.bNMajor) return ACLTENSOR_STATUS_NOT_SUPPORTED;                 // so is the N-major weight
     blazeFp8GemmArgs a;
     fill_fp8_args(op, splitPolicy, &a);
     size_t n = 0;
@@ -241,8 +243,12 @@ acltensorStatus_t acltensorCreateContraction(const acltensorHandle_t handle, acl
     const int64_t M = lensD[0], N = lensD[1], K = lensA[aK];
     if (lensA[aM] != M || lensB[bN] != N || lensB[bK] != K) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (!fits_int32(M) || !fits_int32(N) || !fits_int32(K)) return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    // K must be the contiguous mode of both operands, n the contiguous mode of the output
-    if (stridesA[aK] != 1 || stridesB[bK] != 1 || stridesD[1] != 1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    // K must be the contiguous mode of A, n the contiguous mode of the output; B is K-contiguous ("DN", what every
+    // config uses) or, for a plain E4M3 matrix, N-contiguous ("ND": transposed once into the workspace)
+    if (stridesA[aK] != 1 || stridesD[1] != 1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    const bool bNMajor = stridesB[bK] != 1 && stridesB[bN] == 1;
+    if (stridesB[bK] != 1 && !bNMajor) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (bNMajor && (groupedB || nBatch > 0 || descB->dataType != ACLTENSOR_R_8F_E4M3)) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (descC != nullptr) {
         for (uint32_t i = 0; i < descD->numModes; ++i) {
             if (modeC[i] != fullD[i] || descC->lens[i] != descD->lens[i]) return ACLTENSOR_STATUS_INVALID_VALUE;
@@ -316,7 +322,8 @@ acltensorStatus_t acltensorCreateContraction(const acltensorHandle_t handle, acl
     d->N = N;
     d->K = K;
     d->lda = stridesA[aM];
-    d->ldb = stridesB[bN];
+    d->ldb = bNMajor ? stridesB[bK] : stridesB[bN];
+    d->bNMajor = bNMajor ? 1 : 0;
     d->ldc = descC ? descC->strides[nBatch] : 0;
     d->ldd = stridesD[0];
     d->groupStrideB = groupStride;

@@ -105,6 +105,7 @@ struct acltensorOperationDescriptor {
     int32_t batchC[4] = {1, 1, 1, 1}, batchA[4] = {1, 1, 1, 1}, batchB[4] = {1, 1, 1, 1};   // right-aligned extents
     int32_t biasPerBatch = 0;                         // bias is [batches][N] instead of [N]
     int32_t scaleModeD = ACLTENSOR_SCALE_NONE;        // MX_E8M0_VEC32: the epilogue quantises D
+    int32_t bNMajor = 0;                              // B is stored [K][N] with N contiguous (ldb = its K stride)
 
     size_t getTotalElements() const { return descD ? descD->totalElements : 0; }
     acltensorDataType_t getDataType() const { return descD ? descD->dataType : ACLTENSOR_R_32F; }

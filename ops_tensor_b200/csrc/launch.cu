@@ -148,8 +148,8 @@ struct MxPlan {
     int tile_n;
     int sfb_replicas;   // copies of every 512-byte scale block of B in the re-tiled array
     int m_tiles, n_tiles, k_steps;
-    size_t sfa_bytes, sfb_bytes, b_expand_bytes;
-    size_t sfa_off, sfb_off, b_expand_off, total;
+    size_t sfa_bytes, sfb_bytes, b_expand_bytes, b_scale_rows_bytes;
+    size_t sfa_off, sfb_off, b_expand_off, b_scale_rows_off, total;
 };
 
 static int choose_tile_n(int M, int N, int sms, int requested) {
@@ -190,6 +190,8 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scal
     if (a->b_elem != BLAZE_ELEM_E4M3 && a->b_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->a_elem != BLAZE_ELEM_E4M3 && a->a_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->d_type < BLAZE_OUT_BF16 || a->d_type > BLAZE_OUT_MX_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->b_layout != BLAZE_B_K_MAJOR && a->b_layout != BLAZE_B_N_MAJOR) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->b_layout == BLAZE_B_N_MAJOR && a->b_elem != BLAZE_ELEM_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     // legal operand pairs: FP8 x FP8, FP8 x FP4 (W4A8) and FP4 x FP4; a 4-bit A is only read natively
     if (a->a_elem == BLAZE_ELEM_E2M1 && (a->b_elem != BLAZE_ELEM_E2M1 || (a->K % 128) != 0))
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
@@ -214,11 +216,14 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scal
     pl->sfa_bytes = (size_t)sf_tiled_bytes(a->M, a->K, 128);
     pl->sfb_replicas = (pl->pair && wide_scale_copy) ? 4 : 1;        // the wide copy has no lane broadcast
     pl->sfb_bytes = (size_t)sf_tiled_bytes(a->N, a->K, pl->tile_n, pl->sfb_replicas);
-    pl->b_expand_bytes = a->b_elem == BLAZE_ELEM_E2M1 ? (size_t)a->N * (size_t)a->K : 0;
+    // room for a one-byte-per-code K-major copy of B: the expansion of a packed E2M1 B, or the transpose of an N-major B
+    pl->b_expand_bytes = (a->b_elem == BLAZE_ELEM_E2M1 || a->b_layout == BLAZE_B_N_MAJOR) ? (size_t)a->N * (size_t)a->K : 0;
+    pl->b_scale_rows_bytes = a->b_layout == BLAZE_B_N_MAJOR ? (size_t)a->N * (size_t)(((a->K + 63) / 64) * 2) : 0;
     pl->sfa_off = 0;
     pl->sfb_off = round256(pl->sfa_bytes);
     pl->b_expand_off = pl->sfb_off + round256(pl->sfb_bytes);
-    pl->total = pl->b_expand_off + round256(pl->b_expand_bytes);
+    pl->b_scale_rows_off = pl->b_expand_off + round256(pl->b_expand_bytes);
+    pl->total = pl->b_scale_rows_off + round256(pl->b_scale_rows_bytes);
     return ACLTENSOR_STATUS_SUCCESS;
 }
 
@@ -416,7 +421,7 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
     if (a->M == 0 || a->N == 0) return ACLTENSOR_STATUS_SUCCESS;
     if (!a->A || !a->B || !a->scaleA || !a->scaleB || !a->D) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->K == 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    const int64_t min_ldb = a->b_elem == BLAZE_ELEM_E2M1 ? a->K / 2 : a->K;
+    const int64_t min_ldb = a->b_layout == BLAZE_B_N_MAJOR ? a->N : (a->b_elem == BLAZE_ELEM_E2M1 ? a->K / 2 : a->K);
     const int64_t min_lda = a->a_elem == BLAZE_ELEM_E2M1 ? a->K / 2 : a->K;
     if (a->lda < min_lda || a->ldb < min_ldb || a->ldd < a->N || (a->residual && a->ldr < a->N))
         return ACLTENSOR_STATUS_INVALID_VALUE;
@@ -453,12 +458,22 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
             !make_tmap_packed4(&ta_packed, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128))
             return ACLTENSOR_STATUS_NOT_SUPPORTED;
     }
-    if (a->b_elem == BLAZE_ELEM_E2M1 && !native4) {
+    if ((a->b_elem == BLAZE_ELEM_E2M1 && !native4) || a->b_layout == BLAZE_B_N_MAJOR) {
         b_codes = ws + pl.b_expand_off;
         b_pitch = a->K;
     }
     if (!a->reuse_b_prepass) {
-        e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleB), a->N, a->K, pl.tile_n, pl.sfb_replicas, sfb_tiled, ctx->sm_count,
+        const uint8_t* scale_b_rows = static_cast<const uint8_t*>(a->scaleB);
+        if (a->b_layout == BLAZE_B_N_MAJOR) {
+            // B arrives [K][N]: keep a K-major copy and row-major scales in the workspace (once per weight)
+            e = launch_transpose_bytes(static_cast<const uint8_t*>(a->B), a->ldb, a->K, a->N, ws + pl.b_expand_off, a->K,
+                                       stream);
+            if (e != cudaSuccess) return status_of(e);
+            e = launch_scale_pairs_to_rows(scale_b_rows, a->N, a->K, ws + pl.b_scale_rows_off, ctx->sm_count, stream);
+            if (e != cudaSuccess) return status_of(e);
+            scale_b_rows = ws + pl.b_scale_rows_off;
+        }
+        e = launch_sf_retile(scale_b_rows, a->N, a->K, pl.tile_n, pl.sfb_replicas, sfb_tiled, ctx->sm_count,
                              stream);
         if (e != cudaSuccess) return status_of(e);
         if (a->b_elem == BLAZE_ELEM_E2M1 && !native4) {
@@ -496,6 +511,7 @@ static int check_batch(const blazeMxGemmArgs* a, const blazeBatchDims* bd, Batch
         b_one = b_one && bd->b[i] == 1;
     }
     if (w->count_c > 0x7fffffffLL) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->b_layout != BLAZE_B_K_MAJOR && w->count_b > 1) return ACLTENSOR_STATUS_NOT_SUPPORTED;   // batches of B are K-major
     // one tall GEMM: same weight for every batch, one A per batch, one bias, rows of consecutive batches adjacent
     w->folds = a_full && b_one && !bd->bias_per_batch && w->count_c * (long long)a->M <= 0x7fffffffLL;
     return ACLTENSOR_STATUS_SUCCESS;
@@ -902,6 +918,7 @@ extern "C" int blazeMxGemmNoAlloc(const blazeMxGemmArgs* a, int32_t* device_stat
         if (st != ACLTENSOR_STATUS_SUCCESS) return st;
     }
     if (a->b_elem != BLAZE_ELEM_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;      // packed E2M1 needs an N x K expansion buffer
+    if (a->b_layout != BLAZE_B_K_MAJOR) return ACLTENSOR_STATUS_NOT_SUPPORTED;    // so does the transpose of an N-major B
     if (pl.total > kNoAllocScratchBytes) return ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE;   // problem too large for the fixed array
     if (a->M == 0 || a->N == 0) return ACLTENSOR_STATUS_SUCCESS;
     if (!a->A || !a->B || !a->scaleA || !a->scaleB || !a->D) return ACLTENSOR_STATUS_INVALID_VALUE;

@@ -36,6 +36,10 @@ cudaError_t launch_sf_retile(const uint8_t* in, int rows, int K, int tile_rows, 
                              int sm_count, cudaStream_t stream);
 cudaError_t launch_e2m1_expand(const uint8_t* in, long long ld_in, int rows, int K, uint8_t* out, long long ld_out,
                                int sm_count, cudaStream_t stream);
+// Pre-pass for a B stored [K][N] (N contiguous): its transpose [N][K] and its scales as rows [N][ceil(K/64)*2].
+cudaError_t launch_transpose_bytes(const uint8_t* in, long long ld_in, int K, int N, uint8_t* out, long long ld_out,
+                                   cudaStream_t stream);
+cudaError_t launch_scale_pairs_to_rows(const uint8_t* in, int N, int K, uint8_t* out, int sm_count, cudaStream_t stream);
 // Zeroes `words` 32-bit words (the stream-K flags) with a kernel, so that the GEMM behind it can be launched with
 // programmatic stream serialisation (a memset node gives the next kernel nothing to overlap with).
 cudaError_t launch_zero_words(int* p, int words, cudaStream_t stream);

@@ -299,12 +299,59 @@ __global__ void __launch_bounds__(256) add_f32_kernel(const float* __restrict__ 
     }
 }
 
+// in [K][ld_in] bytes (N contiguous) -> out [N][ld_out] bytes (K contiguous), 64 x 64 tiles through shared memory.
+__global__ void __launch_bounds__(256) transpose_bytes_kernel(const uint8_t* __restrict__ in, long long ld_in, int K, int N,
+                                                              uint8_t* __restrict__ out, long long ld_out) {
+    __shared__ uint8_t tile[64][64 + 4];
+    const int k0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        const int kk = i >> 6, nn = i & 63;
+        tile[kk][nn] = (k0 + kk < K && n0 + nn < N) ? in[(long long)(k0 + kk) * ld_in + n0 + nn] : (uint8_t)0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        const int nn = i >> 6, kk = i & 63;
+        if (n0 + nn < N && k0 + kk < K) out[(long long)(n0 + nn) * ld_out + k0 + kk] = tile[kk][nn];
+    }
+}
+
+// MX scales of an N-major B, stored [scale_cols / 2][N][2] (the two K groups of a pair side by side for every n:
+// include/tensor_api/impl/tensor_api/tensor/layout_pattern.h:204-215) -> row-major [N][scale_cols].
+__global__ void __launch_bounds__(256) scale_pairs_to_rows_kernel(const uint8_t* __restrict__ in, int N, int scale_cols,
+                                                                 uint8_t* __restrict__ out) {
+    const long long total = (long long)N * (scale_cols >> 1);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int pair = (int)(i / N);
+        const int n = (int)(i - (long long)pair * N);
+        const uint16_t v = *reinterpret_cast<const uint16_t*>(in + 2 * i);          // in[pair][n][0..1]
+        *reinterpret_cast<uint16_t*>(out + (long long)n * scale_cols + 2 * pair) = v;
+    }
+}
+
 __global__ void __launch_bounds__(256) zero_words_kernel(int* __restrict__ p, int words) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the GEMM behind may start setting up
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < words; i += gridDim.x * blockDim.x) p[i] = 0;
 }
 
 // ---------------------------------------------------------------------------------------------------- launchers
+
+cudaError_t launch_transpose_bytes(const uint8_t* in, long long ld_in, int K, int N, uint8_t* out, long long ld_out,
+                                   cudaStream_t stream) {
+    if (K <= 0 || N <= 0) return cudaSuccess;
+    transpose_bytes_kernel<<<dim3((N + 63) / 64, (K + 63) / 64), 256, 0, stream>>>(in, ld_in, K, N, out, ld_out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scale_pairs_to_rows(const uint8_t* in, int N, int K, uint8_t* out, int sm_count, cudaStream_t stream) {
+    const int scale_cols = ((K + 63) / 64) * 2;
+    if (N <= 0 || scale_cols <= 0) return cudaSuccess;
+    long long blocks = ((long long)N * (scale_cols / 2) + 255) / 256;
+    if (blocks > (long long)sm_count * 8) blocks = (long long)sm_count * 8;
+    const int grid = (int)blocks;
+    scale_pairs_to_rows_kernel<<<grid, 256, 0, stream>>>(in, N, scale_cols, out);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_zero_words(int* p, int words, cudaStream_t stream) {
     if (words <= 0) return cudaSuccess;

@@ -52,7 +52,7 @@ class MxGemmArgs(C.Structure):
         ("cta_pair", C.c_int32),
         ("a_elem", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("d_type", C.c_int32), ("reserved", C.c_int32),
+        ("d_type", C.c_int32), ("b_layout", C.c_int32),
         ("scaleD", C.c_void_p),
     ]
 
@@ -204,11 +204,11 @@ def quantize_fp8_blocks(w):
 
 def mx_gemm_args(a, sa, b, sb, out, *, b_elem=ELEM_E4M3, bias=None, residual=None, activation=ACT_IDENTITY,
                  tile_n=0, reuse_b_prepass=False, sm_limit=0, cta_pair=0, workspace=None, a_elem=ELEM_E4M3,
-                 scale_out=None) -> MxGemmArgs:
+                 scale_out=None, b_n_major=False) -> MxGemmArgs:
     M, K = a.shape
     if a_elem == ELEM_E2M1:
         K *= 2                       # two codes per byte
-    N = b.shape[0]
+    N = b.shape[1] if b_n_major else b.shape[0]
     args = MxGemmArgs()
     args.struct_size = C.sizeof(MxGemmArgs)
     args.M, args.N, args.K = M, N, K
@@ -228,6 +228,7 @@ def mx_gemm_args(a, sa, b, sb, out, *, b_elem=ELEM_E4M3, bias=None, residual=Non
     args.cta_pair = cta_pair
     args.a_elem = a_elem
     args.scaleD = scale_out.data_ptr() if scale_out is not None else None
+    args.b_layout = 1 if b_n_major else 0
     if workspace is not None:
         args.workspace, args.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
     return args
@@ -243,7 +244,7 @@ def mx_gemm(a, sa, b, sb, *, out=None, workspace=None, **kw):
     """D = act(A x B^T + bias) + residual for MX operands; allocates `out` / `workspace` when not given."""
     import torch
     M = a.shape[0]
-    N = b.shape[0]
+    N = b.shape[1] if kw.get("b_n_major") else b.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
     args = mx_gemm_args(a, sa, b, sb, out, workspace=workspace, **kw)

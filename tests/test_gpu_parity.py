@@ -560,6 +560,58 @@ def test_fp8_quantised_output_feeds_the_next_gemm(cuda_device, M, N, K, split):
     assert H.device_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 520, 1040), (128, 136, 96), (512, 768, 2048)])
+def test_mx_n_major_weight(cuda_device, M, N, K):
+    """B stored [K][N] (N contiguous) with the scale layout the reference pairs with it, [K/64][N][2]
+    (include/tensor_api/impl/tensor_api/tensor/layout_pattern.h:204-215): same bits as the K-major call, through the
+    C ABI and through a descriptor whose n stride is 1."""
+    import ctypes as C
+    import torch
+    from ops_tensor_b200 import native
+    a = o.normal_f32(31, 0, (M, K), 1.0)
+    w = o.normal_f32(31, 1, (N, K), 1.0)
+    MX = H.SCALE_MX_E8M0_VEC32
+    qa, sa = H.quantize(dev_tensor(a, cuda_device), MX)
+    qb, sb = H.quantize(dev_tensor(w, cuda_device), MX)
+    want = native.mx_gemm(qa, sa, qb, sb)
+    ldb = -(-N // 16) * 16
+    qb_t = torch.zeros((K, ldb), dtype=torch.uint8, device=cuda_device)[:, :N]
+    qb_t.copy_(qb.t())
+    pairs = sb.shape[1] // 2
+    sb_pairs = sb.view(N, pairs, 2).permute(1, 0, 2).contiguous()            # [K/64][N][2]
+    got = native.mx_gemm(qa, sa, qb_t, sb_pairs, b_n_major=True)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    # host API: B described as [n, k] with strides (1, ldb)
+    h = H.create_handle()
+    dA = H.create_tensor_descriptor(h, [M, K], [K, 1], H.R_8F_E4M3)
+    dB = H.create_tensor_descriptor(h, [N, K], [1, ldb], H.R_8F_E4M3)
+    dD = H.create_tensor_descriptor(h, [M, N], [N, 1], H.R_16BF)
+    op, pref, plan = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    H.check(H.api.acltensorCreateContraction(h, C.byref(op), dA, H.i32([0, 2]), H.OP_IDENTITY, dB, H.i32([1, 2]),
+                                             H.OP_IDENTITY, None, None, H.OP_IDENTITY, dD, H.i32([0, 1]),
+                                             H.COMPUTE_DESC_32F), "create")
+    H.set_attribute(h, op, H.ATTR_SCALE_MODE_A, MX)
+    H.set_attribute(h, op, H.ATTR_SCALE_MODE_B, MX)
+    H.check(H.api.acltensorCreatePlanPreference(h, C.byref(pref), H.ALGO_DEFAULT), "pref")
+    H.check(H.api.acltensorCreatePlan(h, C.byref(plan), op, pref, 2 ** 62), "plan")
+    need = C.c_uint64(0)
+    H.check(H.api.acltensorPlanGetRequiredWorkspace(plan, C.byref(need)), "ws")
+    ws = torch.empty(need.value, dtype=torch.uint8, device=cuda_device)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=cuda_device)
+    aux = H.ContractionAux(sa.data_ptr(), sb_pairs.data_ptr(), None, None, None)
+    H.check(H.api.acltensorContract(h, plan, None, qa.data_ptr(), qb_t.data_ptr(), None, None, out.data_ptr(),
+                                    C.byref(aux), ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream),
+            "contract")
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    for obj, destroy in ((plan, H.api.acltensorDestroyPlan), (pref, H.api.acltensorDestroyPlanPreference),
+                         (op, H.api.acltensorDestroyOperationDescriptor)):
+        destroy(obj)
+    for d in (dA, dB, dD):
+        H.api.acltensorDestroyTensorDescriptor(d)
+    H.api.acltensorDestroy(h)
+    assert H.device_status() == 0
+
+
 def test_mx_agrees_with_vendor_mxfp8_gemm(cuda_device):
     """An independent implementation of the same format: the vendor library's MXFP8 GEMM (torch._scaled_mm with E8M0
     scales per 32 K) on the same codes and scales.  Both accumulate in float32 and round once to bf16, so they may
