@@ -348,3 +348,24 @@ def test_batched_contraction_descriptor_rules(built_library):
     bd.a[3] = 4
     assert native.lib().blazeMxGemmBatchedWorkspaceSize(C.byref(a), C.byref(bd), C.byref(n)) == H.STATUS_SUCCESS
     assert n.value > 0
+
+
+def test_c99_client_compiles_and_runs(built_library, tmp_path):
+    """The public headers are plain C and the library links from C: tests/c_client/client.c walks the reference's call
+    sequence (handle, descriptors, operation, preference, plan) and the contraction planning flow on the host."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    root = Path(__file__).resolve().parent.parent
+    exe = tmp_path / "blaze_c_client"
+    libdir = Path(built_library).parent
+    cmd = [gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", f"-I{root / 'include'}",
+           str(root / "tests" / "c_client" / "client.c"), f"-L{libdir}", "-lops_tensor_b200", f"-Wl,-rpath,{libdir}",
+           "-o", str(exe)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "c client ok" in r.stdout
