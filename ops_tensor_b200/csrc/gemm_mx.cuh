@@ -27,6 +27,7 @@ namespace blaze {
 struct MxGemmParams {
     int M, N, K;
     int m_tiles, n_tiles, k_steps;
+    int sf_k_steps;                // 128-K blocks per tile row in the re-tiled scale arrays (= k_steps except for kind::mxf4)
     int window;                    // M-tile rows per serpentine band
     const uint8_t* sfa_tiled;      // [m_tiles][k_steps][512]
     const uint8_t* sfb_tiled;      // [n_tiles][k_steps][kSfbBytes]

@@ -21,20 +21,23 @@
 
 namespace blaze {
 
-template <int kBN, int kStages, bool kWide = true>
+template <int kBN, int kStages, bool kWide = true, bool kMxf4 = false>
 struct MxPairSmem {
     static constexpr int kBM = 128;                       // rows of A per CTA (256 per pair)
     static constexpr int kBK = 128;
     static constexpr int kABytes = kBM * kBK;
     static constexpr int kBHalfBytes = (kBN / 2) * kBK;
     static constexpr int kStageBytes = kABytes + kBHalfBytes;
-    static constexpr int kSfaBytes = 512;
+    // kMxf4: operands are dense 4-bit codes, a 128-byte row holds K = 256, i.e. two 128-K scale blocks per stage
+    static constexpr int kSfKPerStage = kMxf4 ? 2 : 1;
+    static constexpr int kSfaBytes = 512 * kSfKPerStage;
     static constexpr int kSfbAtoms = (kBN + 127) / 128;
     // kWide: both scale atoms of B go into TMEM with one 128x256b tcgen05.cp (a scale copy costs tensor-pipe time per
     // instruction, not per byte).  That shape has no lane broadcast, so the re-tiled scale array holds each
     // 512-byte atom four times, once per 32-lane quadrant: [atom][quadrant][32 lanes][16 B] per K step.
     static constexpr bool kWideSfb = kWide;
-    static constexpr int kSfbBlocks = kWideSfb ? kSfbAtoms * 4 : kSfbAtoms;     // 512-byte blocks per K step
+    static constexpr int kSfbBlocksPerK = kWideSfb ? kSfbAtoms * 4 : kSfbAtoms;   // 512-byte blocks per 128 K
+    static constexpr int kSfbBlocks = kSfbBlocksPerK * kSfKPerStage;              // per stage
     static constexpr int kSfbBytes = kSfbBlocks * 512;
     static constexpr int kSfOffset = kStages * kStageBytes;
     static constexpr int kBarOffset = kSfOffset + kStages * (kSfaBytes + kSfbBytes);
@@ -64,20 +67,22 @@ __device__ __forceinline__ void tma_load_2d_to_pair_bar(void* smem_dst, const CU
         : "memory");
 }
 
-template <int kBN, int kStages, int kAct, bool kWide = true>
+template <int kBN, int kStages, int kAct, bool kWide = true, bool kMxf4 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                     const __grid_constant__ CUtensorMap tmap_d, const MxGemmParams p) {
-    using L = MxPairSmem<kBN, kStages, kWide>;
+    using L = MxPairSmem<kBN, kStages, kWide, kMxf4>;
+    static_assert(!kMxf4 || kWide, "the FP4 form copies B's scales with the wide copy");
     static_assert(kBN % 32 == 0 && kBN >= 32 && kBN <= 256, "tile N");
     constexpr int kAccStages = 2;
-    constexpr int kSfCols = 4 + 4 * L::kSfbAtoms;
+    constexpr int kSfCols = (4 + 4 * L::kSfbAtoms) * L::kSfKPerStage;
+    constexpr int kSfReserve = (kSfCols + 15) / 16 * 16;
     constexpr bool kOverlap = kAccStages * kBN + kSfCols > 512;         // accumulators share their edge columns
-    constexpr int kSfaCol = kOverlap ? 512 - 16 : kAccStages * kBN;
-    constexpr int kSfbCol = kSfaCol + 4;
+    constexpr int kSfaCol = kOverlap ? 512 - kSfReserve : kAccStages * kBN;
+    constexpr int kSfbCol = kSfaCol + 4 * L::kSfKPerStage;
     constexpr int kAccStride = kOverlap ? kSfaCol - kBN : kBN;           // column of accumulator 1
-    static_assert(kSfbCol + 4 * L::kSfbAtoms <= 512, "TMEM budget");
+    static_assert(kSfbCol + 4 * L::kSfbAtoms * L::kSfKPerStage <= 512, "TMEM budget");
     static_assert(!kOverlap || (kBN - kAccStride <= 32 && kAccStride % 16 == 0), "shared columns fit one chunk");
     constexpr int kChunks = kBN / 32;
     constexpr uint32_t kTmemCols = 512;
@@ -144,8 +149,8 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);
                 const int a_row = mt * 256 + (int)cta_rank * 128;
                 const int b_row = nt * kBN + (int)cta_rank * (kBN / 2);
-                const int sfa_row = (mt * 2 + (int)cta_rank) * p.k_steps;
-                const int sfb_row = nt * p.k_steps * L::kSfbBlocks;
+                const int sfa_row = (mt * 2 + (int)cta_rank) * p.sf_k_steps;
+                const int sfb_row = nt * p.sf_k_steps * L::kSfbBlocksPerK;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
@@ -161,7 +166,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t bar = map_to_cta(&full_bar[stage], 0);
                     tma_load_2d_to_pair_bar(a_dst, &tmap_a, bar, ks * L::kBK, a_row, kEvictNormal);
                     tma_load_2d_to_pair_bar(b_dst, &tmap_b, bar, ks * L::kBK, b_row, kEvictNormal);
-                    tma_load_2d_to_pair_bar(sfa_dst, &tmap_sfa, bar, 0, sfa_row + ks, kEvictNormal);
+                    tma_load_2d_to_pair_bar(sfa_dst, &tmap_sfa, bar, 0, sfa_row + ks * L::kSfKPerStage, kEvictNormal);
                     tma_load_2d_to_pair_bar(sfb_dst, &tmap_sfb, bar, 0, sfb_row + ks * L::kSfbBlocks, kEvictNormal);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
@@ -195,6 +200,27 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t b_addr = a_addr + L::kABytes;
                     const uint32_t sfa_addr = smem_u32(smem + L::kSfOffset + stage * (L::kSfaBytes + L::kSfbBytes));
                     const uint32_t sfb_addr = sfa_addr + L::kSfaBytes;
+                    const uint64_t a_desc = umma_desc_sw128(a_addr);
+                    const uint64_t b_desc = umma_desc_sw128(b_addr);
+                    if constexpr (kMxf4) {
+                        // two 128-K scale blocks per stage: A's by the broadcasting copy, B's two atoms by one wide copy
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            utccp_sf<2>(tmem_base + kSfaCol + 4 * h, umma_desc_sf(sfa_addr + 512 * h));
+                            utccp_sf_wide<2>(tmem_base + kSfbCol + 8 * h,
+                                             umma_desc_sf_wide(sfb_addr + h * (L::kSfbBytes / 2), 4 * 512));
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            // K = 64 per instruction = 32 bytes of packed codes; scale bytes 2 (j % 2) and + 1 of
+                            // block j / 2
+                            const uint32_t id = (uint32_t)(j & 1) * 2;
+                            umma_mxf4_pair(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
+                                           umma_idesc_mx(FMT_MXF4_E2M1, FMT_MXF4_E2M1, 256, kBN, id, id),
+                                           (ks | j) != 0 ? 1u : 0u, tmem_base + kSfaCol + 4 * (j >> 1),
+                                           tmem_base + kSfbCol + 8 * (j >> 1));
+                        }
+                    } else {
                     utccp_sf<2>(tmem_base + kSfaCol, umma_desc_sf(sfa_addr));
                     if constexpr (L::kWideSfb) {
                         utccp_sf_wide<2>(tmem_base + kSfbCol, umma_desc_sf_wide(sfb_addr, 4 * 512));
@@ -204,13 +230,12 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                             utccp_sf<2>(tmem_base + kSfbCol + 4 * i, umma_desc_sf(sfb_addr + 512 * i));
                         }
                     }
-                    const uint64_t a_desc = umma_desc_sw128(a_addr);
-                    const uint64_t b_desc = umma_desc_sw128(b_addr);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         umma_mx<2>(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
                                    umma_idesc_mx(p.a_format, p.b_format, 256, kBN, j, j), (ks | j) != 0 ? 1u : 0u,
                                    tmem_base + kSfaCol, tmem_base + kSfbCol);
+                    }
                     }
                     umma_commit_pair(&empty_bar[stage], 0x3);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }

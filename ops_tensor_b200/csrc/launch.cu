@@ -147,6 +147,8 @@ struct MxPlan {
     bool pair;          // 256-row tiles on 2-CTA clusters
     int tile_n;
     int sfb_replicas;   // copies of every 512-byte scale block of B in the re-tiled array
+    bool mxf4;          // FP4 x FP4 on kind::mxf4 (dense 4-bit tiles, K = 256 per stage)
+    int sf_k_steps;     // 128-K blocks of the re-tiled scale arrays
     int m_tiles, n_tiles, k_steps;
     size_t sfa_bytes, sfb_bytes, b_expand_bytes, b_scale_rows_bytes;
     size_t sfa_off, sfb_off, b_expand_off, b_scale_rows_off, total;
@@ -210,14 +212,20 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scal
     } else {
         pl->tile_n = choose_tile_n(a->M, a->N, sms, a->tile_n);
     }
+    // FP4 x FP4 at the double rate needs the 2-CTA 256-wide tiles, whole 256-K stages and the replicated scale blocks
+    pl->mxf4 = a->a_elem == BLAZE_ELEM_E2M1 && a->b_elem == BLAZE_ELEM_E2M1 && pl->pair && wide_scale_copy &&
+               (a->tile_n == 0 || a->tile_n == 256) && (a->K % 256) == 0 && a->K > 0;
+    if (pl->mxf4) pl->tile_n = 256;
     pl->m_tiles = pl->pair ? (a->M + 255) / 256 : (a->M + 127) / 128;
     pl->n_tiles = (a->N + pl->tile_n - 1) / pl->tile_n;
-    pl->k_steps = (a->K + 127) / 128;
+    pl->sf_k_steps = (a->K + 127) / 128;
+    pl->k_steps = pl->mxf4 ? a->K / 256 : pl->sf_k_steps;
     pl->sfa_bytes = (size_t)sf_tiled_bytes(a->M, a->K, 128);
     pl->sfb_replicas = (pl->pair && wide_scale_copy) ? 4 : 1;        // the wide copy has no lane broadcast
     pl->sfb_bytes = (size_t)sf_tiled_bytes(a->N, a->K, pl->tile_n, pl->sfb_replicas);
     // room for a one-byte-per-code K-major copy of B: the expansion of a packed E2M1 B, or the transpose of an N-major B
-    pl->b_expand_bytes = (a->b_elem == BLAZE_ELEM_E2M1 || a->b_layout == BLAZE_B_N_MAJOR) ? (size_t)a->N * (size_t)a->K : 0;
+    pl->b_expand_bytes = ((a->b_elem == BLAZE_ELEM_E2M1 && !pl->mxf4) || a->b_layout == BLAZE_B_N_MAJOR)
+                             ? (size_t)a->N * (size_t)a->K : 0;
     pl->b_scale_rows_bytes = a->b_layout == BLAZE_B_N_MAJOR ? (size_t)a->N * (size_t)(((a->K + 63) / 64) * 2) : 0;
     pl->sfa_off = 0;
     pl->sfb_off = round256(pl->sfa_bytes);
@@ -290,13 +298,13 @@ static bool make_tmap_sf_blocks(CUtensorMap* map, const void* base, uint64_t blo
     return r == CUDA_SUCCESS;
 }
 
-template <int kBN, int kAct, bool kWide>
+template <int kBN, int kAct, bool kWide, bool kMxf4 = false>
 static cudaError_t launch_mx_pair_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
                                            const CUtensorMap& tsb, const CUtensorMap& td, const MxGemmParams& p,
                                            int pairs, cudaStream_t stream) {
     constexpr int kStages = kWide ? 5 : 6;           // the replicated scale block costs a stage of shared memory
-    using L = MxPairSmem<kBN, kStages, kWide>;
-    auto kernel = mx_gemm_pair_kernel<kBN, kStages, kAct, kWide>;
+    using L = MxPairSmem<kBN, kStages, kWide, kMxf4>;
+    auto kernel = mx_gemm_pair_kernel<kBN, kStages, kAct, kWide, kMxf4>;
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -309,17 +317,17 @@ static cudaError_t launch_mx_pair_instance(const CUtensorMap& ta, const CUtensor
     return launch_after_prepass(kernel, 2 * pairs, 192, L::kDynamicBytes, stream, ta, tb, tsa, tsb, td, p);
 }
 
-template <int kBN, bool kWide>
+template <int kBN, bool kWide, bool kMxf4 = false>
 static cudaError_t launch_mx_pair_act(int act, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
                                       const CUtensorMap& tsb, const CUtensorMap& td, const MxGemmParams& p, int pairs,
                                       cudaStream_t stream) {
     switch (act) {
-        case BLAZE_ACT_RELU: return launch_mx_pair_instance<kBN, ACT_RELU, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
-        case BLAZE_ACT_GELU_TANH: return launch_mx_pair_instance<kBN, ACT_GELU_TANH, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
-        case BLAZE_ACT_SILU: return launch_mx_pair_instance<kBN, ACT_SILU, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
-        case BLAZE_ACT_SIGMOID: return launch_mx_pair_instance<kBN, ACT_SIGMOID, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
-        case BLAZE_ACT_TANH: return launch_mx_pair_instance<kBN, ACT_TANH, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
-        default: return launch_mx_pair_instance<kBN, ACT_IDENTITY, kWide>(ta, tb, tsa, tsb, td, p, pairs, stream);
+        case BLAZE_ACT_RELU: return launch_mx_pair_instance<kBN, ACT_RELU, kWide, kMxf4>(ta, tb, tsa, tsb, td, p, pairs, stream);
+        case BLAZE_ACT_GELU_TANH: return launch_mx_pair_instance<kBN, ACT_GELU_TANH, kWide, kMxf4>(ta, tb, tsa, tsb, td, p, pairs, stream);
+        case BLAZE_ACT_SILU: return launch_mx_pair_instance<kBN, ACT_SILU, kWide, kMxf4>(ta, tb, tsa, tsb, td, p, pairs, stream);
+        case BLAZE_ACT_SIGMOID: return launch_mx_pair_instance<kBN, ACT_SIGMOID, kWide, kMxf4>(ta, tb, tsa, tsb, td, p, pairs, stream);
+        case BLAZE_ACT_TANH: return launch_mx_pair_instance<kBN, ACT_TANH, kWide, kMxf4>(ta, tb, tsa, tsb, td, p, pairs, stream);
+        default: return launch_mx_pair_instance<kBN, ACT_IDENTITY, kWide, kMxf4>(ta, tb, tsa, tsb, td, p, pairs, stream);
     }
 }
 
@@ -334,6 +342,7 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
     MxGemmParams p;
     p.M = a->M; p.N = a->N; p.K = a->K;
     p.m_tiles = pl.m_tiles; p.n_tiles = pl.n_tiles; p.k_steps = pl.k_steps;
+    p.sf_k_steps = pl.sf_k_steps;
     p.window = pl.pair ? (pl.m_tiles < 8 ? pl.m_tiles : 8) : (pl.m_tiles < 16 ? pl.m_tiles : 16);
     p.sfa_tiled = sfa_tiled;
     p.sfb_tiled = sfb_tiled;
@@ -361,11 +370,14 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
         return ACLTENSOR_STATUS_INTERNAL_ERROR;
     if (pl.pair) {
         CUtensorMap tsa, tsb;
-        const uint64_t sfa_blocks = (uint64_t)((a->M + 127) / 128) * pl.k_steps;
-        const uint64_t sfb_blocks = (uint64_t)pl.n_tiles * pl.k_steps * 2 * pl.sfb_replicas;
-        if (!(ta_packed || make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128)) ||
-            !(tb_packed || make_tmap_bytes(&tb, b_codes, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n / 2)) ||
-            !make_tmap_sf_blocks(&tsa, sfa_tiled, sfa_blocks, 1) || !make_tmap_sf_blocks(&tsb, sfb_tiled, sfb_blocks, 2 * pl.sfb_replicas))
+        const uint64_t sfa_blocks = (uint64_t)((a->M + 127) / 128) * pl.sf_k_steps;
+        const uint64_t sfb_blocks = (uint64_t)pl.n_tiles * pl.sf_k_steps * 2 * pl.sfb_replicas;
+        const uint64_t k_bytes = pl.mxf4 ? (uint64_t)a->K / 2 : (uint64_t)a->K;      // dense 4-bit rows for kind::mxf4
+        const uint32_t sf_per_stage = pl.mxf4 ? 2 : 1;
+        if (!(ta_packed || make_tmap_bytes(&ta, a->A, k_bytes, (uint64_t)a->M, (uint64_t)a->lda, 128)) ||
+            !(tb_packed || make_tmap_bytes(&tb, b_codes, k_bytes, (uint64_t)a->N, (uint64_t)b_pitch, (uint32_t)pl.tile_n / 2)) ||
+            !make_tmap_sf_blocks(&tsa, sfa_tiled, sfa_blocks, sf_per_stage) ||
+            !make_tmap_sf_blocks(&tsb, sfb_tiled, sfb_blocks, 2 * pl.sfb_replicas * sf_per_stage))
             return ACLTENSOR_STATUS_INTERNAL_ERROR;
         if (tb_packed) tb = *tb_packed;
         if (ta_packed) ta = *ta_packed;
@@ -373,7 +385,9 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
         if (pairs < 1) pairs = 1;
         if (tiles < pairs) pairs = (int)tiles;
         const bool wide = pl.sfb_replicas == 4;
-        if (pl.tile_n == 256) {
+        if (pl.mxf4) {
+            e = launch_mx_pair_act<256, true, true>(a->activation, ta, tb, tsa, tsb, td, p, pairs, stream);
+        } else if (pl.tile_n == 256) {
             e = wide ? launch_mx_pair_act<256, true>(a->activation, ta, tb, tsa, tsb, td, p, pairs, stream)
                      : launch_mx_pair_act<256, false>(a->activation, ta, tb, tsa, tsb, td, p, pairs, stream);
         } else {
@@ -444,6 +458,15 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
     if (e != cudaSuccess) return status_of(e);
     // A packed E2M1 weight is fed to the tensor core as it is when TMA can unpack it (whole 128-code boxes along K,
     // 32-byte aligned rows); otherwise it is expanded once to one-byte E4M3 codes of the same values.
+    if (pl.mxf4) {
+        // FP4 x FP4 at the double rate: both operands stay packed, plain byte loads, kind::mxf4
+        if (!a->reuse_b_prepass) {
+            e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleB), a->N, a->K, pl.tile_n, pl.sfb_replicas, sfb_tiled,
+                                 ctx->sm_count, stream);
+            if (e != cudaSuccess) return status_of(e);
+        }
+        return run_mx_kernel(a, pl, sfa_tiled, sfb_tiled, b_codes, b_pitch, ctx->status_word, ctx->sm_count, stream);
+    }
     CUtensorMap tb_packed;
     bool native4 = false;
     if (a->b_elem == BLAZE_ELEM_E2M1 && (a->K % 128) == 0 && (a->ldb % 32) == 0 &&

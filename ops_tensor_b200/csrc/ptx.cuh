@@ -336,6 +336,7 @@ __device__ __forceinline__ uint64_t umma_desc_sf_wide(uint32_t smem_addr, uint32
 }
 
 enum UmmaFormat : uint32_t { FMT_E4M3 = 0, FMT_E5M2 = 1, FMT_E2M1 = 5 };
+constexpr uint32_t FMT_MXF4_E2M1 = 1;     // E2M1 in the format numbering of kind::mxf4
 
 // Instruction descriptor for kind::f8f6f4 (fp32 accumulate, both operands K-major).
 __host__ __device__ constexpr uint32_t umma_idesc_f8(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n) {
@@ -432,6 +433,21 @@ __device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t a_desc, uint64
             "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
             : "memory");
     }
+}
+
+// FP4 x FP4 with one E8M0 scale per 32 K: dense 4-bit operands (two codes per byte in shared memory), K = 64 per
+// instruction, i.e. two scale bytes of each operand per instruction (ids 0 or 2 pick the byte pair of the TMEM cell).
+// Twice the rate of kind::mxf8f6f4.  2-CTA form only.
+__device__ __forceinline__ void umma_mxf4_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate, uint32_t tmem_sfa, uint32_t tmem_sfb) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
 }
 
 // Copy one 32-row x 16-byte scale-factor block from shared memory into 4 TMEM columns, replicated into all

@@ -431,6 +431,37 @@ def test_mxfp4_both_operands(cuda_device, M, N, K):
         H.Contraction(M, N, K, scale_mode_a=MX, scale_mode_b=MX, a_dtype=H.R_4F_E2M1)
 
 
+@pytest.mark.parametrize("M,N,K,sm_limit", [(1000, 1544, 768, 4), (512, 1024, 2048, 0), (300, 520, 256, 0)])
+def test_mxfp4_double_rate_kernel(cuda_device, M, N, K, sm_limit):
+    """FP4 x FP4 on kind::mxf4 (dense 4-bit tiles, K = 64 per instruction; chosen for 2-CTA tiles when K % 256 == 0)
+    against the float64 reference, and against the same product computed through kind::mxf8f6f4 (tile width 224 forces
+    that route): products of E2M1 codes and power-of-two scales are exact, so the two may differ only by summation
+    order."""
+    import torch
+    a = o.normal_f32(32, 0, (M, K), 1.0)
+    w = o.normal_f32(32, 1, (N, K), 0.05)
+    bias = o.normal_f32(32, 2, (N,), 0.5)
+    MX = H.SCALE_MX_E8M0_VEC32
+    qa, sa = H.quantize(dev_tensor(a, cuda_device), MX, H.R_4F_E2M1)
+    qb, sb = H.quantize(dev_tensor(w, cuda_device), MX, H.R_4F_E2M1)
+    outs = []
+    for tile_n in (0, 224):
+        out = torch.full((M, N), float("nan"), dtype=torch.float32, device=cuda_device)
+        with H.Contraction(M, N, K, scale_mode_a=MX, scale_mode_b=MX, a_dtype=H.R_4F_E2M1, b_dtype=H.R_4F_E2M1,
+                           activation=H.OP_RELU, bias=True, d_dtype=H.R_32F, tile_n=tile_n, cta_pair=2,
+                           sm_limit=sm_limit) as c:
+            c(qa, sa, qb, sb, out, bias=bf16_tensor(bias, cuda_device))
+        outs.append(out.cpu().numpy().astype(np.float64))
+    da = o.dequant_mx(to_np(qa), to_np(sa), K, "e2m1")
+    db = o.dequant_mx(to_np(qb), to_np(sb), K, "e2m1")
+    ref = o.matmul_ref64(da, db, o.bf16_round(bias), o.ACT_RELU)
+    for got in outs:
+        assert np.all(np.isfinite(got))
+        assert o.maxrel(got, ref) <= 2.0 ** -13
+    assert o.maxrel(outs[0], outs[1]) <= 2.0 ** -13
+    assert H.device_status() == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 224, 128), (200, 448, 1024), (64, 1000, 4096), (150, 264, 96), (300, 520, 1056)])
 def test_w4a8_mx(cuda_device, M, N, K):
     a = o.normal_f32(23, 0, (M, K), 1.0)
