@@ -38,6 +38,8 @@ WORKLOADS = {
     "c3": ("mx4", 4096, 14336, 4096, "W4A8 MX GEMM 4096x14336x4096, bf16 out"),
     "c4": ("grouped", 32768, 768, 2048, "MoE grouped FP8 matmul G=128, K=2048, N=768, 32768 tokens"),
     "c5": ("fp8sk", 128, 7168, 18432, "stream-K decode FP8 GEMM M=128, N=7168, K=18432 + bf16 residual"),
+    # beyond the five configurations: C2's shape with both operands MXFP4, on kind::mxf4
+    "c6": ("mxf4", 8192, 8192, 8192, "MXFP4 x MXFP4 GEMM 8192^3 + bf16 bias + GELU(tanh), bf16 out"),
 }
 
 
@@ -45,6 +47,8 @@ def algorithmic_bytes(kind, M, N, K, G=128):
     """Minimum HBM traffic: operands, scales, epilogue inputs and the output, each moved once."""
     if kind == "mx":
         return M * K + N * K + (M + N) * (K // 32) + 2 * N + 2 * M * N
+    if kind == "mxf4":
+        return M * K // 2 + N * K // 2 + (M + N) * (K // 32) + 2 * N + 2 * M * N
     if kind == "mx4":
         return M * K + N * K // 2 + (M + N) * (K // 32) + 2 * M * N
     if kind == "grouped":
@@ -145,18 +149,20 @@ def make_cpu_golden(workload):
         pass
     kind, M, N, K, desc = WORKLOADS[workload]
     cfg = int(workload[1:])
-    if kind in ("mx", "mx4"):
+    if kind in ("mx", "mx4", "mxf4"):
         rows, cols = min(2048, M), min(4096, N)
-        name = "e2m1" if kind == "mx4" else "e4m3"
+        name = "e4m3" if kind == "mx" else "e2m1"
+        name_a = "e2m1" if kind == "mxf4" else "e4m3"
+        dense = kind in ("mx", "mxf4")                     # C2-style: N(0,1) weights, bias + GELU
         a = o.normal_f32(cfg, 0, (rows, K), 1.0)
-        w = o.normal_f32(cfg, 1, (cols, K), 1.0 if kind == "mx" else 0.02)
-        bias = o.bf16_round(o.normal_f32(cfg, 2, (cols,), 0.1)) if kind == "mx" else None
-        act = o.ACT_GELU_TANH if kind == "mx" else o.ACT_IDENTITY
-        qa, sa = o.quant_mx(a)
+        w = o.normal_f32(cfg, 1, (cols, K), 1.0 if dense else 0.02)
+        bias = o.bf16_round(o.normal_f32(cfg, 2, (cols,), 0.1)) if dense else None
+        act = o.ACT_GELU_TANH if dense else o.ACT_IDENTITY
+        qa, sa = o.quant_mx(a, name_a)
         qb, sb = o.quant_mx(w, name)
 
         def run():
-            da = o.dequant_mx(qa, sa, K, "e4m3", np.float32)
+            da = o.dequant_mx(qa, sa, K, name_a, np.float32)
             db = o.dequant_mx(qb, sb, K, name, np.float32)
             return o.matmul_golden32(da, db, bias, act)
         what = f"{rows} rows of A x {cols} rows of B x K={K}"
@@ -279,21 +285,22 @@ def gpu_arm(args):
     # ---- inputs (seeded, generated on the host once) -----------------------------------------------------------
     a_host = torch.from_numpy(o.normal_f32(cfg_id, 0, (M, K), 1.0)).pin_memory()
     a_dev = a_host.to(dev, non_blocking=True)
-    sigma_b = 1.0 if kind == "mx" else 0.02
+    sigma_b = 1.0 if kind in ("mx", "mxf4") else 0.02
     b_rows = G * N if kind == "grouped" else N
     w_dev = torch.from_numpy(o.normal_f32(cfg_id, 1 + 16 * rank, (b_rows, K), sigma_b)).to(dev)
     bias = residual = None
-    if kind == "mx":
+    if kind in ("mx", "mxf4"):
         bias = torch.from_numpy(o.normal_f32(cfg_id, 2, (N,), 0.1)).to(dev).to(torch.bfloat16)   # nearest-even
     if kind == "fp8sk":
         residual = torch.from_numpy(o.normal_f32(cfg_id, 3, (M, N), 1.0)).to(dev).to(torch.bfloat16)
 
-    if kind in ("mx", "mx4"):
-        b_dtype = H.R_4F_E2M1 if kind == "mx4" else H.R_8F_E4M3
+    a_dtype = H.R_4F_E2M1 if kind == "mxf4" else H.R_8F_E4M3
+    if kind in ("mx", "mx4", "mxf4"):
+        b_dtype = H.R_8F_E4M3 if kind == "mx" else H.R_4F_E2M1
         mode_a = mode_b = H.SCALE_MX_E8M0_VEC32
         qb, sb = H.quantize(w_dev, mode_b, b_dtype)
-        plan = H.Contraction(M, N, K, scale_mode_a=mode_a, scale_mode_b=mode_b, b_dtype=b_dtype,
-                             activation=H.OP_GELU if kind == "mx" else H.OP_IDENTITY, bias=bias is not None,
+        plan = H.Contraction(M, N, K, scale_mode_a=mode_a, scale_mode_b=mode_b, a_dtype=a_dtype, b_dtype=b_dtype,
+                             activation=H.OP_IDENTITY if kind == "mx4" else H.OP_GELU, bias=bias is not None,
                              b_is_static=True)
         launches_per_step = 2                        # scale re-tile of A + GEMM (B's pre-pass is reused)
     else:
@@ -313,7 +320,7 @@ def gpu_arm(args):
         # a plan that asks for workspace runs stream-K: a kernel that zeroes the fix-up flags, then the GEMM
         launches_per_step = 2 if plan.workspace_bytes > 0 else 1
     del w_dev
-    qa, sa = H.quantize(a_dev, mode_a)
+    qa, sa = H.quantize(a_dev, mode_a, a_dtype)
     out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
     out_host = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
     torch.cuda.synchronize()
@@ -351,9 +358,9 @@ def gpu_arm(args):
     dev_ops2 = [dev_ops, {k: torch.empty_like(v) for k, v in dev_ops.items()}]
     a_dev2 = [a_dev, torch.empty_like(a_dev)]
     plan_e2e = plan
-    if kind in ("mx", "mx4"):
-        plan_e2e = H.Contraction(M, N, K, scale_mode_a=mode_a, scale_mode_b=mode_b, b_dtype=b_dtype,
-                                 activation=H.OP_GELU if kind == "mx" else H.OP_IDENTITY, bias=bias is not None,
+    if kind in ("mx", "mx4", "mxf4"):
+        plan_e2e = H.Contraction(M, N, K, scale_mode_a=mode_a, scale_mode_b=mode_b, a_dtype=a_dtype, b_dtype=b_dtype,
+                                 activation=H.OP_IDENTITY if kind == "mx4" else H.OP_GELU, bias=bias is not None,
                                  b_is_static=False)
     h2d_bytes = {"operands": sum(v.numel() * v.element_size() for v in host_ops.values()),
                  "fp32": a_host.numel() * 4}
@@ -381,7 +388,7 @@ def gpu_arm(args):
                      group_rows=d.get("group_rows"))
             ev_consumed[b].record(main)
         else:
-            qa2, sa2 = H.quantize(a_dev2[b], mode_a)
+            qa2, sa2 = H.quantize(a_dev2[b], mode_a, a_dtype)
             ev_consumed[b].record(main)
             plan(qa2, sa2, qb, sb, out2[b], bias=bias, residual=residual, group_rows=group_rows)
         ev_computed[b].record(main)
@@ -455,12 +462,12 @@ def gpu_arm(args):
         peaks = measured_peaks()
         value = flops_job / (ms_per_step * 1e-3) / 1e12
         abytes = algorithmic_bytes(kind, M, N, K, G)
-        tensor_bound = kind in ("mx", "mx4")
+        tensor_bound = kind in ("mx", "mx4", "mxf4")
         if tensor_bound:
             # FP8 operands run at twice the bf16 MMA rate; the loop is timed back to back, so the burst figure
             # applies to short runs and the sustained one to runs of a second or more
             base = peaks["bf16_tflops_sustained"] if total_ms > 1000.0 else peaks["bf16_tflops"]
-            peak = 2.0 * base
+            peak = (4.0 if kind == "mxf4" else 2.0) * base      # FP4 x FP4 (kind::mxf4) runs at twice the FP8 rate
             achieved = flops / (ms_per_step * 1e-3) / 1e12
             unit = "TFLOP/s"
         else:
@@ -476,12 +483,14 @@ def gpu_arm(args):
             "metric": "quantized GEMM TFLOPS", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if strong else "weak",
-            "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
+            "vs_baseline": None, "dtype": "fp4" if kind == "mxf4" else "fp8", "data": "synthetic",
             "config": {"workload": desc, "M_rank0": M, "N_rank0": N, "K": K, "groups_rank0": G if kind == "grouped" else 0,
                        "job_flops_per_step": flops_job, "sharding": sharding,
                        "l2": "operands + output exceed the 126 MB L2" if abytes > 126e6 else "fits in L2 (latency config)",
                        "clock_ramp_steps": ramp_steps,
-                       "pct_of_published_dense_fp8_peak": round(100.0 * value / world / 4500.0, 2)},
+                       "pct_of_published_dense_fp8_peak": round(100.0 * value / world / 4500.0, 2),
+                       **({"pct_of_published_dense_fp4_peak": round(100.0 * value / world / 9000.0, 2)}
+                          if kind == "mxf4" else {})},
             "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak, "unit": unit,
                          "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
                          "algorithmic_bytes": abytes, "flops": flops},
