@@ -107,6 +107,8 @@ typedef struct {
     int32_t d_type;          /* blazeOutType_t of D (ldd counts elements of that type) */
     int32_t b_layout;        /* blazeBLayout_t */
     void* scaleD;            /* device, E8M0 scales of D when d_type is BLAZE_OUT_MX_E4M3, else NULL */
+    int32_t sched;           /* blazeSched_t; stream-K applies to the single-CTA tiles (skinny M or N) */
+    int32_t reserved;
 } blazeMxGemmArgs;
 
 BLAZE_API int blazeMxGemmWorkspaceSize(const blazeMxGemmArgs* args, size_t* bytes);

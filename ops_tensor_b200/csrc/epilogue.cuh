@@ -34,11 +34,13 @@ struct EpilogueArgs {
 // The 32-column chunks are visited in the order first_chunk, first_chunk + 1, ... (wrapping).  `early()` is called
 // once the TMEM read of the first visited chunk has completed, `release()` once the last TMEM read of the tile has
 // completed; both run before the remaining math and stores.
-template <int kBN, int kAct, class Early, class Release>
+// `post_load(c, v)` runs on the 32 raw accumulator values of chunk c before the fused ops (stream-K owners add the
+// other CTAs' partial sums there).
+template <int kBN, int kAct, class Early, class Release, class PostLoad>
 __device__ __forceinline__ void epilogue_store_tile_from(uint32_t tmem_tile, const EpilogueArgs& ea,
                                                          const CUtensorMap* tmap_d, uint8_t* stage, int row0, int col0,
                                                          int lane, uint32_t& chunk_counter, int first_chunk,
-                                                         Early early, Release release) {
+                                                         Early early, Release release, PostLoad post_load) {
     const int row = row0 + lane;
     const bool row_ok = row < ea.M;
     const __nv_bfloat16* r_row = (ea.residual && row_ok) ? ea.residual + (long long)row * ea.ldr : nullptr;
@@ -58,6 +60,7 @@ __device__ __forceinline__ void epilogue_store_tile_from(uint32_t tmem_tile, con
         tmem_ld_wait();
         if (i == 0) early();
         if (i == kChunks - 1) release();
+        post_load(c, v);
 
         // fused ops in place: v[] holds the finished float32 values afterwards
 #pragma unroll
@@ -203,7 +206,16 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t tmem_tile, const Ep
                                                     const CUtensorMap* tmap_d, uint8_t* stage, int row0, int col0,
                                                     int lane, uint32_t& chunk_counter, Release release) {
     epilogue_store_tile_from<kBN, kAct>(tmem_tile, ea, tmap_d, stage, row0, col0, lane, chunk_counter, 0, []() {},
-                                        release);
+                                        release, [](int, uint32_t (&)[32]) {});
+}
+
+template <int kBN, int kAct, class Early, class Release>
+__device__ __forceinline__ void epilogue_store_tile_from(uint32_t tmem_tile, const EpilogueArgs& ea,
+                                                         const CUtensorMap* tmap_d, uint8_t* stage, int row0, int col0,
+                                                         int lane, uint32_t& chunk_counter, int first_chunk,
+                                                         Early early, Release release) {
+    epilogue_store_tile_from<kBN, kAct>(tmem_tile, ea, tmap_d, stage, row0, col0, lane, chunk_counter, first_chunk, early,
+                                        release, [](int, uint32_t (&)[32]) {});
 }
 
 // To be called by lane 0 of every epilogue warp before the kernel ends.

@@ -152,15 +152,6 @@ struct Fp8WorkWalker {
     }
 };
 
-__device__ __forceinline__ int ld_acquire_gpu(const int* ptr) {
-    int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_gpu(int* ptr, int v) {
-    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
-}
-
 template <int kStages, int kAct>
 __global__ void __launch_bounds__(320, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,

@@ -40,6 +40,9 @@ struct MxGemmParams {
     uint32_t b_format;             // UmmaFormat of B in shared memory: FMT_E4M3, or FMT_E2M1 when TMA unpacks 4-bit codes
     uint32_t b_tx_shift;           // 1 when the B loads credit the barrier with the packed (half) byte count, else 0
     uint32_t a_format, a_tx_shift; // the same two for A
+    int stream_k;                  // single-CTA kernel: split the (tile, K step) units evenly over the grid
+    int* flags;                    // [gridDim.x], zeroed before the launch (stream-K only)
+    float* partials;               // [gridDim.x][kBN / 32 chunks][8][128 rows][4] float32 (stream-K only)
     int out_type;                  // OutType of D
     uint8_t* scale_d;              // OUT_MX_E4M3: [M][scale_cols_d] E8M0 scales of D
     int scale_cols_d;
@@ -57,7 +60,7 @@ struct MxGemmSmem {
     static constexpr int kSfOffset = kStages * kStageBytes;
     static constexpr int kBarOffset = kSfOffset + kStages * (kSfaBytes + kSfbBytes);
     // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
-    static constexpr int kNumBars = 2 * kStages + 4;
+    static constexpr int kNumBars = 2 * kStages + 5;
     static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
     static constexpr int kEpiOffset = (kMiscOffset + 16 + 1023) / 1024 * 1024;     // bf16 staging blocks of the epilogue
     static constexpr int kTotal = kEpiOffset + kEpiStageBytes;
@@ -74,6 +77,48 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
     mt = band * window + (r - n_idx * rows);
     nt = (band & 1) ? (n_tiles - 1 - n_idx) : n_idx;
 }
+
+// One unit of work of the single-CTA kernel: K steps [ks0, ks1) of one output tile.
+struct MxSegment {
+    int tile;
+    int ks0, ks1;
+};
+
+// Walks this CTA's segments; every warp role makes one with the same arguments and sees the same sequence.  Whole
+// tiles dealt round-robin, or (stream-K) an even share of all (tile, K step) units: a tail of one tile, whole tiles, and
+// a head of another.  The CTA that holds K step 0 of a tile owns it: it adds the partial sums the other CTAs left in
+// the workspace, in CTA order, and runs the epilogue (the scheme of the reference's stream-K scheduler and epilogue,
+// include/blaze/gemm/block/block_scheduler_matmul_streamk.h:90-146,
+// include/blaze/epilogue/block/block_epilogue_matmul_streamk.h:99-265).
+struct MxWorkWalker {
+    int k_steps, num_tiles, stream_k;
+    int next_tile;
+    long long unit, unit_end;
+
+    __device__ MxWorkWalker(const MxGemmParams& p, int num_tiles_)
+        : k_steps(p.k_steps), num_tiles(num_tiles_), stream_k(p.stream_k), next_tile(blockIdx.x) {
+        const long long total = (long long)num_tiles * k_steps;
+        unit = total * blockIdx.x / gridDim.x;
+        unit_end = total * (blockIdx.x + 1) / gridDim.x;
+    }
+    __device__ bool next(MxSegment& s) {
+        if (!stream_k) {
+            if (next_tile >= num_tiles) return false;
+            s.tile = next_tile;
+            s.ks0 = 0;
+            s.ks1 = k_steps;
+            next_tile += gridDim.x;
+            return true;
+        }
+        if (unit >= unit_end) return false;
+        s.tile = (int)(unit / k_steps);
+        s.ks0 = (int)(unit - (long long)s.tile * k_steps);
+        const long long left = unit_end - unit;
+        s.ks1 = (int)((long long)(k_steps - s.ks0) < left ? k_steps : s.ks0 + left);
+        unit += s.ks1 - s.ks0;
+        return true;
+    }
+};
 
 template <int kBN, int kStages, int kAct>
 __global__ void __launch_bounds__(192, 1)
@@ -94,6 +139,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint64_t* empty_bar = bars + kStages;
     uint64_t* tmem_full_bar = bars + 2 * kStages;
     uint64_t* tmem_empty_bar = bars + 2 * kStages + 2;
+    uint64_t* fix_bar = bars + 2 * kStages + 4;      // the 128 epilogue threads, once, when this CTA leaves a partial tile
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
 
@@ -109,6 +155,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mbar_init(&tmem_full_bar[s], 1);
             mbar_init(&tmem_empty_bar[s], 4);        // one arrival per epilogue warp
         }
+        mbar_init(fix_bar, 128);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -134,12 +181,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             uint32_t phase = 0;
             bool ok = true;
             grid_dependency_wait();        // the re-tiled scales come from the kernel launched just before this one
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            MxWorkWalker walk(p, num_tiles);
+            MxSegment seg;
+            while (ok && walk.next(seg)) {
                 int mt, nt;
-                tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);
+                tile_coords(seg.tile, p.m_tiles, p.n_tiles, p.window, mt, nt);
                 const uint8_t* sfa_src = p.sfa_tiled + (size_t)mt * p.k_steps * L::kSfaBytes;
                 const uint8_t* sfb_src = p.sfb_tiled + (size_t)nt * p.k_steps * L::kSfbBytes;
-                for (int ks = 0; ks < p.k_steps; ++ks) {
+                for (int ks = seg.ks0; ks < seg.ks1; ++ks) {
                     ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
                     uint8_t* a_dst = smem + stage * L::kStageBytes;
@@ -164,12 +213,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            MxWorkWalker walk(p, num_tiles);
+            MxSegment seg;
+            while (ok && walk.next(seg)) {
                 ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kBN;
-                for (int ks = 0; ks < p.k_steps; ++ks) {
+                for (int ks = seg.ks0; ks < seg.ks1; ++ks) {
                     ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
                     tcgen05_fence_after();
@@ -188,8 +239,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     for (int j = 0; j < 4; ++j) {
                         // 32 bytes further along K inside the swizzled row = 2 units of 16 bytes
                         umma_mx<1>(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
-                                   umma_idesc_mx(p.a_format, p.b_format, 128, kBN, j, j), (ks | j) != 0 ? 1u : 0u,
-                                   tmem_base + kSfaCol, tmem_base + kSfbCol);
+                                   umma_idesc_mx(p.a_format, p.b_format, 128, kBN, j, j),
+                                   (ks != seg.ks0 || j != 0) ? 1u : 0u, tmem_base + kSfaCol, tmem_base + kSfbCol);
                     }
                     umma_commit(&empty_bar[stage]);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -208,21 +259,94 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         uint8_t* stage_buf = smem + L::kEpiOffset + warp * kEpiStageBytesPerWarp;
         const EpilogueArgs ea{p.M, p.N, p.bias, p.residual, p.ldr, p.out_type, p.scale_d, p.scale_cols_d};
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        MxWorkWalker walk(p, num_tiles);
+        MxSegment seg;
+        const int r_in_tile = warp * 32 + lane;
+        constexpr int kChunks = kBN / 32;
+        while (ok && walk.next(seg)) {
             int mt, nt;
-            tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);
+            tile_coords(seg.tile, p.m_tiles, p.n_tiles, p.window, mt, nt);
             ok = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tcgen05_fence_after();
             uint64_t* release_bar = &tmem_empty_bar[acc];
-            epilogue_store_tile<kBN, kAct>(tmem_base + lane_base + acc * kBN, ea, &tmap_d, stage_buf,
-                                           mt * L::kBM + warp * 32, nt * kBN, lane, chunk_counter, [&]() {
-                                               tcgen05_fence_before();
-                                               __syncwarp();
-                                               if (lane == 0) mbar_arrive(release_bar);
-                                           });
+            const uint32_t tmem_tile = tmem_base + lane_base + acc * kBN;
+            auto release = [&]() {
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(release_bar);
+            };
             if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+
+            if (seg.ks0 > 0) {
+                // -------- contributor: leave the partial tile in this CTA's slot, [chunk][8][row][4] so that a warp
+                // writes 512 contiguous bytes per instruction, then raise the flag
+                float4* slot4 = reinterpret_cast<float4*>(p.partials + (size_t)blockIdx.x * (128 * kBN)) + r_in_tile;
+#pragma unroll 1
+                for (int c = 0; c < kChunks; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_tile + c * 32, v);
+                    tmem_ld_wait();
+                    if (c == kChunks - 1) release();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        __stcg(slot4 + (c * 8 + q) * 128,
+                               make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                           __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3])));
+                    }
+                }
+                __threadfence();
+                mbar_arrive(fix_bar);
+                if (threadIdx.x == 0) {
+                    if (mbar_wait(fix_bar, 0, abort_flag, p.status, DEV_TIMEOUT_FIXUP_FLAG)) {
+                        __threadfence();
+                        st_release_gpu(p.flags + blockIdx.x, 1);
+                    }
+                }
+                continue;
+            }
+            int j_first = 0, j_last = -1;                // CTAs whose partial sums belong to this tile
+            if (seg.ks1 < p.k_steps) {
+                // -------- owner of a split tile: wait for the CTAs that hold its later K ranges
+                const long long total = (long long)num_tiles * p.k_steps;
+                const long long tile_end = (long long)(seg.tile + 1) * p.k_steps;
+                j_first = blockIdx.x + 1;
+                for (int j = j_first; j < (int)gridDim.x; ++j) {
+                    if (total * j / gridDim.x >= tile_end) break;
+                    const long long t0 = clock64();
+                    while (ld_acquire_gpu(p.flags + j) == 0) {
+                        if (*abort_flag != 0) { ok = false; break; }
+                        if (clock64() - t0 > BLAZE_WAIT_LIMIT_CYCLES) {
+                            *abort_flag = 1;
+                            atomicCAS(p.status, 0, DEV_TIMEOUT_FIXUP_FLAG);
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(64);
+                    }
+                    if (!ok) break;
+                    j_last = j;
+                }
+                ok = __all_sync(0xffffffffu, ok);        // also re-converges the warp after the per-thread polling
+                if (!ok) break;
+            }
+            epilogue_store_tile_from<kBN, kAct>(
+                tmem_tile, ea, &tmap_d, stage_buf, mt * L::kBM + warp * 32, nt * kBN, lane, chunk_counter, 0, []() {},
+                release, [&](int c, uint32_t (&v)[32]) {
+                    for (int j = j_first; j <= j_last; ++j) {       // in CTA order: the sum is the same on every run
+                        const float4* slot4 =
+                            reinterpret_cast<const float4*>(p.partials + (size_t)j * (128 * kBN)) + r_in_tile;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const float4 w = __ldcg(slot4 + (c * 8 + q) * 128);
+                            v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + w.x);
+                            v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + w.y);
+                            v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) + w.z);
+                            v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) + w.w);
+                        }
+                    }
+                });
         }
         if (lane == 0) epilogue_drain_stores();
     }

@@ -86,9 +86,10 @@ void fill_batch(const acltensorOperationDescriptor& op, blazeBatchDims* b) {
     b->bias_per_batch = op.biasPerBatch;
 }
 
-acltensorStatus_t MxWorkspace(const acltensorOperationDescriptor& op, int32_t, uint64_t* bytes) {
+acltensorStatus_t MxWorkspace(const acltensorOperationDescriptor& op, int32_t splitPolicy, uint64_t* bytes) {
     blazeMxGemmArgs a;
     fill_mx_args(op, &a);
+    a.sched = sched_of(splitPolicy);
     size_t n = 0;
     blazeBatchDims bd;
     fill_batch(op, &bd);
@@ -100,6 +101,7 @@ acltensorStatus_t MxWorkspace(const acltensorOperationDescriptor& op, int32_t, u
 acltensorStatus_t MxExecute(const ContractionArgs& c) {
     blazeMxGemmArgs a;
     fill_mx_args(*c.op, &a);
+    a.sched = sched_of(c.splitPolicy);
     a.A = c.A;
     a.B = c.B;
     a.scaleA = c.scaleA;

@@ -148,6 +148,9 @@ struct MxPlan {
     int tile_n;
     int sfb_replicas;   // copies of every 512-byte scale block of B in the re-tiled array
     bool mxf4;          // FP4 x FP4 on kind::mxf4 (dense 4-bit tiles, K = 256 per stage)
+    bool stream_k;      // single-CTA tiles only: (tile, K step) units split evenly over the grid
+    int grid;           // CTAs of the single-CTA kernel
+    size_t flags_off, partials_off, flags_bytes, partials_bytes;
     int sf_k_steps;     // 128-K blocks of the re-tiled scale arrays
     int m_tiles, n_tiles, k_steps;
     size_t sfa_bytes, sfb_bytes, b_expand_bytes, b_scale_rows_bytes;
@@ -186,7 +189,8 @@ static int choose_pair_tile_n(int M, int N, int sms) {
 
 // `wide_scale_copy` = false keeps one copy of B's scale blocks (a quarter of the workspace, one more tensor-pipe copy
 // per K step); the allocation-free entry uses it when the replicated form does not fit its fixed array.
-static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scale_copy = true) {
+// `allow_split` = false keeps whole tiles per CTA (no stream-K workspace), likewise for that entry.
+static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scale_copy = true, bool allow_split = true) {
     if (!a || a->struct_size != sizeof(blazeMxGemmArgs)) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->M < 0 || a->N < 0 || a->K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->b_elem != BLAZE_ELEM_E4M3 && a->b_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
@@ -231,7 +235,29 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scal
     pl->sfb_off = round256(pl->sfa_bytes);
     pl->b_expand_off = pl->sfb_off + round256(pl->sfb_bytes);
     pl->b_scale_rows_off = pl->b_expand_off + round256(pl->b_expand_bytes);
-    pl->total = pl->b_scale_rows_off + round256(pl->b_scale_rows_bytes);
+    // Skinny problems (few single-CTA tiles, long K) split along K as well: the cost model of the FP8 scheduler, in units
+    // of one K step on one SM
+    int eff_sms = sms;
+    if (a->sm_limit > 0 && a->sm_limit < eff_sms) eff_sms = a->sm_limit;
+    const long long tiles = (long long)pl->m_tiles * pl->n_tiles;
+    pl->stream_k = false;
+    pl->grid = (int)(tiles < eff_sms ? (tiles > 0 ? tiles : 1) : eff_sms);
+    if (a->sched < BLAZE_SCHED_AUTO || a->sched > BLAZE_SCHED_STREAM_K) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (!pl->pair && allow_split && tiles > 0 && pl->k_steps >= 2 && a->sched != BLAZE_SCHED_DATA_PARALLEL) {
+        const long long units = tiles * pl->k_steps;
+        const long long used = units < eff_sms ? units : eff_sms;
+        const double whole_tiles = (double)((tiles + eff_sms - 1) / eff_sms) * pl->k_steps;
+        const double split = (double)((units + used - 1) / used) + 17.0 + (double)used / (double)tiles;
+        if (a->sched == BLAZE_SCHED_STREAM_K || split < whole_tiles) {
+            pl->stream_k = true;
+            pl->grid = (int)used;
+        }
+    }
+    pl->flags_bytes = pl->stream_k ? round256((size_t)pl->grid * sizeof(int)) : 0;
+    pl->partials_bytes = pl->stream_k ? (size_t)pl->grid * 128 * (size_t)pl->tile_n * sizeof(float) : 0;
+    pl->flags_off = pl->b_scale_rows_off + round256(pl->b_scale_rows_bytes);
+    pl->partials_off = pl->flags_off + pl->flags_bytes;
+    pl->total = pl->partials_off + round256(pl->partials_bytes);
     return ACLTENSOR_STATUS_SUCCESS;
 }
 
@@ -354,6 +380,9 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
     p.status = status_word;
     p.b_format = tb_packed ? FMT_E2M1 : FMT_E4M3;
     p.b_tx_shift = tb_packed ? 1 : 0;        // a 4-bit load reports the bytes it read, not the bytes it wrote
+    p.stream_k = pl.stream_k ? 1 : 0;
+    p.flags = pl.stream_k ? reinterpret_cast<int*>(static_cast<uint8_t*>(a->workspace) + pl.flags_off) : nullptr;
+    p.partials = pl.stream_k ? reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + pl.partials_off) : nullptr;
     p.out_type = a->d_type;
     p.scale_d = static_cast<uint8_t*>(a->scaleD);
     p.scale_cols_d = ((a->N + 63) / 64) * 2;
@@ -401,7 +430,7 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
         return ACLTENSOR_STATUS_INTERNAL_ERROR;
     if (tb_packed) tb = *tb_packed;
     if (ta_packed) ta = *ta_packed;
-    const int grid = (int)(tiles < sms ? tiles : sms);
+    const int grid = pl.grid;
     if (pl.tile_n == 224)
         e = launch_mx_act<224>(a->activation, ta, tb, td, p, grid, stream);
     else
@@ -933,11 +962,11 @@ extern "C" int blazeMxGemmNoAlloc(const blazeMxGemmArgs* a, int32_t* device_stat
     if (nd->cc_major != 10) return ACLTENSOR_STATUS_ARCH_MISMATCH;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     MxPlan pl;
-    st = plan_mx(a, nd->sm_count, &pl);
+    st = plan_mx(a, nd->sm_count, &pl, true, false);        // no stream-K: its partial tiles would not fit the array
     if (st != ACLTENSOR_STATUS_SUCCESS) return st;
     if (pl.total > kNoAllocScratchBytes) {
         // four copies of B's scale blocks do not fit the array: keep one copy (one more scale copy per K step)
-        st = plan_mx(a, nd->sm_count, &pl, false);
+        st = plan_mx(a, nd->sm_count, &pl, false, false);
         if (st != ACLTENSOR_STATUS_SUCCESS) return st;
     }
     if (a->b_elem != BLAZE_ELEM_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;      // packed E2M1 needs an N x K expansion buffer

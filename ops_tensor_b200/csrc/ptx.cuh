@@ -184,6 +184,18 @@ __device__ __forceinline__ void tma_load_2d_addr(uint32_t smem_dst, const CUtens
         : "memory");
 }
 
+// ------------------------------------------------------------------------------------------------ global flags
+
+// Flag hand-over between CTAs of one grid (stream-K partial tiles): release store / acquire load at GPU scope.
+__device__ __forceinline__ int ld_acquire_gpu(const int* ptr) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* ptr, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+
 // ------------------------------------------------------------------------------------------------ dependent launch
 
 // A kernel launched with programmatic stream serialisation may start while its predecessor in the stream is still

@@ -54,6 +54,7 @@ class MxGemmArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("d_type", C.c_int32), ("b_layout", C.c_int32),
         ("scaleD", C.c_void_p),
+        ("sched", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -204,7 +205,7 @@ def quantize_fp8_blocks(w):
 
 def mx_gemm_args(a, sa, b, sb, out, *, b_elem=ELEM_E4M3, bias=None, residual=None, activation=ACT_IDENTITY,
                  tile_n=0, reuse_b_prepass=False, sm_limit=0, cta_pair=0, workspace=None, a_elem=ELEM_E4M3,
-                 scale_out=None, b_n_major=False) -> MxGemmArgs:
+                 scale_out=None, b_n_major=False, sched=SCHED_AUTO) -> MxGemmArgs:
     M, K = a.shape
     if a_elem == ELEM_E2M1:
         K *= 2                       # two codes per byte
@@ -229,6 +230,7 @@ def mx_gemm_args(a, sa, b, sb, out, *, b_elem=ELEM_E4M3, bias=None, residual=Non
     args.a_elem = a_elem
     args.scaleD = scale_out.data_ptr() if scale_out is not None else None
     args.b_layout = 1 if b_n_major else 0
+    args.sched = sched
     if workspace is not None:
         args.workspace, args.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
     return args

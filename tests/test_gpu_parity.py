@@ -643,6 +643,40 @@ def test_mx_n_major_weight(cuda_device, M, N, K):
     assert H.device_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K,tile_n,b_dtype", [
+    (128, 1024, 8192, 128, H.R_8F_E4M3), (100, 520, 4128, 224, H.R_8F_E4M3), (16, 2048, 6144, 128, H.R_4F_E2M1),
+    (128, 264, 512, 128, H.R_8F_E4M3)])
+def test_mx_stream_k_decode_shapes(cuda_device, M, N, K, tile_n, b_dtype):
+    """Skinny MX GEMMs (one row of 128-row tiles, long K) split along K over the SMs: the CTA that holds K step 0 of a
+    tile adds the other CTAs' float32 partial tiles in CTA order and runs the fused epilogue.  Checked against the
+    float64 reference, against whole-tile scheduling, and for run-to-run bit equality (run_mx calls twice)."""
+    import torch
+    from ops_tensor_b200 import native
+    name = "e2m1" if b_dtype == H.R_4F_E2M1 else "e4m3"
+    a = o.normal_f32(33, 0, (M, K), 1.0)
+    w = o.normal_f32(33, 1, (N, K), 0.05)
+    bias = o.normal_f32(33, 2, (N,), 0.5)
+    residual = o.normal_f32(33, 3, (M, N), 1.0)
+    MX = H.SCALE_MX_E8M0_VEC32
+    qa, sa = H.quantize(dev_tensor(a, cuda_device), MX)
+    qb, sb = H.quantize(dev_tensor(w, cuda_device), MX, b_dtype)
+    outs = {}
+    for split in (H.SPLIT_STREAM_K, H.SPLIT_DATA_PARALLEL):
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+        with H.Contraction(M, N, K, scale_mode_a=MX, scale_mode_b=MX, b_dtype=b_dtype, activation=H.OP_SILU, bias=True,
+                           residual=True, tile_n=tile_n, cta_pair=1, split=split) as c:
+            if split == H.SPLIT_STREAM_K:
+                assert c.workspace_bytes > 128 * tile_n * 4            # room for partial tiles
+            for _ in range(2):
+                c(qa, sa, qb, sb, out, bias=bf16_tensor(bias, cuda_device), residual=bf16_tensor(residual, cuda_device))
+                outs.setdefault(split, []).append(to_np(out).copy())
+    first, second = outs[H.SPLIT_STREAM_K]
+    assert np.array_equal(first.view(np.uint32), second.view(np.uint32)), "stream-K is not deterministic"
+    ref, gold = mx_reference(to_np(qa), to_np(sa), to_np(qb), to_np(sb), K, name, o.ACT_SILU, bias, residual)
+    assert_gemm_ok(first, ref, gold)
+    assert_gemm_ok(outs[H.SPLIT_DATA_PARALLEL][0], ref, gold)
+
+
 def test_mx_agrees_with_vendor_mxfp8_gemm(cuda_device):
     """An independent implementation of the same format: the vendor library's MXFP8 GEMM (torch._scaled_mm with E8M0
     scales per 32 K) on the same codes and scales.  Both accumulate in float32 and round once to bf16, so they may
