@@ -156,6 +156,7 @@ template <int kStages, int kAct>
 __global__ void __launch_bounds__(320, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const Fp8GemmParams p) {
+    grid_launch_dependents();        // the next kernel in the stream may start setting up as this one's CTAs retire
     using L = Fp8GemmSmem<kStages>;
     constexpr int kAccStages = L::kAccStages;
     constexpr uint32_t kTmemCols = 512;
@@ -192,7 +193,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         fence_mbar_init();
     }
     if (threadIdx.x == 288 && p.groups > 0) {
-        // prefix sums of rows and of 128-row tiles over the group list
+        // prefix sums of rows and of 128-row tiles over the group list (which an earlier kernel may have produced)
+        grid_dependency_wait();
         int rows = 0, tiles = 0;
         for (int g = 0; g < p.groups; ++g) {
             row_start[g] = rows;
@@ -217,7 +219,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
-    if (p.stream_k) grid_dependency_wait();      // the fix-up flags are zeroed by the kernel launched just before
+    // Launched with programmatic stream serialisation: everything above may overlap the tail of the previous kernel
+    // in the stream; nothing below touches global memory before that kernel has finished.
+    grid_dependency_wait();
 
     // The two single-thread loops below run once per 128-deep K block, i.e. every 256 tensor-core cycles: they are
     // written with precomputed shared-memory addresses and descriptor words so that their instruction count, not

@@ -124,6 +124,7 @@ template <int kBN, int kStages, int kAct>
 __global__ void __launch_bounds__(192, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_d, const MxGemmParams p) {
+    grid_launch_dependents();        // the next kernel in the stream may start setting up as this one's CTAs retire
     using L = MxGemmSmem<kBN, kStages>;
     static_assert(kBN % 32 == 0 && kBN >= 32 && kBN <= 256, "tile N");
     constexpr int kAccStages = 2;

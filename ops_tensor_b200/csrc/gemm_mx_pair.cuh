@@ -72,6 +72,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                     const __grid_constant__ CUtensorMap tmap_d, const MxGemmParams p) {
+    grid_launch_dependents();        // the next kernel in the stream may start setting up as this one's CTAs retire
     using L = MxPairSmem<kBN, kStages, kWide, kMxf4>;
     static_assert(!kMxf4 || kWide, "the FP4 form copies B's scales with the wide copy");
     static_assert(kBN % 32 == 0 && kBN >= 32 && kBN <= 256, "tile N");

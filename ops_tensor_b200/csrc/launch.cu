@@ -699,13 +699,9 @@ static cudaError_t launch_fp8_instance(const CUtensorMap& ta, const CUtensorMap&
         if (e != cudaSuccess) return e;
         attr_done[dev & 63] = true;
     }
-    if (p.stream_k) {
-        // behind the kernel that zeroes the fix-up flags: set-up overlaps it, every thread waits for it before the
-        // role loops start
-        return launch_after_prepass(kernel, grid, 320, L::kDynamicBytes, stream, ta, tb, p);
-    }
-    kernel<<<grid, 320, L::kDynamicBytes, stream>>>(ta, tb, p);
-    return cudaGetLastError();
+    // behind whatever precedes it in the stream (the kernel that zeroes the fix-up flags, or the previous GEMM): set-up
+    // overlaps that kernel's tail, every thread waits for it before the role loops start
+    return launch_after_prepass(kernel, grid, 320, L::kDynamicBytes, stream, ta, tb, p);
 }
 
 }  // namespace blaze

@@ -223,6 +223,9 @@ __global__ void __launch_bounds__(256) sf_retile_kernel(const uint8_t* __restric
     // the GEMM that follows may set itself up (barriers, TMEM, descriptors) while this kernel runs; it waits for this
     // grid to finish before it loads the first scale block
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // launched with programmatic stream serialisation itself: the previous kernel in the stream (a GEMM that reads
+    // these tiles, or the producer of the scales) must have finished before anything is read or written
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < out_words;
          i += (long long)gridDim.x * blockDim.x) {
         long long r = i;
@@ -331,10 +334,29 @@ __global__ void __launch_bounds__(256) scale_pairs_to_rows_kernel(const uint8_t*
 
 __global__ void __launch_bounds__(256) zero_words_kernel(int* __restrict__ p, int words) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the GEMM behind may start setting up
+    asm volatile("griddepcontrol.wait;" ::: "memory");                   // the GEMM before may still read the flags
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < words; i += gridDim.x * blockDim.x) p[i] = 0;
 }
 
 // ---------------------------------------------------------------------------------------------------- launchers
+
+// Launch with programmatic stream serialisation: the kernel may be scheduled while its predecessor in the stream is
+// still running, and waits for it (griddepcontrol.wait) before it touches memory.
+template <class... KArgs, class... Args>
+static cudaError_t launch_programmatic(void (*kernel)(KArgs...), int grid, int block, cudaStream_t stream,
+                                       const Args&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)block, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
 cudaError_t launch_transpose_bytes(const uint8_t* in, long long ld_in, int K, int N, uint8_t* out, long long ld_out,
                                    cudaStream_t stream) {
@@ -355,8 +377,7 @@ cudaError_t launch_scale_pairs_to_rows(const uint8_t* in, int N, int K, uint8_t*
 
 cudaError_t launch_zero_words(int* p, int words, cudaStream_t stream) {
     if (words <= 0) return cudaSuccess;
-    zero_words_kernel<<<(words + 255) / 256, 256, 0, stream>>>(p, words);
-    return cudaGetLastError();
+    return launch_programmatic(zero_words_kernel, (words + 255) / 256, 256, stream, p, words);
 }
 
 static int grid_for(long long work_items, int per_block, int sm_count) {
@@ -406,9 +427,8 @@ cudaError_t launch_sf_retile(const uint8_t* in, int rows, int K, int tile_rows, 
     const long long words = sf_tiled_bytes(rows, K, tile_rows, replicas) / 4;
     if (words <= 0) return cudaSuccess;
     const int grid = grid_for(words, 256, sm_count);
-    sf_retile_kernel<<<grid, 256, 0, stream>>>(in, rows, scale_cols, valid_groups, tile_rows, k_steps, replicas,
-                                               reinterpret_cast<uint32_t*>(out), words);
-    return cudaGetLastError();
+    return launch_programmatic(sf_retile_kernel, grid, 256, stream, in, rows, scale_cols, valid_groups, tile_rows, k_steps,
+                               replicas, reinterpret_cast<uint32_t*>(out), words);
 }
 
 cudaError_t launch_e2m1_expand(const uint8_t* in, long long ld_in, int rows, int K, uint8_t* out, long long ld_out,
