@@ -677,6 +677,60 @@ def test_mx_stream_k_decode_shapes(cuda_device, M, N, K, tile_n, b_dtype):
     assert_gemm_ok(outs[H.SPLIT_DATA_PARALLEL][0], ref, gold)
 
 
+def test_calls_capture_into_a_cuda_graph(cuda_device):
+    """A serving loop records the quantiser, an MX GEMM with its pre-pass and an FP8 stream-K GEMM once and replays
+    them: the launch path allocates nothing and never synchronises, and the programmatic launches inside keep their
+    order in the graph.  Replays on new input data must equal eager calls on the same data."""
+    import torch
+    M, N, K = 256, 512, 1024
+    MX = H.SCALE_MX_E8M0_VEC32
+    x = dev_tensor(o.normal_f32(34, 0, (M, K), 1.0), cuda_device)
+    w = dev_tensor(o.normal_f32(34, 1, (N, K), 0.1), cuda_device)
+    qb, sb = H.quantize(w, MX)
+    qb8, sb8 = H.quantize(w, H.SCALE_FP32_128X128)
+    qa = torch.empty((M, K), dtype=torch.uint8, device=cuda_device)
+    sa = torch.empty((M, K // 32), dtype=torch.uint8, device=cuda_device)
+    qa8 = torch.empty((M, K), dtype=torch.uint8, device=cuda_device)
+    sa8 = torch.empty((M, K // 128), dtype=torch.float32, device=cuda_device)
+    out_mx = torch.empty((M, N), dtype=torch.bfloat16, device=cuda_device)
+    out_f8 = torch.empty((M, N), dtype=torch.bfloat16, device=cuda_device)
+    mx = H.Contraction(M, N, K, scale_mode_a=MX, scale_mode_b=MX, activation=H.OP_GELU)
+    f8 = H.Contraction(M, N, K, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128,
+                       split=H.SPLIT_STREAM_K)
+    ws_mx = torch.empty(mx.workspace_bytes, dtype=torch.uint8, device=cuda_device)
+    ws_f8 = torch.empty(f8.workspace_bytes, dtype=torch.uint8, device=cuda_device)
+
+    def step(stream):
+        s = stream.cuda_stream
+        H.check(H.api.acltensorQuantize(None, x.data_ptr(), K, M, K, MX, H.R_8F_E4M3, qa.data_ptr(), K, sa.data_ptr(), s), "q")
+        H.check(H.api.acltensorQuantize(None, x.data_ptr(), K, M, K, H.SCALE_FP32_1X128, H.R_8F_E4M3, qa8.data_ptr(), K,
+                                        sa8.data_ptr(), s), "q8")
+        mx(qa, sa, qb, sb, out_mx, workspace=ws_mx, stream=s)
+        f8(qa8, sa8, qb8, sb8, out_f8, workspace=ws_f8, stream=s)
+
+    side = torch.cuda.Stream(device=cuda_device)
+    with torch.cuda.stream(side):
+        step(side)                                   # first calls outside the capture (one-time set-up)
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step(side)
+    for seed in (35, 36):
+        x.copy_(dev_tensor(o.normal_f32(seed, 0, (M, K), 1.0), cuda_device))
+        graph.replay()
+        torch.cuda.synchronize()
+        got_mx, got_f8 = out_mx.clone(), out_f8.clone()
+        with torch.cuda.stream(side):
+            step(side)
+        side.synchronize()
+        assert torch.equal(got_mx.view(torch.int16), out_mx.view(torch.int16))
+        assert torch.equal(got_f8.view(torch.int16), out_f8.view(torch.int16))
+        assert torch.isfinite(out_mx.float()).all() and torch.isfinite(out_f8.float()).all()
+    mx.close()
+    f8.close()
+    assert H.device_status() == 0
+
+
 def test_mx_agrees_with_vendor_mxfp8_gemm(cuda_device):
     """An independent implementation of the same format: the vendor library's MXFP8 GEMM (torch._scaled_mm with E8M0
     scales per 32 K) on the same codes and scales.  Both accumulate in float32 and round once to bf16, so they may
