@@ -369,3 +369,45 @@ def test_c99_client_compiles_and_runs(built_library, tmp_path):
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "c client ok" in r.stdout
+
+
+def test_plan_choices_show_in_the_workspace_size(built_library):
+    """The planner's decisions for the benchmark shapes, read off the workspace sizes (148 SMs assumed without a device):
+    256-wide 2-CTA tiles with four-fold B scale blocks for C2; stream-K for the decode shapes of both kernel families and
+    whole tiles for the small and the grouped ones."""
+    lib = native.lib()
+
+    def mx_bytes(M, N, K, **kw):
+        a = native.MxGemmArgs()
+        a.struct_size = C.sizeof(a)
+        a.M, a.N, a.K = M, N, K
+        for k, v in kw.items():
+            setattr(a, k, v)
+        n = C.c_size_t(0)
+        assert lib.blazeMxGemmWorkspaceSize(C.byref(a), C.byref(n)) == H.STATUS_SUCCESS
+        return n.value
+
+    def fp8_bytes(M, N, K, **kw):
+        a = native.Fp8GemmArgs()
+        a.struct_size = C.sizeof(a)
+        a.M, a.N, a.K = M, N, K
+        for k, v in kw.items():
+            setattr(a, k, v)
+        n = C.c_size_t(0)
+        assert lib.blazeFp8GemmWorkspaceSize(C.byref(a), C.byref(n)) == H.STATUS_SUCCESS
+        return n.value
+
+    sfa = 8192 // 128 * 64 * 512                          # re-tiled scales of A: 64 row tiles x 64 K steps
+    sfb_256 = 8192 // 256 * 64 * 2 * 4 * 512              # 32 column tiles x 64 K steps x 2 atoms x 4 copies
+    assert mx_bytes(8192, 8192, 8192) == sfa + sfb_256
+    assert mx_bytes(8192, 8192, 8192, tile_n=224, cta_pair=2) == sfa + 37 * 64 * 2 * 4 * 512
+    # skinny MX problem: stream-K adds flags and 148 partial tiles of 128 x 128 floats; whole tiles when forbidden
+    whole = mx_bytes(128, 7168, 18432, sched=native.SCHED_DATA_PARALLEL)
+    split = mx_bytes(128, 7168, 18432)
+    assert split - whole == 148 * 128 * 128 * 4 + 768
+    assert mx_bytes(256, 512, 1024) == mx_bytes(256, 512, 1024, sched=native.SCHED_DATA_PARALLEL)
+    # FP8 family: C5 splits along K, C1 and the grouped C4 do not
+    assert fp8_bytes(128, 7168, 18432) == 148 * 128 * 128 * 4 + 768
+    assert fp8_bytes(256, 512, 1024) == 0
+    assert fp8_bytes(32768, 768, 2048, groups=128) == 0
+    assert fp8_bytes(256, 512, 1024, sched=native.SCHED_STREAM_K) > 0
