@@ -239,20 +239,26 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             Fp8Segment seg;
             uint32_t stage = 0;
             uint32_t phase = 0;
+            bool first_round = true;
             bool ok = true;
             // B is streamed once when there is a single row of tiles; keep A (re-read by every N tile) instead
             const uint64_t b_hint = (p.groups == 0 && p.m_tiles == 1) ? kEvictFirst : kEvictNormal;
             while (ok && walk.next(seg)) {
                 const int b_row = seg.group * p.N + seg.nt * 128;
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
-                    ok = mbar_wait_addr(empty0 + stage * 8, phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
+                    // kStages == kAccStages: shared-memory stage and TMEM stage move as one ring; the stage is free once
+                    // the MMAs that read it have finished, which is what the accumulator's "full" barrier of the same
+                    // slot says, so the stage needs no commit of its own (a commit costs ~86 tensor-pipe cycles)
+                    ok = (kStages == L::kAccStages)
+                             ? (first_round || mbar_wait_addr(tfull0 + stage * 8, phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY))
+                             : mbar_wait_addr(empty0 + stage * 8, phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
                     const uint32_t bar = full0 + stage * 8;
                     mbar_arrive_expect_tx_addr(bar, L::kTxBytes);
                     tma_load_2d_addr(a_dst, &tmap_a, bar, kb * 128, seg.m0, kEvictNormal);
                     tma_load_2d_addr(a_dst + L::kABytes, &tmap_b, bar, kb * 128, b_row, b_hint);
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    if (++stage == kStages) { stage = 0; phase ^= 1; first_round = false; }
                 }
             }
         }
@@ -279,7 +285,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     tcgen05_fence_after();
                     const uint32_t a_lo = desc_lo0 + stage * (L::kStageBytes >> 4);
                     umma_f8_kblock(tmem_base + acc * 128, a_lo, a_lo + (L::kABytes >> 4), desc_hi, idesc);
-                    umma_commit_addr(empty0 + stage * 8);
+                    if (kStages != L::kAccStages) umma_commit_addr(empty0 + stage * 8);
                     umma_commit_addr(tfull0 + acc * 8);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                     if (++acc == (uint32_t)kAccStages) { acc = 0; acc_phase ^= 1; }
