@@ -15,7 +15,7 @@
 // float32 scales cannot ride on the hardware block-scale path, so every 128-deep K block is multiplied into a
 // fresh TMEM accumulator (4 stages of 128 columns) and promoted into registers by eight epilogue warps (two per
 // TMEM lane quadrant, 64 columns each): acc += (sa * sb) * block, while the tensor core works on the next blocks.
-// Warps 0-7: promotion + epilogue, warp 8: TMA producer, warp 9: MMA issuer.
+// Warps 0-7: promotion + epilogue, warp 8: TMA producer, warps 9 and 10: MMA issuers taking K blocks in turn.
 #pragma once
 
 #include "ptx.cuh"
@@ -55,12 +55,12 @@ struct Fp8GemmSmem {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarOffset = kStages * kStageBytes;
     static constexpr int kAccStages = 4;
-    // full[kStages], empty[kStages], tmem_full[4], tmem_empty[4], fixup, amax exchange
-    static constexpr int kNumBars = 2 * kStages + 2 * kAccStages + 2;
+    // full[kStages], tmem_full[4], tmem_empty[4], fixup, amax exchange
+    static constexpr int kNumBars = kStages + 2 * kAccStages + 2;
     static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
     static constexpr int kGroupOffset = kMiscOffset + 16;       // int row_start[G+1], int mtile_start[G+1]
-    static constexpr int kAmaxOffset = kGroupOffset + 2 * (kFp8MaxGroups + 1) * 4;   // float amax[2 tiles][2 halves][128]
-    static constexpr int kTotal = kAmaxOffset + 2 * 2 * 128 * 4;
+    static constexpr int kAmaxOffset = kGroupOffset + 2 * (kFp8MaxGroups + 1) * 4;   // float amax[2 tiles][<= 4 column parts][128]
+    static constexpr int kTotal = kAmaxOffset + 2 * 4 * 128 * 4;
     static constexpr int kDynamicBytes = kTotal + 1024;
     static constexpr uint32_t kTxBytes = kABytes + kBBytes;
 };
@@ -152,21 +152,28 @@ struct Fp8WorkWalker {
     }
 };
 
-template <int kStages, int kAct>
-__global__ void __launch_bounds__(320, 1)
+template <int kStages, int kAct, int kIssuers = 1, int kParts = 2>
+__global__ void __launch_bounds__(128 * kParts + 32 + 32 * kIssuers, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const Fp8GemmParams p) {
     grid_launch_dependents();        // the next kernel in the stream may start setting up as this one's CTAs retire
     using L = Fp8GemmSmem<kStages>;
     constexpr int kAccStages = L::kAccStages;
+    static_assert(kStages == kAccStages, "shared-memory stages and TMEM stages move as one ring");
     constexpr uint32_t kTmemCols = 512;
+    // warp roles: 4 * kParts promotion warps (TMEM lane quadrant = warp % 4, column part = warp / 4), one TMA warp, then
+    // the MMA issuer warps
+    constexpr int kPromoWarps = 4 * kParts;
+    constexpr int kCols = 128 / kParts;              // accumulator columns per promotion thread
+    constexpr int kTmaWarp = kPromoWarps;
+    constexpr int kMmaWarp0 = kPromoWarps + 1;
+    static_assert(kParts == 2 || kParts == 4, "64 or 32 columns per promotion thread");
 
     extern __shared__ uint8_t smem_unaligned[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
     uint64_t* full_bar = bars;
-    uint64_t* empty_bar = bars + kStages;
-    uint64_t* tmem_full_bar = bars + 2 * kStages;
+    uint64_t* tmem_full_bar = bars + kStages;
     uint64_t* tmem_empty_bar = tmem_full_bar + kAccStages;
     uint64_t* fix_bar = tmem_empty_bar + kAccStages;
     uint64_t* amax_bar = fix_bar + 1;              // the 256 promotion threads, once per quantised output tile
@@ -181,18 +188,17 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], 1);
         }
         for (int s = 0; s < kAccStages; ++s) {
             mbar_init(&tmem_full_bar[s], 1);
-            mbar_init(&tmem_empty_bar[s], 8);
+            mbar_init(&tmem_empty_bar[s], kPromoWarps);
         }
-        mbar_init(fix_bar, 256);
-        mbar_init(amax_bar, 256);
+        mbar_init(fix_bar, 32 * kPromoWarps);
+        mbar_init(amax_bar, 32 * kPromoWarps);
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (threadIdx.x == 288 && p.groups > 0) {
+    if (threadIdx.x == kMmaWarp0 * 32 && p.groups > 0) {
         // prefix sums of rows and of 128-row tiles over the group list (which an earlier kernel may have produced)
         grid_dependency_wait();
         int rows = 0, tiles = 0;
@@ -208,10 +214,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         row_start[p.groups] = rows;
         mtile_start[p.groups] = tiles;
     }
-    if (warp == 9) {
+    if (warp == kMmaWarp0) {
         tmem_alloc<1>(tmem_base_slot, kTmemCols);
     }
-    if (warp == 8 && lane == 0) {
+    if (warp == kTmaWarp && lane == 0) {
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
     }
@@ -228,11 +234,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     // the tensor core, does not set the pace.
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full0 = smem_u32(&full_bar[0]);
-    const uint32_t empty0 = smem_u32(&empty_bar[0]);
     const uint32_t tfull0 = smem_u32(&tmem_full_bar[0]);
     const uint32_t tempty0 = smem_u32(&tmem_empty_bar[0]);
 
-    if (warp == 8) {
+    if (warp == kTmaWarp) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             Fp8WorkWalker walk(p, row_start, mtile_start);
@@ -246,12 +251,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             while (ok && walk.next(seg)) {
                 const int b_row = seg.group * p.N + seg.nt * 128;
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
-                    // kStages == kAccStages: shared-memory stage and TMEM stage move as one ring; the stage is free once
+                    // shared-memory stage and TMEM stage move as one ring; the stage is free once
                     // the MMAs that read it have finished, which is what the accumulator's "full" barrier of the same
                     // slot says, so the stage needs no commit of its own (a commit costs ~86 tensor-pipe cycles)
-                    ok = (kStages == L::kAccStages)
-                             ? (first_round || mbar_wait_addr(tfull0 + stage * 8, phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY))
-                             : mbar_wait_addr(empty0 + stage * 8, phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
+                    ok = first_round || mbar_wait_addr(tfull0 + stage * 8, phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
                     const uint32_t bar = full0 + stage * 8;
@@ -262,8 +265,12 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 }
             }
         }
-    } else if (warp == 9) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp >= kMmaWarp0) {
+        // ------------------------------------------------------------------ MMA issuer(s)
+        // A K block has its own accumulator stage, so blocks are independent and kIssuers threads (one per warp) take
+        // them in turn: while one thread polls its barriers the other's MMAs keep the tensor core busy (the tensor
+        // core's instruction queue is too short to cover one thread's waits).
+        static_assert(kIssuers == 1 || (Fp8GemmSmem<kStages>::kAccStages % kIssuers) == 0, "issuers own whole stages");
         if (lane == 0) {
             Fp8WorkWalker walk(p, row_start, mtile_start);
             Fp8Segment seg;
@@ -271,6 +278,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             uint32_t phase = 0;
             uint32_t acc = 0;
             uint32_t acc_phase = 0;
+            uint32_t turn = 0;
+            const uint32_t my_turn = (uint32_t)(warp - kMmaWarp0);
             bool ok = true;
             constexpr uint32_t idesc = umma_idesc_f8(FMT_E4M3, FMT_E4M3, 128, 128);
             const uint64_t desc0 = umma_desc_sw128(0);
@@ -278,22 +287,24 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             const uint32_t desc_lo0 = (uint32_t)desc0 + (smem_base >> 4);          // start-address field of stage 0's A tile
             while (ok && walk.next(seg)) {
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
-                    ok = mbar_wait_addr(tempty0 + acc * 8, acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
-                    if (!ok) break;
-                    ok = mbar_wait_addr(full0 + stage * 8, phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
-                    if (!ok) break;
-                    tcgen05_fence_after();
-                    const uint32_t a_lo = desc_lo0 + stage * (L::kStageBytes >> 4);
-                    umma_f8_kblock(tmem_base + acc * 128, a_lo, a_lo + (L::kABytes >> 4), desc_hi, idesc);
-                    if (kStages != L::kAccStages) umma_commit_addr(empty0 + stage * 8);
-                    umma_commit_addr(tfull0 + acc * 8);
+                    if (kIssuers == 1 || turn == my_turn) {
+                        ok = mbar_wait_addr(tempty0 + acc * 8, acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                        if (!ok) break;
+                        ok = mbar_wait_addr(full0 + stage * 8, phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
+                        if (!ok) break;
+                        tcgen05_fence_after();
+                        const uint32_t a_lo = desc_lo0 + stage * (L::kStageBytes >> 4);
+                        umma_f8_kblock(tmem_base + acc * 128, a_lo, a_lo + (L::kABytes >> 4), desc_hi, idesc);
+                        umma_commit_addr(tfull0 + acc * 8);
+                    }
+                    if (kIssuers > 1 && ++turn == (uint32_t)kIssuers) turn = 0;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                     if (++acc == (uint32_t)kAccStages) { acc = 0; acc_phase ^= 1; }
                 }
             }
         }
     } else {
-        // ------------------------------------------------------------------ promotion + epilogue warps 0..7
+        // ------------------------------------------------------------------ promotion + epilogue warps
         Fp8WorkWalker walk(p, row_start, mtile_start);
         Fp8Segment seg;
         int acc = 0;
@@ -302,19 +313,19 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         float* amax_smem = reinterpret_cast<float*>(smem + L::kAmaxOffset);
         int tile_parity = 0;
         const int quad = warp & 3;                      // TMEM lane quadrant this warp may read
-        const int half = warp >> 2;                     // which 64 of the tile's 128 columns
+        const int part = warp >> 2;                     // which kCols of the tile's 128 columns
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         const int r_in_tile = quad * 32 + lane;
-        const int c0 = half * 64;
+        const int c0 = part * kCols;
         while (ok && walk.next(seg)) {
             const int row = seg.m0 + r_in_tile;
             const bool row_ok = row < seg.row_end;
             const bool warp_has_rows = seg.m0 + quad * 32 < seg.row_end;      // warp-uniform
             const float* sa_row = p.sa + (long long)(row_ok ? row : 0) * p.k_blocks;
             const float* sb_col = p.sb + (long long)seg.group * p.k_blocks * p.n_blocks + seg.nt;
-            float accum[64];
+            float accum[kCols];
 #pragma unroll
-            for (int j = 0; j < 64; ++j) accum[j] = 0.0f;
+            for (int j = 0; j < kCols; ++j) accum[j] = 0.0f;
 
             // The two scale factors of a K block come from global memory (L2 latency); they are fetched kScaleAhead
             // blocks ahead into a register ring so that the promotion never waits for them.
@@ -344,14 +355,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     if (!ok) break;
                     tcgen05_fence_after();
                     if (warp_has_rows) {
-                        uint32_t v[64];
-                        tmem_ld_32x64(tmem_base + lane_base + acc * 128 + c0, v);
+                        uint32_t v[kCols];
+                        if constexpr (kCols == 64) tmem_ld_32x64(tmem_base + lane_base + acc * 128 + c0, v);
+                        else tmem_ld_32x32(tmem_base + lane_base + acc * 128 + c0, v);
                         tmem_ld_wait();
                         tcgen05_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);    // the block is in registers: free the stage
 #pragma unroll
-                        for (int e = 0; e < 64; e += 2) fma_f32x2(accum[e], accum[e + 1], v[e], v[e + 1], s);
+                        for (int e = 0; e < kCols; e += 2) fma_f32x2(accum[e], accum[e + 1], v[e], v[e + 1], s);
                     } else {
                         tcgen05_fence_before();
                         __syncwarp();
@@ -370,7 +382,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     // layout [column quad][row][4]: a warp writes 512 contiguous bytes per instruction
                     float4* slot4 = reinterpret_cast<float4*>(slot) + (size_t)(c0 >> 2) * 128 + r_in_tile;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < kCols / 4; ++j) {
                         __stcg(slot4 + j * 128, make_float4(accum[4 * j], accum[4 * j + 1], accum[4 * j + 2], accum[4 * j + 3]));
                     }
                 }
@@ -407,7 +419,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     if (row_ok) {
                         const float4* slot4 = reinterpret_cast<const float4*>(slot) + (size_t)(c0 >> 2) * 128 + r_in_tile;
 #pragma unroll
-                        for (int c = 0; c < 16; ++c) {
+                        for (int c = 0; c < kCols / 4; ++c) {
                             const float4 v4 = __ldcg(slot4 + c * 128);
                             accum[4 * c] += v4.x;
                             accum[4 * c + 1] += v4.y;
@@ -420,11 +432,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 if (!ok) break;
             }
 
-            // -------- fused epilogue: bias, activation, residual, cast; 64 consecutive outputs per thread
+            // -------- fused epilogue: bias, activation, residual, cast; kCols consecutive outputs per thread
             const __nv_bfloat16* r_row = (p.residual && row_ok) ? p.residual + (long long)row * p.ldr : nullptr;
             float row_amax = 0.0f;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
+            for (int q = 0; q < kCols / 8; ++q) {
                 const int n = seg.nt * 128 + c0 + q * 8;
                 if (row_ok && n < p.N) {
                     float x[8];
@@ -464,19 +476,21 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 // Quantising output: one float32 scale per row per 128 columns (this tile's width), amax / 448, and
                 // E4M3 codes of x / scale - the A operand of the next FP8 GEMM, by the rules of quant_fp8_1x128_kernel.
                 // The two warps that share a row (column halves) exchange their maxima through shared memory.
-                float* amax_buf = amax_smem + (tile_parity * 2) * 128;
-                amax_buf[half * 128 + r_in_tile] = row_amax;
-                mbar_arrive(amax_bar);                                     // all eight promotion warps
+                float* amax_buf = amax_smem + (tile_parity * kParts) * 128;
+                amax_buf[part * 128 + r_in_tile] = row_amax;
+                mbar_arrive(amax_bar);                                     // all promotion warps
                 ok = mbar_wait(amax_bar, (uint32_t)tile_parity, abort_flag, p.status, DEV_TIMEOUT_FIXUP_FLAG);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                const float amax = fmaxf(row_amax, amax_buf[(half ^ 1) * 128 + r_in_tile]);
+                float amax = row_amax;
+#pragma unroll
+                for (int o = 1; o < kParts; ++o) amax = fmaxf(amax, amax_buf[((part + o) % kParts) * 128 + r_in_tile]);
                 tile_parity ^= 1;
                 const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 448.0f);
                 if (row_ok) {
                     uint8_t* d_row = reinterpret_cast<uint8_t*>(p.D) + (long long)row * p.ldd;
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
+                    for (int q = 0; q < kCols / 16; ++q) {
                         const int n = seg.nt * 128 + c0 + q * 16;
                         uint32_t w[4];
 #pragma unroll
@@ -492,13 +506,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                             *reinterpret_cast<uint2*>(d_row + n) = make_uint2(w[0], w[1]);
                         }
                     }
-                    if (half == 0 && seg.nt * 128 < p.N) p.scale_d[(long long)row * p.n_blocks + seg.nt] = scale;
+                    if (part == 0 && seg.nt * 128 < p.N) p.scale_d[(long long)row * p.n_blocks + seg.nt] = scale;
                 }
             } else if (row_ok) {
                 const int elem_bytes = p.out_type == OUT_F32 ? 4 : 2;
                 uint8_t* d_row = reinterpret_cast<uint8_t*>(p.D) + (long long)row * p.ldd * elem_bytes;
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
+                for (int q = 0; q < kCols / 8; ++q) {
                     const int n = seg.nt * 128 + c0 + q * 8;
                     if (n < p.N) {
                         const float* x = accum + q * 8;
@@ -529,7 +543,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         for (int i = 0; i < 64; ++i) __nanosleep(2000);
         __syncthreads();
     }
-    if (warp == 9) {
+    if (warp == kMmaWarp0) {
         __syncwarp();
         tcgen05_fence_after();
         tmem_dealloc<1>(tmem_base, kTmemCols);
