@@ -60,7 +60,12 @@ struct Fp8GemmSmem {
     static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
     static constexpr int kGroupOffset = kMiscOffset + 16;       // int row_start[G+1], int mtile_start[G+1]
     static constexpr int kAmaxOffset = kGroupOffset + 2 * (kFp8MaxGroups + 1) * 4;   // float amax[2 tiles][<= 4 column parts][128]
-    static constexpr int kTotal = kAmaxOffset + 2 * 4 * 128 * 4;
+    // 16-bit outputs pass through shared memory so that a store instruction writes whole 128-byte lines: per promotion
+    // warp 32 rows of up to 64 columns, rows padded by 16 bytes against bank conflicts
+    static constexpr int kStoreRowPitch = 64 * 2 + 16;
+    static constexpr int kStoreOffset = (kAmaxOffset + 2 * 4 * 128 * 4 + 127) & ~127;    // 16-byte vector accesses
+    static_assert(kStoreRowPitch % 16 == 0 && kStoreOffset % 16 == 0, "staged rows are read and written as uint4");
+    static constexpr int kTotal = kStoreOffset + 16 * 32 * kStoreRowPitch;
     static constexpr int kDynamicBytes = kTotal + 1024;
     static constexpr uint32_t kTxBytes = kABytes + kBBytes;
 };
@@ -198,21 +203,44 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (threadIdx.x == kMmaWarp0 * 32 && p.groups > 0) {
-        // prefix sums of rows and of 128-row tiles over the group list (which an earlier kernel may have produced)
+    if (warp == kMmaWarp0 && p.groups > 0) {
+        // Prefix sums of rows and of 128-row tiles over the group list (which an earlier kernel may have produced),
+        // 32 groups per step with warp scans: one thread walking the list paid an L2 round trip per group, 27 us
+        // for 128 groups.  Counts are clamped so that the groups never step outside A.
         grid_dependency_wait();
-        int rows = 0, tiles = 0;
-        for (int g = 0; g < p.groups; ++g) {
-            row_start[g] = rows;
-            mtile_start[g] = tiles;
-            long long r = p.group_rows[g];
-            if (r < 0) r = 0;
-            if (rows + r > p.M) r = p.M - rows;          // never step outside A
-            rows += (int)r;
-            tiles += (int)((r + 127) >> 7);
+        long long carry_rows = 0;
+        int carry_tiles = 0;
+#pragma unroll 4
+        for (int base = 0; base < p.groups; base += 32) {
+            const int g = base + lane;
+            long long r = (g < p.groups) ? __ldg(p.group_rows + g) : 0;
+            r = r < 0 ? 0 : (r > p.M ? (long long)p.M : r);
+            long long incl = r;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const long long o = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += o;
+            }
+            const long long end = min(carry_rows + incl, (long long)p.M);
+            const long long start = min(carry_rows + incl - r, (long long)p.M);
+            const int t = (int)((end - start + 127) >> 7);
+            int t_incl = t;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, t_incl, d);
+                if (lane >= d) t_incl += o;
+            }
+            if (g < p.groups) {
+                row_start[g] = (int)start;
+                mtile_start[g] = carry_tiles + t_incl - t;
+            }
+            carry_rows = __shfl_sync(0xffffffffu, end, 31);
+            carry_tiles += __shfl_sync(0xffffffffu, t_incl, 31);
         }
-        row_start[p.groups] = rows;
-        mtile_start[p.groups] = tiles;
+        if (lane == 0) {
+            row_start[p.groups] = (int)carry_rows;
+            mtile_start[p.groups] = carry_tiles;
+        }
     }
     if (warp == kMmaWarp0) {
         tmem_alloc<1>(tmem_base_slot, kTmemCols);
@@ -508,29 +536,45 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     }
                     if (part == 0 && seg.nt * 128 < p.N) p.scale_d[(long long)row * p.n_blocks + seg.nt] = scale;
                 }
-            } else if (row_ok) {
-                const int elem_bytes = p.out_type == OUT_F32 ? 4 : 2;
-                uint8_t* d_row = reinterpret_cast<uint8_t*>(p.D) + (long long)row * p.ldd * elem_bytes;
+            } else if (p.out_type != OUT_F32) {
+                // bf16 / f16: a thread holds kCols consecutive outputs of one row, so storing from registers would touch
+                // 32 different lines per instruction (2.2 us per 128x128 tile, a fifth of a 16-block tile's time).  Each
+                // warp transposes through its own shared-memory rows instead and writes 128 contiguous bytes per row.
+                uint8_t* stage_rows = smem + L::kStoreOffset + warp * (32 * L::kStoreRowPitch);
 #pragma unroll
                 for (int q = 0; q < kCols / 8; ++q) {
-                    const int n = seg.nt * 128 + c0 + q * 8;
+                    const float* x = accum + q * 8;
+                    uint4 o;
+                    if (p.out_type == OUT_F16) {
+                        o = make_uint4(pack_f16(x[0], x[1]), pack_f16(x[2], x[3]), pack_f16(x[4], x[5]), pack_f16(x[6], x[7]));
+                    } else {
+                        o = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+                    }
+                    *reinterpret_cast<uint4*>(stage_rows + lane * L::kStoreRowPitch + q * 16) = o;
+                }
+                __syncwarp();
+                constexpr int kChunks = kCols / 8;              // 16-byte chunks per row
+                constexpr int kRowsPerStore = 32 / kChunks;
+                const int chunk = lane % kChunks;
+                const int n = seg.nt * 128 + c0 + chunk * 8;
+#pragma unroll
+                for (int it = 0; it < kChunks; ++it) {
+                    const int rr = it * kRowsPerStore + lane / kChunks;
+                    const int out_row = seg.m0 + quad * 32 + rr;
+                    if (out_row < seg.row_end && n < p.N) {
+                        const uint4 o = *reinterpret_cast<const uint4*>(stage_rows + rr * L::kStoreRowPitch + chunk * 16);
+                        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.D) + ((long long)out_row * p.ldd + n) * 2) = o;
+                    }
+                }
+                __syncwarp();                                    // the next tile reuses the rows
+            } else if (row_ok) {
+                float* d_row = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd;
+#pragma unroll
+                for (int q = 0; q < kCols / 4; ++q) {
+                    const int n = seg.nt * 128 + c0 + q * 4;
                     if (n < p.N) {
-                        const float* x = accum + q * 8;
-                        if (p.out_type == OUT_F32) {
-                            float4* dst = reinterpret_cast<float4*>(d_row + (long long)n * 4);
-                            dst[0] = make_float4(x[0], x[1], x[2], x[3]);
-                            dst[1] = make_float4(x[4], x[5], x[6], x[7]);
-                        } else {
-                            uint4 o;
-                            if (p.out_type == OUT_F16) {
-                                o = make_uint4(pack_f16(x[0], x[1]), pack_f16(x[2], x[3]), pack_f16(x[4], x[5]),
-                                               pack_f16(x[6], x[7]));
-                            } else {
-                                o = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]),
-                                               pack_bf16(x[6], x[7]));
-                            }
-                            *reinterpret_cast<uint4*>(d_row + (long long)n * 2) = o;
-                        }
+                        *reinterpret_cast<float4*>(d_row + n) =
+                            make_float4(accum[q * 4], accum[q * 4 + 1], accum[q * 4 + 2], accum[q * 4 + 3]);
                     }
                 }
             }
