@@ -16,6 +16,8 @@
 // fresh TMEM accumulator (4 stages of 128 columns) and promoted into registers by eight epilogue warps (two per
 // TMEM lane quadrant, 64 columns each): acc += (sa * sb) * block, while the tensor core works on the next blocks.
 // Warps 0-7: promotion + epilogue, warp 8: TMA producer, warps 9 and 10: MMA issuers taking K blocks in turn.
+// One tcgen05.commit per K block: "block g is done" is barrier g % 8; the promotion warps wait on it for the accumulator
+// (TMEM stage g % 4), the TMA thread for the operand stage (g % kStages).
 #pragma once
 
 #include "ptx.cuh"
@@ -55,17 +57,21 @@ struct Fp8GemmSmem {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarOffset = kStages * kStageBytes;
     static constexpr int kAccStages = 4;
-    // full[kStages], tmem_full[4], tmem_empty[4], fixup, amax exchange
-    static constexpr int kNumBars = kStages + 2 * kAccStages + 2;
+    // "MMAs of K block g have finished" is signalled on barrier g % 8 (parity (g / 8) % 2).  The promotion warps wait on
+    // it for the accumulator (TMEM stage g % 4) and the TMA thread for the operand stage (g % kStages), so one
+    // tcgen05.commit per block serves both rings; eight barriers keep the parities unambiguous for any kStages <= 8.
+    static constexpr int kDoneBars = 8;
+    // full[kStages], done[8], tmem_empty[4], fixup, amax exchange
+    static constexpr int kNumBars = kStages + kDoneBars + kAccStages + 2;
     static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
     static constexpr int kGroupOffset = kMiscOffset + 16;       // int row_start[G+1], int mtile_start[G+1]
     static constexpr int kAmaxOffset = kGroupOffset + 2 * (kFp8MaxGroups + 1) * 4;   // float amax[2 tiles][<= 4 column parts][128]
-    // 16-bit outputs pass through shared memory so that a store instruction writes whole 128-byte lines: per promotion
+    // 16-bit outputs leave through shared memory, one bulk copy of up to 128 contiguous bytes per thread: per promotion
     // warp 32 rows of up to 64 columns, rows padded by 16 bytes against bank conflicts
     static constexpr int kStoreRowPitch = 64 * 2 + 16;
     static constexpr int kStoreOffset = (kAmaxOffset + 2 * 4 * 128 * 4 + 127) & ~127;    // 16-byte vector accesses
     static_assert(kStoreRowPitch % 16 == 0 && kStoreOffset % 16 == 0, "staged rows are read and written as uint4");
-    static constexpr int kTotal = kStoreOffset + 16 * 32 * kStoreRowPitch;
+    static constexpr int kTotal = kStoreOffset + 8 * 32 * kStoreRowPitch;
     static constexpr int kDynamicBytes = kTotal + 1024;
     static constexpr uint32_t kTxBytes = kABytes + kBBytes;
 };
@@ -164,7 +170,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     grid_launch_dependents();        // the next kernel in the stream may start setting up as this one's CTAs retire
     using L = Fp8GemmSmem<kStages>;
     constexpr int kAccStages = L::kAccStages;
-    static_assert(kStages == kAccStages, "shared-memory stages and TMEM stages move as one ring");
+    static_assert(kStages <= L::kDoneBars && kAccStages <= kStages, "see Fp8GemmSmem::kDoneBars");
+    static_assert(kParts == 2, "the output staging area holds eight warps' rows");
     constexpr uint32_t kTmemCols = 512;
     // warp roles: 4 * kParts promotion warps (TMEM lane quadrant = warp % 4, column part = warp / 4), one TMA warp, then
     // the MMA issuer warps
@@ -178,8 +185,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
     uint64_t* full_bar = bars;
-    uint64_t* tmem_full_bar = bars + kStages;
-    uint64_t* tmem_empty_bar = tmem_full_bar + kAccStages;
+    uint64_t* tmem_full_bar = bars + kStages;                       // the eight "block done" barriers
+    uint64_t* tmem_empty_bar = tmem_full_bar + L::kDoneBars;
     uint64_t* fix_bar = tmem_empty_bar + kAccStages;
     uint64_t* amax_bar = fix_bar + 1;              // the 256 promotion threads, once per quantised output tile
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
@@ -194,10 +201,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full_bar[s], 1);
         }
-        for (int s = 0; s < kAccStages; ++s) {
-            mbar_init(&tmem_full_bar[s], 1);
-            mbar_init(&tmem_empty_bar[s], kPromoWarps);
-        }
+        for (int s = 0; s < L::kDoneBars; ++s) mbar_init(&tmem_full_bar[s], 1);
+        for (int s = 0; s < kAccStages; ++s) mbar_init(&tmem_empty_bar[s], kPromoWarps);
         mbar_init(fix_bar, 32 * kPromoWarps);
         mbar_init(amax_bar, 32 * kPromoWarps);
         *abort_flag = 0;
@@ -271,25 +276,27 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             Fp8WorkWalker walk(p, row_start, mtile_start);
             Fp8Segment seg;
             uint32_t stage = 0;
-            uint32_t phase = 0;
-            bool first_round = true;
+            uint32_t g = 0;                  // K blocks issued by this CTA so far
             bool ok = true;
             // B is streamed once when there is a single row of tiles; keep A (re-read by every N tile) instead
             const uint64_t b_hint = (p.groups == 0 && p.m_tiles == 1) ? kEvictFirst : kEvictNormal;
             while (ok && walk.next(seg)) {
                 const int b_row = seg.group * p.N + seg.nt * 128;
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
-                    // shared-memory stage and TMEM stage move as one ring; the stage is free once
-                    // the MMAs that read it have finished, which is what the accumulator's "full" barrier of the same
-                    // slot says, so the stage needs no commit of its own (a commit costs ~86 tensor-pipe cycles)
-                    ok = first_round || mbar_wait_addr(tfull0 + stage * 8, phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
-                    if (!ok) break;
+                    // the stage is free once the MMAs of the block that used it last (g - kStages) have finished; the
+                    // block's "done" barrier says so, and the stage needs no commit of its own (~86 tensor-pipe cycles)
+                    if (g >= (uint32_t)kStages) {
+                        const uint32_t d = g - kStages;
+                        ok = mbar_wait_addr(tfull0 + (d & 7) * 8, (d >> 3) & 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
+                        if (!ok) break;
+                    }
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
                     const uint32_t bar = full0 + stage * 8;
                     mbar_arrive_expect_tx_addr(bar, L::kTxBytes);
                     tma_load_2d_addr(a_dst, &tmap_a, bar, kb * 128, seg.m0, kEvictNormal);
                     tma_load_2d_addr(a_dst + L::kABytes, &tmap_b, bar, kb * 128, b_row, b_hint);
-                    if (++stage == kStages) { stage = 0; phase ^= 1; first_round = false; }
+                    if (++stage == kStages) stage = 0;
+                    ++g;
                 }
             }
         }
@@ -304,9 +311,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             Fp8Segment seg;
             uint32_t stage = 0;
             uint32_t phase = 0;
-            uint32_t acc = 0;
-            uint32_t acc_phase = 0;
-            uint32_t turn = 0;
+            uint32_t g = 0;
             const uint32_t my_turn = (uint32_t)(warp - kMmaWarp0);
             bool ok = true;
             constexpr uint32_t idesc = umma_idesc_f8(FMT_E4M3, FMT_E4M3, 128, 128);
@@ -315,19 +320,19 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             const uint32_t desc_lo0 = (uint32_t)desc0 + (smem_base >> 4);          // start-address field of stage 0's A tile
             while (ok && walk.next(seg)) {
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
-                    if (kIssuers == 1 || turn == my_turn) {
-                        ok = mbar_wait_addr(tempty0 + acc * 8, acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                    if (kIssuers == 1 || (g % kIssuers) == my_turn) {
+                        const uint32_t acc = g & 3;
+                        ok = mbar_wait_addr(tempty0 + acc * 8, ((g >> 2) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
                         if (!ok) break;
                         ok = mbar_wait_addr(full0 + stage * 8, phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
                         if (!ok) break;
                         tcgen05_fence_after();
                         const uint32_t a_lo = desc_lo0 + stage * (L::kStageBytes >> 4);
                         umma_f8_kblock(tmem_base + acc * 128, a_lo, a_lo + (L::kABytes >> 4), desc_hi, idesc);
-                        umma_commit_addr(tfull0 + acc * 8);
+                        umma_commit_addr(tfull0 + (g & 7) * 8);
                     }
-                    if (kIssuers > 1 && ++turn == (uint32_t)kIssuers) turn = 0;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
-                    if (++acc == (uint32_t)kAccStages) { acc = 0; acc_phase ^= 1; }
+                    ++g;
                 }
             }
         }
@@ -335,8 +340,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         // ------------------------------------------------------------------ promotion + epilogue warps
         Fp8WorkWalker walk(p, row_start, mtile_start);
         Fp8Segment seg;
-        int acc = 0;
-        uint32_t acc_phase = 0;
+        uint32_t g = 0;
         bool ok = true;
         float* amax_smem = reinterpret_cast<float*>(smem + L::kAmaxOffset);
         int tile_parity = 0;
@@ -345,7 +349,28 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         const int r_in_tile = quad * 32 + lane;
         const int c0 = part * kCols;
-        while (ok && walk.next(seg)) {
+        // The two scale factors of a K block come from global memory (L2 latency); they are fetched kScaleAhead
+        // blocks ahead into a register ring so that the promotion never waits for them.  The ring is idle during a
+        // tile's epilogue, so the first scales of the next segment are requested before the epilogue starts.
+        constexpr int kScaleAhead = 4;
+        float sa_q[kScaleAhead], sb_q[kScaleAhead];
+        auto fetch_first_scales = [&](const Fp8Segment& sg) {
+            const int row_f = sg.m0 + r_in_tile;
+            const bool in_rows = row_f < sg.row_end;
+            const float* sa_f = p.sa + (long long)(in_rows ? row_f : 0) * p.k_blocks;
+            const float* sb_f = p.sb + (long long)sg.group * p.k_blocks * p.n_blocks + sg.nt;
+#pragma unroll
+            for (int u = 0; u < kScaleAhead; ++u) {
+                const int kq = sg.kb0 + u;
+                const bool in = in_rows && kq < sg.kb1;
+                sa_q[u] = in ? __ldg(sa_f + kq) : 0.0f;
+                sb_q[u] = in ? __ldg(sb_f + (long long)kq * p.n_blocks) : 0.0f;
+            }
+        };
+        Fp8Segment next_seg;
+        bool have = walk.next(seg);
+        if (have) fetch_first_scales(seg);
+        for (; ok && have; seg = next_seg) {
             const int row = seg.m0 + r_in_tile;
             const bool row_ok = row < seg.row_end;
             const bool warp_has_rows = seg.m0 + quad * 32 < seg.row_end;      // warp-uniform
@@ -354,18 +379,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             float accum[kCols];
 #pragma unroll
             for (int j = 0; j < kCols; ++j) accum[j] = 0.0f;
-
-            // The two scale factors of a K block come from global memory (L2 latency); they are fetched kScaleAhead
-            // blocks ahead into a register ring so that the promotion never waits for them.
-            constexpr int kScaleAhead = 4;
-            float sa_q[kScaleAhead], sb_q[kScaleAhead];
-#pragma unroll
-            for (int u = 0; u < kScaleAhead; ++u) {
-                const int kq = seg.kb0 + u;
-                const bool in = row_ok && kq < seg.kb1;
-                sa_q[u] = in ? __ldg(sa_row + kq) : 0.0f;
-                sb_q[u] = in ? __ldg(sb_col + (long long)kq * p.n_blocks) : 0.0f;
-            }
             for (int kb0 = seg.kb0; kb0 < seg.kb1 && ok; kb0 += kScaleAhead) {
 #pragma unroll
                 for (int u = 0; u < kScaleAhead; ++u) {
@@ -378,7 +391,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                         sa_q[u] = in ? __ldg(sa_row + kq) : 0.0f;
                         sb_q[u] = in ? __ldg(sb_col + (long long)kq * p.n_blocks) : 0.0f;
                     }
-                    ok = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
+                    const int acc = (int)(g & 3);
+                    ok = mbar_wait(&tmem_full_bar[g & 7], (g >> 3) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tcgen05_fence_after();
@@ -397,10 +411,12 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
                     }
-                    if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+                    ++g;
                 }
             }
             if (!ok) break;
+            have = walk.next(next_seg);
+            if (have) fetch_first_scales(next_seg);
 
             const bool full_tile = (seg.kb0 == 0 && seg.kb1 == p.k_blocks);
             if (!full_tile && seg.kb0 > 0) {
@@ -463,8 +479,12 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             // -------- fused epilogue: bias, activation, residual, cast; kCols consecutive outputs per thread
             const __nv_bfloat16* r_row = (p.residual && row_ok) ? p.residual + (long long)row * p.ldr : nullptr;
             float row_amax = 0.0f;
+            const bool quantised_out = p.out_type == OUT_FP8_128;
+            // a plain cast (grouped and dense GEMMs without epilogue operands) skips the pass over the accumulators
+            const bool has_epilogue_math = kAct != ACT_IDENTITY || p.bias || p.residual || quantised_out;
 #pragma unroll
             for (int q = 0; q < kCols / 8; ++q) {
+                if (!has_epilogue_math) break;
                 const int n = seg.nt * 128 + c0 + q * 8;
                 if (row_ok && n < p.N) {
                     float x[8];
@@ -539,8 +559,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             } else if (p.out_type != OUT_F32) {
                 // bf16 / f16: a thread holds kCols consecutive outputs of one row, so storing from registers would touch
                 // 32 different lines per instruction (2.2 us per 128x128 tile, a fifth of a 16-block tile's time).  Each
-                // warp transposes through its own shared-memory rows instead and writes 128 contiguous bytes per row.
-                uint8_t* stage_rows = smem + L::kStoreOffset + warp * (32 * L::kStoreRowPitch);
+                // thread writes its row into shared memory instead and hands it to the copy engine as one bulk copy of
+                // up to 128 contiguous bytes.
+                uint8_t* my_row = smem + L::kStoreOffset + (warp * 32 + lane) * L::kStoreRowPitch;
+                tma_store_wait_read<0>();                        // the previous tile's copy has read the row
 #pragma unroll
                 for (int q = 0; q < kCols / 8; ++q) {
                     const float* x = accum + q * 8;
@@ -550,23 +572,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     } else {
                         o = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
                     }
-                    *reinterpret_cast<uint4*>(stage_rows + lane * L::kStoreRowPitch + q * 16) = o;
+                    *reinterpret_cast<uint4*>(my_row + q * 16) = o;
                 }
-                __syncwarp();
-                constexpr int kChunks = kCols / 8;              // 16-byte chunks per row
-                constexpr int kRowsPerStore = 32 / kChunks;
-                const int chunk = lane % kChunks;
-                const int n = seg.nt * 128 + c0 + chunk * 8;
-#pragma unroll
-                for (int it = 0; it < kChunks; ++it) {
-                    const int rr = it * kRowsPerStore + lane / kChunks;
-                    const int out_row = seg.m0 + quad * 32 + rr;
-                    if (out_row < seg.row_end && n < p.N) {
-                        const uint4 o = *reinterpret_cast<const uint4*>(stage_rows + rr * L::kStoreRowPitch + chunk * 16);
-                        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.D) + ((long long)out_row * p.ldd + n) * 2) = o;
-                    }
+                fence_proxy_async();                             // the copy engine reads what this thread just wrote
+                const int n0 = seg.nt * 128 + c0;
+                if (row_ok && n0 < p.N) {
+                    const uint32_t bytes = (uint32_t)min(kCols, p.N - n0) * 2u;      // N is a multiple of 8
+                    bulk_store(reinterpret_cast<uint8_t*>(p.D) + ((long long)row * p.ldd + n0) * 2, my_row, bytes);
                 }
-                __syncwarp();                                    // the next tile reuses the rows
+                tma_store_commit();
             } else if (row_ok) {
                 float* d_row = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd;
 #pragma unroll
@@ -582,6 +596,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
 
     // ---------------------------------------------------------------------- teardown
+    if (warp < kPromoWarps) tma_store_wait_read<0>();     // output rows the copy engine has not read yet
     __syncthreads();
     if (*abort_flag != 0) {
         for (int i = 0; i < 64; ++i) __nanosleep(2000);

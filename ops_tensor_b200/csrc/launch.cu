@@ -685,16 +685,12 @@ static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
     return ACLTENSOR_STATUS_SUCCESS;
 }
 
-template <int kAct>
-static cudaError_t launch_fp8_instance(const CUtensorMap& ta, const CUtensorMap& tb, const Fp8GemmParams& p, int grid,
-                                       cudaStream_t stream) {
-    // Four shared-memory stages, one per TMEM accumulator stage: one ring, one tcgen05.commit per K block (with six
-    // stages and a second commit for the stage hand-back the same shapes ran 5-10 % slower).  Two MMA-issuing
-    // threads take the K blocks in turn (grouped C4: 144 -> 135 us; 16 promotion warps of 32 columns each instead of
-    // 8 of 64: 157 us; a 6-deep shared-memory ring handed back by a promotion thread: 140 us).
-    constexpr int kStages = 4;
+template <int kAct, int kStages>
+static cudaError_t launch_fp8_stages(const CUtensorMap& ta, const CUtensorMap& tb, const Fp8GemmParams& p, int grid,
+                                     cudaStream_t stream) {
     constexpr int kIssuers = 2;
     using L = Fp8GemmSmem<kStages>;
+    static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory per CTA");
     auto kernel = fp8_gemm_kernel<kStages, kAct, kIssuers>;
     static bool attr_done[64] = {};
     int dev = 0;
@@ -707,6 +703,17 @@ static cudaError_t launch_fp8_instance(const CUtensorMap& ta, const CUtensorMap&
     // behind whatever precedes it in the stream (the kernel that zeroes the fix-up flags, or the previous GEMM): set-up
     // overlaps that kernel's tail, every thread waits for it before the role loops start
     return launch_after_prepass(kernel, grid, 288 + 32 * kIssuers, L::kDynamicBytes, stream, ta, tb, p);
+}
+
+template <int kAct>
+static cudaError_t launch_fp8_instance(const CUtensorMap& ta, const CUtensorMap& tb, const Fp8GemmParams& p, int grid,
+                                       cudaStream_t stream) {
+    // One tcgen05.commit per K block serves the accumulator ring (4 TMEM stages) and the operand ring.  Two MMA-issuing
+    // threads take the K blocks in turn.  Operand stages: 5 when the weights are streamed once by a single row of
+    // tiles (decode, C5: 36.7 -> 35.7 us), else 4 (grouped C4: 115 us with 4, 118 us with 5 - those shapes are bound
+    // by the L2 -> shared-memory traffic of 128x128 tiles, 32 KB per K block, not by load latency).
+    if (p.groups == 0 && p.m_tiles == 1) return launch_fp8_stages<kAct, 5>(ta, tb, p, grid, stream);
+    return launch_fp8_stages<kAct, 4>(ta, tb, p, grid, stream);
 }
 
 }  // namespace blaze
