@@ -9,7 +9,8 @@
 
 The reference is single-device (its multi-device line is an unchecked roadmap item, docs/implementation.md:168); this
 module is the B200 build's own.  The only collective the path ever needs is an all-gather of output shards when a
-consumer wants the whole matrix (`gather_columns`).
+consumer wants the whole matrix: `gather_columns` after the GEMM, or `gemm_gather_overlapped`, which computes the
+shard in column chunks and gathers each finished chunk while the next one computes.
 """
 from __future__ import annotations
 
@@ -94,3 +95,62 @@ def max_over_ranks(value: float, device=None, group=None) -> float:
     t = torch.tensor([float(value)], dtype=torch.float64, device=device if device is not None else "cpu")
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return float(t.item())
+
+
+def column_chunks(width: int, chunks: int, multiple: int = 128) -> List[Tuple[int, int]]:
+    """Cuts a shard of `width` columns into at most `chunks` ranges of whole `multiple`-column blocks (the last may be ragged)."""
+    if width <= 0 or chunks < 1:
+        raise ValueError("bad width/chunks")
+    blocks = -(-width // multiple)
+    chunks = min(chunks, blocks)
+    base, extra = divmod(blocks, chunks)
+    out, b0 = [], 0
+    for c in range(chunks):
+        b1 = b0 + base + (1 if c < extra else 0)
+        out.append((min(b0 * multiple, width), min(b1 * multiple, width)))
+        b0 = b1
+    return out
+
+
+def gemm_gather_overlapped(run_chunk, M: int, width: int, world: int, *, chunks: int = 4, dtype=None, device=None,
+                           group=None, multiple: int = 128):
+    """N-sharded GEMM whose consumer needs the whole [M, world * width] output on every rank.
+
+    The rank's shard is computed as `chunks` launches, `run_chunk(c0, c1, out)` filling the contiguous [M, c1 - c0]
+    tensor `out` with columns [c0, c1) of the shard on the current stream; each finished chunk is all-gathered on a
+    second stream while the next one computes, so only the last chunk's gather is exposed.  Every rank must use the
+    same `width` and `chunks`.  Returns the whole matrix (columns in rank order); on CPU tensors (gloo) the gathers are
+    asynchronous work handles instead of a stream.
+    """
+    import torch
+    import torch.distributed as dist
+    ranges = column_chunks(width, chunks, multiple)
+    outs = [torch.empty((M, c1 - c0), dtype=dtype, device=device) for c0, c1 in ranges]
+    if world == 1:
+        for (c0, c1), out in zip(ranges, outs):
+            run_chunk(c0, c1, out)
+        return torch.cat(outs, dim=1)
+    gathered = [torch.empty((world, M, c1 - c0), dtype=dtype, device=device) for c0, c1 in ranges]
+    on_gpu = outs[0].is_cuda
+    if on_gpu:
+        compute = torch.cuda.current_stream(outs[0].device)
+        comm = torch.cuda.Stream(device=outs[0].device)
+        for (c0, c1), out, g in zip(ranges, outs, gathered):
+            run_chunk(c0, c1, out)
+            done = torch.cuda.Event()
+            done.record(compute)
+            comm.wait_event(done)
+            with torch.cuda.stream(comm):
+                dist.all_gather_into_tensor(g.view(world * M, -1), out, group=group)
+            out.record_stream(comm)
+            g.record_stream(comm)
+        compute.wait_stream(comm)
+    else:
+        pending = []
+        for (c0, c1), out, g in zip(ranges, outs, gathered):
+            run_chunk(c0, c1, out)
+            pending.append(dist.all_gather_into_tensor(g.view(world * M, -1), out, group=group, async_op=True))
+        for w in pending:
+            w.wait()
+    # rank r's shard = its chunks side by side; the whole = the shards side by side
+    return torch.cat([g[r] for r in range(world) for g in gathered], dim=1)

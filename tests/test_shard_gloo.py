@@ -43,6 +43,26 @@ def test_expert_plan_balances_and_covers():
     assert max(shard.plan_loads(shard.plan_experts(big, 4))) < 3000
 
 
+def test_column_chunks_cover_whole_blocks():
+    for width, chunks in ((8192, 4), (896, 4), (1000, 3), (100, 4), (128, 1), (7168, 7)):
+        ranges = shard.column_chunks(width, chunks)
+        assert ranges[0][0] == 0 and ranges[-1][1] == width and len(ranges) <= chunks
+        for (a0, a1), (b0, b1) in zip(ranges, ranges[1:]):
+            assert a1 == b0 and a0 % 128 == 0 and a1 % 128 == 0 and a1 > a0
+    with pytest.raises(ValueError):
+        shard.column_chunks(0, 2)
+
+
+def test_overlapped_gather_single_rank_is_a_plain_chunked_gemm():
+    import torch
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((8, 16)).astype(np.float32)
+    b = rng.standard_normal((300, 16)).astype(np.float32)
+    out = shard.gemm_gather_overlapped(lambda c0, c1, o_: o_.copy_(torch.from_numpy(a @ b[c0:c1].T)), 8, 300, 1,
+                                       chunks=3, dtype=torch.float32)
+    assert np.array_equal(out.numpy(), a @ b.T)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -71,6 +91,16 @@ def _worker(rank, world, port, fail_rank, results):
         local = torch.from_numpy(da @ db[n0:n1].T)
         whole = shard.gather_columns(local, world)
         ok_gemm = np.array_equal(whole.numpy(), da @ db.T)
+        # the same product with the shard computed in column chunks, each gathered while the next one computes
+        calls = []
+
+        def run_chunk(c0, c1, out):
+            calls.append((c0, c1))
+            out.copy_(torch.from_numpy(da @ db[n0 + c0:n0 + c1].T))
+
+        whole2 = shard.gemm_gather_overlapped(run_chunk, 32, n1 - n0, world, chunks=2, dtype=local.dtype)
+        chunked = np.concatenate([da @ db[c:c + 128].T for c in range(0, 512, 128)], axis=1)   # same BLAS calls
+        ok_gemm = ok_gemm and np.array_equal(whole2.numpy(), chunked) and calls == [(0, 128), (128, 256)]
         # grouped: every rank derives the same plan; its pieces, summed over ranks, cover every token once
         rows = o.moe_group_rows()
         plan = shard.plan_experts(rows, world)
