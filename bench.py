@@ -442,6 +442,39 @@ def gpu_arm(args):
     total_ms = timed(step, steps)
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = total_ms / steps
+    # Optional: the same step followed by the one collective the path can need, an all-gather of the output shards,
+    # either after the GEMM or chunk by chunk while the next chunk computes (reported beside the headline, not in it).
+    gather_info = None
+    if args.gather != "none" and world > 1 and kind in ("mx", "mx4", "mxf4"):
+        ranges = shard.column_chunks(N, args.gather_chunks, 256)
+        act = H.OP_IDENTITY if kind == "mx4" else H.OP_GELU
+        chunk_plans = {r: H.Contraction(M, r[1] - r[0], K, scale_mode_a=mode_a, scale_mode_b=mode_b, a_dtype=a_dtype,
+                                        b_dtype=b_dtype, activation=act, bias=bias is not None, b_is_static=True,
+                                        sm_limit=args.gather_gemm_sms)
+                       for r in ranges}
+        whole = torch.empty((world * M, N), dtype=torch.bfloat16, device=dev)
+        bufs = shard.gather_buffers(M, N, world, len(ranges), torch.bfloat16, dev, 256)
+        peer = shard.PeerGatherBuffers(M, N, world, rank, len(ranges), torch.bfloat16, dev, 256) if args.gather == "peer" else None
+
+        def run_chunk(c0, c1, o_):
+            chunk_plans[(c0, c1)](qa, sa, qb[c0:c1], sb[c0:c1], o_, bias=None if bias is None else bias[c0:c1])
+
+        def step_gather():
+            if args.gather == "after":
+                step()
+                dist.all_gather_into_tensor(whole, out)
+            else:
+                shard.gemm_gather_overlapped(run_chunk, M, N, world, chunks=len(ranges), dtype=torch.bfloat16,
+                                             device=dev, multiple=256, assemble=False, buffers=bufs, peer_buffers=peer)
+
+        for _ in range(warmup):
+            step_gather()
+        torch.cuda.synchronize()
+        g_ms = timed(step_gather, steps) / steps
+        gather_info = {"mode": args.gather, "chunks": 1 if args.gather == "after" else len(ranges),
+                       "gemm_sms": args.gather_gemm_sms or "all", "nccl_max_ctas": os.environ.get("NCCL_MAX_CTAS"),
+                       "ms_per_step": g_ms, "gemm_only_ms_per_step": ms_per_step,
+                       "gathered_bytes_per_rank": (world - 1) * M * N * 2}
     e2e_ms = {"operands": float("nan"), "fp32": float("nan")}
     if not args.kernel_only:
         e2e_steps = max(4, min(steps, 20))
@@ -507,6 +540,7 @@ def gpu_arm(args):
                                                "weights resident"},
             "gpu_launches": launches_per_step * steps,
             "clocks": clocks,
+            **({"gather": gather_info} if gather_info else {}),
             "device_status": status,
         }
         if world == 1 and not args.kernel_only:
@@ -531,6 +565,11 @@ def main():
                     help="with N GPUs: weak = every GPU runs the whole single-GPU problem on its own shard of a "
                          "gpus-times larger N (default); strong = the single-GPU problem itself is split (along N, or by "
                          "expert for the grouped workload)")
+    ap.add_argument("--gather", default="none", choices=["none", "after", "overlapped", "peer"],
+                    help="N > 1, MX workloads: also time the step followed by / overlapped with an all-gather of the output")
+    ap.add_argument("--gather-chunks", type=int, default=4)
+    ap.add_argument("--gather-gemm-sms", type=int, default=0,
+                    help="overlapped gather: SMs the chunk GEMMs may use (0 = all); the rest stay free for NCCL's CTAs")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (used for profiler captures)")
     args = ap.parse_args()

@@ -112,29 +112,100 @@ def column_chunks(width: int, chunks: int, multiple: int = 128) -> List[Tuple[in
     return out
 
 
+_comm_streams = {}          # one side stream per device for the gathers
+
+
+def gather_buffers(M: int, width: int, world: int, chunks: int, dtype, device, multiple: int = 128):
+    """Chunk outputs [M, wc] and gathered chunks [world, M, wc] for `gemm_gather_overlapped`."""
+    import torch
+    ranges = column_chunks(width, chunks, multiple)
+    outs = [torch.empty((M, c1 - c0), dtype=dtype, device=device) for c0, c1 in ranges]
+    gathered = [torch.empty((world, M, c1 - c0), dtype=dtype, device=device) for c0, c1 in ranges] if world > 1 else []
+    return outs, gathered
+
+
+class PeerGatherBuffers:
+    """Gathered output chunks in symmetric memory (one process per GPU, one box).
+
+    Every rank maps every peer's copy, so a finished chunk is pushed into the peers' buffers with plain device-to-device
+    copies over NVLink: no communication kernel competes with the persistent GEMM for SMs (an NCCL all-gather needs
+    ~32 CTAs for its bandwidth and waits for the GEMM's CTAs to retire).  `gathered[c]` is this rank's
+    [world, M, chunk width] tensor of chunk c; `peer_slots[c][p]` is the [M, chunk width] slot of this rank inside
+    rank p's copy.
+    """
+
+    def __init__(self, M: int, width: int, world: int, rank: int, chunks: int, dtype, device, multiple: int = 128,
+                 group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.ranges = column_chunks(width, chunks, multiple)
+        self.world, self.rank = world, rank
+        self.local = symm.empty(world * M * width, dtype=dtype, device=device)
+        self.handle = symm.rendezvous(self.local, group if group is not None else dist.group.WORLD)
+        self.gathered, self.peer_slots = [], []
+        offset = 0
+        for c0, c1 in self.ranges:
+            shape = (world, M, c1 - c0)
+            count = world * M * (c1 - c0)
+            self.gathered.append(self.local[offset:offset + count].view(shape))
+            self.peer_slots.append([None if p == rank else self.handle.get_buffer(p, shape, dtype, offset)[rank]
+                                    for p in range(world)])
+            offset += count
+        self.token = torch.zeros(1, dtype=torch.float32, device=device)
+
+
 def gemm_gather_overlapped(run_chunk, M: int, width: int, world: int, *, chunks: int = 4, dtype=None, device=None,
-                           group=None, multiple: int = 128):
+                           group=None, multiple: int = 128, assemble: bool = True, buffers=None, peer_buffers=None):
     """N-sharded GEMM whose consumer needs the whole [M, world * width] output on every rank.
 
     The rank's shard is computed as `chunks` launches, `run_chunk(c0, c1, out)` filling the contiguous [M, c1 - c0]
     tensor `out` with columns [c0, c1) of the shard on the current stream; each finished chunk is all-gathered on a
     second stream while the next one computes, so only the last chunk's gather is exposed.  Every rank must use the
-    same `width` and `chunks`.  Returns the whole matrix (columns in rank order); on CPU tensors (gloo) the gathers are
-    asynchronous work handles instead of a stream.
+    same `width` and `chunks`.  Returns the whole matrix (columns in rank order), or with `assemble=False` the gathered
+    chunks as they arrived, one [world, M, chunk width] tensor per chunk, without the final copy.  On CPU tensors (gloo)
+    the gathers are asynchronous work handles instead of a stream.  `buffers` = (chunk outputs, gathered chunks) from
+    `gather_buffers` lets a caller that repeats the step reuse its memory.  With `peer_buffers` (a
+    `PeerGatherBuffers`, GPUs only) each chunk is computed straight into its slot of the gathered buffer and pushed to
+    the peers by device-to-device copies instead of an NCCL all-gather; a one-element all-reduce behind the copies tells
+    every rank that its peers' chunks have landed.
     """
     import torch
     import torch.distributed as dist
+    if peer_buffers is not None:
+        pb = peer_buffers
+        compute = torch.cuda.current_stream(pb.local.device)
+        comm = _comm_streams.get(pb.local.device)
+        if comm is None:
+            comm = _comm_streams[pb.local.device] = torch.cuda.Stream(device=pb.local.device)
+        for i, (c0, c1) in enumerate(pb.ranges):
+            mine = pb.gathered[i][pb.rank]
+            run_chunk(c0, c1, mine)
+            done = torch.cuda.Event()
+            done.record(compute)
+            comm.wait_event(done)
+            with torch.cuda.stream(comm):
+                for slot in pb.peer_slots[i]:
+                    if slot is not None:
+                        slot.copy_(mine, non_blocking=True)
+        with torch.cuda.stream(comm):
+            dist.all_reduce(pb.token, group=group)        # behind the copies: when it ends, every peer's copies have too
+        compute.wait_stream(comm)
+        if not assemble:
+            return pb.gathered
+        return torch.cat([g[r] for r in range(pb.world) for g in pb.gathered], dim=1)
     ranges = column_chunks(width, chunks, multiple)
-    outs = [torch.empty((M, c1 - c0), dtype=dtype, device=device) for c0, c1 in ranges]
+    outs, gathered = buffers if buffers is not None else gather_buffers(M, width, world, chunks, dtype, device, multiple)
     if world == 1:
         for (c0, c1), out in zip(ranges, outs):
             run_chunk(c0, c1, out)
-        return torch.cat(outs, dim=1)
-    gathered = [torch.empty((world, M, c1 - c0), dtype=dtype, device=device) for c0, c1 in ranges]
+        return torch.cat(outs, dim=1) if assemble else [o.unsqueeze(0) for o in outs]
     on_gpu = outs[0].is_cuda
     if on_gpu:
         compute = torch.cuda.current_stream(outs[0].device)
-        comm = torch.cuda.Stream(device=outs[0].device)
+        comm = _comm_streams.get(outs[0].device)
+        if comm is None:
+            comm = _comm_streams[outs[0].device] = torch.cuda.Stream(device=outs[0].device)
         for (c0, c1), out, g in zip(ranges, outs, gathered):
             run_chunk(c0, c1, out)
             done = torch.cuda.Event()
@@ -152,5 +223,7 @@ def gemm_gather_overlapped(run_chunk, M: int, width: int, world: int, *, chunks:
             pending.append(dist.all_gather_into_tensor(g.view(world * M, -1), out, group=group, async_op=True))
         for w in pending:
             w.wait()
+    if not assemble:
+        return gathered
     # rank r's shard = its chunks side by side; the whole = the shards side by side
     return torch.cat([g[r] for r in range(world) for g in gathered], dim=1)
