@@ -283,8 +283,9 @@ static cudaError_t launch_after_prepass(void (*kernel)(KArgs...), int grid, int 
 template <int kBN, int kAct>
 static cudaError_t launch_mx_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
                                       const MxGemmParams& p, int grid, cudaStream_t stream) {
-    constexpr int kStages = 4;
+    constexpr int kStages = kBN <= 128 ? 6 : 4;       // as many operand stages as fit beside the epilogue's staging blocks
     using L = MxGemmSmem<kBN, kStages>;
+    static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory per CTA");
     auto kernel = mx_gemm_kernel<kBN, kStages, kAct>;
     static bool attr_done[64] = {};
     int dev = 0;
