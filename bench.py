@@ -459,8 +459,27 @@ def gpu_arm(args):
         def run_chunk(c0, c1, o_):
             chunk_plans[(c0, c1)](qa, sa, qb[c0:c1], sb[c0:c1], o_, bias=None if bias is None else bias[c0:c1])
 
+        fused = None
+        if args.gather == "fused":
+            # one full-width GEMM whose epilogue stores every tile to all ranks' gathered buffers (C ABI: peerD)
+            fused = shard.PeerGatherBuffers(M, N, world, rank, 1, torch.bfloat16, dev, 256)
+            f_kw = dict(b_elem=native.ELEM_E4M3 if kind == "mx" else native.ELEM_E2M1,
+                        a_elem=native.ELEM_E2M1 if kind == "mxf4" else native.ELEM_E4M3, bias=bias,
+                        activation=native.ACT_IDENTITY if kind == "mx4" else native.ACT_GELU_TANH)
+            probe = native.mx_gemm_args(qa, sa, qb, sb, fused.gathered[0][rank],
+                                        peer_outs=[s_ for s_ in fused.peer_slots[0] if s_ is not None], **f_kw)
+            f_ws = torch.empty(max(native.mx_gemm_workspace_bytes(probe), 256), dtype=torch.uint8, device=dev)
+            f_calls = [0]
+
+            def run_fused(out_, peers):
+                native.mx_gemm(qa, sa, qb, sb, out=out_, workspace=f_ws, peer_outs=peers,
+                               reuse_b_prepass=f_calls[0] > 0, **f_kw)
+                f_calls[0] += 1
+
         def step_gather():
-            if args.gather == "after":
+            if args.gather == "fused":
+                shard.gemm_gather_fused(run_fused, fused)
+            elif args.gather == "after":
                 step()
                 dist.all_gather_into_tensor(whole, out)
             else:
@@ -471,7 +490,7 @@ def gpu_arm(args):
             step_gather()
         torch.cuda.synchronize()
         g_ms = timed(step_gather, steps) / steps
-        gather_info = {"mode": args.gather, "chunks": 1 if args.gather == "after" else len(ranges),
+        gather_info = {"mode": args.gather, "chunks": 1 if args.gather in ("after", "fused") else len(ranges),
                        "gemm_sms": args.gather_gemm_sms or "all", "nccl_max_ctas": os.environ.get("NCCL_MAX_CTAS"),
                        "ms_per_step": g_ms, "gemm_only_ms_per_step": ms_per_step,
                        "gathered_bytes_per_rank": (world - 1) * M * N * 2}
@@ -565,7 +584,7 @@ def main():
                     help="with N GPUs: weak = every GPU runs the whole single-GPU problem on its own shard of a "
                          "gpus-times larger N (default); strong = the single-GPU problem itself is split (along N, or by "
                          "expert for the grouped workload)")
-    ap.add_argument("--gather", default="none", choices=["none", "after", "overlapped", "peer"],
+    ap.add_argument("--gather", default="none", choices=["none", "after", "overlapped", "peer", "fused"],
                     help="N > 1, MX workloads: also time the step followed by / overlapped with an all-gather of the output")
     ap.add_argument("--gather-chunks", type=int, default=4)
     ap.add_argument("--gather-gemm-sms", type=int, default=0,

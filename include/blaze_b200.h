@@ -108,8 +108,14 @@ typedef struct {
     int32_t b_layout;        /* blazeBLayout_t */
     void* scaleD;            /* device, E8M0 scales of D when d_type is BLAZE_OUT_MX_E4M3, else NULL */
     int32_t sched;           /* blazeSched_t; stream-K applies to the single-CTA tiles (skinny M or N) */
-    int32_t reserved;
+    int32_t n_peers;         /* 0..BLAZE_MAX_PEERS: copies of D that the epilogue also writes (see peerD) */
+    void* peerD[7];          /* device pointers this GPU can store to - typically the slot of this rank in the other
+                                GPUs' gathered output (peer-mapped symmetric memory) - same shape, ldd and type as D.
+                                Every output tile is stored to D and to each of them straight from the epilogue, so an
+                                N-sharded GEMM ends with the whole matrix on every GPU without a separate all-gather.
+                                Needs the 2-CTA tiles, a bf16 / f16 D and 1 KB more workspace. */
 } blazeMxGemmArgs;
+#define BLAZE_MAX_PEERS 7
 
 BLAZE_API int blazeMxGemmWorkspaceSize(const blazeMxGemmArgs* args, size_t* bytes);
 BLAZE_API int blazeMxGemm(const blazeMxGemmArgs* args, void* stream);

@@ -26,6 +26,8 @@ struct EpilogueArgs {
     int out_type;       // OutType of D; the tensor map handed to the store has the matching element size and box
     uint8_t* scale_d;   // OUT_MX_E4M3: E8M0 scales of D, [M][scale_cols_d]
     int scale_cols_d;   // ceil(N / 64) * 2
+    const CUtensorMap* peer_maps = nullptr;   // global memory: n_peers more maps of D's shape (16-bit outputs only);
+    int n_peers = 0;                          // every staged block is stored through each of them as well
 };
 
 // Drains one accumulator tile.  `tmem_tile` = TMEM address of column 0 of the accumulator, lane field already set to
@@ -194,6 +196,7 @@ __device__ __forceinline__ void epilogue_store_tile_from(uint32_t tmem_tile, con
         __syncwarp();
         if (lane == 0) {
             tma_store_2d(tmap_d, block, n0, row0);
+            for (int q = 0; q < ea.n_peers; ++q) tma_store_2d(ea.peer_maps + q, block, n0, row0);
             tma_store_commit();
         }
         ++chunk_counter;

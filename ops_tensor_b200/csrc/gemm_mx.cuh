@@ -46,6 +46,8 @@ struct MxGemmParams {
     int out_type;                  // OutType of D
     uint8_t* scale_d;              // OUT_MX_E4M3: [M][scale_cols_d] E8M0 scales of D
     int scale_cols_d;
+    const CUtensorMap* peer_maps;  // global memory: maps of the n_peers further copies of D (2-CTA kernel only)
+    int n_peers;
 };
 
 template <int kBN, int kStages>

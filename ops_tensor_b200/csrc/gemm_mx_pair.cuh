@@ -254,7 +254,8 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         bool ok = true;
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         uint8_t* stage_buf = smem + L::kEpiOffset + warp * kEpiStageBytesPerWarp;
-        const EpilogueArgs ea{p.M, p.N, p.bias, p.residual, p.ldr, p.out_type, p.scale_d, p.scale_cols_d};
+        const EpilogueArgs ea{p.M, p.N, p.bias, p.residual, p.ldr, p.out_type, p.scale_d, p.scale_cols_d,
+                              p.peer_maps, p.n_peers};
         for (int t = pair; t < num_tiles && ok; t += num_pairs) {
             int mt, nt;
             tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);

@@ -155,6 +155,7 @@ struct MxPlan {
     int m_tiles, n_tiles, k_steps;
     size_t sfa_bytes, sfb_bytes, b_expand_bytes, b_scale_rows_bytes;
     size_t sfa_off, sfb_off, b_expand_off, b_scale_rows_off, total;
+    size_t peer_maps_off;   // tensor maps of the peer outputs (1 KB), when the call names any
 };
 
 static int choose_tile_n(int M, int N, int sms, int requested) {
@@ -258,6 +259,13 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scal
     pl->flags_off = pl->b_scale_rows_off + round256(pl->b_scale_rows_bytes);
     pl->partials_off = pl->flags_off + pl->flags_bytes;
     pl->total = pl->partials_off + round256(pl->partials_bytes);
+    pl->peer_maps_off = pl->total;
+    if (a->n_peers < 0 || a->n_peers > BLAZE_MAX_PEERS) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->n_peers > 0) {
+        // the epilogue of the 2-CTA kernel stores 16-bit tiles through the extra maps; nothing else does
+        if (!pl->pair || (a->d_type != BLAZE_OUT_BF16 && a->d_type != BLAZE_OUT_F16)) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+        pl->total += 1024;
+    }
     return ACLTENSOR_STATUS_SUCCESS;
 }
 
@@ -390,6 +398,22 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
     if (a->d_type == BLAZE_OUT_MX_E4M3 && (!a->scaleD || (a->ldd % 16) != 0)) return ACLTENSOR_STATUS_INVALID_VALUE;
     p.a_format = ta_packed ? FMT_E2M1 : FMT_E4M3;
     p.a_tx_shift = ta_packed ? 1 : 0;
+    p.peer_maps = nullptr;
+    p.n_peers = 0;
+    if (a->n_peers > 0) {
+        // one more map of D's shape per peer copy, handed to the kernel through the workspace
+        CUtensorMap peer[BLAZE_MAX_PEERS];
+        for (int i = 0; i < a->n_peers; ++i) {
+            if (!a->peerD[i] || !aligned16(a->peerD[i])) return ACLTENSOR_STATUS_INVALID_VALUE;
+            if (!make_tmap_store(&peer[i], a->peerD[i], (uint64_t)a->N, (uint64_t)a->M, (uint64_t)a->ldd, a->d_type))
+                return ACLTENSOR_STATUS_INTERNAL_ERROR;
+        }
+        void* dst = static_cast<uint8_t*>(a->workspace) + pl.peer_maps_off;
+        cudaError_t ce = cudaMemcpyAsync(dst, peer, sizeof(CUtensorMap) * a->n_peers, cudaMemcpyHostToDevice, stream);
+        if (ce != cudaSuccess) return status_of(ce);
+        p.peer_maps = static_cast<const CUtensorMap*>(dst);
+        p.n_peers = a->n_peers;
+    }
 
     const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
     int sms = sm_count;
@@ -586,6 +610,7 @@ extern "C" int blazeMxGemmBatched(const blazeMxGemmArgs* args, const blazeBatchD
     BatchWalk w;
     int st = check_batch(args, bd, &w);
     if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    if (args->n_peers != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;      // peer copies belong to the plain call
     blazeMxGemmArgs one = *args;
     if (w.folds) {
         one.M = (int32_t)(w.count_c * args->M);
@@ -973,6 +998,7 @@ extern "C" int blazeMxGemmNoAlloc(const blazeMxGemmArgs* a, int32_t* device_stat
     MxPlan pl;
     st = plan_mx(a, nd->sm_count, &pl, true, false);        // no stream-K: its partial tiles would not fit the array
     if (st != ACLTENSOR_STATUS_SUCCESS) return st;
+    if (a->n_peers != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (pl.total > kNoAllocScratchBytes) {
         // four copies of B's scale blocks do not fit the array: keep one copy (one more scale copy per K step)
         st = plan_mx(a, nd->sm_count, &pl, false, false);

@@ -54,7 +54,8 @@ class MxGemmArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("d_type", C.c_int32), ("b_layout", C.c_int32),
         ("scaleD", C.c_void_p),
-        ("sched", C.c_int32), ("reserved", C.c_int32),
+        ("sched", C.c_int32), ("n_peers", C.c_int32),
+        ("peerD", C.c_void_p * 7),
     ]
 
 
@@ -205,7 +206,7 @@ def quantize_fp8_blocks(w):
 
 def mx_gemm_args(a, sa, b, sb, out, *, b_elem=ELEM_E4M3, bias=None, residual=None, activation=ACT_IDENTITY,
                  tile_n=0, reuse_b_prepass=False, sm_limit=0, cta_pair=0, workspace=None, a_elem=ELEM_E4M3,
-                 scale_out=None, b_n_major=False, sched=SCHED_AUTO) -> MxGemmArgs:
+                 scale_out=None, b_n_major=False, sched=SCHED_AUTO, peer_outs=None) -> MxGemmArgs:
     M, K = a.shape
     if a_elem == ELEM_E2M1:
         K *= 2                       # two codes per byte
@@ -231,6 +232,14 @@ def mx_gemm_args(a, sa, b, sb, out, *, b_elem=ELEM_E4M3, bias=None, residual=Non
     args.scaleD = scale_out.data_ptr() if scale_out is not None else None
     args.b_layout = 1 if b_n_major else 0
     args.sched = sched
+    if peer_outs:
+        # further copies of `out` (same shape, pitch and dtype) that the epilogue stores every tile to as well
+        if len(peer_outs) > 7 or any(t.shape != out.shape or t.stride(0) != out.stride(0) or t.dtype != out.dtype
+                                     for t in peer_outs):
+            raise ValueError("peer outputs must match the output's shape, pitch and dtype (at most 7)")
+        args.n_peers = len(peer_outs)
+        for i, t in enumerate(peer_outs):
+            args.peerD[i] = t.data_ptr()
     if workspace is not None:
         args.workspace, args.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
     return args

@@ -155,6 +155,24 @@ class PeerGatherBuffers:
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
 
 
+def gemm_gather_fused(run_gemm, peer_buffers: "PeerGatherBuffers", group=None):
+    """N-sharded GEMM whose epilogue itself writes every output tile into all ranks' gathered buffers.
+
+    `peer_buffers` must have one chunk.  `run_gemm(out, peer_outs)` launches one GEMM on the current stream that stores
+    its result to `out` (this rank's slot of its own buffer) and to each tensor of `peer_outs` (this rank's slot in the
+    peers' buffers; `native.mx_gemm(..., peer_outs=...)`).  The stores cross NVLink tile by tile while later tiles
+    compute; a one-element all-reduce behind the GEMM tells every rank that its peers' GEMMs, and with them their
+    stores, have finished.  Returns this rank's [world, M, width] buffer.
+    """
+    import torch.distributed as dist
+    pb = peer_buffers
+    if len(pb.ranges) != 1:
+        raise ValueError("the fused form writes the whole shard at once: build the buffers with chunks=1")
+    run_gemm(pb.gathered[0][pb.rank], [slot for slot in pb.peer_slots[0] if slot is not None])
+    dist.all_reduce(pb.token, group=group)
+    return pb.gathered[0]
+
+
 def gemm_gather_overlapped(run_chunk, M: int, width: int, world: int, *, chunks: int = 4, dtype=None, device=None,
                            group=None, multiple: int = 128, assemble: bool = True, buffers=None, peer_buffers=None):
     """N-sharded GEMM whose consumer needs the whole [M, world * width] output on every rank.

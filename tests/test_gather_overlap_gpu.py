@@ -68,6 +68,19 @@ def _worker(rank, world, port, results):
             torch.cuda.synchronize()
             dist.barrier()                                # nobody overwrites a buffer that a peer still reads
         same = same and bool(torch.equal(whole_p.view(torch.int16), whole_after.view(torch.int16)))
+        # and with one full-width GEMM whose epilogue stores every tile to both GPUs' buffers (C ABI: peerD)
+        from ops_tensor_b200 import native
+        fused = shard.PeerGatherBuffers(M, width, world, rank, 1, torch.bfloat16, dev, 256)
+
+        def run_fused(out, peers):
+            native.mx_gemm(qa, sa, qb, sb, out=out, bias=bias, activation=native.ACT_GELU_TANH, peer_outs=peers)
+
+        for _ in range(2):
+            g = shard.gemm_gather_fused(run_fused, fused)
+            torch.cuda.synchronize()
+            dist.barrier()
+        whole_f = torch.cat([g[r] for r in range(world)], dim=1)
+        same = same and bool(torch.equal(whole_f.view(torch.int16), whole_after.view(torch.int16)))
         results[rank] = (same, tuple(whole.shape), H.device_status())
     finally:
         dist.destroy_process_group()
