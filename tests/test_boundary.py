@@ -411,3 +411,37 @@ def test_plan_choices_show_in_the_workspace_size(built_library):
     assert fp8_bytes(256, 512, 1024) == 0
     assert fp8_bytes(32768, 768, 2048, groups=128) == 0
     assert fp8_bytes(256, 512, 1024, sched=native.SCHED_STREAM_K) > 0
+
+
+def test_peer_outputs_are_validated_at_plan_time(built_library):
+    """`n_peers` / `peerD` (the epilogue's extra copies of D): 1 KB more workspace for the tensor maps, only with the 2-CTA
+    tiles and a 16-bit D, never through the batched or the allocation-free entry."""
+    lib = native.lib()
+
+    def size(M, N, K, **kw):
+        a = native.MxGemmArgs()
+        a.struct_size = C.sizeof(a)
+        a.M, a.N, a.K = M, N, K
+        for k, v in kw.items():
+            setattr(a, k, v)
+        n = C.c_size_t(0)
+        return lib.blazeMxGemmWorkspaceSize(C.byref(a), C.byref(n)), n.value
+
+    ok, plain = size(8192, 8192, 8192)
+    assert ok == H.STATUS_SUCCESS
+    assert size(8192, 8192, 8192, n_peers=1) == (H.STATUS_SUCCESS, plain + 1024)
+    assert size(8192, 8192, 8192, n_peers=7) == (H.STATUS_SUCCESS, plain + 1024)
+    assert size(8192, 8192, 8192, n_peers=8)[0] == H.STATUS_INVALID_VALUE
+    assert size(8192, 8192, 8192, n_peers=-1)[0] == H.STATUS_INVALID_VALUE
+    assert size(128, 7168, 18432, n_peers=1)[0] == H.STATUS_NOT_SUPPORTED               # single-CTA tiles
+    assert size(8192, 8192, 8192, n_peers=1, d_type=native.OUT_F32)[0] == H.STATUS_NOT_SUPPORTED
+    # batched entry
+    a = native.MxGemmArgs()
+    a.struct_size = C.sizeof(a)
+    a.M, a.N, a.K, a.n_peers = 256, 256, 256, 1
+    bd = native.BatchDims()
+    for i in range(4):
+        bd.c[i] = bd.a[i] = bd.b[i] = 1
+    n = C.c_size_t(0)
+    assert lib.blazeMxGemmBatched(C.byref(a), C.byref(bd), None) == H.STATUS_NOT_SUPPORTED
+
