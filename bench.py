@@ -494,6 +494,29 @@ def gpu_arm(args):
                        "gemm_sms": args.gather_gemm_sms or "all", "nccl_max_ctas": os.environ.get("NCCL_MAX_CTAS"),
                        "ms_per_step": g_ms, "gemm_only_ms_per_step": ms_per_step,
                        "gathered_bytes_per_rank": (world - 1) * M * N * 2}
+    if args.gather in ("after", "fused") and world > 1 and kind == "fp8sk":
+        # the decode GEMM: its output is small, so a separate all-gather is mostly launch latency
+        whole = torch.empty((world * M, N), dtype=torch.bfloat16, device=dev)
+        if args.gather == "fused":
+            fused = shard.PeerGatherBuffers(M, N, world, rank, 1, torch.bfloat16, dev, 128)
+            probe = native.fp8_gemm_args(qa, sa, qb, sb, fused.gathered[0][rank], residual=residual,
+                                         peer_outs=[s_ for s_ in fused.peer_slots[0] if s_ is not None])
+            f_ws = torch.empty(max(native.fp8_gemm_workspace_bytes(probe), 256), dtype=torch.uint8, device=dev)
+
+        def step_gather():
+            if args.gather == "fused":
+                shard.gemm_gather_fused(lambda out_, peers: native.fp8_gemm(qa, sa, qb, sb, out=out_, workspace=f_ws,
+                                                                            residual=residual, peer_outs=peers), fused)
+            else:
+                step()
+                dist.all_gather_into_tensor(whole, out)
+
+        for _ in range(max(warmup, 20)):
+            step_gather()
+        torch.cuda.synchronize()
+        g_ms = timed(step_gather, steps) / steps
+        gather_info = {"mode": args.gather, "chunks": 1, "ms_per_step": g_ms, "gemm_only_ms_per_step": ms_per_step,
+                       "gathered_bytes_per_rank": (world - 1) * M * N * 2}
     e2e_ms = {"operands": float("nan"), "fp32": float("nan")}
     if not args.kernel_only:
         e2e_steps = max(4, min(steps, 20))

@@ -79,6 +79,8 @@ typedef enum {
  * pointers 16-byte aligned.  A packed E2M1 B with K % 128 == 0, ldb % 32 == 0 and a 32-byte aligned base is read as it
  * is; any other packed B is first expanded to one-byte codes in the workspace (same results, N x K more bytes).
  * ------------------------------------------------------------------------------------------------------------ */
+#define BLAZE_MAX_PEERS 7 /* further copies of D that a GEMM epilogue can write (peerD) */
+
 typedef struct {
     size_t struct_size; /* sizeof(blazeMxGemmArgs), for forward compatibility */
     int32_t M, N, K;
@@ -115,7 +117,6 @@ typedef struct {
                                 N-sharded GEMM ends with the whole matrix on every GPU without a separate all-gather.
                                 Needs the 2-CTA tiles, a bf16 / f16 D and 1 KB more workspace. */
 } blazeMxGemmArgs;
-#define BLAZE_MAX_PEERS 7
 
 BLAZE_API int blazeMxGemmWorkspaceSize(const blazeMxGemmArgs* args, size_t* bytes);
 BLAZE_API int blazeMxGemm(const blazeMxGemmArgs* args, void* stream);
@@ -199,6 +200,9 @@ typedef struct {
     void* workspace;
     size_t workspace_bytes;
     void* scaleD;     /* device float32 scales of D when d_type is BLAZE_OUT_FP8_128, else NULL */
+    int32_t n_peers;  /* 0..BLAZE_MAX_PEERS further copies of D, as in blazeMxGemmArgs (bf16 / f16 D only) */
+    int32_t reserved;
+    void* peerD[7];
 } blazeFp8GemmArgs;
 
 BLAZE_API int blazeFp8GemmWorkspaceSize(const blazeFp8GemmArgs* args, size_t* bytes);

@@ -47,6 +47,8 @@ struct Fp8GemmParams {
     float* scale_d;                 // OUT_FP8_128: [M][n_blocks] float32 scales of D
     int* flags;                     // [gridDim.x], zeroed before the launch (stream-K only)
     int* status;
+    uint8_t* peer_d[7];             // further copies of D (same pitch and type) that 16-bit output rows are also sent to:
+    int n_peers;                    // this GPU's slot in the other GPUs' gathered outputs
 };
 
 template <int kStages>
@@ -578,7 +580,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 const int n0 = seg.nt * 128 + c0;
                 if (row_ok && n0 < p.N) {
                     const uint32_t bytes = (uint32_t)min(kCols, p.N - n0) * 2u;      // N is a multiple of 8
-                    bulk_store(reinterpret_cast<uint8_t*>(p.D) + ((long long)row * p.ldd + n0) * 2, my_row, bytes);
+                    const long long at = ((long long)row * p.ldd + n0) * 2;
+                    bulk_store(reinterpret_cast<uint8_t*>(p.D) + at, my_row, bytes);
+                    for (int q = 0; q < p.n_peers; ++q) bulk_store(p.peer_d[q] + at, my_row, bytes);
                 }
                 tma_store_commit();
             } else if (row_ok) {

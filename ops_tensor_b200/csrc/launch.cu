@@ -670,6 +670,9 @@ static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
     if (a->M < 0 || a->N < 0 || a->K < 0 || a->groups < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->groups > kFp8MaxGroups) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->n_peers < 0 || a->n_peers > BLAZE_MAX_PEERS) return ACLTENSOR_STATUS_INVALID_VALUE;
+    // only the 16-bit output rows leave as bulk copies that can be repeated towards the peers
+    if (a->n_peers > 0 && a->d_type != BLAZE_OUT_BF16 && a->d_type != BLAZE_OUT_F16) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->sched < BLAZE_SCHED_AUTO || a->sched > BLAZE_SCHED_STREAM_K) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->d_type != BLAZE_OUT_FP8_128 && (a->d_type < BLAZE_OUT_BF16 || a->d_type > BLAZE_OUT_F32))
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
@@ -801,6 +804,11 @@ extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
     p.out_type = a->d_type;
     p.scale_d = static_cast<float*>(a->scaleD);
     if (a->d_type == BLAZE_OUT_FP8_128 && (!a->scaleD || (a->ldd % 16) != 0)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    p.n_peers = a->n_peers;
+    for (int i = 0; i < BLAZE_MAX_PEERS; ++i) {
+        p.peer_d[i] = i < a->n_peers ? static_cast<uint8_t*>(a->peerD[i]) : nullptr;
+        if (i < a->n_peers && (!a->peerD[i] || !aligned16(a->peerD[i]))) return ACLTENSOR_STATUS_INVALID_VALUE;
+    }
     p.stream_k = pl.stream_k;
     p.flags = nullptr;
     p.partials = nullptr;

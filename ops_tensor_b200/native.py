@@ -83,6 +83,8 @@ class Fp8GemmArgs(C.Structure):
         ("d_type", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("scaleD", C.c_void_p),
+        ("n_peers", C.c_int32), ("reserved", C.c_int32),
+        ("peerD", C.c_void_p * 7),
     ]
 
 
@@ -268,7 +270,7 @@ def mx_gemm(a, sa, b, sb, *, out=None, workspace=None, **kw):
 
 
 def fp8_gemm_args(a, sa, b, sb, out, *, group_rows=None, bias=None, residual=None, activation=ACT_IDENTITY,
-                  sched=SCHED_AUTO, sm_limit=0, workspace=None, scale_out=None) -> Fp8GemmArgs:
+                  sched=SCHED_AUTO, sm_limit=0, workspace=None, scale_out=None, peer_outs=None) -> Fp8GemmArgs:
     M, K = a.shape
     if b.dim() == 3:
         G, N, _ = b.shape
@@ -293,6 +295,13 @@ def fp8_gemm_args(a, sa, b, sb, out, *, group_rows=None, bias=None, residual=Non
     args.activation = activation
     args.sched = sched
     args.sm_limit = sm_limit
+    if peer_outs:
+        if len(peer_outs) > 7 or any(t.shape != out.shape or t.stride(0) != out.stride(0) or t.dtype != out.dtype
+                                     for t in peer_outs):
+            raise ValueError("peer outputs must match the output's shape, pitch and dtype (at most 7)")
+        args.n_peers = len(peer_outs)
+        for i, t in enumerate(peer_outs):
+            args.peerD[i] = t.data_ptr()
     if workspace is not None:
         args.workspace, args.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
     return args

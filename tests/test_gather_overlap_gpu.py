@@ -81,6 +81,23 @@ def _worker(rank, world, port, results):
             dist.barrier()
         whole_f = torch.cat([g[r] for r in range(world)], dim=1)
         same = same and bool(torch.equal(whole_f.view(torch.int16), whole_after.view(torch.int16)))
+        # the FP8 kernel (stream-K decode shape): output rows go to both GPUs as bulk copies
+        Mf, Kf = 128, 2048
+        af = torch.from_numpy(syn.normal_f32(8, 0, (Mf, Kf), 1.0)).to(dev)
+        wf = (torch.from_numpy(syn.normal_f32(8, 1, (N, Kf), 1.0)).to(dev) * 0.02)[n0:n1].contiguous()
+        res = torch.from_numpy(syn.normal_f32(8, 3, (Mf, N), 1.0)).to(dev).to(torch.bfloat16)[:, n0:n1].contiguous()
+        qaf, saf = H.quantize(af, H.SCALE_FP32_1X128)
+        qbf, sbf = H.quantize(wf, H.SCALE_FP32_128X128)
+        for sched in (native.SCHED_STREAM_K, native.SCHED_DATA_PARALLEL):
+            plain = native.fp8_gemm(qaf, saf, qbf, sbf, residual=res, sched=sched)
+            ref_whole = shard.gather_columns(plain, world)
+            fused8 = shard.PeerGatherBuffers(Mf, width, world, rank, 1, torch.bfloat16, dev, 128)
+            g8 = shard.gemm_gather_fused(lambda out, peers: native.fp8_gemm(qaf, saf, qbf, sbf, out=out, residual=res,
+                                                                            sched=sched, peer_outs=peers), fused8)
+            torch.cuda.synchronize()
+            dist.barrier()
+            whole8 = torch.cat([g8[r] for r in range(world)], dim=1)
+            same = same and bool(torch.equal(whole8.view(torch.int16), ref_whole.view(torch.int16)))
         results[rank] = (same, tuple(whole.shape), H.device_status())
     finally:
         dist.destroy_process_group()
