@@ -444,4 +444,14 @@ def test_peer_outputs_are_validated_at_plan_time(built_library):
         bd.c[i] = bd.a[i] = bd.b[i] = 1
     n = C.c_size_t(0)
     assert lib.blazeMxGemmBatched(C.byref(a), C.byref(bd), None) == H.STATUS_NOT_SUPPORTED
+    # the FP8 GEMM takes the same fields and needs no workspace for them
+    f = native.Fp8GemmArgs()
+    f.struct_size = C.sizeof(f)
+    f.M, f.N, f.K = 256, 512, 1024
+    for peers, d_type, want in ((0, native.OUT_BF16, H.STATUS_SUCCESS), (7, native.OUT_F16, H.STATUS_SUCCESS),
+                                (8, native.OUT_BF16, H.STATUS_INVALID_VALUE), (1, native.OUT_F32, H.STATUS_NOT_SUPPORTED),
+                                (1, native.OUT_FP8_128, H.STATUS_NOT_SUPPORTED)):
+        f.n_peers, f.d_type = peers, d_type
+        assert lib.blazeFp8GemmWorkspaceSize(C.byref(f), C.byref(n)) == want
+        assert want != H.STATUS_SUCCESS or n.value == 0
 
