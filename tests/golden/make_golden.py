@@ -1,6 +1,6 @@
 """Generates the committed golden fixtures of this directory.  Run in the build container:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference        (or REFERENCE_ROOT=/path/to/reference)
 
 1. ref_gen_data.npz - inputs and goldens produced by the reference's own data generators, imported from the
    reference tree (tests/ut/op_kernel/mat_mul/matmul_data/gen_data.py and
@@ -28,7 +28,9 @@ def _load(path, name):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT")
+    if not ref:
+        sys.exit("usage: make_golden.py /path/to/reference")
     here = os.path.dirname(os.path.abspath(__file__))
     out = {}
     mm = _load(os.path.join(ref, "tests/ut/op_kernel/mat_mul/matmul_data/gen_data.py"), "ref_mm_gen")
