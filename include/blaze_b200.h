@@ -118,6 +118,13 @@ typedef struct {
                                 Needs the 2-CTA tiles, a bf16 / f16 D and 1 KB more workspace. */
 } blazeMxGemmArgs;
 
+/* Device timer on a stream (a pair of CUDA events), for callers above this ABI that have no CUDA headers: Start
+ * records, Stop records, waits for the stream to get there and returns the milliseconds in between. */
+BLAZE_API int blazeTimerCreate(void** timer);
+BLAZE_API int blazeTimerStart(void* timer, void* stream);
+BLAZE_API int blazeTimerStop(void* timer, void* stream, float* milliseconds);
+BLAZE_API int blazeTimerDestroy(void* timer);
+
 BLAZE_API int blazeMxGemmWorkspaceSize(const blazeMxGemmArgs* args, size_t* bytes);
 BLAZE_API int blazeMxGemm(const blazeMxGemmArgs* args, void* stream);
 

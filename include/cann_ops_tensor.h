@@ -114,6 +114,27 @@ ACLTENSOR_API acltensorStatus_t acltensorEstimateWorkspaceSize(const acltensorHa
 /* Workspace bytes the plan needs at execution (0 for elementwise plans). */
 ACLTENSOR_API acltensorStatus_t acltensorPlanGetRequiredWorkspace(const acltensorPlan_t plan, uint64_t* bytes);
 
+/*
+ * Plan cache of a handle: contraction problem signature -> kernel choice (tile width, 1- or 2-CTA tiles, scheduler
+ * mode).  The reference reserves these three names and leaves them unimplemented (lib/core/handle.cpp:105-108,
+ * docs/implementation.md:62-64).  A plan whose descriptor leaves the choice open takes it from the cache when the
+ * signature is there.  A plan created with ACLTENSOR_ALGO_DEFAULT_PATIENT (include/cann_ops_tensor_types.h:113) and
+ * no cached entry times its candidates on the device during its first acltensorContract call (which therefore runs
+ * the product several times and synchronises the stream), keeps the fastest and stores it in the cache.
+ * The file is text: the line "acltensor-plan-cache 1", then "<signature> <tileN> <ctaPair> <splitPolicy>" per entry.
+ * A missing or unreadable file gives IO_ERROR, a damaged one INVALID_VALUE and leaves the cache as it was.
+ */
+ACLTENSOR_API acltensorStatus_t acltensorHandleResizePlanCache(acltensorHandle_t handle, const uint32_t numEntries);
+ACLTENSOR_API acltensorStatus_t acltensorHandleWritePlanCacheToFile(const acltensorHandle_t handle,
+                                                                    const char filename[]);
+ACLTENSOR_API acltensorStatus_t acltensorHandleReadPlanCacheFromFile(acltensorHandle_t handle, const char filename[],
+                                                                     uint32_t* numCachelinesRead);
+/* What the plan runs with (0 / ACLTENSOR_SPLIT_AUTO = left to the launch layer); *pendingTuning = 1 while a PATIENT
+ * plan has not timed its candidates yet.  Any out-pointer may be NULL. */
+ACLTENSOR_API acltensorStatus_t acltensorPlanGetKernelChoice(const acltensorPlan_t plan, int32_t* tileN,
+                                                             int32_t* ctaPair, int32_t* splitPolicy,
+                                                             int32_t* pendingTuning);
+
 /* Device pointers that accompany the operands of a contraction.  Unused ones are NULL. */
 typedef struct {
     const void* scaleA;    /* scales of A, layout given by SCALE_MODE_A */

@@ -5,8 +5,11 @@
 // The entry-point names are the ones the reference reserves (lib/core/operation_descriptor.cpp:183-189,
 // lib/core/plan_preference.cpp:58, docs/implementation.md:57-74); argument checking follows the conventions of its
 // implemented entry points: NULL required argument -> INVALID_VALUE, anything the build cannot do -> NOT_SUPPORTED.
+#include <cstdio>
 #include <cstring>
+#include <memory>
 #include <new>
+#include <string>
 
 #include "blaze_b200.h"
 #include "cann_ops_tensor.h"
@@ -458,13 +461,68 @@ acltensorStatus_t acltensorEstimateWorkspaceSize(const acltensorHandle_t handle,
     return solution->workspaceSize(*desc, policy, workspaceSizeEstimate);
 }
 
+namespace {
+
+// Everything that decides which kernel configuration is best, as one token without blanks.
+std::string contraction_key(const acltensorOperationDescriptor& op, const acltensorHandle* handle) {
+    char buf[256];
+    std::snprintf(buf, sizeof(buf), "c:%lld:%lld:%lld:a%d:b%d:d%d:c%d:sa%d:sb%d:sd%d:act%d:bias%d:g%d:bm%d:nm%d:st%d:sm%d",
+                  (long long)op.M, (long long)op.N, (long long)op.K, (int)op.descA->dataType, (int)op.descB->dataType,
+                  (int)op.descD->dataType, op.descC ? 1 : 0, op.scaleModeA, op.scaleModeB, op.scaleModeD, op.epilogueAct,
+                  op.biasType, op.groupCount, op.batchModes, op.bNMajor, op.bIsStatic,
+                  op.smLimit > 0 ? op.smLimit : (handle ? handle->smCount : 0));
+    return buf;
+}
+
+std::unique_ptr<acltensorOperationDescriptor> with_choice(const acltensorOperationDescriptor& op, const PlanChoice& c) {
+    std::unique_ptr<acltensorOperationDescriptor> t(new (std::nothrow) acltensorOperationDescriptor(op));
+    if (t) {
+        t->tileN = c.tileN;
+        t->ctaPair = c.ctaPair;
+        t->splitPolicy = c.splitPolicy;
+    }
+    return t;
+}
+
+// What a PATIENT plan times: the launch layer's own choice, then each tile shape and scheduler mode by itself.
+const PlanChoice kCandidates[] = {
+    {0, 0, ACLTENSOR_SPLIT_AUTO},          {256, 2, ACLTENSOR_SPLIT_AUTO},          {224, 2, ACLTENSOR_SPLIT_AUTO},
+    {128, 1, ACLTENSOR_SPLIT_AUTO},        {224, 1, ACLTENSOR_SPLIT_AUTO},          {0, 0, ACLTENSOR_SPLIT_DATA_PARALLEL},
+    {0, 0, ACLTENSOR_SPLIT_STREAM_K},
+};
+
+}  // namespace
+
 namespace acltensor {
 
-acltensorStatus_t FinishContractionPlan(acltensorPlan* plan, uint64_t workspaceSizeLimit) {
-    const acltensorOperationDescriptor& op = *plan->opDesc;
-    if (op.descA == nullptr || op.descB == nullptr || op.descD == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
-    auto solution = solution_for(op);
+acltensorStatus_t FinishContractionPlan(acltensorPlan* plan, uint64_t workspaceSizeLimit, const acltensorHandle* handle) {
+    const acltensorOperationDescriptor& caller_op = *plan->opDesc;
+    if (caller_op.descA == nullptr || caller_op.descB == nullptr || caller_op.descD == nullptr)
+        return ACLTENSOR_STATUS_INVALID_VALUE;
+    auto solution = solution_for(caller_op);
     if (!solution) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    plan->choice = PlanChoice{caller_op.tileN, caller_op.ctaPair, caller_op.splitPolicy};
+    // a descriptor that leaves tile shape and scheduler open may take them from the handle's plan cache, or have them
+    // timed at the first execution (PATIENT)
+    const bool open_choice = handle != nullptr && caller_op.tileN == 0 && caller_op.ctaPair == 0 &&
+                             caller_op.splitPolicy == ACLTENSOR_SPLIT_AUTO;
+    if (open_choice) {
+        plan->cache = handle->planCache;
+        plan->cacheKey = contraction_key(caller_op, handle);
+        PlanChoice cached;
+        if (plan->cache->find(plan->cacheKey, &cached)) {
+            auto tuned = with_choice(caller_op, cached);
+            uint64_t bytes = 0;
+            if (tuned && solution->workspaceSize(*tuned, cached.splitPolicy, &bytes) == ACLTENSOR_STATUS_SUCCESS &&
+                bytes <= workspaceSizeLimit) {
+                plan->tunedOp = std::move(tuned);
+                plan->choice = cached;
+            }
+        } else if (plan->pref->algo == ACLTENSOR_ALGO_DEFAULT_PATIENT) {
+            plan->needsTuning = true;
+        }
+    }
+    const acltensorOperationDescriptor& op = plan->tunedOp ? *plan->tunedOp : caller_op;
     int32_t policy = op.splitPolicy;
     uint64_t need = 0;
     acltensorStatus_t st = solution->workspaceSize(op, policy, &need);
@@ -480,8 +538,19 @@ acltensorStatus_t FinishContractionPlan(acltensorPlan* plan, uint64_t workspaceS
         }
     }
     if (need > workspaceSizeLimit) return ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE;
+    if (plan->needsTuning) {
+        // ask for enough workspace to try every candidate the limit allows
+        for (const PlanChoice& c : kCandidates) {
+            auto cand = with_choice(caller_op, c);
+            uint64_t bytes = 0;
+            if (cand && solution->workspaceSize(*cand, c.splitPolicy, &bytes) == ACLTENSOR_STATUS_SUCCESS &&
+                bytes <= workspaceSizeLimit && bytes > need)
+                need = bytes;
+        }
+    }
     plan->requiredWorkspace = need;
     plan->splitPolicy = policy;
+    plan->choice.splitPolicy = policy;
     plan->solution = solution;
     plan->pref->solution = solution;
     return ACLTENSOR_STATUS_SUCCESS;
@@ -524,7 +593,7 @@ acltensorStatus_t acltensorContract(const acltensorHandle_t handle, const aclten
     if (plan->requiredWorkspace > 0 && workspace == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
 
     ContractionArgs args;
-    args.op = op;
+    args.op = plan->tunedOp ? plan->tunedOp.get() : op;
     args.splitPolicy = plan->splitPolicy;
     args.A = A;
     args.B = B;
@@ -541,6 +610,51 @@ acltensorStatus_t acltensorContract(const acltensorHandle_t handle, const aclten
     args.reuseBPrepass = op->bIsStatic != 0 && plan->preparedB == B && plan->preparedScaleB == aux->scaleB &&
                          plan->preparedWorkspace == workspace && workspace != nullptr;
     auto solution = std::static_pointer_cast<ContractionSolution>(plan->solution);
+    if (plan->needsTuning) {
+        // PATIENT: time every candidate that is valid for this problem and fits the workspace given, keep the fastest.
+        // An in-place residual (C == D) would be added once per timed run, so such a call is left untuned.
+        plan->needsTuning = false;
+        void* timer = nullptr;
+        if (!(use_c && C == D) && blazeTimerCreate(&timer) == ACLTENSOR_STATUS_SUCCESS) {
+            float best_ms = 0.0f;
+            int best = -1;
+            std::unique_ptr<acltensorOperationDescriptor> best_op;
+            for (int i = 0; i < (int)(sizeof(kCandidates) / sizeof(kCandidates[0])); ++i) {
+                const PlanChoice& c = kCandidates[i];
+                auto cand = with_choice(*op, c);
+                uint64_t bytes = 0;
+                if (!cand || solution->workspaceSize(*cand, c.splitPolicy, &bytes) != ACLTENSOR_STATUS_SUCCESS ||
+                    bytes > workspaceSize)
+                    continue;
+                ContractionArgs trial = args;
+                trial.op = cand.get();
+                trial.splitPolicy = c.splitPolicy;
+                trial.reuseBPrepass = false;
+                if (solution->execute(trial) != ACLTENSOR_STATUS_SUCCESS) continue;      // warm-up, weight pre-pass
+                trial.reuseBPrepass = op->bIsStatic != 0 && workspace != nullptr;
+                float ms = 0.0f;
+                bool ok = blazeTimerStart(timer, stream) == ACLTENSOR_STATUS_SUCCESS;
+                for (int r = 0; r < 3 && ok; ++r) ok = solution->execute(trial) == ACLTENSOR_STATUS_SUCCESS;
+                ok = ok && blazeTimerStop(timer, stream, &ms) == ACLTENSOR_STATUS_SUCCESS;
+                if (ok && (best < 0 || ms < best_ms)) {
+                    best = i;
+                    best_ms = ms;
+                    best_op = std::move(cand);
+                }
+            }
+            blazeTimerDestroy(timer);
+            if (best >= 0) {
+                plan->choice = kCandidates[best];
+                plan->splitPolicy = kCandidates[best].splitPolicy;
+                plan->tunedOp = std::move(best_op);
+                if (plan->cache && !plan->cacheKey.empty()) plan->cache->insert(plan->cacheKey, plan->choice);
+                args.op = plan->tunedOp.get();
+                args.splitPolicy = plan->splitPolicy;
+            }
+        }
+        plan->preparedB = nullptr;                 // the workspace holds the last candidate's pre-pass, not ours
+        args.reuseBPrepass = false;
+    }
     const acltensorStatus_t st = solution->execute(args);
     if (st == ACLTENSOR_STATUS_SUCCESS) {
         plan->preparedB = B;

@@ -1,8 +1,11 @@
 // Handle, tensor descriptor, operation descriptor, plan preference, plan, error strings and version: the object
 // management half of the host API.  Behaviour per entry point follows the reference implementation cited beside
 // each function; the code is new.
+#include <cstdio>
 #include <cstring>
+#include <fstream>
 #include <new>
+#include <sstream>
 
 #include "blaze_b200.h"
 #include "cann_ops_tensor.h"
@@ -67,6 +70,56 @@ acltensorStatus_t acltensorCreate(acltensorHandle_t* handle) {
 
 acltensorStatus_t acltensorDestroy(acltensorHandle_t handle) {
     delete handle;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------------------ plan cache
+// The three entry points the reference reserves (lib/core/handle.cpp:105-108, docs/implementation.md:62-64).  The
+// file is text: a header line, then "<problem signature> <tileN> <ctaPair> <splitPolicy>" per entry, oldest first.
+
+static const char kPlanCacheMagic[] = "acltensor-plan-cache 1";
+
+acltensorStatus_t acltensorHandleResizePlanCache(acltensorHandle_t handle, const uint32_t numEntries) {
+    if (handle == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    handle->planCache->resize(numEntries);
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+acltensorStatus_t acltensorHandleWritePlanCacheToFile(const acltensorHandle_t handle, const char filename[]) {
+    if (handle == nullptr || filename == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    std::ofstream f(filename, std::ios::trunc);
+    if (!f) return ACLTENSOR_STATUS_IO_ERROR;
+    f << kPlanCacheMagic << "\n";
+    for (const auto& e : handle->planCache->snapshot())
+        f << e.first << ' ' << e.second.tileN << ' ' << e.second.ctaPair << ' ' << e.second.splitPolicy << "\n";
+    f.flush();
+    return f ? ACLTENSOR_STATUS_SUCCESS : ACLTENSOR_STATUS_IO_ERROR;
+}
+
+acltensorStatus_t acltensorHandleReadPlanCacheFromFile(acltensorHandle_t handle, const char filename[],
+                                                       uint32_t* numCachelinesRead) {
+    if (handle == nullptr || filename == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (numCachelinesRead) *numCachelinesRead = 0;
+    std::ifstream f(filename);
+    if (!f) return ACLTENSOR_STATUS_IO_ERROR;
+    std::string line;
+    if (!std::getline(f, line) || line != kPlanCacheMagic) return ACLTENSOR_STATUS_INVALID_VALUE;
+    // parse everything before touching the cache: a damaged file changes nothing
+    std::vector<std::pair<std::string, acltensor::PlanChoice>> entries;
+    while (std::getline(f, line)) {
+        if (line.empty()) continue;
+        std::istringstream in(line);
+        std::string key, rest;
+        acltensor::PlanChoice c;
+        if (!(in >> key >> c.tileN >> c.ctaPair >> c.splitPolicy) || (in >> rest)) return ACLTENSOR_STATUS_INVALID_VALUE;
+        const bool tile_ok = c.tileN == 0 || c.tileN == 128 || c.tileN == 224 || c.tileN == 256;
+        if (!tile_ok || c.ctaPair < 0 || c.ctaPair > 2 || c.splitPolicy < ACLTENSOR_SPLIT_AUTO ||
+            c.splitPolicy > ACLTENSOR_SPLIT_STREAM_K)
+            return ACLTENSOR_STATUS_INVALID_VALUE;
+        entries.emplace_back(key, c);
+    }
+    for (const auto& e : entries) handle->planCache->insert(e.first, e.second);
+    if (numCachelinesRead) *numCachelinesRead = static_cast<uint32_t>(entries.size());
     return ACLTENSOR_STATUS_SUCCESS;
 }
 
@@ -144,13 +197,14 @@ acltensorStatus_t acltensorDestroyOperationDescriptor(acltensorOperationDescript
 }
 
 // ------------------------------------------------------------------------------------------------ plan preference
-// reference: lib/core/plan_preference.cpp:22-56 (ALGO_DEFAULT only)
+// reference: lib/core/plan_preference.cpp:22-56 (ALGO_DEFAULT only; ALGO_DEFAULT_PATIENT is declared in its enum,
+// include/cann_ops_tensor_types.h:113, "more exact but slower choice": here a contraction plan times its candidates)
 
 acltensorStatus_t acltensorCreatePlanPreference(const acltensorHandle_t handle, acltensorPlanPreference_t* pref,
                                                 acltensorAlgo_t algo) {
     (void)handle;
     if (pref == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
-    if (algo != ACLTENSOR_ALGO_DEFAULT) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (algo != ACLTENSOR_ALGO_DEFAULT && algo != ACLTENSOR_ALGO_DEFAULT_PATIENT) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     acltensorPlanPreference* p = new (std::nothrow) acltensorPlanPreference();
     if (p == nullptr) return ACLTENSOR_STATUS_ALLOC_FAILED;
     p->algo = algo;
@@ -168,13 +222,12 @@ acltensorStatus_t acltensorDestroyPlanPreference(acltensorPlanPreference_t pref)
 // Contraction plans pick their solution here and apply the limit (see api_contraction.cpp).
 
 namespace acltensor {
-acltensorStatus_t FinishContractionPlan(acltensorPlan* plan, uint64_t workspaceSizeLimit);
+acltensorStatus_t FinishContractionPlan(acltensorPlan* plan, uint64_t workspaceSizeLimit, const acltensorHandle* handle);
 }
 
 acltensorStatus_t acltensorCreatePlan(const acltensorHandle_t handle, acltensorPlan_t* plan,
                                       const acltensorOperationDescriptor_t desc, const acltensorPlanPreference_t pref,
                                       uint64_t workspaceSizeLimit) {
-    (void)handle;
     if (plan == nullptr || desc == nullptr || pref == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (desc->operationType != acltensor::OperationType::ELEMENTWISE_BINARY &&
         desc->operationType != acltensor::OperationType::CONTRACTION)
@@ -185,7 +238,7 @@ acltensorStatus_t acltensorCreatePlan(const acltensorHandle_t handle, acltensorP
     p->pref = pref;
     p->requiredWorkspace = 0;
     if (desc->operationType == acltensor::OperationType::CONTRACTION) {
-        const acltensorStatus_t st = acltensor::FinishContractionPlan(p, workspaceSizeLimit);
+        const acltensorStatus_t st = acltensor::FinishContractionPlan(p, workspaceSizeLimit, handle);
         if (st != ACLTENSOR_STATUS_SUCCESS) {
             delete p;
             return st;
@@ -197,6 +250,16 @@ acltensorStatus_t acltensorCreatePlan(const acltensorHandle_t handle, acltensorP
 
 acltensorStatus_t acltensorDestroyPlan(acltensorPlan_t plan) {
     delete plan;      // operation descriptor and preference belong to the caller
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+acltensorStatus_t acltensorPlanGetKernelChoice(const acltensorPlan_t plan, int32_t* tileN, int32_t* ctaPair,
+                                               int32_t* splitPolicy, int32_t* pendingTuning) {
+    if (plan == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (tileN) *tileN = plan->choice.tileN;
+    if (ctaPair) *ctaPair = plan->choice.ctaPair;
+    if (splitPolicy) *splitPolicy = plan->choice.splitPolicy;
+    if (pendingTuning) *pendingTuning = plan->needsTuning ? 1 : 0;
     return ACLTENSOR_STATUS_SUCCESS;
 }
 

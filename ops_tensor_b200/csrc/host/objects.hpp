@@ -9,6 +9,9 @@
 #include <cstddef>
 #include <cstdint>
 #include <memory>
+#include <mutex>
+#include <string>
+#include <utility>
 #include <vector>
 
 #include "cann_ops_tensor_types.h"
@@ -56,7 +59,53 @@ acltensorStatus_t CheckComputeDescriptor(acltensorComputeDescriptor_t desc);
 
 }  // namespace acltensor
 
+namespace acltensor {
+
+// What a contraction plan may choose when the caller left it open: tile width, 1- or 2-CTA tiles, scheduler mode.
+struct PlanChoice {
+    int32_t tileN = 0, ctaPair = 0, splitPolicy = ACLTENSOR_SPLIT_AUTO;
+};
+
+// The handle's plan cache (the reference reserves acltensorHandleResizePlanCache / WritePlanCacheToFile /
+// ReadPlanCacheFromFile for it, lib/core/handle.cpp:105-108): problem signature -> choice, oldest entry evicted first.
+class PlanCache {
+public:
+    bool find(const std::string& key, PlanChoice* out) {
+        std::lock_guard<std::mutex> lock(m_);
+        for (const auto& e : entries_)
+            if (e.first == key) { *out = e.second; return true; }
+        return false;
+    }
+    void insert(const std::string& key, const PlanChoice& c) {
+        std::lock_guard<std::mutex> lock(m_);
+        for (auto& e : entries_)
+            if (e.first == key) { e.second = c; return; }
+        entries_.emplace_back(key, c);
+        trim();
+    }
+    void resize(uint32_t n) {
+        std::lock_guard<std::mutex> lock(m_);
+        capacity_ = n;
+        trim();
+    }
+    std::vector<std::pair<std::string, PlanChoice>> snapshot() {
+        std::lock_guard<std::mutex> lock(m_);
+        return entries_;
+    }
+
+private:
+    void trim() {
+        if (entries_.size() > capacity_) entries_.erase(entries_.begin(), entries_.end() - capacity_);
+    }
+    std::mutex m_;
+    uint32_t capacity_ = 64;
+    std::vector<std::pair<std::string, PlanChoice>> entries_;
+};
+
+}  // namespace acltensor
+
 struct acltensorHandle {
+    std::shared_ptr<acltensor::PlanCache> planCache = std::make_shared<acltensor::PlanCache>();
     int32_t deviceId = -1;      // CUDA device current at creation (-1: none visible)
     int32_t smCount = 0;
     int32_t ccMajor = 0, ccMinor = 0;
@@ -127,6 +176,13 @@ struct acltensorPlan {
     const void* preparedB = nullptr;              // B / scaleB / workspace whose pre-pass results are still valid
     const void* preparedScaleB = nullptr;
     const void* preparedWorkspace = nullptr;
+    // A choice taken from the handle's plan cache or found by timing (ALGO_DEFAULT_PATIENT) lives in a private copy of
+    // the operation descriptor with tile width and CTA pairing filled in; the caller's descriptor stays as it is.
+    std::unique_ptr<acltensorOperationDescriptor> tunedOp;
+    acltensor::PlanChoice choice;                 // what the plan runs with (0 / AUTO = left to the launch layer)
+    std::shared_ptr<acltensor::PlanCache> cache;  // the creating handle's cache (outlives the handle if need be)
+    std::string cacheKey;                         // empty: the caller fixed the choice, nothing to cache
+    bool needsTuning = false;                     // PATIENT plan that has not timed its candidates yet
 
     size_t getTotalElements() const { return opDesc ? opDesc->getTotalElements() : 0; }
 };

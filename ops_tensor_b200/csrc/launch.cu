@@ -833,6 +833,46 @@ extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
 
 // ------------------------------------------------------------------------------------------------ quantisers & misc
 
+namespace blaze {
+struct EventTimer {
+    cudaEvent_t begin, end;
+};
+}  // namespace blaze
+
+extern "C" int blazeTimerCreate(void** timer) {
+    if (!timer) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (!current_context()) return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    EventTimer* t = new (std::nothrow) EventTimer();
+    if (!t) return ACLTENSOR_STATUS_ALLOC_FAILED;
+    if (cudaEventCreate(&t->begin) != cudaSuccess) { delete t; return ACLTENSOR_STATUS_INTERNAL_ERROR; }
+    if (cudaEventCreate(&t->end) != cudaSuccess) { cudaEventDestroy(t->begin); delete t; return ACLTENSOR_STATUS_INTERNAL_ERROR; }
+    *timer = t;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+extern "C" int blazeTimerStart(void* timer, void* stream) {
+    if (!timer) return ACLTENSOR_STATUS_INVALID_VALUE;
+    return status_of(cudaEventRecord(static_cast<EventTimer*>(timer)->begin, static_cast<cudaStream_t>(stream)));
+}
+
+extern "C" int blazeTimerStop(void* timer, void* stream, float* milliseconds) {
+    if (!timer || !milliseconds) return ACLTENSOR_STATUS_INVALID_VALUE;
+    EventTimer* t = static_cast<EventTimer*>(timer);
+    cudaError_t e = cudaEventRecord(t->end, static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) e = cudaEventSynchronize(t->end);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(milliseconds, t->begin, t->end);
+    return status_of(e);
+}
+
+extern "C" int blazeTimerDestroy(void* timer) {
+    if (!timer) return ACLTENSOR_STATUS_SUCCESS;
+    EventTimer* t = static_cast<EventTimer*>(timer);
+    cudaEventDestroy(t->begin);
+    cudaEventDestroy(t->end);
+    delete t;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
 extern "C" int blazeQuantizeMx(const void* x, int64_t ldx, int32_t rows, int32_t K, int32_t elem, void* codes,
                                int64_t ld_codes, void* scales, void* stream) {
     if (rows < 0 || K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;

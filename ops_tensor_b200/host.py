@@ -33,6 +33,7 @@ STATUS_EXECUTION_FAILED = 13
 STATUS_INTERNAL_ERROR = 14
 STATUS_NOT_SUPPORTED = 15
 STATUS_INSUFFICIENT_WORKSPACE = 19
+STATUS_IO_ERROR = 21
 
 
 class ContractionAux(C.Structure):
@@ -63,6 +64,11 @@ _PROTOTYPES = {
     "acltensorOperationDescriptorGetAttribute": [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t],
     "acltensorEstimateWorkspaceSize": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_uint64)],
     "acltensorPlanGetRequiredWorkspace": [C.c_void_p, C.POINTER(C.c_uint64)],
+    "acltensorHandleResizePlanCache": [C.c_void_p, C.c_uint32],
+    "acltensorHandleWritePlanCacheToFile": [C.c_void_p, C.c_char_p],
+    "acltensorHandleReadPlanCacheFromFile": [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint32)],
+    "acltensorPlanGetKernelChoice": [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                     C.POINTER(C.c_int32)],
     "acltensorContract": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                           C.c_void_p, C.POINTER(ContractionAux), C.c_void_p, C.c_uint64, C.c_void_p],
     "acltensorQuantize": [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p,
@@ -122,6 +128,22 @@ def create_handle() -> C.c_void_p:
     h = C.c_void_p()
     check(api.acltensorCreate(C.byref(h)), "acltensorCreate")
     return h
+
+
+def resize_plan_cache(handle, entries: int) -> None:
+    check(api.acltensorHandleResizePlanCache(handle, entries), "acltensorHandleResizePlanCache")
+
+
+def write_plan_cache(handle, path: str) -> None:
+    check(api.acltensorHandleWritePlanCacheToFile(handle, str(path).encode()), "acltensorHandleWritePlanCacheToFile")
+
+
+def read_plan_cache(handle, path: str) -> int:
+    """Entries read from the file into the handle's plan cache."""
+    n = C.c_uint32(0)
+    check(api.acltensorHandleReadPlanCacheFromFile(handle, str(path).encode(), C.byref(n)),
+          "acltensorHandleReadPlanCacheFromFile")
+    return n.value
 
 
 def create_tensor_descriptor(handle, lens, strides=None, dtype=R_32F, align=256) -> C.c_void_p:
@@ -187,9 +209,11 @@ class Contraction:
     def __init__(self, M, N, K, *, scale_mode_a, scale_mode_b, b_dtype=R_8F_E4M3, groups=0, activation=OP_IDENTITY,
                  bias=False, residual=False, split=SPLIT_AUTO, tile_n=0, sm_limit=0, b_is_static=False, cta_pair=0,
                  lda=None, ldb=None, ldd=None, ldc=None, workspace_limit=2 ** 62, batch=(), batch_a=None, batch_b=None,
-                 bias_per_batch=False, a_dtype=R_8F_E4M3, d_dtype=R_16BF):
+                 bias_per_batch=False, a_dtype=R_8F_E4M3, d_dtype=R_16BF, handle=None, algo=ALGO_DEFAULT):
         self.M, self.N, self.K, self.groups = M, N, K, groups
-        self.handle = create_handle()
+        # a handle passed in is shared (its plan cache with it) and stays the caller's to destroy
+        self._own_handle = handle is None
+        self.handle = create_handle() if handle is None else handle
         self._descs = []
         m, n, k, g = 0, 1, 2, 3
         lda = lda or K
@@ -250,7 +274,7 @@ class Contraction:
             set_attribute(self.handle, self.op, ATTR_B_IS_STATIC, 1)
         if cta_pair:
             set_attribute(self.handle, self.op, ATTR_CTA_PAIR, cta_pair)
-        check(api.acltensorCreatePlanPreference(self.handle, C.byref(self.pref), ALGO_DEFAULT),
+        check(api.acltensorCreatePlanPreference(self.handle, C.byref(self.pref), algo),
               "acltensorCreatePlanPreference")
         check(api.acltensorCreatePlan(self.handle, C.byref(self.plan), self.op, self.pref, workspace_limit),
               "acltensorCreatePlan")
@@ -277,6 +301,13 @@ class Contraction:
                                     workspace.numel() if workspace is not None else 0, stream), "acltensorContract")
         return out
 
+    def kernel_choice(self):
+        """(tile_n, cta_pair, split policy, tuning still pending) of the plan; 0 = left to the launch layer."""
+        t, p, s, pend = C.c_int32(0), C.c_int32(0), C.c_int32(0), C.c_int32(0)
+        check(api.acltensorPlanGetKernelChoice(self.plan, C.byref(t), C.byref(p), C.byref(s), C.byref(pend)),
+              "acltensorPlanGetKernelChoice")
+        return t.value, p.value, s.value, bool(pend.value)
+
     def close(self):
         api.acltensorDestroyPlan(self.plan)
         api.acltensorDestroyPlanPreference(self.pref)
@@ -284,7 +315,8 @@ class Contraction:
         for d in (self.dA, self.dB, self.dD, self.dC):
             if d is not None:
                 api.acltensorDestroyTensorDescriptor(d)
-        api.acltensorDestroy(self.handle)
+        if self._own_handle:
+            api.acltensorDestroy(self.handle)
         self.plan = self.pref = self.op = self.handle = None
 
     def __enter__(self):

@@ -90,7 +90,11 @@ def test_elementwise_descriptor_checks(api):
 
     pref, plan = C.c_void_p(), C.c_void_p()
     assert api.acltensorCreatePlanPreference(h, None, H.ALGO_DEFAULT) == H.STATUS_INVALID_VALUE
-    assert api.acltensorCreatePlanPreference(h, C.byref(pref), H.ALGO_DEFAULT_PATIENT) == H.STATUS_NOT_SUPPORTED
+    # the reference accepts ALGO_DEFAULT only (lib/core/plan_preference.cpp:34-36); here the PATIENT value of its enum is
+    # accepted too (contraction plans time their candidates), anything else is refused as there
+    assert api.acltensorCreatePlanPreference(h, C.byref(pref), -2) == H.STATUS_NOT_SUPPORTED
+    assert api.acltensorCreatePlanPreference(h, C.byref(pref), H.ALGO_DEFAULT_PATIENT) == H.STATUS_SUCCESS
+    assert api.acltensorDestroyPlanPreference(pref) == H.STATUS_SUCCESS
     assert api.acltensorCreatePlanPreference(h, C.byref(pref), H.ALGO_DEFAULT) == H.STATUS_SUCCESS
     assert api.acltensorCreatePlan(h, None, op, pref, 0) == H.STATUS_INVALID_VALUE
     assert api.acltensorCreatePlan(h, C.byref(plan), None, pref, 0) == H.STATUS_INVALID_VALUE
@@ -455,3 +459,82 @@ def test_peer_outputs_are_validated_at_plan_time(built_library):
         assert lib.blazeFp8GemmWorkspaceSize(C.byref(f), C.byref(n)) == want
         assert want != H.STATUS_SUCCESS or n.value == 0
 
+
+
+def test_plan_cache_file_round_trip_and_lookup(built_library, tmp_path):
+    """The handle's plan cache (names reserved by the reference, lib/core/handle.cpp:105-108): entries read from a file
+    decide the kernel choice of plans that leave it open, survive a write / read round trip, are evicted oldest first,
+    and a damaged file changes nothing."""
+    mx = H.SCALE_MX_E8M0_VEC32
+    h = H.create_handle()
+    try:
+        base = H.Contraction(8192, 8192, 8192, scale_mode_a=mx, scale_mode_b=mx, handle=h)
+        assert base.kernel_choice() == (0, 0, H.SPLIT_AUTO, False)
+        default_bytes = base.workspace_bytes
+        base.close()
+        # learn the signature the library uses for this problem from a PATIENT plan's cache key: write an empty cache,
+        # then a hand-made one with the same key format
+        H.write_plan_cache(h, tmp_path / "empty.txt")
+        assert (tmp_path / "empty.txt").read_text() == "acltensor-plan-cache 1\n"
+        key = "c:8192:8192:8192:a%d:b%d:d%d:c0:sa%d:sb%d:sd0:act%d:bias-1:g0:bm0:nm0:st0:sm0" % (
+            H.R_8F_E4M3, H.R_8F_E4M3, H.R_16BF, mx, mx, H.OP_IDENTITY)
+        (tmp_path / "one.txt").write_text("acltensor-plan-cache 1\n%s 224 2 %d\n" % (key, H.SPLIT_DATA_PARALLEL))
+        assert H.read_plan_cache(h, tmp_path / "one.txt") == 1
+        tuned = H.Contraction(8192, 8192, 8192, scale_mode_a=mx, scale_mode_b=mx, handle=h)
+        assert tuned.kernel_choice() == (224, 2, H.SPLIT_DATA_PARALLEL, False)
+        forced = H.Contraction(8192, 8192, 8192, scale_mode_a=mx, scale_mode_b=mx, handle=h, tile_n=224, cta_pair=2)
+        assert tuned.workspace_bytes == forced.workspace_bytes != default_bytes
+        # a descriptor that fixes its own choice ignores the cache; another problem misses it
+        assert forced.kernel_choice()[:2] == (224, 2)
+        other = H.Contraction(4096, 8192, 8192, scale_mode_a=mx, scale_mode_b=mx, handle=h)
+        assert other.kernel_choice() == (0, 0, H.SPLIT_AUTO, False)
+        for c in (tuned, forced, other):
+            c.close()
+        # round trip into a second handle
+        H.write_plan_cache(h, tmp_path / "copy.txt")
+        h2 = H.create_handle()
+        assert H.read_plan_cache(h2, tmp_path / "copy.txt") == 1
+        again = H.Contraction(8192, 8192, 8192, scale_mode_a=mx, scale_mode_b=mx, handle=h2)
+        assert again.kernel_choice() == (224, 2, H.SPLIT_DATA_PARALLEL, False)
+        again.close()
+        # capacity: the oldest entry goes first
+        (tmp_path / "two.txt").write_text("acltensor-plan-cache 1\nk1 128 1 0\nk2 256 2 0\n")
+        H.resize_plan_cache(h2, 2)
+        assert H.read_plan_cache(h2, tmp_path / "two.txt") == 2
+        H.write_plan_cache(h2, tmp_path / "after.txt")
+        assert (tmp_path / "after.txt").read_text().splitlines()[1:] == ["k1 128 1 0", "k2 256 2 0"]
+        # damaged or missing files
+        (tmp_path / "bad1.txt").write_text("something else\n")
+        (tmp_path / "bad2.txt").write_text("acltensor-plan-cache 1\nk3 100 1 0\n")
+        (tmp_path / "bad3.txt").write_text("acltensor-plan-cache 1\nk3 128 1\n")
+        for name in ("bad1.txt", "bad2.txt", "bad3.txt"):
+            with pytest.raises(native.BlazeError) as e:
+                H.read_plan_cache(h2, tmp_path / name)
+            assert e.value.status == H.STATUS_INVALID_VALUE
+        with pytest.raises(native.BlazeError) as e:
+            H.read_plan_cache(h2, tmp_path / "missing.txt")
+        assert e.value.status == H.STATUS_IO_ERROR
+        H.write_plan_cache(h2, tmp_path / "still.txt")
+        assert (tmp_path / "still.txt").read_text().splitlines()[1:] == ["k1 128 1 0", "k2 256 2 0"]
+        H.api.acltensorDestroy(h2)
+    finally:
+        H.api.acltensorDestroy(h)
+
+
+def test_patient_preference_marks_the_plan_for_tuning(built_library):
+    """ALGO_DEFAULT_PATIENT (include/cann_ops_tensor_types.h:113): accepted; a contraction plan with an open choice and
+    no cached entry waits to time its candidates at the first execution and asks for the workspace of the hungriest one."""
+    mx = H.SCALE_MX_E8M0_VEC32
+    h = H.create_handle()
+    try:
+        quick = H.Contraction(256, 7168, 4096, scale_mode_a=mx, scale_mode_b=mx, handle=h)
+        patient = H.Contraction(256, 7168, 4096, scale_mode_a=mx, scale_mode_b=mx, handle=h, algo=H.ALGO_DEFAULT_PATIENT)
+        assert quick.kernel_choice()[3] is False and patient.kernel_choice()[3] is True
+        assert patient.workspace_bytes >= quick.workspace_bytes
+        fixed = H.Contraction(256, 7168, 4096, scale_mode_a=mx, scale_mode_b=mx, handle=h, algo=H.ALGO_DEFAULT_PATIENT,
+                              tile_n=128, cta_pair=1)
+        assert fixed.kernel_choice() == (128, 1, H.SPLIT_AUTO, False)          # nothing left open, nothing to tune
+        for c in (quick, patient, fixed):
+            c.close()
+    finally:
+        H.api.acltensorDestroy(h)
