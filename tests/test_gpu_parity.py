@@ -837,3 +837,62 @@ def test_config3_w4a8_4096x14336x4096(cuda_device):
     cols = np.arange(0, N, 61)
     rb, rsb = o.quant_mx(w[cols], "e2m1")
     assert np.array_equal(qb[cols], rb) and np.array_equal(sb[cols], rsb)
+
+
+# ------------------------------------------------------------------------------------------------ plan cache / PATIENT
+
+def test_patient_plan_times_candidates_and_fills_the_cache(cuda_device, tmp_path):
+    """An ALGO_DEFAULT_PATIENT plan times its candidate configurations during its first execution, keeps one, stores it
+    in the handle's plan cache; results stay within the acceptance bounds whichever candidate wins, and a default plan
+    for the same problem on the same handle then runs with the cached choice and gives the same bits."""
+    import torch
+    M, N, K = 512, 1024, 1024
+    mx = H.SCALE_MX_E8M0_VEC32
+    a = o.normal_f32(21, 0, (M, K), 1.0)
+    w = o.normal_f32(21, 1, (N, K), 1.0)
+    bias = o.normal_f32(21, 2, (N,), 0.1)
+    qa, sa = H.quantize(dev_tensor(a, cuda_device), mx)
+    qb, sb = H.quantize(dev_tensor(w, cuda_device), mx)
+    bias_d = bf16_tensor(bias, cuda_device)
+    ref, gold = mx_reference(to_np(qa), to_np(sa), to_np(qb), to_np(sb), K, act=o.ACT_GELU_TANH, bias=bias)
+    h = H.create_handle()
+    try:
+        patient = H.Contraction(M, N, K, scale_mode_a=mx, scale_mode_b=mx, activation=H.OP_GELU, bias=True, handle=h,
+                                algo=H.ALGO_DEFAULT_PATIENT, b_is_static=True)
+        assert patient.kernel_choice()[3] is True
+        out1 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+        patient(qa, sa, qb, sb, out1, bias=bias_d)
+        torch.cuda.synchronize()
+        tile_n, cta_pair, split, pending = patient.kernel_choice()
+        assert pending is False and (tile_n, cta_pair) in ((0, 0), (256, 2), (224, 2), (128, 1), (224, 1))
+        assert_gemm_ok(to_np(out1), ref, gold)
+        out2 = torch.full_like(out1, float("nan"))
+        patient(qa, sa, qb, sb, out2, bias=bias_d)                      # second call: no timing, weight pre-pass reused
+        torch.cuda.synchronize()
+        assert torch.equal(out1.view(torch.int16), out2.view(torch.int16))
+        H.write_plan_cache(h, tmp_path / "cache.txt")
+        lines = (tmp_path / "cache.txt").read_text().splitlines()
+        assert len(lines) == 2 and lines[1].endswith(" %d %d %d" % (tile_n, cta_pair, split))
+        quick = H.Contraction(M, N, K, scale_mode_a=mx, scale_mode_b=mx, activation=H.OP_GELU, bias=True, handle=h,
+                              b_is_static=True)
+        assert quick.kernel_choice() == (tile_n, cta_pair, split, False)
+        out3 = torch.full_like(out1, float("nan"))
+        quick(qa, sa, qb, sb, out3, bias=bias_d)
+        torch.cuda.synchronize()
+        assert torch.equal(out1.view(torch.int16), out3.view(torch.int16))
+        # the FP8 family has scheduler modes to choose from
+        af, wf = fp8_problem(22, 128, 1024, 2048)
+        qaf, saf = H.quantize(dev_tensor(af, cuda_device), H.SCALE_FP32_1X128)
+        qbf, sbf = H.quantize(dev_tensor(wf, cuda_device), H.SCALE_FP32_128X128)
+        p8 = H.Contraction(128, 1024, 2048, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128, handle=h,
+                           algo=H.ALGO_DEFAULT_PATIENT)
+        out8 = torch.full((128, 1024), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+        p8(qaf, saf, qbf, sbf, out8)
+        torch.cuda.synchronize()
+        assert p8.kernel_choice()[3] is False
+        ref8, gold8 = fp8_reference(to_np(qaf), to_np(saf), to_np(qbf), to_np(sbf))
+        assert_gemm_ok(to_np(out8), ref8, gold8)
+        for c in (patient, quick, p8):
+            c.close()
+    finally:
+        H.api.acltensorDestroy(h)
