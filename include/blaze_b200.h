@@ -136,7 +136,8 @@ BLAZE_API int blazeMxGemm(const blazeMxGemmArgs* args, void* stream);
  * args->workspace and args->workspace_bytes are ignored: the re-tiled scale factors live in a fixed 8 MiB array that
  * is part of the library image (every GPU that loads the library holds those 8 MiB until the process exits).  The
  * call allocates nothing and frees nothing.  Limits and rules:
- *   - B must be BLAZE_ELEM_E4M3 (packed E2M1 would need an N x K expansion buffer): NOT_SUPPORTED otherwise;
+ *   - B must be BLAZE_ELEM_E4M3 (packed E2M1 would need an N x K expansion buffer) and K-major (an N-major B would
+ *     need a transposed copy): NOT_SUPPORTED otherwise; stream-K and peer outputs are not offered either;
  *   - a problem whose re-tiled scales exceed 8 MiB - about 512*(ceil(M/128) + 2*ceil(N/224))*ceil(K/128) bytes, e.g.
  *     M = N = K = 8192 needs 4.4 MiB - is refused with ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE before anything runs
  *     (blazeMxGemm keeps four copies of B's scale blocks on 2-CTA tiles to save a tensor-pipe copy per K step; this
@@ -147,7 +148,8 @@ BLAZE_API int blazeMxGemm(const blazeMxGemmArgs* args, void* stream);
  *     uses, so calls must not overlap on the GPU (use one stream, or order them with events) - overlapping calls race;
  *   - reuse_b_prepass is ignored (the weight's scale tiles are rebuilt every call).
  * device_status is an optional device pointer to a zero-initialised int32 that receives the code of a kernel wait
- * that gave up (see blazeDeviceStatus); NULL keeps that code in a word inside the library.
+ * that gave up (see blazeDeviceStatus); with NULL the code goes to a word inside the library, which blazeDeviceStatus /
+ * acltensorGetDeviceStatus report (and reset) together with the status of the other entry points.
  */
 BLAZE_API int blazeMxGemmNoAlloc(const blazeMxGemmArgs* args, int32_t* device_status, void* stream);
 
@@ -234,7 +236,8 @@ BLAZE_API int blazeQuantizeFp8Blocks(const void* w, int64_t ldw, int32_t N, int3
 BLAZE_API int blazeAddF32(const void* A, const void* C, void* D, int64_t n, void* stream);
 
 /* Device status word of the current device: 0 while every kernel wait completed, else the code of the first
- * wait that gave up (see DeviceStatus in csrc/ptx.cuh).  Synchronises the device.  reset != 0 clears it. */
+ * wait that gave up (see DeviceStatus in csrc/ptx.cuh), including waits inside blazeMxGemmNoAlloc calls that were given
+ * no status pointer.  Synchronises the device.  reset != 0 clears it. */
 BLAZE_API int blazeDeviceStatus(int32_t* value, int32_t reset);
 
 /* Diagnostic of the failure-reporting path (no counterpart in the reference): launches one CTA that waits, for at most
@@ -244,6 +247,10 @@ BLAZE_API int blazeSelfTestWaitTimeout(int64_t limit_cycles, void* stream);
 
 /* SM count and compute capability of the current device (the handle's device query). */
 BLAZE_API int blazeDeviceInfo(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor);
+
+/* Ordinal of the CUDA device current in the calling thread: what a handle binds to at acltensorCreate (the role of
+ * the reference's platform query in lib/core/handle.cpp:75-92). */
+BLAZE_API int blazeCurrentDevice(int32_t* device);
 
 #ifdef __cplusplus
 }

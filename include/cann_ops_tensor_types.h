@@ -134,7 +134,9 @@ typedef enum {
     ACLTENSOR_OPERATION_DESCRIPTOR_TILE_N = 7,           /* int32: 0 = heuristic */
     ACLTENSOR_OPERATION_DESCRIPTOR_SM_LIMIT = 8,         /* int32: 0 = all SMs */
     ACLTENSOR_OPERATION_DESCRIPTOR_B_IS_STATIC = 9,      /* int32: 1 = B and its scales do not change between calls,
-                                                            so weight pre-passes kept in the workspace are reused */
+                                                            so weight pre-passes kept in the workspace are reused
+                                                            while this plan was the last one to use that workspace
+                                                            (another plan's call on the same buffer re-runs them) */
     ACLTENSOR_OPERATION_DESCRIPTOR_SCALE_MODE_D = 12,    /* acltensorScaleMode_t of a quantised D (dtype R_8F_E4M3): must equal SCALE_MODE_A; scales go to aux->scaleD */
     ACLTENSOR_OPERATION_DESCRIPTOR_BIAS_PER_BATCH = 11,  /* int32: 1 = bias is [batches][N] (batched contraction) */
     ACLTENSOR_OPERATION_DESCRIPTOR_CTA_PAIR = 10,        /* int32: 0 = heuristic, 1 = single-CTA tiles, 2 = 2-CTA 256-row tiles */

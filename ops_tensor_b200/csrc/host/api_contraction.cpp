@@ -5,11 +5,14 @@
 // The entry-point names are the ones the reference reserves (lib/core/operation_descriptor.cpp:183-189,
 // lib/core/plan_preference.cpp:58, docs/implementation.md:57-74); argument checking follows the conventions of its
 // implemented entry points: NULL required argument -> INVALID_VALUE, anything the build cannot do -> NOT_SUPPORTED.
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <memory>
+#include <mutex>
 #include <new>
 #include <string>
+#include <vector>
 
 #include "blaze_b200.h"
 #include "cann_ops_tensor.h"
@@ -560,13 +563,52 @@ acltensorStatus_t FinishContractionPlan(acltensorPlan* plan, uint64_t workspaceS
 
 // ------------------------------------------------------------------------------------------------ execution
 
+namespace {
+
+// Which plan wrote into a workspace buffer last.  A plan with B_IS_STATIC keeps its weight's pre-pass (re-tiled scales,
+// expanded or transposed codes) in the workspace between calls; if another plan has used the same buffer in between
+// (one workspace shared by several plans, as callers of BLAS-style libraries do), those bytes are gone and the
+// pre-pass must run again.  Small table, most recently used last.
+std::mutex g_workspace_mutex;
+std::vector<std::pair<const void*, uint64_t>> g_workspace_user;
+std::atomic<uint64_t> g_next_plan_stamp{1};
+
+bool workspace_last_used_by(const void* workspace, uint64_t stamp) {
+    std::lock_guard<std::mutex> lock(g_workspace_mutex);
+    for (const auto& e : g_workspace_user)
+        if (e.first == workspace) return e.second == stamp;
+    return false;
+}
+
+void note_workspace_user(const void* workspace, uint64_t stamp) {
+    if (workspace == nullptr) return;
+    std::lock_guard<std::mutex> lock(g_workspace_mutex);
+    for (size_t i = 0; i < g_workspace_user.size(); ++i) {
+        if (g_workspace_user[i].first == workspace) {
+            g_workspace_user.erase(g_workspace_user.begin() + static_cast<std::ptrdiff_t>(i));
+            break;
+        }
+    }
+    g_workspace_user.emplace_back(workspace, stamp);
+    // a buffer that fell out of the table simply runs its pre-pass again
+    if (g_workspace_user.size() > 256) g_workspace_user.erase(g_workspace_user.begin());
+}
+
+}  // namespace
+
 acltensorStatus_t acltensorContract(const acltensorHandle_t handle, const acltensorPlan_t plan, const void* alpha,
                                     const void* A, const void* B, const void* beta, const void* C, void* D,
                                     const acltensorContractionAux_t* aux, void* workspace, uint64_t workspaceSize,
                                     aclrtStream stream) {
-    (void)handle;
     if (plan == nullptr || A == nullptr || B == nullptr || D == nullptr || aux == nullptr)
         return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (handle != nullptr && handle->deviceId >= 0) {
+        // a handle is bound to the device that was current when it was created; a call made with another device
+        // current would launch there with this handle's SM count and plan cache
+        int32_t device = -1;
+        if (blazeCurrentDevice(&device) == ACLTENSOR_STATUS_SUCCESS && device != handle->deviceId)
+            return ACLTENSOR_STATUS_INVALID_VALUE;
+    }
     acltensorOperationDescriptor* op = plan->opDesc;
     if (op == nullptr || plan->pref == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (op->operationType != OperationType::CONTRACTION) return ACLTENSOR_STATUS_NOT_SUPPORTED;
@@ -607,8 +649,11 @@ acltensorStatus_t acltensorContract(const acltensorHandle_t handle, const aclten
     args.workspace = workspace;
     args.workspaceSize = workspaceSize;
     args.stream = stream;
+    if (plan->stamp == 0) plan->stamp = g_next_plan_stamp.fetch_add(1);
     args.reuseBPrepass = op->bIsStatic != 0 && plan->preparedB == B && plan->preparedScaleB == aux->scaleB &&
-                         plan->preparedWorkspace == workspace && workspace != nullptr;
+                         plan->preparedWorkspace == workspace && workspace != nullptr &&
+                         workspace_last_used_by(workspace, plan->stamp);
+    note_workspace_user(workspace, plan->stamp);
     auto solution = std::static_pointer_cast<ContractionSolution>(plan->solution);
     if (plan->needsTuning) {
         // PATIENT: time every candidate that is valid for this problem and fits the workspace given, keep the fastest.

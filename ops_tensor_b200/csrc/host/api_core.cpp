@@ -56,8 +56,10 @@ acltensorStatus_t acltensorCreate(acltensorHandle_t* handle) {
     acltensorHandle* h = new (std::nothrow) acltensorHandle();
     if (h == nullptr) return ACLTENSOR_STATUS_ALLOC_FAILED;
     int32_t sms = 0, major = 0, minor = 0;
-    if (blazeDeviceInfo(&sms, &major, &minor) == ACLTENSOR_STATUS_SUCCESS) {
-        h->deviceId = 0;
+    int32_t device = -1;
+    if (blazeDeviceInfo(&sms, &major, &minor) == ACLTENSOR_STATUS_SUCCESS &&
+        blazeCurrentDevice(&device) == ACLTENSOR_STATUS_SUCCESS) {
+        h->deviceId = device;               // the handle belongs to the device that is current now
         h->smCount = sms;
         h->ccMajor = major;
         h->ccMinor = minor;

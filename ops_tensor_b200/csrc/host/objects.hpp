@@ -176,6 +176,7 @@ struct acltensorPlan {
     const void* preparedB = nullptr;              // B / scaleB / workspace whose pre-pass results are still valid
     const void* preparedScaleB = nullptr;
     const void* preparedWorkspace = nullptr;
+    uint64_t stamp = 0;                           // unique per plan, given at its first contraction call (0 = none yet)
     // A choice taken from the handle's plan cache or found by timing (ALGO_DEFAULT_PATIENT) lives in a private copy of
     // the operation descriptor with tile width and CTA pairing filled in; the caller's descriptor stays as it is.
     std::unique_ptr<acltensorOperationDescriptor> tunedOp;

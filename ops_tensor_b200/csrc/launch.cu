@@ -507,8 +507,11 @@ extern "C" int blazeMxGemm(const blazeMxGemmArgs* a, void* stream_v) {
     const uint8_t* b_codes = static_cast<const uint8_t*>(a->B);
     int64_t b_pitch = a->ldb;
 
+    // the kernel that re-tiles A's scales runs on every call: it also clears the stream-K fix-up flags, which the GEMM
+    // expects at zero and which still hold the previous call's marks (or whatever the workspace held before)
     cudaError_t e = launch_sf_retile(static_cast<const uint8_t*>(a->scaleA), a->M, a->K, 128, 1, sfa_tiled, ctx->sm_count,
-                                     stream);
+                                     stream, pl.stream_k ? reinterpret_cast<int*>(ws + pl.flags_off) : nullptr,
+                                     (int)(pl.flags_bytes / 4));
     if (e != cudaSuccess) return status_of(e);
     // A packed E2M1 weight is fed to the tensor core as it is when TMA can unpack it (whole 128-code boxes along K,
     // 32-byte aligned rows); otherwise it is expanded once to one-byte E4M3 codes of the same values.
@@ -619,7 +622,10 @@ extern "C" int blazeMxGemmBatched(const blazeMxGemmArgs* args, const blazeBatchD
     const int64_t scale_cols = ((int64_t)(args->K + 63) / 64) * 2;
     const int64_t a_bytes = (int64_t)args->M * args->lda, sa_bytes = (int64_t)args->M * scale_cols;
     const int64_t b_bytes = (int64_t)args->N * args->ldb, sb_bytes = (int64_t)args->N * scale_cols;
-    const int64_t d_bytes = (int64_t)args->M * args->ldd * 2, r_bytes = (int64_t)args->M * args->ldr * 2;
+    // D's element size follows its type; a quantised D also advances its scale rows batch by batch
+    const int64_t d_elem = args->d_type == BLAZE_OUT_F32 ? 4 : (args->d_type == BLAZE_OUT_MX_E4M3 ? 1 : 2);
+    const int64_t d_bytes = (int64_t)args->M * args->ldd * d_elem, r_bytes = (int64_t)args->M * args->ldr * 2;
+    const int64_t sd_bytes = (int64_t)args->M * (((int64_t)args->N + 63) / 64) * 2;
     // strides of the operands' own batch spaces, innermost dimension last
     long long stride_a[4], stride_b[4];
     long long sa = 1, sb = 1;
@@ -642,6 +648,7 @@ extern "C" int blazeMxGemmBatched(const blazeMxGemmArgs* args, const blazeBatchD
                     one.B = static_cast<const uint8_t*>(args->B) + ib * b_bytes;
                     one.scaleB = static_cast<const uint8_t*>(args->scaleB) + ib * sb_bytes;
                     one.D = static_cast<uint8_t*>(args->D) + ic * d_bytes;
+                    if (args->scaleD) one.scaleD = static_cast<uint8_t*>(args->scaleD) + ic * sd_bytes;
                     if (args->residual) one.residual = static_cast<const uint8_t*>(args->residual) + ic * r_bytes;
                     if (args->bias && bd->bias_per_batch)
                         one.bias = static_cast<const uint8_t*>(args->bias) + ic * (int64_t)args->N * 2;
@@ -931,6 +938,12 @@ extern "C" int blazeAddF32(const void* A, const void* C, void* D, int64_t n, voi
                                     n, ctx->sm_count, static_cast<cudaStream_t>(stream)));
 }
 
+namespace blaze {
+// Status word of the allocation-free entry point on device `dev` (it lives in the library image, not in the
+// context's allocation): 0 if that entry has not run on the device.  Defined with the entry point below.
+static int noalloc_status_fetch(int dev, bool reset);
+}  // namespace blaze
+
 extern "C" int blazeDeviceStatus(int32_t* value, int32_t reset) {
     if (!value) return ACLTENSOR_STATUS_INVALID_VALUE;
     DeviceContext* ctx = current_context();
@@ -938,8 +951,10 @@ extern "C" int blazeDeviceStatus(int32_t* value, int32_t reset) {
     int v = 0;
     if (cudaMemcpy(&v, ctx->status_word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
         return status_of(cudaErrorUnknown);
-    *value = v;
     if (reset && v != 0) cudaMemset(ctx->status_word, 0, sizeof(int));
+    // calls of blazeMxGemmNoAlloc that were given no status pointer report here as well
+    const int w = noalloc_status_fetch(ctx->device, reset != 0);
+    *value = v != 0 ? v : w;
     return ACLTENSOR_STATUS_SUCCESS;
 }
 
@@ -975,6 +990,17 @@ extern "C" int blazeDeviceInfo(int32_t* sm_count, int32_t* cc_major, int32_t* cc
     if (sm_count) *sm_count = ctx->sm_count;
     if (cc_major) *cc_major = ctx->cc_major;
     if (cc_minor) *cc_minor = ctx->cc_minor;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+extern "C" int blazeCurrentDevice(int32_t* device) {
+    if (!device) return ACLTENSOR_STATUS_INVALID_VALUE;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    }
+    *device = dev;
     return ACLTENSOR_STATUS_SUCCESS;
 }
 
@@ -1033,6 +1059,22 @@ static int noalloc_setup(NoAllocDevice** out) {
     }
     *out = &d;
     return ACLTENSOR_STATUS_SUCCESS;
+}
+
+static int noalloc_status_fetch(int dev, bool reset) {
+    int* word = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (dev < 0 || dev >= 64 || !g_noalloc[dev].ready) return 0;
+        word = g_noalloc[dev].status;
+    }
+    int v = 0;
+    if (cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    if (reset && v != 0) cudaMemset(word, 0, sizeof(int));
+    return v;
 }
 
 }  // namespace blaze

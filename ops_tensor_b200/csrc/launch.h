@@ -32,8 +32,9 @@ cudaError_t launch_quant_fp8_1x128(const float* x, long long ldx, int rows, int 
                                    float* scales, int sm_count, cudaStream_t stream);
 cudaError_t launch_quant_fp8_128x128(const float* w, long long ldw, int N, int K, uint8_t* codes, long long ldc,
                                      float* scales, int sm_count, cudaStream_t stream);
+// `zero_ptr` / `zero_words`: 32-bit words the same kernel also clears (the stream-K flags of the GEMM that follows).
 cudaError_t launch_sf_retile(const uint8_t* in, int rows, int K, int tile_rows, int replicas, uint8_t* out,
-                             int sm_count, cudaStream_t stream);
+                             int sm_count, cudaStream_t stream, int* zero_ptr = nullptr, int zero_words = 0);
 cudaError_t launch_e2m1_expand(const uint8_t* in, long long ld_in, int rows, int K, uint8_t* out, long long ld_out,
                                int sm_count, cudaStream_t stream);
 // Pre-pass for a B stored [K][N] (N contiguous): its transpose [N][K] and its scales as rows [N][ceil(K/64)*2].

@@ -218,7 +218,8 @@ __global__ void __launch_bounds__(256) quant_fp8_128x128_kernel(const float* __r
 // or 4 where the kernel copies the block into TMEM without the lane broadcast (one copy per 32-lane quadrant).
 __global__ void __launch_bounds__(256) sf_retile_kernel(const uint8_t* __restrict__ in, int rows, int scale_cols,
                                                         int valid_groups, int tile_rows, int k_steps, int replicas,
-                                                        uint32_t* __restrict__ out, long long out_words) {
+                                                        uint32_t* __restrict__ out, long long out_words,
+                                                        int* __restrict__ zero_ptr, int zero_words) {
     const int atoms = (tile_rows + 127) >> 7;
     // the GEMM that follows may set itself up (barriers, TMEM, descriptors) while this kernel runs; it waits for this
     // grid to finish before it loads the first scale block
@@ -226,6 +227,8 @@ __global__ void __launch_bounds__(256) sf_retile_kernel(const uint8_t* __restric
     // launched with programmatic stream serialisation itself: the previous kernel in the stream (a GEMM that reads
     // these tiles, or the producer of the scales) must have finished before anything is read or written
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // side job for the GEMM behind this kernel: its stream-K fix-up flags start at zero
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < zero_words; i += gridDim.x * blockDim.x) zero_ptr[i] = 0;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < out_words;
          i += (long long)gridDim.x * blockDim.x) {
         long long r = i;
@@ -420,7 +423,7 @@ cudaError_t launch_quant_fp8_128x128(const float* w, long long ldw, int N, int K
 }
 
 cudaError_t launch_sf_retile(const uint8_t* in, int rows, int K, int tile_rows, int replicas, uint8_t* out,
-                             int sm_count, cudaStream_t stream) {
+                             int sm_count, cudaStream_t stream, int* zero_ptr, int zero_words) {
     const int scale_cols = ((K + 63) / 64) * 2;
     const int valid_groups = (K + 31) / 32;
     const int k_steps = (K + 127) / 128;
@@ -428,7 +431,7 @@ cudaError_t launch_sf_retile(const uint8_t* in, int rows, int K, int tile_rows, 
     if (words <= 0) return cudaSuccess;
     const int grid = grid_for(words, 256, sm_count);
     return launch_programmatic(sf_retile_kernel, grid, 256, stream, in, rows, scale_cols, valid_groups, tile_rows, k_steps,
-                               replicas, reinterpret_cast<uint32_t*>(out), words);
+                               replicas, reinterpret_cast<uint32_t*>(out), words, zero_ptr, zero_ptr ? zero_words : 0);
 }
 
 cudaError_t launch_e2m1_expand(const uint8_t* in, long long ld_in, int rows, int K, uint8_t* out, long long ld_out,

@@ -14,6 +14,14 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
 
 
+def pytest_collection_modifyitems(config, items):
+    """The allocation-free entry point's tests run last: a run that stops at the first failure (-x) has then already
+    run every other test."""
+    last = [it for it in items if it.fspath.basename == "test_no_alloc.py"]
+    if last:
+        items[:] = [it for it in items if it.fspath.basename != "test_no_alloc.py"] + last
+
+
 @pytest.fixture(scope="session")
 def built_library():
     """Path of libops_tensor_b200.so; builds it with nvcc when a source is newer (no GPU needed for that)."""

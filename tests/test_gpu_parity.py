@@ -660,6 +660,8 @@ def test_mx_stream_k_decode_shapes(cuda_device, M, N, K, tile_n, b_dtype):
     MX = H.SCALE_MX_E8M0_VEC32
     qa, sa = H.quantize(dev_tensor(a, cuda_device), MX)
     qb, sb = H.quantize(dev_tensor(w, cuda_device), MX, b_dtype)
+    a2 = o.normal_f32(33, 4, (M, K), 1.0)                # a second activation matrix for the same workspace
+    qa2, sa2 = H.quantize(dev_tensor(a2, cuda_device), MX)
     outs = {}
     for split in (H.SPLIT_STREAM_K, H.SPLIT_DATA_PARALLEL):
         out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
@@ -667,14 +669,52 @@ def test_mx_stream_k_decode_shapes(cuda_device, M, N, K, tile_n, b_dtype):
                            residual=True, tile_n=tile_n, cta_pair=1, split=split) as c:
             if split == H.SPLIT_STREAM_K:
                 assert c.workspace_bytes > 128 * tile_n * 4            # room for partial tiles
-            for _ in range(2):
-                c(qa, sa, qb, sb, out, bias=bf16_tensor(bias, cuda_device), residual=bf16_tensor(residual, cuda_device))
+            # the workspace arrives dirty: every byte 0xFF, so flags read as "set" and partial tiles as NaN unless the
+            # call clears and rewrites what it uses
+            ws = torch.full((max(c.workspace_bytes, 256),), 0xFF, dtype=torch.uint8, device=cuda_device)
+            for qx, sx in ((qa, sa), (qa, sa), (qa2, sa2), (qa, sa)):
+                c(qx, sx, qb, sb, out, bias=bf16_tensor(bias, cuda_device), residual=bf16_tensor(residual, cuda_device),
+                  workspace=ws)
                 outs.setdefault(split, []).append(to_np(out).copy())
-    first, second = outs[H.SPLIT_STREAM_K]
-    assert np.array_equal(first.view(np.uint32), second.view(np.uint32)), "stream-K is not deterministic"
+    first, second, other, again = outs[H.SPLIT_STREAM_K]
+    assert np.array_equal(first.view(np.uint16), second.view(np.uint16)), "stream-K is not deterministic"
+    assert np.array_equal(first.view(np.uint16), again.view(np.uint16)), "stale partial tiles leaked into a later call"
     ref, gold = mx_reference(to_np(qa), to_np(sa), to_np(qb), to_np(sb), K, name, o.ACT_SILU, bias, residual)
     assert_gemm_ok(first, ref, gold)
     assert_gemm_ok(outs[H.SPLIT_DATA_PARALLEL][0], ref, gold)
+    ref2, gold2 = mx_reference(to_np(qa2), to_np(sa2), to_np(qb), to_np(sb), K, name, o.ACT_SILU, bias, residual)
+    assert_gemm_ok(other, ref2, gold2)
+    assert_gemm_ok(outs[H.SPLIT_DATA_PARALLEL][2], ref2, gold2)
+
+
+def test_static_weight_plans_sharing_one_workspace(cuda_device):
+    """Two plans that treat their weights as static keep their pre-pass results in the workspace; when they share one
+    buffer, each call of the other plan overwrites them, and the next call must rebuild them instead of trusting the
+    remembered pointers."""
+    import torch
+    MX = H.SCALE_MX_E8M0_VEC32
+    M, N, K = 256, 520, 544            # K % 128 != 0: the packed 4-bit weight goes through the expansion pre-pass
+    a = o.normal_f32(41, 0, (M, K), 1.0)
+    qa, sa = H.quantize(dev_tensor(a, cuda_device), MX)
+    weights = [H.quantize(dev_tensor(o.normal_f32(41, 1 + i, (N, K), 0.5), cuda_device), MX, dt)
+               for i, dt in enumerate((H.R_8F_E4M3, H.R_4F_E2M1))]
+    plans = [H.Contraction(M, N, K, scale_mode_a=MX, scale_mode_b=MX, b_dtype=dt, b_is_static=True, tile_n=128, cta_pair=1)
+             for dt in (H.R_8F_E4M3, H.R_4F_E2M1)]
+    ws = torch.empty(max(p.workspace_bytes for p in plans), dtype=torch.uint8, device=cuda_device)
+    outs = []
+    for which in (0, 0, 1, 0, 1, 1):
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+        plans[which](qa, sa, *weights[which], out, workspace=ws)
+        outs.append((which, to_np(out).copy()))
+    for which, got in outs:
+        want = next(g for w, g in outs if w == which)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        name = "e4m3" if which == 0 else "e2m1"
+        ref, gold = mx_reference(to_np(qa), to_np(sa), to_np(weights[which][0]), to_np(weights[which][1]), K, name,
+                                 o.ACT_IDENTITY, None)
+        assert_gemm_ok(got, ref, gold)
+    for p in plans:
+        p.close()
 
 
 def test_calls_capture_into_a_cuda_graph(cuda_device):
@@ -769,7 +809,8 @@ def test_mx_agrees_with_vendor_mxfp8_gemm(cuda_device):
     ((2, 3), (False, True), (True, False), True),          # A broadcast over the outer, B over the inner dimension
     ((2, 1, 2, 2), (True, True, True, True), (True, False, False, True), False),
 ])
-def test_mx_batched_broadcast(cuda_device, batch, batch_a, batch_b, per_batch_bias):
+@pytest.mark.parametrize("d_dtype", ["bfloat16", "float32"])
+def test_mx_batched_broadcast(cuda_device, batch, batch_a, batch_b, per_batch_bias, d_dtype):
     """Batched MX GEMM with numpy-style broadcast of either operand over up to four batch dimensions
     (include/blaze/gemm/kernel/kernel_qbmm_mx.h:282-377)."""
     import torch
@@ -783,10 +824,11 @@ def test_mx_batched_broadcast(cuda_device, batch, batch_a, batch_b, per_batch_bi
     residual = o.normal_f32(24, 3, (nc * M, N), 1.0)
     qa, sa = H.quantize(dev_tensor(a, cuda_device), H.SCALE_MX_E8M0_VEC32)
     qb, sb = H.quantize(dev_tensor(w, cuda_device), H.SCALE_MX_E8M0_VEC32)
-    out = torch.full((nc * M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    # a float32 D has another batch pitch in bytes than the 16-bit ones: every batch must land in its own rows
+    out = torch.full((nc * M, N), float("nan"), dtype=getattr(torch, d_dtype), device=cuda_device)
     with H.Contraction(M, N, K, scale_mode_a=H.SCALE_MX_E8M0_VEC32, scale_mode_b=H.SCALE_MX_E8M0_VEC32,
                        activation=H.OP_RELU, bias=True, residual=True, batch=batch, batch_a=batch_a, batch_b=batch_b,
-                       bias_per_batch=per_batch_bias) as c:
+                       bias_per_batch=per_batch_bias, d_dtype=H.R_32F if d_dtype == "float32" else H.R_16BF) as c:
         c(qa, sa, qb, sb, out, bias=bf16_tensor(bias, cuda_device), residual=bf16_tensor(residual, cuda_device))
     got = to_np(out).reshape(*batch, M, N)
     da = o.dequant_mx(to_np(qa), to_np(sa), K).reshape(*dims_a, M, K)

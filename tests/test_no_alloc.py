@@ -5,7 +5,8 @@ whole device for its own pool, or a real-time loop where an allocation would sta
 its scratch (the re-tiled scale factors) in a fixed 8 MiB array inside the library.  This test calls that entry
 point through the C ABI twice in a row, on two different problems, so the second call finds the first call's data in
 the shared array, and requires the same bits as the regular entry point produces with caller-provided workspace.
-It is collected last so that a run stopping at the first failure has already run every other test.
+tests/conftest.py moves this file's tests to the end of the collection, so that a run stopping at the first failure
+has already run every other test.
 """
 import ctypes as C
 
@@ -77,14 +78,49 @@ def test_no_alloc_entry_keeps_one_scale_copy_when_four_do_not_fit(cuda_device):
 
 
 def test_no_alloc_entry_refuses_what_does_not_fit(cuda_device):
-    """Too large for the 8 MiB array, or needing an expansion buffer: refused before any launch."""
+    """Too large for the 8 MiB array, or needing an expansion buffer: refused before any launch.  Every operand pointer
+    is NULL, so no ordering of the checks could ever start a kernel: were the size check not first, the NULL check would
+    answer INVALID_VALUE instead and this test would fail without touching the GPU."""
     a = native.MxGemmArgs()
     a.struct_size = C.sizeof(a)
     a.M = a.N = a.K = 32768                       # re-tiled scales alone need ~70 MiB
-    a.A = a.B = a.scaleA = a.scaleB = a.D = 4096  # never dereferenced: the size check comes first
     a.lda = a.ldb = a.ldd = 32768
     assert native.lib().blazeMxGemmNoAlloc(C.byref(a), None, None) == native.STATUS_INSUFFICIENT_WORKSPACE
     a.M = a.N = a.K = 256
     a.lda = a.ldb = a.ldd = 256
     a.b_elem = native.ELEM_E2M1
     assert native.lib().blazeMxGemmNoAlloc(C.byref(a), None, None) == native.STATUS_NOT_SUPPORTED
+    a.b_elem = native.ELEM_E4M3
+    a.b_layout = 1                                # an N-major B would need a transposed copy
+    assert native.lib().blazeMxGemmNoAlloc(C.byref(a), None, None) == native.STATUS_NOT_SUPPORTED
+    a.b_layout = 0
+    assert native.lib().blazeMxGemmNoAlloc(C.byref(a), None, None) == native.STATUS_INVALID_VALUE     # NULL operands
+
+
+def test_no_alloc_calls_on_two_streams_ordered_by_an_event(cuda_device):
+    """The documented way to use the entry from more than one stream: the calls share one scratch array, so the second
+    stream waits for an event recorded behind the first call.  Ordered like that, both calls give the regular bits."""
+    import torch
+    first = _problem(cuda_device, 35, 384, 520, 512, with_bias=True)
+    second = _problem(cuda_device, 36, 200, 264, 1024, with_bias=False)
+    want1 = native.mx_gemm(*first[:4], bias=first[4], activation=native.ACT_RELU)
+    want2 = native.mx_gemm(*second[:4], bias=None, activation=native.ACT_IDENTITY)
+    got1, got2 = torch.empty_like(want1), torch.empty_like(want2)
+    args1 = native.mx_gemm_args(*first[:4], got1, bias=first[4], activation=native.ACT_RELU)
+    args2 = native.mx_gemm_args(*second[:4], got2, activation=native.ACT_IDENTITY)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(device=cuda_device), torch.cuda.Stream(device=cuda_device)
+    done = torch.cuda.Event()
+    for _ in range(3):
+        assert native.lib().blazeMxGemmNoAlloc(C.byref(args1), None, C.c_void_p(s1.cuda_stream)) == native.STATUS_SUCCESS
+        done.record(s1)
+        s2.wait_event(done)
+        assert native.lib().blazeMxGemmNoAlloc(C.byref(args2), None, C.c_void_p(s2.cuda_stream)) == native.STATUS_SUCCESS
+        done.record(s2)
+        s1.wait_event(done)
+    s1.synchronize()
+    s2.synchronize()
+    assert torch.equal(got1.view(torch.int16), want1.view(torch.int16))
+    assert torch.equal(got2.view(torch.int16), want2.view(torch.int16))
+    # with no status pointer given, a wait that gave up would show in the device status query: nothing did
+    assert native.device_status() == 0
