@@ -345,7 +345,7 @@ class Case:
                               b_is_static=b_is_static)
         else:
             p = H.Contraction(self.M, self.N, self.K, scale_mode_a=self.mode_a, scale_mode_b=self.mode_b,
-                              groups=self.G, residual=self.residual is not None)
+                              groups=self.G, residual=self.residual is not None, b_is_static=b_is_static)
         self.plans.append(p)
         return p
 
@@ -356,8 +356,7 @@ class Case:
         if self.kind in TENSOR_BOUND:
             self.launches = 2                        # scale re-tile of A + GEMM (B's pre-pass is reused)
         else:
-            # a plan that asks for workspace runs stream-K: a kernel that zeroes the fix-up flags, then the GEMM
-            self.launches = 2 if self.plan.workspace_bytes > 0 else 1
+            self.launches = 1                        # the GEMM alone, stream-K fix-up included
         self.flops = 2.0 * self.M * self.N * self.K
         self.abytes = algorithmic_bytes(self.kind, self.M, self.N, self.K, self.G or 128)
         base = {"qa": self.qa, "sa": self.sa, "qb": self.qb, "sb": self.sb, "out": self.out, "residual": self.residual}
@@ -451,9 +450,29 @@ def timed_loop(env, fn, n, after=None):
     return env.shard.max_over_ranks(e0.elapsed_time(e1), env.dev)
 
 
-def measure(env, step, steps, warmup, min_region_ms=40.0):
+def graph_of(env, step, count):
+    """`count` consecutive steps recorded into one CUDA graph (the launch path allocates nothing and never
+    synchronises, so it can be captured); replaying it takes the host's per-call cost out of the timed region."""
+    torch = env.torch
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(device=env.dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(count):
+                step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    return g
+
+
+def measure(env, step, steps, warmup, min_region_ms=40.0, graph_below_ms=0.2):
     """Warm-up, clock ramp, then `steps` timed steps (more when the region would be too short for the clock sampler to
-    see it).  Returns (ms per step, steps timed, clock record, ramp steps)."""
+    see it).  Steps shorter than `graph_below_ms` are replayed from a CUDA graph of several steps: with eight processes
+    on one host the Python call path (tens of microseconds) would otherwise be what is timed.
+    Returns (ms per step, steps timed, clock record, info)."""
     torch = env.torch
     step()                                           # first call: module load, workspace allocation
     torch.cuda.synchronize()
@@ -464,25 +483,32 @@ def measure(env, step, steps, warmup, min_region_ms=40.0):
     w1.record()
     torch.cuda.synchronize()
     per_step = max(w0.elapsed_time(w1) / max(warmup, 1), 1e-3)
+    if env.world > 1:
+        per_step = env.shard.max_over_ranks(per_step, env.dev)     # every rank takes the same decisions below
+    n = steps
+    if per_step * steps < min_region_ms:
+        n = min(20000, int(math.ceil(min_region_ms / per_step)))
+    fn, per_call, launch = step, 1, "one host call per step"
+    if per_step < graph_below_ms:
+        per_call = next(c for c in (25, 20, 10, 5, 4, 2, 1) if steps % c == 0) if n == steps else 25
+        n = -(-n // per_call) * per_call
+        graph = graph_of(env, step, per_call)
+        fn = graph.replay
+        launch = f"CUDA graph of {per_call} steps, replayed {n // per_call} times"
     # A short step (tens of microseconds) finishes its warm-up before the SM clock has left its idle state: keep
     # stepping, untimed, until the GPU has been busy for about 20 ms.  Long steps (C2) get exactly `warmup` steps.
     ramp_steps = 0
     if per_step * warmup < 1.0:
         ramp_steps = min(5000, int(20.0 / per_step))
-        for _ in range(ramp_steps):
-            step()
+        for _ in range(-(-ramp_steps // per_call)):
+            fn()
         torch.cuda.synchronize()
-    n = steps
-    if per_step * steps < min_region_ms:
-        n = min(20000, int(math.ceil(min_region_ms / per_step)))
-    if env.world > 1:
-        n = int(env.shard.max_over_ranks(float(n), env.dev))       # the same count on every rank
     sampler = ClockSampler(env.local_rank).start() if env.rank == 0 else None
     if sampler is not None:
         time.sleep(0.01)
-    total_ms = timed_loop(env, step, n)
+    total_ms = timed_loop(env, fn, n // per_call)
     clocks = sampler.stop() if sampler is not None else None
-    return total_ms / n, n, clocks, ramp_steps
+    return total_ms / n, n, clocks, {"clock_ramp_steps": ramp_steps, "launch": launch}
 
 
 def roofline_of(case, ms, total_ms, peaks):
@@ -512,13 +538,13 @@ def roofline_of(case, ms, total_ms, peaks):
 
 
 def workload_entry(env, name, case, steps, warmup, peaks):
-    ms, n, clocks, ramp = measure(env, case.step, steps, warmup)
+    ms, n, clocks, info = measure(env, case.step, steps, warmup)
     tf = case.flops / (ms * 1e-3) / 1e12
     return {"workload": name, "description": case.desc, "M": case.M, "N": case.N, "K": case.K, "groups": case.G,
             "ms_per_step": ms, "steps": n, "value": tf, "unit": "TFLOPS",
             "pct_of_published_dense_fp8_peak": round(100.0 * tf / 4500.0, 2),
             "roofline": roofline_of(case, ms, ms * n, peaks), "l2": case.l2_note(), "gpu_launches": case.launches * n,
-            "clocks": clocks, "clock_ramp_steps": ramp}
+            "clocks": clocks, **info}
 
 
 def library_mxfp8(env, case, steps):
@@ -604,7 +630,7 @@ class E2E:
         self.host_ops = {k: v.cpu().pin_memory() for k, v in dev_ops.items()}
         self.dev_ops2 = [dev_ops, {k: torch.empty_like(v) for k, v in dev_ops.items()}]
         self.a_dev2 = [case.a_dev, torch.empty_like(case.a_dev)]
-        self.plan = case._plan(b_is_static=False) if case.kind in TENSOR_BOUND else case.plan
+        self.plan = case._plan(b_is_static=False)      # every operand arrives from the host each step: nothing is static
         self.h2d = {"operands": sum(v.numel() * v.element_size() for v in self.host_ops.values()),
                     "fp32": case.a_host.numel() * 4}
         self.d2h = case.out.numel() * 2
@@ -750,7 +776,7 @@ def gpu_arm(args):
         sharding = (f"{world} replicas: every GPU runs the whole problem (N-shards of a {world} times wider weight), no "
                     "collective; see --shard strong for the split of the problem itself")
 
-    ms_per_step, n_timed, clocks, ramp_steps = measure(env, case.step, steps, warmup, min_region_ms=0.0)
+    ms_per_step, n_timed, clocks, info = measure(env, case.step, steps, warmup, min_region_ms=0.0)
     total_ms = ms_per_step * n_timed
     flops_job = full.flops * (world if (world > 1 and not strong) else 1)
 
@@ -759,9 +785,9 @@ def gpu_arm(args):
         for name in ([wl] + [w for w in ("c2", "c3", "c4", "c5") if w != wl] if not args.kernel_only else [wl]):
             f = full if name == wl else Case(env, name)
             p = case if name == wl else (f.expert_split(world, rank) if f.kind == "grouped" else f.n_split(world, rank))
-            t_full, n1, clk1, _ = measure(env, f.step, steps, warmup)
+            t_full, n1, clk1, info1 = measure(env, f.step, steps, warmup)
             # (the headline's own loop is exactly `steps` long; this one runs long enough for the clock sampler)
-            t_part, nP, clkP, _ = measure(env, p.step, steps, warmup)
+            t_part, nP, clkP, infoP = measure(env, p.step, steps, warmup)
             loads = None
             if f.kind == "grouped":
                 loads = env.shard.plan_loads(env.shard.plan_experts(f.group_rows_host, world))
@@ -771,7 +797,8 @@ def gpu_arm(args):
                 "single_gpu_ms_per_step": t_full, "efficiency": t_full / (world * t_part),
                 "rank0_shape": {"M": p.M, "N": p.N, "K": p.K, "groups": p.G},
                 **({"tokens_per_rank": loads} if loads else {}),
-                "l2": p.l2_note(), "clocks": clkP, "single_gpu_clocks": clk1})
+                "l2": p.l2_note(), "launch": infoP["launch"], "single_gpu_launch": info1["launch"],
+                "clocks": clkP, "single_gpu_clocks": clk1})
             if name != wl:
                 p.close()
                 f.close()
@@ -812,7 +839,7 @@ def gpu_arm(args):
             "vs_baseline": None, "dtype": "fp4" if full.kind == "mxf4" else "fp8", "data": "synthetic",
             "config": headline_config(wl, full.M, full.N, full.K, full.G, world, sharding, {
                 "rank0_shape": {"M": case.M, "N": case.N, "K": case.K, "groups": case.G},
-                "job_flops_per_step": flops_job, "l2": case.l2_note(), "clock_ramp_steps": ramp_steps,
+                "job_flops_per_step": flops_job, "l2": case.l2_note(), **info,
                 "pct_of_published_dense_fp8_peak": round(100.0 * value / world / 4500.0, 2),
                 **({"pct_of_published_dense_fp4_peak": round(100.0 * value / world / 9000.0, 2)}
                    if full.kind == "mxf4" else {})}),

@@ -210,7 +210,8 @@ typedef struct {
     size_t workspace_bytes;
     void* scaleD;     /* device float32 scales of D when d_type is BLAZE_OUT_FP8_128, else NULL */
     int32_t n_peers;  /* 0..BLAZE_MAX_PEERS further copies of D, as in blazeMxGemmArgs (bf16 / f16 D only) */
-    int32_t reserved;
+    int32_t b_is_static; /* 1: B and scaleB are not written by the kernel that precedes this call in the stream (weights):
+                            a dense problem then requests its first weight tiles while that kernel is still running */
     void* peerD[7];
 } blazeFp8GemmArgs;
 

@@ -41,11 +41,19 @@ struct Fp8GemmParams {
     long long ldr;
     __nv_bfloat16* D;
     long long ldd;
-    int stream_k;                   // 1: split the (tile, k-block) units evenly over the grid
+    int stream_k;                   // 0: whole tiles per CTA; 1: the (tile, k-block) units split evenly over the grid;
+                                    // 2: the kernel chooses between the two once it knows the tile count (grouped)
     float* partials;                // [gridDim.x][32 column quads][128 rows][4] fp32 (stream-K only)
     int out_type;                   // OutType of D (ldd counts elements of that type)
     float* scale_d;                 // OUT_FP8_128: [M][n_blocks] float32 scales of D
-    int* flags;                     // [gridDim.x], zeroed before the launch (stream-K only)
+    // Stream-K hand-over marks, [gridDim.x]: a contributor stores `epoch` (a value no earlier launch of this process
+    // used, so whatever the workspace held before cannot be mistaken for it) behind its partial tile; the tile's owner
+    // waits for exactly that value and clears the mark before the kernel ends, so that a replay of the same launch
+    // from a CUDA graph - same epoch - starts from cleared marks as well.  No reset pass before the launch.
+    unsigned long long* flags;
+    unsigned long long epoch;
+    int b_static;                   // B does not depend on the preceding kernel in the stream: its first tiles may be
+                                    // requested while that kernel is still running (dense problems only)
     int* status;
     uint8_t* peer_d[7];             // further copies of D (same pitch and type) that 16-bit output rows are also sent to:
     int n_peers;                    // this GPU's slot in the other GPUs' gathered outputs
@@ -96,6 +104,7 @@ struct Fp8WorkWalker {
     const int* mtile_start;   // shared memory, grouped only
     int total_m_tiles;
     int num_tiles;
+    bool split;               // stream-K: units of (tile, k-block) instead of whole tiles
     // data-parallel state
     int next_tile;
     // stream-K state
@@ -105,6 +114,16 @@ struct Fp8WorkWalker {
         : p(p_), row_start(row_start_), mtile_start(mtile_start_) {
         total_m_tiles = p.groups > 0 ? mtile_start[p.groups] : p.m_tiles;
         num_tiles = total_m_tiles * p.n_tiles;
+        split = p.stream_k == 1;
+        if (p.stream_k == 2 && num_tiles > 0) {
+            // the host's cost model (plan_fp8), evaluated here because a grouped problem's tile count is only known on
+            // the device: K blocks per SM for whole tiles against an even split plus its fix-up cost
+            const int cta = (int)gridDim.x;
+            const float whole = (float)((num_tiles + cta - 1) / cta) * (float)p.k_blocks;
+            const long long units = (long long)num_tiles * p.k_blocks;
+            const float even = (float)((units + cta - 1) / cta) + 17.0f + (float)cta / (float)num_tiles;
+            split = p.k_blocks >= 2 && even < whole;
+        }
         next_tile = blockIdx.x;
         const long long total = (long long)num_tiles * p.k_blocks;
         unit = total * blockIdx.x / gridDim.x;
@@ -144,7 +163,7 @@ struct Fp8WorkWalker {
     }
 
     __device__ bool next(Fp8Segment& s) {
-        if (p.stream_k) {
+        if (split) {
             if (unit >= unit_end) return false;
             const int t = (int)(unit / p.k_blocks);
             const int kb = (int)(unit - (long long)t * p.k_blocks);
@@ -193,6 +212,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     uint64_t* amax_bar = fix_bar + 1;              // the 256 promotion threads, once per quantised output tile
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
+    int* fix_range = reinterpret_cast<int*>(smem + L::kMiscOffset + 8);     // contributors of the split tile this CTA owns
     int* row_start = reinterpret_cast<int*>(smem + L::kGroupOffset);
     int* mtile_start = row_start + (kFp8MaxGroups + 1);
 
@@ -208,6 +228,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         mbar_init(fix_bar, 32 * kPromoWarps);
         mbar_init(amax_bar, 32 * kPromoWarps);
         *abort_flag = 0;
+        fix_range[0] = 0;
+        fix_range[1] = -1;
         fence_mbar_init();
     }
     if (warp == kMmaWarp0 && p.groups > 0) {
@@ -261,8 +283,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
     // Launched with programmatic stream serialisation: everything above may overlap the tail of the previous kernel
-    // in the stream; nothing below touches global memory before that kernel has finished.
-    grid_dependency_wait();
+    // in the stream; nothing below touches global memory before that kernel has finished - except the TMA thread's
+    // first weight tiles when the caller has declared the weights independent of that kernel.
+    if (warp != kTmaWarp) grid_dependency_wait();
 
     // The two single-thread loops below run once per 128-deep K block, i.e. every 256 tensor-core cycles: they are
     // written with precomputed shared-memory addresses and descriptor words so that their instruction count, not
@@ -282,9 +305,32 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             bool ok = true;
             // B is streamed once when there is a single row of tiles; keep A (re-read by every N tile) instead
             const uint64_t b_hint = (p.groups == 0 && p.m_tiles == 1) ? kEvictFirst : kEvictNormal;
+            // Static weights of a dense problem: arm the first stages and request their B tiles now, while the previous
+            // kernel in the stream may still be running; the A tiles follow once it has finished.
+            uint32_t early = 0;
+            if (p.b_static && p.groups == 0) {
+                Fp8WorkWalker ahead(p, row_start, mtile_start);
+                Fp8Segment sg;
+                while (early < (uint32_t)kStages && ahead.next(sg)) {
+                    for (int kb = sg.kb0; kb < sg.kb1 && early < (uint32_t)kStages; ++kb, ++early) {
+                        const uint32_t bar = full0 + early * 8;
+                        mbar_arrive_expect_tx_addr(bar, L::kTxBytes);
+                        tma_load_2d_addr(smem_base + early * L::kStageBytes + L::kABytes, &tmap_b, bar, kb * 128,
+                                         sg.nt * 128, b_hint);
+                    }
+                }
+            }
+            grid_dependency_wait();
             while (ok && walk.next(seg)) {
                 const int b_row = seg.group * p.N + seg.nt * 128;
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
+                    if (g < early) {                 // stage armed and B requested above: only A is missing
+                        tma_load_2d_addr(smem_base + stage * L::kStageBytes, &tmap_a, full0 + stage * 8, kb * 128, seg.m0,
+                                         kEvictNormal);
+                        if (++stage == kStages) stage = 0;
+                        ++g;
+                        continue;
+                    }
                     // the stage is free once the MMAs of the block that used it last (g - kStages) have finished; the
                     // block's "done" barrier says so, and the stage needs no commit of its own (~86 tensor-pipe cycles)
                     if (g >= (uint32_t)kStages) {
@@ -437,7 +483,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 if (threadIdx.x == 0) {
                     if (mbar_wait(fix_bar, 0, abort_flag, p.status, DEV_TIMEOUT_FIXUP_FLAG)) {
                         __threadfence();
-                        st_release_gpu(p.flags + blockIdx.x, 1);
+                        st_release_gpu_u64(p.flags + blockIdx.x, p.epoch);
                     }
                 }
                 continue;
@@ -449,8 +495,12 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 for (int j = blockIdx.x + 1; j < (int)gridDim.x; ++j) {
                     const long long lo_j = total * j / gridDim.x;
                     if (lo_j >= tile_end) break;
+                    if (threadIdx.x == 0) {             // marks to clear when the kernel ends
+                        if (fix_range[1] < 0) fix_range[0] = j;
+                        fix_range[1] = j;
+                    }
                     const long long t0 = clock64();
-                    while (ld_acquire_gpu(p.flags + j) == 0) {
+                    while (ld_acquire_gpu_u64(p.flags + j) != p.epoch) {
                         if (*abort_flag != 0) { ok = false; break; }
                         if (clock64() - t0 > BLAZE_WAIT_LIMIT_CYCLES) {
                             *abort_flag = 1;
@@ -602,6 +652,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     // ---------------------------------------------------------------------- teardown
     if (warp < kPromoWarps) tma_store_wait_read<0>();     // output rows the copy engine has not read yet
     __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag == 0) {
+        // every thread of this CTA has seen these marks: clear them for the next launch that carries the same epoch
+        for (int j = fix_range[0]; j <= fix_range[1]; ++j) p.flags[j] = 0ull;
+    }
     if (*abort_flag != 0) {
         for (int i = 0; i < 64; ++i) __nanosleep(2000);
         __syncthreads();

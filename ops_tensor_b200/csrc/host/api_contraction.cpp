@@ -144,6 +144,7 @@ void fill_fp8_args(const acltensorOperationDescriptor& op, int32_t splitPolicy, 
     a->d_type = op.descD->dataType == ACLTENSOR_R_8F_E4M3 ? BLAZE_OUT_FP8_128 : out_type_of(op.descD->dataType);
     a->sched = sched_of(splitPolicy);
     a->sm_limit = op.smLimit;
+    a->b_is_static = op.bIsStatic != 0 ? 1 : 0;
 }
 
 acltensorStatus_t Fp8Workspace(const acltensorOperationDescriptor& op, int32_t splitPolicy, uint64_t* bytes) {

@@ -4,9 +4,12 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
+#include <chrono>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <random>
 
 #include "blaze_b200.h"
 #include "cann_ops_tensor_types.h"
@@ -684,7 +687,6 @@ static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
     if (a->d_type != BLAZE_OUT_FP8_128 && (a->d_type < BLAZE_OUT_BF16 || a->d_type > BLAZE_OUT_F32))
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if ((a->K % 16) != 0 || (a->N % 8) != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    if (a->groups > 0 && a->sched == BLAZE_SCHED_STREAM_K) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     int sms = sm_count;
     if (a->sm_limit > 0 && a->sm_limit < sms) sms = a->sm_limit;
     pl->n_tiles = (a->N + 127) / 128;
@@ -707,6 +709,11 @@ static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
             if (split < whole_tiles) stream_k = 1;
         }
     }
+    if (a->groups > 0 && tiles > 0 && pl->k_blocks >= 2 && a->sched != BLAZE_SCHED_DATA_PARALLEL) {
+        // grouped: the tile count depends on the group list, which lives on the device; the kernel applies the same
+        // cost model itself unless the caller forces the split
+        stream_k = a->sched == BLAZE_SCHED_STREAM_K ? 1 : 2;
+    }
     pl->stream_k = stream_k;
     long long grid = tiles < sms ? tiles : sms;
     if (stream_k) {
@@ -715,10 +722,25 @@ static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
     }
     if (grid < 1) grid = 1;
     pl->grid = (int)grid;
-    pl->flags_bytes = stream_k ? round256((size_t)grid * sizeof(int)) : 0;
+    pl->flags_bytes = stream_k ? round256((size_t)grid * sizeof(unsigned long long)) : 0;
     pl->partial_bytes = stream_k ? (size_t)grid * 128 * 128 * sizeof(float) : 0;
     pl->total = pl->flags_bytes + pl->partial_bytes;
     return ACLTENSOR_STATUS_SUCCESS;
+}
+
+// A value for the stream-K hand-over marks that no earlier launch of this process has used: a per-process random
+// high word (so bytes left in a workspace by anything else cannot match) over a launch counter that skips zero.
+static unsigned long long next_stream_k_epoch() {
+    static const unsigned long long nonce = []() {
+        std::random_device rd;
+        unsigned long long n = (static_cast<unsigned long long>(rd()) << 32) ^ static_cast<unsigned long long>(
+                                   std::chrono::steady_clock::now().time_since_epoch().count());
+        return (n | (1ull << 63)) & 0xFFFFFFFF00000000ull;
+    }();
+    static std::atomic<uint32_t> counter{0};
+    uint32_t c = counter.fetch_add(1) + 1;
+    if (c == 0) c = counter.fetch_add(1) + 1;
+    return nonce | c;
 }
 
 template <int kAct, int kStages>
@@ -820,11 +842,12 @@ extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
     p.flags = nullptr;
     p.partials = nullptr;
     p.status = ctx->status_word;
+    p.epoch = 0;
+    p.b_static = a->b_is_static != 0 ? 1 : 0;
     if (pl.stream_k) {
-        p.flags = static_cast<int*>(a->workspace);
+        p.flags = static_cast<unsigned long long*>(a->workspace);
         p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + pl.flags_bytes);
-        cudaError_t e = launch_zero_words(p.flags, (int)(pl.flags_bytes / 4), stream);
-        if (e != cudaSuccess) return status_of(e);
+        p.epoch = next_stream_k_epoch();
     }
     cudaError_t e;
     switch (a->activation) {

@@ -41,9 +41,6 @@ cudaError_t launch_e2m1_expand(const uint8_t* in, long long ld_in, int rows, int
 cudaError_t launch_transpose_bytes(const uint8_t* in, long long ld_in, int K, int N, uint8_t* out, long long ld_out,
                                    cudaStream_t stream);
 cudaError_t launch_scale_pairs_to_rows(const uint8_t* in, int N, int K, uint8_t* out, int sm_count, cudaStream_t stream);
-// Zeroes `words` 32-bit words (the stream-K flags) with a kernel, so that the GEMM behind it can be launched with
-// programmatic stream serialisation (a memset node gives the next kernel nothing to overlap with).
-cudaError_t launch_zero_words(int* p, int words, cudaStream_t stream);
 cudaError_t launch_add_f32(const float* a, const float* c, float* d, long long n, int sm_count, cudaStream_t stream);
 
 }  // namespace blaze

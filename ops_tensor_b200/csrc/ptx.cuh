@@ -196,6 +196,15 @@ __device__ __forceinline__ void st_release_gpu(int* ptr, int v) {
     asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ unsigned long long ld_acquire_gpu_u64(const unsigned long long* ptr) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ptr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu_u64(unsigned long long* ptr, unsigned long long v) {
+    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(ptr), "l"(v) : "memory");
+}
+
 // ------------------------------------------------------------------------------------------------ dependent launch
 
 // A kernel launched with programmatic stream serialisation may start while its predecessor in the stream is still

@@ -335,12 +335,6 @@ __global__ void __launch_bounds__(256) scale_pairs_to_rows_kernel(const uint8_t*
     }
 }
 
-__global__ void __launch_bounds__(256) zero_words_kernel(int* __restrict__ p, int words) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the GEMM behind may start setting up
-    asm volatile("griddepcontrol.wait;" ::: "memory");                   // the GEMM before may still read the flags
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < words; i += gridDim.x * blockDim.x) p[i] = 0;
-}
-
 // ---------------------------------------------------------------------------------------------------- launchers
 
 // Launch with programmatic stream serialisation: the kernel may be scheduled while its predecessor in the stream is
@@ -376,11 +370,6 @@ cudaError_t launch_scale_pairs_to_rows(const uint8_t* in, int N, int K, uint8_t*
     const int grid = (int)blocks;
     scale_pairs_to_rows_kernel<<<grid, 256, 0, stream>>>(in, N, scale_cols, out);
     return cudaGetLastError();
-}
-
-cudaError_t launch_zero_words(int* p, int words, cudaStream_t stream) {
-    if (words <= 0) return cudaSuccess;
-    return launch_programmatic(zero_words_kernel, (words + 255) / 256, 256, stream, p, words);
 }
 
 static int grid_for(long long work_items, int per_block, int sm_count) {

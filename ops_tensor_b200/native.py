@@ -83,7 +83,7 @@ class Fp8GemmArgs(C.Structure):
         ("d_type", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("scaleD", C.c_void_p),
-        ("n_peers", C.c_int32), ("reserved", C.c_int32),
+        ("n_peers", C.c_int32), ("b_is_static", C.c_int32),
         ("peerD", C.c_void_p * 7),
     ]
 
@@ -270,7 +270,8 @@ def mx_gemm(a, sa, b, sb, *, out=None, workspace=None, **kw):
 
 
 def fp8_gemm_args(a, sa, b, sb, out, *, group_rows=None, bias=None, residual=None, activation=ACT_IDENTITY,
-                  sched=SCHED_AUTO, sm_limit=0, workspace=None, scale_out=None, peer_outs=None) -> Fp8GemmArgs:
+                  sched=SCHED_AUTO, sm_limit=0, workspace=None, scale_out=None, peer_outs=None,
+                  b_is_static=False) -> Fp8GemmArgs:
     M, K = a.shape
     if b.dim() == 3:
         G, N, _ = b.shape
@@ -295,6 +296,7 @@ def fp8_gemm_args(a, sa, b, sb, out, *, group_rows=None, bias=None, residual=Non
     args.activation = activation
     args.sched = sched
     args.sm_limit = sm_limit
+    args.b_is_static = 1 if b_is_static else 0
     if peer_outs:
         if len(peer_outs) > 7 or any(t.shape != out.shape or t.stride(0) != out.stride(0) or t.dtype != out.dtype
                                      for t in peer_outs):

@@ -241,8 +241,15 @@ def test_streamk_plan_falls_back_without_workspace(api):
 def test_grouped_and_w4_descriptors(api):
     with H.Contraction(4096, 768, 2048, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128,
                        groups=16) as c:
-        assert c.workspace_bytes == 0
+        # room for the split along K, which the kernel may choose once it has counted the tiles of the group list
+        assert c.workspace_bytes >= 148 * 128 * 128 * 4
         assert H.get_attribute(c.handle, c.op, H.ATTR_GROUP_COUNT) == 16
+    with H.Contraction(4096, 768, 2048, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128,
+                       groups=16, split=H.SPLIT_DATA_PARALLEL) as c:
+        assert c.workspace_bytes == 0                       # whole tiles per CTA need none
+    with H.Contraction(4096, 768, 2048, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128,
+                       groups=16, workspace_limit=0) as c:
+        assert c.workspace_bytes == 0                       # and a caller without workspace falls back to them
     with pytest.raises(native.BlazeError) as e:           # grouped MX is not registered
         H.Contraction(4096, 768, 2048, scale_mode_a=H.SCALE_MX_E8M0_VEC32, scale_mode_b=H.SCALE_MX_E8M0_VEC32, groups=4)
     assert e.value.status == H.STATUS_NOT_SUPPORTED
@@ -293,8 +300,10 @@ def test_kernel_abi_argument_checks(built_library):
     f.struct_size = C.sizeof(f)
     f.M, f.N, f.K, f.groups = 128, 128, 128, 2000
     assert l.blazeFp8GemmWorkspaceSize(C.byref(f), C.byref(n)) == H.STATUS_NOT_SUPPORTED       # too many groups
-    f.groups, f.sched = 4, native.SCHED_STREAM_K
-    assert l.blazeFp8GemmWorkspaceSize(C.byref(f), C.byref(n)) == H.STATUS_NOT_SUPPORTED       # grouped stream-K
+    f.M, f.K = 1024, 1024
+    f.groups, f.sched = 4, native.SCHED_STREAM_K                                               # grouped, split along K
+    assert l.blazeFp8GemmWorkspaceSize(C.byref(f), C.byref(n)) == H.STATUS_SUCCESS and n.value >= 128 * 128 * 4
+    f.M, f.K = 128, 128
     f.groups, f.sched = 0, native.SCHED_DATA_PARALLEL
     assert l.blazeFp8GemmWorkspaceSize(C.byref(f), C.byref(n)) == H.STATUS_SUCCESS and n.value == 0
     assert l.blazeQuantizeMx(None, 0, 4, 32, 0, None, 0, None, None) == H.STATUS_INVALID_VALUE
@@ -410,10 +419,12 @@ def test_plan_choices_show_in_the_workspace_size(built_library):
     split = mx_bytes(128, 7168, 18432)
     assert split - whole == 148 * 128 * 128 * 4 + 768
     assert mx_bytes(256, 512, 1024) == mx_bytes(256, 512, 1024, sched=native.SCHED_DATA_PARALLEL)
-    # FP8 family: C5 splits along K, C1 and the grouped C4 do not
-    assert fp8_bytes(128, 7168, 18432) == 148 * 128 * 128 * 4 + 768
+    # FP8 family: C5 splits along K (148 partial tiles + 148 eight-byte marks, rounded to 256), C1 does not; a grouped
+    # problem reserves the room and lets the kernel decide once it has counted the tiles
+    assert fp8_bytes(128, 7168, 18432) == 148 * 128 * 128 * 4 + 1280
     assert fp8_bytes(256, 512, 1024) == 0
-    assert fp8_bytes(32768, 768, 2048, groups=128) == 0
+    assert fp8_bytes(32768, 768, 2048, groups=128) == 148 * 128 * 128 * 4 + 1280
+    assert fp8_bytes(32768, 768, 2048, groups=128, sched=native.SCHED_DATA_PARALLEL) == 0
     assert fp8_bytes(256, 512, 1024, sched=native.SCHED_STREAM_K) > 0
 
 

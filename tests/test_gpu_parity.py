@@ -261,7 +261,7 @@ def test_config5_decode_streamk(cuda_device, M):
     assert_gemm_ok(got, ref, gold)
 
 
-def run_grouped(device, cfg, group_rows, N, K, sigma_b=0.02):
+def run_grouped(device, cfg, group_rows, N, K, sigma_b=0.02, split=H.SPLIT_AUTO, dirty_workspace=False):
     import torch
     G = len(group_rows)
     M = int(group_rows.sum())
@@ -277,8 +277,17 @@ def run_grouped(device, cfg, group_rows, N, K, sigma_b=0.02):
         sb[g].copy_(s)
     out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=device)
     rows_t = dev_tensor(group_rows.astype(np.int64), device)
-    with H.Contraction(M, N, K, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128, groups=G) as c:
-        c(qa, sa, qb, sb, out, group_rows=rows_t)
+    with H.Contraction(M, N, K, scale_mode_a=H.SCALE_FP32_1X128, scale_mode_b=H.SCALE_FP32_128X128, groups=G,
+                       split=split) as c:
+        ws = None
+        if dirty_workspace and c.workspace_bytes:
+            ws = torch.full((c.workspace_bytes,), 0xFF, dtype=torch.uint8, device=device)
+        c(qa, sa, qb, sb, out, group_rows=rows_t, workspace=ws)
+        if split != H.SPLIT_DATA_PARALLEL:
+            first = to_np(out).copy()
+            out.fill_(float("nan"))
+            c(qa, sa, qb, sb, out, group_rows=rows_t, workspace=ws)
+            assert np.array_equal(to_np(out).view(np.uint32), first.view(np.uint32)), "two runs differ"
     got = to_np(out)
     da = o.dequant_fp8_1x128(to_np(qa), to_np(sa))
     qb_n, sb_n = to_np(qb), to_np(sb)
@@ -290,6 +299,19 @@ def run_grouped(device, cfg, group_rows, N, K, sigma_b=0.02):
 def test_grouped_small_with_empty_groups(cuda_device):
     rows = np.array([0, 5, 128, 0, 129, 1, 300, 0], dtype=np.int64)
     got, ref = run_grouped(cuda_device, 14, rows, 264, 400)
+    assert_gemm_ok(got, ref)
+
+
+@pytest.mark.parametrize("split", [H.SPLIT_STREAM_K, H.SPLIT_AUTO, H.SPLIT_DATA_PARALLEL])
+@pytest.mark.parametrize("rows,N,K", [
+    ([0, 5, 128, 0, 129, 1, 300, 0], 264, 1040),               # a handful of tiles, far fewer than SMs
+    ([700, 0, 64, 1500, 333, 1, 0, 2050, 129, 127], 768, 2048),   # ~1.7 tiles per SM: the case the split is for
+])
+def test_grouped_split_along_k(cuda_device, split, rows, N, K):
+    """Grouped matmul with the (tile, K block) units dealt evenly over the SMs: partial tiles of ragged groups go
+    through the float32 workspace (handed over dirty) and are added in CTA order; forced, chosen by the kernel's own
+    cost model once it has counted the tiles, and switched off."""
+    got, ref = run_grouped(cuda_device, 15, np.array(rows, dtype=np.int64), N, K, split=split, dirty_workspace=True)
     assert_gemm_ok(got, ref)
 
 
