@@ -41,7 +41,7 @@ struct MxPairSmem {
     static constexpr int kSfbBytes = kSfbBlocks * 512;
     static constexpr int kSfOffset = kStages * kStageBytes;
     static constexpr int kBarOffset = kSfOffset + kStages * (kSfaBytes + kSfbBytes);
-    static constexpr int kNumBars = 2 * kStages + 5;
+    static constexpr int kNumBars = 2 * kStages + 6;
     static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
     static constexpr int kEpiOffset = (kMiscOffset + 16 + 1023) / 1024 * 1024;
     static constexpr int kTotal = kEpiOffset + kEpiStageBytes;
@@ -66,6 +66,46 @@ __device__ __forceinline__ void tma_load_2d_to_pair_bar(void* smem_dst, const CU
         "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y), "l"(hint)
         : "memory");
 }
+
+// Walks the segments of one CTA pair.  Whole tiles are dealt round-robin; with `stream_k` the tiles of the last, partly
+// filled round are instead cut along K so that every pair gets the same number of K steps of them: a pair then ends
+// with a tail of one tile, possibly whole tiles, and a head of another.  The pair that holds K step 0 of a tile owns
+// it, as in MxWorkWalker; the reference balances the same last round by re-splitting its tiles along M and N
+// (include/blaze/gemm/block/block_scheduler_qbmm.h:120-136, :193-248).
+struct MxPairWalker {
+    int k_steps, num_tiles, num_pairs, full_tiles;
+    int next_tile;
+    long long unit, unit_end;      // K steps of the tiles [full_tiles, num_tiles), this pair's share
+
+    __device__ MxPairWalker(const MxGemmParams& p, int num_tiles_, int pair, int num_pairs_)
+        : k_steps(p.k_steps), num_tiles(num_tiles_), num_pairs(num_pairs_), next_tile(pair) {
+        full_tiles = p.stream_k ? (num_tiles / num_pairs) * num_pairs : num_tiles;
+        const long long total = (long long)(num_tiles - full_tiles) * k_steps;
+        unit = total * pair / num_pairs;
+        unit_end = total * (pair + 1) / num_pairs;
+    }
+    // first K step (in the numbering of the split tiles) of pair `q`
+    __device__ long long first_unit_of(int q) const {
+        return (long long)(num_tiles - full_tiles) * k_steps * q / num_pairs;
+    }
+    __device__ bool next(MxSegment& s) {
+        if (next_tile < full_tiles) {
+            s.tile = next_tile;
+            s.ks0 = 0;
+            s.ks1 = k_steps;
+            next_tile += num_pairs;
+            return true;
+        }
+        if (unit >= unit_end) return false;
+        const int t = (int)(unit / k_steps);
+        s.tile = full_tiles + t;
+        s.ks0 = (int)(unit - (long long)t * k_steps);
+        const long long left = unit_end - unit;
+        s.ks1 = (int)((long long)(k_steps - s.ks0) < left ? k_steps : s.ks0 + left);
+        unit += s.ks1 - s.ks0;
+        return true;
+    }
+};
 
 template <int kBN, int kStages, int kAct, bool kWide = true, bool kMxf4 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
@@ -96,6 +136,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint64_t* tmem_full_bar = bars + 2 * kStages;    // one per CTA
     uint64_t* tmem_empty_bar = bars + 2 * kStages + 2;   // used in the leader only: 8 epilogue warps arrive
     uint64_t* overlap_bar = bars + 2 * kStages + 4;      // leader only: the shared accumulator columns were read
+    uint64_t* fix_bar = bars + 2 * kStages + 5;          // this CTA's 128 epilogue threads, once: its partial tile is written
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 4);
 
@@ -115,6 +156,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             mbar_init(&tmem_empty_bar[s], 8);
         }
         mbar_init(overlap_bar, 8);
+        mbar_init(fix_bar, 128);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -145,14 +187,16 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             // the re-tiled scales come from the kernel launched just before this one; everything above (barriers,
             // TMEM, descriptor prefetch) may overlap its tail
             grid_dependency_wait();
-            for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+            MxPairWalker walk(p, num_tiles, pair, num_pairs);
+            MxSegment seg;
+            while (ok && walk.next(seg)) {
                 int mt, nt;
-                tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);
+                tile_coords(seg.tile, p.m_tiles, p.n_tiles, p.window, mt, nt);
                 const int a_row = mt * 256 + (int)cta_rank * 128;
                 const int b_row = nt * kBN + (int)cta_rank * (kBN / 2);
                 const int sfa_row = (mt * 2 + (int)cta_rank) * p.sf_k_steps;
                 const int sfb_row = nt * p.sf_k_steps * L::kSfbBlocksPerK;
-                for (int ks = 0; ks < p.k_steps; ++ks) {
+                for (int ks = seg.ks0; ks < seg.ks1; ++ks) {
                     ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
                     uint8_t* a_dst = smem + stage * L::kStageBytes;
@@ -182,7 +226,9 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t acc_phase = 0;
             uint32_t tiles_done = 0;
             bool ok = true;
-            for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+            MxPairWalker walk(p, num_tiles, pair, num_pairs);
+            MxSegment seg;
+            while (ok && walk.next(seg)) {
                 ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
                 if (!ok) break;
                 if (kOverlap && tiles_done != 0) {
@@ -193,7 +239,8 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 ++tiles_done;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kAccStride;
-                for (int ks = 0; ks < p.k_steps; ++ks) {
+                for (int ks = seg.ks0; ks < seg.ks1; ++ks) {
+                    const int first = ks == seg.ks0 ? 0 : 1;          // the segment's first MMA overwrites the accumulator
                     ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
                     tcgen05_fence_after();
@@ -218,7 +265,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                             const uint32_t id = (uint32_t)(j & 1) * 2;
                             umma_mxf4_pair(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
                                            umma_idesc_mx(FMT_MXF4_E2M1, FMT_MXF4_E2M1, 256, kBN, id, id),
-                                           (ks | j) != 0 ? 1u : 0u, tmem_base + kSfaCol + 4 * (j >> 1),
+                                           (first | j) != 0 ? 1u : 0u, tmem_base + kSfaCol + 4 * (j >> 1),
                                            tmem_base + kSfbCol + 8 * (j >> 1));
                         }
                     } else {
@@ -234,7 +281,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         umma_mx<2>(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
-                                   umma_idesc_mx(p.a_format, p.b_format, 256, kBN, j, j), (ks | j) != 0 ? 1u : 0u,
+                                   umma_idesc_mx(p.a_format, p.b_format, 256, kBN, j, j), (first | j) != 0 ? 1u : 0u,
                                    tmem_base + kSfaCol, tmem_base + kSfbCol);
                     }
                     }
@@ -256,9 +303,12 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint8_t* stage_buf = smem + L::kEpiOffset + warp * kEpiStageBytesPerWarp;
         const EpilogueArgs ea{p.M, p.N, p.bias, p.residual, p.ldr, p.out_type, p.scale_d, p.scale_cols_d,
                               p.peer_maps, p.n_peers};
-        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        MxPairWalker walk(p, num_tiles, pair, num_pairs);
+        MxSegment seg;
+        const int r_in_tile = warp * 32 + lane;
+        while (ok && walk.next(seg)) {
             int mt, nt;
-            tile_coords(t, p.m_tiles, p.n_tiles, p.window, mt, nt);
+            tile_coords(seg.tile, p.m_tiles, p.n_tiles, p.window, mt, nt);
             ok = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -266,22 +316,92 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint64_t* release_bar = &tmem_empty_bar[acc];          // owned by the leader CTA
             // accumulator 0 shares its last columns, accumulator 1 its first: start with the chunk that holds them
             const int first_chunk = (kOverlap && acc == 0) ? kChunks - 1 : 0;
-            epilogue_store_tile_from<kBN, kAct>(
-                tmem_base + lane_base + acc * kAccStride, ea, &tmap_d, stage_buf,
-                mt * 256 + (int)cta_rank * 128 + warp * 32, nt * kBN, lane, chunk_counter, first_chunk,
-                [&]() {
-                    if (kOverlap) {
-                        tcgen05_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(overlap_bar, 0);
-                    }
-                },
-                [&]() {
+            const uint32_t tmem_tile = tmem_base + lane_base + acc * kAccStride;
+            auto early = [&]() {
+                if (kOverlap) {
                     tcgen05_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(release_bar, 0);
-                });
+                    if (lane == 0) mbar_arrive_cluster(overlap_bar, 0);
+                }
+            };
+            auto release = [&]() {
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(release_bar, 0);
+            };
             if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+
+            if (seg.ks0 > 0) {
+                // -------- contributor: this CTA's 128 rows of the partial tile go to its slot of the workspace,
+                // [chunk][8][row][4] so that a warp writes 512 contiguous bytes per instruction, then the mark is raised
+                float4* slot4 = reinterpret_cast<float4*>(p.partials + (size_t)blockIdx.x * (128 * kBN)) + r_in_tile;
+#pragma unroll 1
+                for (int i = 0; i < kChunks; ++i) {
+                    int c = first_chunk + i;
+                    if (c >= kChunks) c -= kChunks;
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_tile + c * 32, v);
+                    tmem_ld_wait();
+                    if (i == 0) early();
+                    if (i == kChunks - 1) release();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        __stcg(slot4 + (c * 8 + q) * 128,
+                               make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                           __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3])));
+                    }
+                }
+                __threadfence();
+                mbar_arrive(fix_bar);
+                if (threadIdx.x == 0) {
+                    if (mbar_wait(fix_bar, 0, abort_flag, p.status, DEV_TIMEOUT_FIXUP_FLAG)) {
+                        __threadfence();
+                        st_release_gpu(p.flags + blockIdx.x, 1);
+                    }
+                }
+                continue;
+            }
+            int q_first = 0, q_last = -1;                // pairs whose partial sums belong to this tile
+            if (seg.ks1 < p.k_steps) {
+                // -------- owner of a split tile: wait for the same-ranked CTAs of the pairs that hold its later K ranges
+                const long long tile_end = (long long)(seg.tile - walk.full_tiles + 1) * p.k_steps;
+                q_first = pair + 1;
+                for (int q = q_first; q < num_pairs; ++q) {
+                    if (walk.first_unit_of(q) >= tile_end) break;
+                    const int* flag = p.flags + (2 * q + (int)cta_rank);
+                    const long long t0 = clock64();
+                    while (ld_acquire_gpu(flag) == 0) {
+                        if (*abort_flag != 0) { ok = false; break; }
+                        if (clock64() - t0 > BLAZE_WAIT_LIMIT_CYCLES) {
+                            *abort_flag = 1;
+                            atomicCAS(p.status, 0, DEV_TIMEOUT_FIXUP_FLAG);
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(64);
+                    }
+                    if (!ok) break;
+                    q_last = q;
+                }
+                ok = __all_sync(0xffffffffu, ok);        // also re-converges the warp after the per-thread polling
+                if (!ok) break;
+            }
+            epilogue_store_tile_from<kBN, kAct>(
+                tmem_tile, ea, &tmap_d, stage_buf, mt * 256 + (int)cta_rank * 128 + warp * 32, nt * kBN, lane,
+                chunk_counter, first_chunk, early, release, [&](int c, uint32_t (&v)[32]) {
+                    for (int q = q_first; q <= q_last; ++q) {       // in pair order: the sum is the same on every run
+                        const float4* slot4 = reinterpret_cast<const float4*>(
+                                                  p.partials + (size_t)(2 * q + (int)cta_rank) * (128 * kBN)) + r_in_tile;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const float4 w = __ldcg(slot4 + (c * 8 + u) * 128);
+                            v[4 * u] = __float_as_uint(__uint_as_float(v[4 * u]) + w.x);
+                            v[4 * u + 1] = __float_as_uint(__uint_as_float(v[4 * u + 1]) + w.y);
+                            v[4 * u + 2] = __float_as_uint(__uint_as_float(v[4 * u + 2]) + w.z);
+                            v[4 * u + 3] = __float_as_uint(__uint_as_float(v[4 * u + 3]) + w.w);
+                        }
+                    }
+                });
         }
         if (lane == 0) epilogue_drain_stores();
     }

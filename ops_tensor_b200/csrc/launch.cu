@@ -151,8 +151,9 @@ struct MxPlan {
     int tile_n;
     int sfb_replicas;   // copies of every 512-byte scale block of B in the re-tiled array
     bool mxf4;          // FP4 x FP4 on kind::mxf4 (dense 4-bit tiles, K = 256 per stage)
-    bool stream_k;      // single-CTA tiles only: (tile, K step) units split evenly over the grid
-    int grid;           // CTAs of the single-CTA kernel
+    bool stream_k;      // single-CTA tiles: (tile, K step) units split evenly over the grid; 2-CTA tiles: the tiles of
+                        // the last, partly filled round cut along K so that every pair gets the same share of them
+    int grid;           // CTAs of the kernel (2-CTA tiles: only when stream_k is set)
     size_t flags_off, partials_off, flags_bytes, partials_bytes;
     int sf_k_steps;     // 128-K blocks of the re-tiled scale arrays
     int m_tiles, n_tiles, k_steps;
@@ -255,6 +256,23 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scal
         if (a->sched == BLAZE_SCHED_STREAM_K || split < whole_tiles) {
             pl->stream_k = true;
             pl->grid = (int)used;
+        }
+    }
+    if (pl->pair && allow_split && tiles > 0 && pl->k_steps >= 2 && a->sched != BLAZE_SCHED_DATA_PARALLEL) {
+        // 2-CTA tiles: whole rounds run as they are; the R tiles left for the last round may be cut along K so that
+        // every pair gets an even share of their K steps.  Measured on B200 the fix-up (256 KB of partial sums per tile
+        // through L2, read back chunk by chunk inside the owner's epilogue) costs about 14 us, some 30 K steps:
+        // 8192 x 1024 x 8192 takes 81 us split against 75 us whole, so the split is only chosen by itself for very
+        // long K; a caller can still force it
+        const long long pairs = eff_sms / 2 > 0 ? eff_sms / 2 : 1;
+        const long long rest = tiles % pairs;
+        if (rest > 0) {
+            const double whole = (double)pl->k_steps;
+            const double even = (double)((rest * pl->k_steps + pairs - 1) / pairs) + 30.0 + (double)pairs / (double)rest;
+            if (a->sched == BLAZE_SCHED_STREAM_K || even <= 0.9 * whole) {
+                pl->stream_k = true;
+                pl->grid = (int)(2 * pairs);
+            }
         }
     }
     pl->flags_bytes = pl->stream_k ? round256((size_t)pl->grid * sizeof(int)) : 0;
@@ -440,7 +458,7 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
         if (ta_packed) ta = *ta_packed;
         int pairs = sms / 2;
         if (pairs < 1) pairs = 1;
-        if (tiles < pairs) pairs = (int)tiles;
+        if (tiles < pairs && !pl.stream_k) pairs = (int)tiles;      // a split last round uses every pair
         const bool wide = pl.sfb_replicas == 4;
         if (pl.mxf4) {
             e = launch_mx_pair_act<256, true, true>(a->activation, ta, tb, tsa, tsb, td, p, pairs, stream);

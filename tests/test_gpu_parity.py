@@ -875,6 +875,51 @@ def test_mx_pair_many_tiles_per_pair(cuda_device, tile_n):
     assert_gemm_ok(got, ref, gold)
 
 
+@pytest.mark.parametrize("M,N,K,tile_n,sm_limit,b_dtype", [
+    (1000, 1544, 384, 256, 6, H.R_8F_E4M3),      # 28 tiles on 3 pairs: the 28th is cut three ways
+    (1000, 1544, 384, 224, 10, H.R_8F_E4M3),     # 224-wide tiles (disjoint accumulators), 5 pairs
+    (512, 1024, 2048, 256, 0, H.R_8F_E4M3),      # 8 tiles on 74 pairs: every tile is shared by about nine pairs
+    (512, 1024, 2048, 256, 0, H.R_4F_E2M1),      # the same with a packed 4-bit weight
+    (300, 520, 4096, 0, 0, H.R_8F_E4M3),         # ragged edges
+])
+def test_mx_pair_last_round_split_along_k(cuda_device, M, N, K, tile_n, sm_limit, b_dtype):
+    """2-CTA tiles: the tiles of the last, partly filled round are cut along K so that every CTA pair gets the same
+    share; partial tiles go through the float32 workspace (handed over dirty) and the pair that holds K step 0 adds
+    them in pair order.  Checked against the float64 reference and for run-to-run bit equality; a second activation
+    matrix on the same workspace must not see the first one's partial tiles."""
+    import torch
+    name = "e2m1" if b_dtype == H.R_4F_E2M1 else "e4m3"
+    MX = H.SCALE_MX_E8M0_VEC32
+    a = o.normal_f32(37, 0, (M, K), 1.0)
+    a2 = o.normal_f32(37, 4, (M, K), 1.0)
+    w = o.normal_f32(37, 1, (N, K), 0.05)
+    bias = o.normal_f32(37, 2, (N,), 0.5)
+    residual = o.normal_f32(37, 3, (M, N), 1.0)
+    qa, sa = H.quantize(dev_tensor(a, cuda_device), MX)
+    qa2, sa2 = H.quantize(dev_tensor(a2, cuda_device), MX)
+    qb, sb = H.quantize(dev_tensor(w, cuda_device), MX, b_dtype)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    outs = []
+    with H.Contraction(M, N, K, scale_mode_a=MX, scale_mode_b=MX, b_dtype=b_dtype, activation=H.OP_GELU, bias=True,
+                       residual=True, tile_n=tile_n, cta_pair=2, sm_limit=sm_limit, split=H.SPLIT_STREAM_K) as c:
+        with H.Contraction(M, N, K, scale_mode_a=MX, scale_mode_b=MX, b_dtype=b_dtype, activation=H.OP_GELU, bias=True,
+                           residual=True, tile_n=tile_n, cta_pair=2, sm_limit=sm_limit,
+                           split=H.SPLIT_DATA_PARALLEL) as whole:
+            assert c.workspace_bytes > whole.workspace_bytes + 128 * 224 * 4          # room for partial tiles
+        ws = torch.full((c.workspace_bytes,), 0xFF, dtype=torch.uint8, device=cuda_device)
+        for qx, sx in ((qa, sa), (qa, sa), (qa2, sa2), (qa, sa)):
+            c(qx, sx, qb, sb, out, bias=bf16_tensor(bias, cuda_device), residual=bf16_tensor(residual, cuda_device),
+              workspace=ws)
+            outs.append(to_np(out).copy())
+    first, second, other, again = outs
+    assert np.array_equal(first.view(np.uint32), second.view(np.uint32)), "the split is not deterministic"
+    assert np.array_equal(first.view(np.uint32), again.view(np.uint32)), "stale partial tiles leaked into a later call"
+    ref, gold = mx_reference(to_np(qa), to_np(sa), to_np(qb), to_np(sb), K, name, o.ACT_GELU_TANH, bias, residual)
+    assert_gemm_ok(first, ref, gold)
+    ref2, gold2 = mx_reference(to_np(qa2), to_np(sa2), to_np(qb), to_np(sb), K, name, o.ACT_GELU_TANH, bias, residual)
+    assert_gemm_ok(other, ref2, gold2)
+
+
 def test_config2_mxfp8_8192_bias_gelu(cuda_device):
     """M=N=K=8192, bf16 bias ~N(0,0.1), GELU(tanh), bf16 out; float64 reference on every 37th row."""
     M = N = K = 8192
