@@ -27,8 +27,10 @@ extern "C" {
 /* Element formats of quantized operands (A8/W8/W4). */
 typedef enum {
     BLAZE_ELEM_E4M3 = 0, /* 8-bit, one byte per element */
-    BLAZE_ELEM_E2M1 = 1  /* 4-bit, two per byte, low nibble = even K index
+    BLAZE_ELEM_E2M1 = 1, /* 4-bit, two per byte, low nibble = even K index
                             (include/blaze/gemm/tile/arch35/shift_w4_to_w8.h:88-99) */
+    BLAZE_ELEM_E5M2 = 2  /* 8-bit, one byte per element: with E4M3 the 8-bit types of the reference's MX operand pairs
+                            (include/tensor_api/impl/tensor_api/arch/utils/check_data_type.h:41-50) */
 } blazeElem_t;
 
 /* Element type of the output D: the cast-on-store modes of the reference's fix pipe
@@ -217,6 +219,48 @@ typedef struct {
 
 BLAZE_API int blazeFp8GemmWorkspaceSize(const blazeFp8GemmArgs* args, size_t* bytes);
 BLAZE_API int blazeFp8Gemm(const blazeFp8GemmArgs* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Unscaled GEMMs of the Blaze surface: INT8 x INT8 with int32 accumulation and de-quantisation on store (A8W8), and
+ * fp16 / bf16 with float32 accumulation.  D = act(A x B^T + bias) + residual; A [M][lda], B [N][ldb], both K-contiguous.
+ * INT8 stands in for GemmUniversal<..., KernelQbmmCube> + BlockMmad<...A8W8FixpipeQuant>
+ * (include/blaze/gemm/kernel/kernel_qbmm_cube.h:43-140, include/blaze/gemm/block/block_mmad_a8w8_fixpipe_quant.h:42-527):
+ * the int32 sum (plus an optional int32 bias per column, the reference's accumulator init) is converted to float32
+ * and multiplied by a scale whose low 13 mantissa bits are cleared, as the reference prepares it for its fix pipe
+ * (DEQ_SCALE_MUL, kernel_qbmm_cube.h:68, :190-220): per tensor scaleA[0] * scaleB[0], or per channel the low 32 bits of
+ * scaleN[n]; BLAZE_DENSE_SCALE_NONE stores the plain conversion, or the raw sums when d_type is BLAZE_OUT_S32 (the
+ * reference's int32 output mode, block_mmad_a8w8_fixpipe_quant.h:228).  The 16-bit kinds stand in for the basic
+ * matmul kernel (include/blaze/gemm/kernel/kernel_matmul_basic.h:32-200).
+ * Constraints: K bytes per row a multiple of 16, N % 8 == 0, lda / ldb (elements) give 16-byte multiples, base pointers
+ * 16-byte aligned, ldd / ldr multiples of 8 elements.  No workspace.
+ * ------------------------------------------------------------------------------------------------------------ */
+typedef enum { BLAZE_DENSE_S8 = 0, BLAZE_DENSE_F16 = 1, BLAZE_DENSE_BF16 = 2 } blazeDenseKind_t;
+typedef enum { BLAZE_DENSE_SCALE_NONE = 0, BLAZE_DENSE_SCALE_PER_TENSOR = 1, BLAZE_DENSE_SCALE_PER_CHANNEL = 2 } blazeDenseScale_t;
+#define BLAZE_OUT_S32 5 /* continues blazeOutType_t: raw int32 sums of an INT8 product */
+
+typedef struct {
+    size_t struct_size;
+    int32_t M, N, K;
+    int32_t kind;           /* blazeDenseKind_t */
+    const void* A;          /* device */
+    int64_t lda;            /* elements between rows of A */
+    const void* B;          /* device */
+    int64_t ldb;            /* elements between rows of B */
+    int32_t scale_mode;     /* blazeDenseScale_t (INT8 only) */
+    int32_t activation;     /* blazeActivation_t */
+    const void* scaleA;     /* device float32[1] (per tensor) */
+    const void* scaleB;     /* device float32[1] (per tensor) */
+    const void* scaleN;     /* device uint64[N] (per channel) */
+    const void* bias;       /* device: int32[N] for INT8, bf16[N] for the 16-bit kinds, or NULL */
+    const void* residual;   /* device bf16 [M][ldr] or NULL */
+    int64_t ldr;
+    void* D;                /* device [M][ldd] */
+    int64_t ldd;
+    int32_t d_type;         /* BLAZE_OUT_BF16 / F16 / F32, or BLAZE_OUT_S32 (INT8 without scale) */
+    int32_t sm_limit;       /* 0 = all SMs */
+} blazeDenseGemmArgs;
+
+BLAZE_API int blazeDenseGemm(const blazeDenseGemmArgs* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Quantisers (fp32 source, round-to-nearest-even, saturating).  The reference has no quantiser; these produce the

@@ -113,6 +113,10 @@ typedef enum {
     ACLTENSOR_SCALE_MX_E8M0_VEC32 = 1, /* one E8M0 byte per 32 K, rows of ceil(K/64)*2 bytes */
     ACLTENSOR_SCALE_FP32_1X128 = 2,    /* one float per 128 K of each row */
     ACLTENSOR_SCALE_FP32_128X128 = 3,  /* one float per 128(K) x 128(N) block, indexed [k_block][n_block] */
+    ACLTENSOR_SCALE_PER_TENSOR = 4,    /* INT8: one float32 for the whole operand (QuantMode PERTENSOR,
+                                          include/blaze/gemm/utils/common_utils.h:98-107) */
+    ACLTENSOR_SCALE_PER_CHANNEL = 5,   /* INT8 B: one 64-bit word per output column, float32 bits in the low word
+                                          (QuantMode PERCHANNEL; the scale array of kernel_qbmm_cube.h:190-192) */
 } acltensorScaleMode_t;
 
 /* B200 addition: tile scheduling hint of a contraction. */

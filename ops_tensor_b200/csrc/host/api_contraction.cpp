@@ -68,8 +68,11 @@ void fill_mx_args(const acltensorOperationDescriptor& op, blazeMxGemmArgs* a) {
     a->M = static_cast<int32_t>(op.M);
     a->N = static_cast<int32_t>(op.N);
     a->K = static_cast<int32_t>(op.K);
-    a->b_elem = op.descB->dataType == ACLTENSOR_R_4F_E2M1 ? BLAZE_ELEM_E2M1 : BLAZE_ELEM_E4M3;
-    a->a_elem = op.descA->dataType == ACLTENSOR_R_4F_E2M1 ? BLAZE_ELEM_E2M1 : BLAZE_ELEM_E4M3;
+    auto elem_of = [](acltensorDataType_t t) {
+        return t == ACLTENSOR_R_4F_E2M1 ? BLAZE_ELEM_E2M1 : (t == ACLTENSOR_R_8F_E5M2 ? BLAZE_ELEM_E5M2 : BLAZE_ELEM_E4M3);
+    };
+    a->b_elem = elem_of(op.descB->dataType);
+    a->a_elem = elem_of(op.descA->dataType);
     a->lda = a->a_elem == BLAZE_ELEM_E2M1 ? op.lda / 2 : op.lda;      // bytes
     a->ldb = a->b_elem == BLAZE_ELEM_E2M1 ? op.ldb / 2 : op.ldb;      // bytes
     a->ldr = op.ldc;
@@ -175,10 +178,68 @@ acltensorStatus_t Fp8Execute(const ContractionArgs& c) {
     return static_cast<acltensorStatus_t>(blazeFp8Gemm(&a, c.stream));
 }
 
+// ---- unscaled solutions: INT8 A8W8 and fp16 / bf16 ----------------------------------------------------------
+
+bool is_dense_type(acltensorDataType_t t) {
+    return t == ACLTENSOR_R_8I || t == ACLTENSOR_R_16F || t == ACLTENSOR_R_16BF;
+}
+
+acltensorStatus_t DenseWorkspace(const acltensorOperationDescriptor& op, int32_t splitPolicy, uint64_t* bytes) {
+    (void)splitPolicy;
+    // whole 256 x 256 tiles per CTA pair: no batch modes, groups, N-major weights or quantised outputs here
+    if (op.batchModes > 0 || op.groupCount > 0 || op.bNMajor) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (op.descD->dataType == ACLTENSOR_R_8F_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (op.splitPolicy == ACLTENSOR_SPLIT_STREAM_K) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    *bytes = 0;
+    return ACLTENSOR_STATUS_SUCCESS;
+}
+
+acltensorStatus_t DenseExecute(const ContractionArgs& c) {
+    const acltensorOperationDescriptor& op = *c.op;
+    blazeDenseGemmArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.struct_size = sizeof(a);
+    a.M = static_cast<int32_t>(op.M);
+    a.N = static_cast<int32_t>(op.N);
+    a.K = static_cast<int32_t>(op.K);
+    a.kind = op.descA->dataType == ACLTENSOR_R_8I ? BLAZE_DENSE_S8
+                                                  : (op.descA->dataType == ACLTENSOR_R_16F ? BLAZE_DENSE_F16 : BLAZE_DENSE_BF16);
+    a.A = c.A;
+    a.lda = op.lda;
+    a.B = c.B;
+    a.ldb = op.ldb;
+    if (op.scaleModeB == ACLTENSOR_SCALE_PER_CHANNEL) {
+        a.scale_mode = BLAZE_DENSE_SCALE_PER_CHANNEL;
+        a.scaleN = c.scaleB;
+    } else if (op.scaleModeA == ACLTENSOR_SCALE_PER_TENSOR) {
+        a.scale_mode = BLAZE_DENSE_SCALE_PER_TENSOR;
+        a.scaleA = c.scaleA;
+        a.scaleB = c.scaleB;
+    }
+    a.activation = activation_of(op.epilogueAct);
+    a.bias = c.bias;
+    a.residual = c.C;
+    a.ldr = op.ldc;
+    a.D = c.D;
+    a.ldd = op.ldd;
+    a.d_type = op.descD->dataType == ACLTENSOR_R_32I ? BLAZE_OUT_S32 : out_type_of(op.descD->dataType);
+    a.sm_limit = op.smLimit;
+    return static_cast<acltensorStatus_t>(blazeDenseGemm(&a, c.stream));
+}
+
 }  // namespace
 
+REGISTER_CONTRACTION_SOLUTION(Int8PerTensor, R_8I, R_8I, PER_TENSOR, PER_TENSOR, 2, DenseWorkspace, DenseExecute);
+REGISTER_CONTRACTION_SOLUTION(Int8PerChannel, R_8I, R_8I, NONE, PER_CHANNEL, 2, DenseWorkspace, DenseExecute);
+REGISTER_CONTRACTION_SOLUTION(Int8Sums, R_8I, R_8I, NONE, NONE, 2, DenseWorkspace, DenseExecute);
+REGISTER_CONTRACTION_SOLUTION(HalfMatmul, R_16F, R_16F, NONE, NONE, 2, DenseWorkspace, DenseExecute);
+REGISTER_CONTRACTION_SOLUTION(Bf16Matmul, R_16BF, R_16BF, NONE, NONE, 2, DenseWorkspace, DenseExecute);
 REGISTER_CONTRACTION_SOLUTION(MxFp8, R_8F_E4M3, R_8F_E4M3, MX_E8M0_VEC32, MX_E8M0_VEC32, 2, MxWorkspace, MxExecute);
 REGISTER_CONTRACTION_SOLUTION(MxW4A8, R_8F_E4M3, R_4F_E2M1, MX_E8M0_VEC32, MX_E8M0_VEC32, 2, MxWorkspace, MxExecute);
+REGISTER_CONTRACTION_SOLUTION(MxE5M2, R_8F_E5M2, R_8F_E5M2, MX_E8M0_VEC32, MX_E8M0_VEC32, 2, MxWorkspace, MxExecute);
+REGISTER_CONTRACTION_SOLUTION(MxE4M3E5M2, R_8F_E4M3, R_8F_E5M2, MX_E8M0_VEC32, MX_E8M0_VEC32, 2, MxWorkspace, MxExecute);
+REGISTER_CONTRACTION_SOLUTION(MxE5M2E4M3, R_8F_E5M2, R_8F_E4M3, MX_E8M0_VEC32, MX_E8M0_VEC32, 2, MxWorkspace, MxExecute);
+REGISTER_CONTRACTION_SOLUTION(MxW4E5M2, R_8F_E5M2, R_4F_E2M1, MX_E8M0_VEC32, MX_E8M0_VEC32, 2, MxWorkspace, MxExecute);
 REGISTER_CONTRACTION_SOLUTION(MxFp4, R_4F_E2M1, R_4F_E2M1, MX_E8M0_VEC32, MX_E8M0_VEC32, 2, MxWorkspace, MxExecute);
 REGISTER_CONTRACTION_SOLUTION(Fp8Block, R_8F_E4M3, R_8F_E4M3, FP32_1X128, FP32_128X128, 0, Fp8Workspace, Fp8Execute);
 
@@ -201,17 +262,28 @@ acltensorStatus_t acltensorCreateContraction(const acltensorHandle_t handle, acl
     const acltensorStatus_t cst = CheckComputeDescriptor(descCompute);
     if (cst != ACLTENSOR_STATUS_SUCCESS) return cst;
 
-    if (descA->dataType != ACLTENSOR_R_8F_E4M3 && descA->dataType != ACLTENSOR_R_4F_E2M1)
-        return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    // operand pairs of the reference (check_data_type.h:41-50) plus the mixed W4A8 pair: no FP4 A with an FP8 B
-    if (descA->dataType == ACLTENSOR_R_4F_E2M1 && descB->dataType != ACLTENSOR_R_4F_E2M1)
-        return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    if (descB->dataType != ACLTENSOR_R_8F_E4M3 && descB->dataType != ACLTENSOR_R_4F_E2M1)
-        return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    // output: the three cast-on-store modes (bf16, half, float32), or E4M3 codes for the quantising epilogue
+    const bool dense = is_dense_type(descA->dataType);
+    if (dense) {
+        // INT8 x INT8 (A8W8) and fp16 / bf16: both operands of one type
+        if (descB->dataType != descA->dataType) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    } else {
+        if (descA->dataType != ACLTENSOR_R_8F_E4M3 && descA->dataType != ACLTENSOR_R_8F_E5M2 &&
+            descA->dataType != ACLTENSOR_R_4F_E2M1)
+            return ACLTENSOR_STATUS_NOT_SUPPORTED;
+        // operand pairs of the reference (check_data_type.h:41-50: every pairing of the two 8-bit types, and FP4 x FP4)
+        // plus the mixed W4A8 pairs: no FP4 A with an 8-bit B
+        if (descA->dataType == ACLTENSOR_R_4F_E2M1 && descB->dataType != ACLTENSOR_R_4F_E2M1)
+            return ACLTENSOR_STATUS_NOT_SUPPORTED;
+        if (descB->dataType != ACLTENSOR_R_8F_E4M3 && descB->dataType != ACLTENSOR_R_8F_E5M2 &&
+            descB->dataType != ACLTENSOR_R_4F_E2M1)
+            return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    }
+    // output: the three cast-on-store modes (bf16, half, float32), E4M3 codes for the quantising epilogue, or the raw
+    // int32 sums of an INT8 product
     if (descD->dataType != ACLTENSOR_R_16BF && descD->dataType != ACLTENSOR_R_16F && descD->dataType != ACLTENSOR_R_32F &&
-        descD->dataType != ACLTENSOR_R_8F_E4M3)
+        descD->dataType != ACLTENSOR_R_8F_E4M3 && !(descD->dataType == ACLTENSOR_R_32I && descA->dataType == ACLTENSOR_R_8I))
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (dense && descD->dataType == ACLTENSOR_R_8F_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (descC != nullptr && descC->dataType != ACLTENSOR_R_16BF) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     // D = [batch..., m, n] with up to four batch modes; A = [its batch modes..., m, k]; B = [its batch modes..., n, k]
     // or, without batch modes in D, [group, n, k].  A batch mode missing from an operand is a broadcast.
@@ -257,7 +329,9 @@ acltensorStatus_t acltensorCreateContraction(const acltensorHandle_t handle, acl
     if (stridesA[aK] != 1 || stridesD[1] != 1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     const bool bNMajor = stridesB[bK] != 1 && stridesB[bN] == 1;
     if (stridesB[bK] != 1 && !bNMajor) return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    if (bNMajor && (groupedB || nBatch > 0 || descB->dataType != ACLTENSOR_R_8F_E4M3)) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (bNMajor && (groupedB || nBatch > 0 ||
+                    (descB->dataType != ACLTENSOR_R_8F_E4M3 && descB->dataType != ACLTENSOR_R_8F_E5M2)))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (descC != nullptr) {
         for (uint32_t i = 0; i < descD->numModes; ++i) {
             if (modeC[i] != fullD[i] || descC->lens[i] != descD->lens[i]) return ACLTENSOR_STATUS_INVALID_VALUE;
@@ -378,13 +452,18 @@ acltensorStatus_t acltensorOperationDescriptorSetAttribute(const acltensorHandle
     switch (attr) {
         case ACLTENSOR_OPERATION_DESCRIPTOR_SCALE_MODE_A:
         case ACLTENSOR_OPERATION_DESCRIPTOR_SCALE_MODE_B:
-            if (v < ACLTENSOR_SCALE_NONE || v > ACLTENSOR_SCALE_FP32_128X128) return ACLTENSOR_STATUS_INVALID_VALUE;
+            if (v < ACLTENSOR_SCALE_NONE || v > ACLTENSOR_SCALE_PER_CHANNEL) return ACLTENSOR_STATUS_INVALID_VALUE;
             break;
         case ACLTENSOR_OPERATION_DESCRIPTOR_EPILOGUE_ACT:
             if (activation_of(v) < 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
             break;
         case ACLTENSOR_OPERATION_DESCRIPTOR_BIAS_TYPE:
-            if (v != -1 && v != ACLTENSOR_R_16BF) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+            // bf16 everywhere, except the int32 bias an INT8 product adds to its sums
+            if (v != -1 && v != ACLTENSOR_R_16BF &&
+                !(v == ACLTENSOR_R_32I && desc->descA != nullptr && desc->descA->dataType == ACLTENSOR_R_8I))
+                return ACLTENSOR_STATUS_NOT_SUPPORTED;
+            if (v == ACLTENSOR_R_16BF && desc->descA != nullptr && desc->descA->dataType == ACLTENSOR_R_8I)
+                return ACLTENSOR_STATUS_NOT_SUPPORTED;
             break;
         case ACLTENSOR_OPERATION_DESCRIPTOR_GROUP_COUNT:
             // the group count is fixed by the rank-3 B descriptor; setting it may only restate that value
@@ -623,7 +702,8 @@ acltensorStatus_t acltensorContract(const acltensorHandle_t handle, const aclten
         else if (op->descC == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     }
     if (use_c && C == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
-    if (aux->scaleA == nullptr || aux->scaleB == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (op->scaleModeA != ACLTENSOR_SCALE_NONE && aux->scaleA == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (op->scaleModeB != ACLTENSOR_SCALE_NONE && aux->scaleB == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (op->biasType >= 0 && aux->bias == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (op->groupCount > 0 && aux->groupList == nullptr) return ACLTENSOR_STATUS_INVALID_VALUE;
     // a quantised D needs its scale mode declared and somewhere to put the scales, and nothing else may ask for them
@@ -722,10 +802,12 @@ acltensorStatus_t acltensorQuantize(const acltensorHandle_t handle, const void* 
     const int32_t r = static_cast<int32_t>(rows), c = static_cast<int32_t>(cols);
     switch (scaleMode) {
         case ACLTENSOR_SCALE_MX_E8M0_VEC32:
-            if (dType != ACLTENSOR_R_8F_E4M3 && dType != ACLTENSOR_R_4F_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+            if (dType != ACLTENSOR_R_8F_E4M3 && dType != ACLTENSOR_R_8F_E5M2 && dType != ACLTENSOR_R_4F_E2M1)
+                return ACLTENSOR_STATUS_NOT_SUPPORTED;
             return static_cast<acltensorStatus_t>(blazeQuantizeMx(
-                src, ldSrc, r, c, dType == ACLTENSOR_R_4F_E2M1 ? BLAZE_ELEM_E2M1 : BLAZE_ELEM_E4M3, codes, ldCodesBytes,
-                scales, stream));
+                src, ldSrc, r, c,
+                dType == ACLTENSOR_R_4F_E2M1 ? BLAZE_ELEM_E2M1 : (dType == ACLTENSOR_R_8F_E5M2 ? BLAZE_ELEM_E5M2 : BLAZE_ELEM_E4M3),
+                codes, ldCodesBytes, scales, stream));
         case ACLTENSOR_SCALE_FP32_1X128:
             if (dType != ACLTENSOR_R_8F_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
             return static_cast<acltensorStatus_t>(

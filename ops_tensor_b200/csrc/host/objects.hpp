@@ -46,8 +46,9 @@ inline size_t GetDataTypeSize(acltensorDataType_t t) { return DataTypeBits(t) / 
 inline bool IsDescriptorTypeSupported(acltensorDataType_t t) {
     switch (t) {
         case ACLTENSOR_R_32F: case ACLTENSOR_R_16BF: case ACLTENSOR_R_16F: case ACLTENSOR_R_8F_E4M3:
-        case ACLTENSOR_R_4F_E2M1:
+        case ACLTENSOR_R_8F_E5M2: case ACLTENSOR_R_4F_E2M1:
         case ACLTENSOR_R_8F_UE8M0: case ACLTENSOR_R_8U: case ACLTENSOR_R_64I:
+        case ACLTENSOR_R_8I: case ACLTENSOR_R_32I:          // INT8 operands and their int32 sums / bias
             return true;
         default:
             return false;

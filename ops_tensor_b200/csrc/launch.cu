@@ -13,6 +13,7 @@
 
 #include "blaze_b200.h"
 #include "cann_ops_tensor_types.h"
+#include "gemm_dense_pair.cuh"
 #include "gemm_fp8.cuh"
 #include "gemm_mx.cuh"
 #include "gemm_mx_pair.cuh"
@@ -198,11 +199,11 @@ static int choose_pair_tile_n(int M, int N, int sms) {
 static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scale_copy = true, bool allow_split = true) {
     if (!a || a->struct_size != sizeof(blazeMxGemmArgs)) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (a->M < 0 || a->N < 0 || a->K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
-    if (a->b_elem != BLAZE_ELEM_E4M3 && a->b_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
-    if (a->a_elem != BLAZE_ELEM_E4M3 && a->a_elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->b_elem < BLAZE_ELEM_E4M3 || a->b_elem > BLAZE_ELEM_E5M2) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->a_elem < BLAZE_ELEM_E4M3 || a->a_elem > BLAZE_ELEM_E5M2) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->d_type < BLAZE_OUT_BF16 || a->d_type > BLAZE_OUT_MX_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if (a->b_layout != BLAZE_B_K_MAJOR && a->b_layout != BLAZE_B_N_MAJOR) return ACLTENSOR_STATUS_INVALID_VALUE;
-    if (a->b_layout == BLAZE_B_N_MAJOR && a->b_elem != BLAZE_ELEM_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->b_layout == BLAZE_B_N_MAJOR && a->b_elem == BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     // legal operand pairs: FP8 x FP8, FP8 x FP4 (W4A8) and FP4 x FP4; a 4-bit A is only read natively
     if (a->a_elem == BLAZE_ELEM_E2M1 && (a->b_elem != BLAZE_ELEM_E2M1 || (a->K % 128) != 0))
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
@@ -408,7 +409,8 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
     p.D = static_cast<__nv_bfloat16*>(a->D);
     p.ldd = a->ldd;
     p.status = status_word;
-    p.b_format = tb_packed ? FMT_E2M1 : FMT_E4M3;
+    // one-byte codes are E4M3 or E5M2 as the caller says (an expanded E2M1 weight holds E4M3 codes)
+    p.b_format = tb_packed ? FMT_E2M1 : (a->b_elem == BLAZE_ELEM_E5M2 ? FMT_E5M2 : FMT_E4M3);
     p.b_tx_shift = tb_packed ? 1 : 0;        // a 4-bit load reports the bytes it read, not the bytes it wrote
     p.stream_k = pl.stream_k ? 1 : 0;
     p.flags = pl.stream_k ? reinterpret_cast<int*>(static_cast<uint8_t*>(a->workspace) + pl.flags_off) : nullptr;
@@ -417,7 +419,7 @@ static int run_mx_kernel(const blazeMxGemmArgs* a, const MxPlan& pl, const uint8
     p.scale_d = static_cast<uint8_t*>(a->scaleD);
     p.scale_cols_d = ((a->N + 63) / 64) * 2;
     if (a->d_type == BLAZE_OUT_MX_E4M3 && (!a->scaleD || (a->ldd % 16) != 0)) return ACLTENSOR_STATUS_INVALID_VALUE;
-    p.a_format = ta_packed ? FMT_E2M1 : FMT_E4M3;
+    p.a_format = ta_packed ? FMT_E2M1 : (a->a_elem == BLAZE_ELEM_E5M2 ? FMT_E5M2 : FMT_E4M3);
     p.a_tx_shift = ta_packed ? 1 : 0;
     p.peer_maps = nullptr;
     p.n_peers = 0;
@@ -879,6 +881,110 @@ extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
     return status_of(e);
 }
 
+// ------------------------------------------------------------------------------------------------ unscaled GEMMs
+
+namespace blaze {
+
+template <int kKind, int kAct>
+static cudaError_t launch_dense_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                                         const DenseGemmParams& p, int pairs, cudaStream_t stream) {
+    constexpr int kStages = 6;
+    using L = DensePairSmem<kStages>;
+    static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory per CTA");
+    auto kernel = dense_gemm_pair_kernel<kKind, kStages, kAct>;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+        if (e != cudaSuccess) return e;
+        attr_done[dev & 63] = true;
+    }
+    return launch_after_prepass(kernel, 2 * pairs, 192, L::kDynamicBytes, stream, ta, tb, td, p);
+}
+
+template <int kKind>
+static cudaError_t launch_dense_act(int act, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                                    const DenseGemmParams& p, int pairs, cudaStream_t stream) {
+    switch (act) {
+        case BLAZE_ACT_RELU: return launch_dense_instance<kKind, ACT_RELU>(ta, tb, td, p, pairs, stream);
+        case BLAZE_ACT_GELU_TANH: return launch_dense_instance<kKind, ACT_GELU_TANH>(ta, tb, td, p, pairs, stream);
+        case BLAZE_ACT_SILU: return launch_dense_instance<kKind, ACT_SILU>(ta, tb, td, p, pairs, stream);
+        case BLAZE_ACT_SIGMOID: return launch_dense_instance<kKind, ACT_SIGMOID>(ta, tb, td, p, pairs, stream);
+        case BLAZE_ACT_TANH: return launch_dense_instance<kKind, ACT_TANH>(ta, tb, td, p, pairs, stream);
+        default: return launch_dense_instance<kKind, ACT_IDENTITY>(ta, tb, td, p, pairs, stream);
+    }
+}
+
+}  // namespace blaze
+
+extern "C" int blazeDenseGemm(const blazeDenseGemmArgs* a, void* stream_v) {
+    if (!a || a->struct_size != sizeof(blazeDenseGemmArgs)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->M < 0 || a->N < 0 || a->K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->kind < BLAZE_DENSE_S8 || a->kind > BLAZE_DENSE_BF16) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->activation < BLAZE_ACT_IDENTITY || a->activation > BLAZE_ACT_TANH) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->scale_mode < BLAZE_DENSE_SCALE_NONE || a->scale_mode > BLAZE_DENSE_SCALE_PER_CHANNEL)
+        return ACLTENSOR_STATUS_INVALID_VALUE;
+    const bool s8 = a->kind == BLAZE_DENSE_S8;
+    if (!s8 && a->scale_mode != BLAZE_DENSE_SCALE_NONE) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    const bool raw = a->d_type == BLAZE_OUT_S32;
+    if (!raw && (a->d_type < BLAZE_OUT_BF16 || a->d_type > BLAZE_OUT_F32)) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    // raw int32 sums: INT8 only, nothing that would touch them as floats
+    if (raw && (!s8 || a->scale_mode != BLAZE_DENSE_SCALE_NONE || a->activation != BLAZE_ACT_IDENTITY || a->residual))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    const int64_t esize = s8 ? 1 : 2;
+    if (((int64_t)a->K * esize) % 16 != 0 || (a->N % 8) != 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    DeviceContext* ctx = current_context();
+    if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    if (ctx->cc_major != 10) return ACLTENSOR_STATUS_ARCH_MISMATCH;
+    if (a->M == 0 || a->N == 0) return ACLTENSOR_STATUS_SUCCESS;
+    if (!a->A || !a->B || !a->D) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->K == 0) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (a->scale_mode == BLAZE_DENSE_SCALE_PER_TENSOR && (!a->scaleA || !a->scaleB)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->scale_mode == BLAZE_DENSE_SCALE_PER_CHANNEL && !a->scaleN) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->lda < a->K || a->ldb < a->K || a->ldd < a->N || (a->residual && a->ldr < a->N))
+        return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (((a->lda * esize) % 16) || ((a->ldb * esize) % 16) || (a->ldd % 8) || (a->residual && (a->ldr % 8)))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (!aligned16(a->A) || !aligned16(a->B) || !aligned16(a->D) || !aligned16(a->bias) || !aligned16(a->residual))
+        return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    DenseGemmParams p;
+    p.M = a->M; p.N = a->N; p.K = a->K;
+    p.m_tiles = (a->M + 255) / 256;
+    p.n_tiles = (a->N + 255) / 256;
+    p.k_steps = (int)(((int64_t)a->K * esize + 127) / 128);
+    p.window = p.m_tiles < 8 ? p.m_tiles : 8;
+    p.scale_mode = a->scale_mode;
+    p.scale_a = static_cast<const float*>(a->scaleA);
+    p.scale_b = static_cast<const float*>(a->scaleB);
+    p.scale_n = static_cast<const unsigned long long*>(a->scaleN);
+    p.bias_i32 = s8 ? static_cast<const int*>(a->bias) : nullptr;
+    p.bias = s8 ? nullptr : static_cast<const __nv_bfloat16*>(a->bias);
+    p.residual = static_cast<const __nv_bfloat16*>(a->residual);
+    p.ldr = a->ldr;
+    p.out_type = a->d_type;
+    p.status = ctx->status_word;
+
+    // operands as rows of bytes (a K block is 128 bytes for either element size); D by its own element type
+    CUtensorMap ta, tb, td;
+    if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K * esize, (uint64_t)a->M, (uint64_t)a->lda * esize, 128) ||
+        !make_tmap_bytes(&tb, a->B, (uint64_t)a->K * esize, (uint64_t)a->N, (uint64_t)a->ldb * esize, 128) ||
+        !make_tmap_store(&td, a->D, (uint64_t)a->N, (uint64_t)a->M, (uint64_t)a->ldd, raw ? BLAZE_OUT_F32 : a->d_type))
+        return ACLTENSOR_STATUS_INTERNAL_ERROR;
+    int sms = ctx->sm_count;
+    if (a->sm_limit > 0 && a->sm_limit < sms) sms = a->sm_limit;
+    int pairs = sms / 2 > 0 ? sms / 2 : 1;
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    if (tiles < pairs) pairs = (int)tiles;
+    cudaError_t e;
+    if (a->kind == BLAZE_DENSE_S8) e = launch_dense_act<DENSE_S8>(a->activation, ta, tb, td, p, pairs, stream);
+    else if (a->kind == BLAZE_DENSE_F16) e = launch_dense_act<DENSE_F16>(a->activation, ta, tb, td, p, pairs, stream);
+    else e = launch_dense_act<DENSE_BF16>(a->activation, ta, tb, td, p, pairs, stream);
+    return status_of(e);
+}
+
 // ------------------------------------------------------------------------------------------------ quantisers & misc
 
 namespace blaze {
@@ -926,7 +1032,7 @@ extern "C" int blazeQuantizeMx(const void* x, int64_t ldx, int32_t rows, int32_t
     if (rows < 0 || K < 0) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (rows == 0 || K == 0) return ACLTENSOR_STATUS_SUCCESS;
     if (!x || !codes || !scales) return ACLTENSOR_STATUS_INVALID_VALUE;
-    if (elem != BLAZE_ELEM_E4M3 && elem != BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;
+    if (elem < BLAZE_ELEM_E4M3 || elem > BLAZE_ELEM_E5M2) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     if ((K % 4) || (ldx % 4) || !aligned16(x)) return ACLTENSOR_STATUS_NOT_SUPPORTED;
     const int64_t min_ld = elem == BLAZE_ELEM_E2M1 ? K / 2 : K;
     if (ldx < K || ld_codes < min_ld) return ACLTENSOR_STATUS_INVALID_VALUE;
@@ -934,7 +1040,7 @@ extern "C" int blazeQuantizeMx(const void* x, int64_t ldx, int32_t rows, int32_t
         return ACLTENSOR_STATUS_NOT_SUPPORTED;
     DeviceContext* ctx = current_context();
     if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;
-    return status_of(launch_quant_mx(static_cast<const float*>(x), ldx, rows, K, elem == BLAZE_ELEM_E2M1,
+    return status_of(launch_quant_mx(static_cast<const float*>(x), ldx, rows, K, elem,
                                      static_cast<uint8_t*>(codes), ld_codes, static_cast<uint8_t*>(scales),
                                      ctx->sm_count, static_cast<cudaStream_t>(stream)));
 }
@@ -1135,7 +1241,7 @@ extern "C" int blazeMxGemmNoAlloc(const blazeMxGemmArgs* a, int32_t* device_stat
         st = plan_mx(a, nd->sm_count, &pl, false, false);
         if (st != ACLTENSOR_STATUS_SUCCESS) return st;
     }
-    if (a->b_elem != BLAZE_ELEM_E4M3) return ACLTENSOR_STATUS_NOT_SUPPORTED;      // packed E2M1 needs an N x K expansion buffer
+    if (a->b_elem == BLAZE_ELEM_E2M1) return ACLTENSOR_STATUS_NOT_SUPPORTED;      // packed E2M1 needs an N x K expansion buffer
     if (a->b_layout != BLAZE_B_K_MAJOR) return ACLTENSOR_STATUS_NOT_SUPPORTED;    // so does the transpose of an N-major B
     if (pl.total > kNoAllocScratchBytes) return ACLTENSOR_STATUS_INSUFFICIENT_WORKSPACE;   // problem too large for the fixed array
     if (a->M == 0 || a->N == 0) return ACLTENSOR_STATUS_SUCCESS;

@@ -26,7 +26,8 @@ inline long long sf_tiled_bytes(int rows, int K, int tile_rows, int replicas = 1
     return tiles * k_steps * atoms * replicas * 512;
 }
 
-cudaError_t launch_quant_mx(const float* x, long long ldx, int rows, int K, bool e2m1, uint8_t* codes,
+// `elem`: 0 = E4M3, 1 = packed E2M1, 2 = E5M2.
+cudaError_t launch_quant_mx(const float* x, long long ldx, int rows, int K, int elem, uint8_t* codes,
                             long long ldc_bytes, uint8_t* scales, int sm_count, cudaStream_t stream);
 cudaError_t launch_quant_fp8_1x128(const float* x, long long ldx, int rows, int K, uint8_t* codes, long long ldc,
                                    float* scales, int sm_count, cudaStream_t stream);

@@ -29,6 +29,13 @@ __device__ __forceinline__ uint32_t cvt_e4m3x4(float x, float y, float z, float 
     return (lo & 0xFFFFu) | (hi << 16);
 }
 
+// Four floats -> four E5M2 bytes.
+__device__ __forceinline__ uint32_t cvt_e5m2x4(float x, float y, float z, float w) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(x, y), __NV_SATFINITE, __NV_E5M2);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(z, w), __NV_SATFINITE, __NV_E5M2);
+    return (lo & 0xFFFFu) | (hi << 16);
+}
+
 // Four floats -> four E2M1 nibbles (x in the lowest).
 __device__ __forceinline__ uint16_t cvt_e2m1x4(float x, float y, float z, float w) {
     const uint32_t lo = __nv_cvt_float2_to_fp4x2(make_float2(x, y), __NV_E2M1, cudaRoundNearest);
@@ -57,7 +64,8 @@ __device__ __forceinline__ void split_index(long long w, int d, int& q, int& r) 
 constexpr int kQuantUnroll = 4;
 
 // Within a chunk 8 lanes share a group of 32, 4 floats per lane.
-template <bool kE2M1>
+// kElem: 0 = E4M3, 1 = packed E2M1, 2 = E5M2 (the values of blazeElem_t).
+template <int kElem>
 __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__ x, long long ldx, int rows, int K,
                                                        uint8_t* __restrict__ codes, long long ldc_bytes,
                                                        uint8_t* __restrict__ scales, int scale_cols) {
@@ -65,7 +73,8 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
     const int items_per_row = (chunks_per_row + kQuantUnroll - 1) / kQuantUnroll;
     const long long total = (long long)rows * items_per_row;
     const int lane = threadIdx.x & 31;
-    const int emax = kE2M1 ? 2 : 8;
+    constexpr bool kE2M1 = kElem == 1;
+    const int emax = kE2M1 ? 2 : (kElem == 2 ? 15 : 8);
     const int n_groups = (K + 31) >> 5;
     const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
     for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < total; w += stride) {
@@ -112,6 +121,8 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
             if (k < K) {
                 if (kE2M1) {
                     *reinterpret_cast<uint16_t*>(code_row + (k >> 1)) = cvt_e2m1x4(q0, q1, q2, q3);
+                } else if (kElem == 2) {
+                    *reinterpret_cast<uint32_t*>(code_row + k) = cvt_e5m2x4(q0, q1, q2, q3);
                 } else {
                     *reinterpret_cast<uint32_t*>(code_row + k) = cvt_e4m3x4(q0, q1, q2, q3);
                 }
@@ -380,16 +391,18 @@ static int grid_for(long long work_items, int per_block, int sm_count) {
     return (int)blocks;
 }
 
-cudaError_t launch_quant_mx(const float* x, long long ldx, int rows, int K, bool e2m1, uint8_t* codes,
+cudaError_t launch_quant_mx(const float* x, long long ldx, int rows, int K, int elem, uint8_t* codes,
                             long long ldc_bytes, uint8_t* scales, int sm_count, cudaStream_t stream) {
     if (rows <= 0 || K <= 0) return cudaSuccess;
     const long long warps = (long long)rows * (((K + 127) / 128 + kQuantUnroll - 1) / kQuantUnroll);
     const int grid = grid_for(warps, 8, sm_count);
     const int scale_cols = ((K + 63) / 64) * 2;
-    if (e2m1)
-        quant_mx_kernel<true><<<grid, 256, 0, stream>>>(x, ldx, rows, K, codes, ldc_bytes, scales, scale_cols);
+    if (elem == 1)
+        quant_mx_kernel<1><<<grid, 256, 0, stream>>>(x, ldx, rows, K, codes, ldc_bytes, scales, scale_cols);
+    else if (elem == 2)
+        quant_mx_kernel<2><<<grid, 256, 0, stream>>>(x, ldx, rows, K, codes, ldc_bytes, scales, scale_cols);
     else
-        quant_mx_kernel<false><<<grid, 256, 0, stream>>>(x, ldx, rows, K, codes, ldc_bytes, scales, scale_cols);
+        quant_mx_kernel<0><<<grid, 256, 0, stream>>>(x, ldx, rows, K, codes, ldc_bytes, scales, scale_cols);
     return cudaGetLastError();
 }
 

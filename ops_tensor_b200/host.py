@@ -20,6 +20,7 @@ OP_SIGMOID, OP_TANH = 11, 12
 ALGO_DEFAULT, ALGO_DEFAULT_PATIENT = -1, -6
 WORKSPACE_MIN, WORKSPACE_DEFAULT, WORKSPACE_MAX = 1, 2, 3
 SCALE_NONE, SCALE_MX_E8M0_VEC32, SCALE_FP32_1X128, SCALE_FP32_128X128 = 0, 1, 2, 3
+SCALE_PER_TENSOR, SCALE_PER_CHANNEL = 4, 5
 SPLIT_AUTO, SPLIT_DATA_PARALLEL, SPLIT_STREAM_K = 0, 1, 2
 (ATTR_SCALE_MODE_A, ATTR_SCALE_MODE_B, ATTR_EPILOGUE_ACT, ATTR_BIAS_TYPE, ATTR_GROUP_COUNT, ATTR_SPLIT_POLICY,
  ATTR_TILE_N, ATTR_SM_LIMIT, ATTR_B_IS_STATIC, ATTR_CTA_PAIR, ATTR_BIAS_PER_BATCH, ATTR_SCALE_MODE_D) = range(1, 13)
@@ -209,7 +210,8 @@ class Contraction:
     def __init__(self, M, N, K, *, scale_mode_a, scale_mode_b, b_dtype=R_8F_E4M3, groups=0, activation=OP_IDENTITY,
                  bias=False, residual=False, split=SPLIT_AUTO, tile_n=0, sm_limit=0, b_is_static=False, cta_pair=0,
                  lda=None, ldb=None, ldd=None, ldc=None, workspace_limit=2 ** 62, batch=(), batch_a=None, batch_b=None,
-                 bias_per_batch=False, a_dtype=R_8F_E4M3, d_dtype=R_16BF, handle=None, algo=ALGO_DEFAULT):
+                 bias_per_batch=False, a_dtype=R_8F_E4M3, d_dtype=R_16BF, handle=None, algo=ALGO_DEFAULT,
+                 bias_dtype=R_16BF):
         self.M, self.N, self.K, self.groups = M, N, K, groups
         # a handle passed in is shared (its plan cache with it) and stays the caller's to destroy
         self._own_handle = handle is None
@@ -264,7 +266,7 @@ class Contraction:
         set_attribute(self.handle, self.op, ATTR_SCALE_MODE_B, scale_mode_b)
         set_attribute(self.handle, self.op, ATTR_EPILOGUE_ACT, activation)
         if bias:
-            set_attribute(self.handle, self.op, ATTR_BIAS_TYPE, R_16BF)
+            set_attribute(self.handle, self.op, ATTR_BIAS_TYPE, bias_dtype)
         set_attribute(self.handle, self.op, ATTR_SPLIT_POLICY, split)
         if tile_n:
             set_attribute(self.handle, self.op, ATTR_TILE_N, tile_n)
@@ -290,7 +292,8 @@ class Contraction:
             if self._workspace is None and self.workspace_bytes:
                 self._workspace = torch.empty(self.workspace_bytes, dtype=torch.uint8, device=a.device)
             workspace = self._workspace
-        aux = ContractionAux(scale_a.data_ptr(), scale_b.data_ptr(), bias.data_ptr() if bias is not None else None,
+        aux = ContractionAux(scale_a.data_ptr() if scale_a is not None else None,
+                             scale_b.data_ptr() if scale_b is not None else None, bias.data_ptr() if bias is not None else None,
                              group_rows.data_ptr() if group_rows is not None else None,
                              scale_out.data_ptr() if scale_out is not None else None)
         if stream is None:

@@ -21,7 +21,7 @@ STATUS_INTERNAL_ERROR = 14
 STATUS_NOT_SUPPORTED = 15
 STATUS_INSUFFICIENT_WORKSPACE = 19
 
-ELEM_E4M3, ELEM_E2M1 = 0, 1
+ELEM_E4M3, ELEM_E2M1, ELEM_E5M2 = 0, 1, 2
 ACT_IDENTITY, ACT_RELU, ACT_GELU_TANH, ACT_SILU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3, 4, 5
 SCHED_AUTO, SCHED_DATA_PARALLEL, SCHED_STREAM_K = 0, 1, 2
 OUT_BF16, OUT_F16, OUT_F32, OUT_MX_E4M3, OUT_FP8_128 = 0, 1, 2, 3, 4
@@ -88,6 +88,28 @@ class Fp8GemmArgs(C.Structure):
     ]
 
 
+class DenseGemmArgs(C.Structure):
+    """blazeDenseGemmArgs: INT8 (A8W8) and fp16 / bf16 GEMMs without block scales."""
+    _fields_ = [
+        ("struct_size", C.c_size_t),
+        ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
+        ("kind", C.c_int32),
+        ("A", C.c_void_p), ("lda", C.c_int64),
+        ("B", C.c_void_p), ("ldb", C.c_int64),
+        ("scale_mode", C.c_int32), ("activation", C.c_int32),
+        ("scaleA", C.c_void_p), ("scaleB", C.c_void_p), ("scaleN", C.c_void_p),
+        ("bias", C.c_void_p),
+        ("residual", C.c_void_p), ("ldr", C.c_int64),
+        ("D", C.c_void_p), ("ldd", C.c_int64),
+        ("d_type", C.c_int32), ("sm_limit", C.c_int32),
+    ]
+
+
+DENSE_S8, DENSE_F16, DENSE_BF16 = 0, 1, 2
+DENSE_SCALE_NONE, DENSE_SCALE_PER_TENSOR, DENSE_SCALE_PER_CHANNEL = 0, 1, 2
+OUT_S32 = 5
+
+
 class BlazeError(RuntimeError):
     def __init__(self, status: int, where: str):
         self.status = status
@@ -119,6 +141,8 @@ def _declare(l: C.CDLL) -> None:
     l.blazeMxGemmBatchedWorkspaceSize.restype = C.c_int
     l.blazeMxGemmBatched.argtypes = [C.POINTER(MxGemmArgs), C.POINTER(BatchDims), C.c_void_p]
     l.blazeMxGemmBatched.restype = C.c_int
+    l.blazeDenseGemm.argtypes = [C.POINTER(DenseGemmArgs), C.c_void_p]
+    l.blazeDenseGemm.restype = C.c_int
     l.blazeFp8GemmWorkspaceSize.argtypes = [C.POINTER(Fp8GemmArgs), C.POINTER(C.c_size_t)]
     l.blazeFp8Gemm.argtypes = [C.POINTER(Fp8GemmArgs), C.c_void_p]
     l.blazeQuantizeMx.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int64,
@@ -328,6 +352,40 @@ def fp8_gemm(a, sa, b, sb, *, out=None, workspace=None, **kw):
             workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
             args.workspace, args.workspace_bytes = workspace.data_ptr(), workspace.numel()
     check(lib().blazeFp8Gemm(C.byref(args), _stream()), "blazeFp8Gemm")
+    return out
+
+
+def dense_gemm(a, b, *, out=None, out_dtype=None, scale_a=None, scale_b=None, scale_n=None, bias=None, residual=None,
+               activation=ACT_IDENTITY, sm_limit=0):
+    """D = act(A x B^T + bias) + residual for int8, half or bf16 operands (A [M, K], B [N, K], K contiguous).
+    int8: `scale_a` and `scale_b` (one float32 each) or `scale_n` (uint64 per column) de-quantise on store, `bias` is
+    int32; with no scale and an int32 `out` the raw sums are stored."""
+    import torch
+    M, K = a.shape
+    N = b.shape[0]
+    kind = {torch.int8: DENSE_S8, torch.float16: DENSE_F16, torch.bfloat16: DENSE_BF16}[a.dtype]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or (torch.float16 if kind != DENSE_BF16 else torch.bfloat16),
+                          device=a.device)
+    args = DenseGemmArgs()
+    args.struct_size = C.sizeof(DenseGemmArgs)
+    args.M, args.N, args.K = M, N, K
+    args.kind = kind
+    args.A, args.lda = a.data_ptr(), a.stride(0)
+    args.B, args.ldb = b.data_ptr(), b.stride(0)
+    args.scale_mode = DENSE_SCALE_PER_CHANNEL if scale_n is not None else (
+        DENSE_SCALE_PER_TENSOR if scale_a is not None else DENSE_SCALE_NONE)
+    args.activation = activation
+    args.scaleA = scale_a.data_ptr() if scale_a is not None else None
+    args.scaleB = scale_b.data_ptr() if scale_b is not None else None
+    args.scaleN = scale_n.data_ptr() if scale_n is not None else None
+    args.bias = bias.data_ptr() if bias is not None else None
+    args.residual = residual.data_ptr() if residual is not None else None
+    args.ldr = residual.stride(0) if residual is not None else 0
+    args.D, args.ldd = out.data_ptr(), out.stride(0)
+    args.d_type = OUT_S32 if out.dtype == torch.int32 else out_type_of(out)
+    args.sm_limit = sm_limit
+    check(lib().blazeDenseGemm(C.byref(args), _stream()), "blazeDenseGemm")
     return out
 
 

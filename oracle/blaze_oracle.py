@@ -36,6 +36,8 @@ import numpy as np
 
 E4M3_MAX = 448.0
 E2M1_MAX = 6.0
+E5M2_MAX = 57344.0
+E5M2_EMAX = 15         # 57344 = 1.75 * 2**15
 E4M3_EMAX = 8          # 448 = 1.75 * 2**8
 E2M1_EMAX = 2          # 6   = 1.5  * 2**2
 MX_GROUP = 32          # elements sharing one E8M0 scale
@@ -59,6 +61,18 @@ def _e2m1_table() -> np.ndarray:
     return np.concatenate([mags, -mags]).astype(np.float32)
 
 
+def _e5m2_table() -> np.ndarray:
+    """Value of every E5M2 code (IEEE-like: exponent 31 is infinity / NaN), as float32."""
+    codes = np.arange(256, dtype=np.uint32)
+    sign = np.where(codes & 0x80, -1.0, 1.0)
+    exp = (codes >> 2) & 0x1F
+    man = codes & 0x3
+    val = np.where(exp == 0, man * 2.0 ** -16, (4 + man) * 2.0 ** (exp.astype(np.float64) - 17))
+    val = np.where(exp == 31, np.where(man == 0, np.inf, np.nan), val)
+    return (sign * val).astype(np.float32)
+
+
+E5M2_VALUES = _e5m2_table()
 E4M3_VALUES = _e4m3_table()
 E2M1_VALUES = _e2m1_table()
 
@@ -94,6 +108,34 @@ def e4m3_encode(x: np.ndarray) -> np.ndarray:
     exp_field = np.where(sub, 0, er + 7).astype(np.int64)
     man_field = np.where(sub, np.rint(r * 2.0 ** 9), np.rint(r / np.exp2(er) * 8.0) - 8).astype(np.int64)
     code = (exp_field << 3) | man_field
+    code = np.where(np.signbit(x), code | 0x80, code)
+    code = np.where(nan, 0x7F, code)
+    return code.astype(np.uint8)
+
+
+def e5m2_decode(codes: np.ndarray) -> np.ndarray:
+    return E5M2_VALUES[np.asarray(codes, dtype=np.uint8)]
+
+
+def e5m2_encode(x: np.ndarray) -> np.ndarray:
+    """float32 -> E5M2 code, round-to-nearest-even, saturating to +-57344 (infinities saturate too).  NaN maps to
+    0x7F.  The sign of zero is kept.  (The second 8-bit element type of the reference's MX operand pairs:
+    include/tensor_api/impl/tensor_api/arch/utils/check_data_type.h:41-50.)"""
+    x = np.asarray(x, dtype=np.float32)
+    a = np.abs(x).astype(np.float64)
+    nan = np.isnan(x)
+    a = np.where(nan, 0.0, np.minimum(a, E5M2_MAX))
+    with np.errstate(divide="ignore"):
+        e = np.floor(np.log2(np.where(a > 0, a, 1.0)))
+    e = np.maximum(e, -14.0)                      # subnormal binade
+    step = np.exp2(e - 2.0)                       # spacing inside the binade (2 mantissa bits)
+    r = np.minimum(np.rint(a / step) * step, E5M2_MAX)
+    with np.errstate(divide="ignore"):
+        er = np.floor(np.log2(np.where(r > 0, r, 1.0)))
+    sub = r < 2.0 ** -14
+    exp_field = np.where(sub, 0, er + 15).astype(np.int64)
+    man_field = np.where(sub, np.rint(r * 2.0 ** 16), np.rint(r / np.exp2(er) * 4.0) - 4).astype(np.int64)
+    code = (exp_field << 2) | man_field
     code = np.where(np.signbit(x), code | 0x80, code)
     code = np.where(nan, 0x7F, code)
     return code.astype(np.uint8)
@@ -211,7 +253,7 @@ def quant_mx(x: np.ndarray, elem: str = "e4m3"):
     """
     x = np.asarray(x, dtype=np.float32)
     rows, K = x.shape
-    emax = E4M3_EMAX if elem == "e4m3" else E2M1_EMAX
+    emax = {"e4m3": E4M3_EMAX, "e5m2": E5M2_EMAX, "e2m1": E2M1_EMAX}[elem]
     ng = -(-K // MX_GROUP)
     xp = np.zeros((rows, ng * MX_GROUP), dtype=np.float32)
     xp[:, :K] = x
@@ -225,6 +267,8 @@ def quant_mx(x: np.ndarray, elem: str = "e4m3"):
     q = (g * inv[:, :, None]).astype(np.float32)
     if elem == "e4m3":
         codes = e4m3_encode(q).reshape(rows, ng * MX_GROUP)[:, :K]
+    elif elem == "e5m2":
+        codes = e5m2_encode(q).reshape(rows, ng * MX_GROUP)[:, :K]
     else:
         assert K % 2 == 0
         codes = e2m1_pack(e2m1_encode(q).reshape(rows, ng * MX_GROUP)[:, :K])
@@ -236,6 +280,8 @@ def quant_mx(x: np.ndarray, elem: str = "e4m3"):
 def dequant_mx(codes: np.ndarray, scales: np.ndarray, K: int, elem: str = "e4m3", dtype=np.float64) -> np.ndarray:
     if elem == "e4m3":
         v = e4m3_decode(codes).astype(dtype)
+    elif elem == "e5m2":
+        v = e5m2_decode(codes).astype(dtype)
     else:
         v = e2m1_decode(e2m1_unpack(codes)).astype(dtype)
     ng = -(-K // MX_GROUP)
@@ -351,6 +397,47 @@ def grouped_matmul_ref(a_deq, b_deq_gnk, group_rows, dtype=np.float64):
             out[r0:r1] = a_deq[r0:r1].astype(dtype) @ b_deq_gnk[g].astype(dtype).T
         r0 = r1
     return out
+
+
+# ------------------------------------------------------------------------------------------------ A8W8 (INT8)
+
+DEQ_SCALE_MASK = 0xFFFFE000     # include/blaze/gemm/kernel/kernel_qbmm_cube.h:68 (DEQ_SCALE_MUL)
+
+
+def masked_scale(scale) -> np.ndarray:
+    """float32 scale(s) with the low 13 mantissa bits cleared, as the reference prepares them for its fix pipe
+    (include/blaze/gemm/kernel/kernel_qbmm_cube.h:190-220)."""
+    bits = np.asarray(scale, dtype=np.float32).view(np.uint32) & np.uint32(DEQ_SCALE_MASK)
+    return bits.view(np.float32)
+
+
+def per_channel_scale_words(scale_f32: np.ndarray) -> np.ndarray:
+    """The per-column scale array the A8W8 kernel takes: one uint64 per column, float32 bits in the low word."""
+    return np.asarray(scale_f32, dtype=np.float32).view(np.uint32).astype(np.uint64)
+
+
+def a8w8_sums(a_i8: np.ndarray, b_i8_nk: np.ndarray, bias_i32=None) -> np.ndarray:
+    """Exact int32 sums of an INT8 product (B given [N][K]) plus the optional int32 bias per column: the accumulator
+    the reference's cube unit holds before its fix pipe (block_mmad_a8w8_fixpipe_quant.h:309, :227-234)."""
+    # float64 holds these integer sums exactly (|sum| <= K * 2^14 < 2^53) and goes through BLAS
+    acc = np.rint(a_i8.astype(np.float64) @ b_i8_nk.astype(np.float64).T).astype(np.int64)
+    if bias_i32 is not None:
+        acc = acc + np.asarray(bias_i32, dtype=np.int64)[None, :]
+    assert np.all(np.abs(acc) < 2 ** 31)
+    return acc.astype(np.int32)
+
+
+def a8w8_ref(a_i8, b_i8_nk, scale=None, bias_i32=None, act=ACT_IDENTITY, residual=None, out=np.float16):
+    """De-quantisation on store, in the reference's golden style (tests/ut/op_kernel/quant_batch_matmul/qbmm_data/
+    gen_data.py:30-40: product in float32, times the scales, cast): float32(int32 sum) * masked scale -> activation ->
+    + residual -> cast.  `scale` is a scalar (per tensor: scaleA * scaleB multiplied in float32 by the caller) or one
+    float32 per column; None stores the plain conversion."""
+    acc = a8w8_sums(a_i8, b_i8_nk, bias_i32).astype(np.float32)          # int32 -> float32, nearest even
+    if scale is not None:
+        acc = acc * masked_scale(scale).reshape(1, -1)
+    y = epilogue(acc.astype(np.float64), None, act, residual).astype(np.float32) if (act != ACT_IDENTITY or residual is not None) else acc
+    with np.errstate(over="ignore"):
+        return bf16_round(y) if out == "bf16" else y.astype(out)
 
 
 def maxrel(y, y64, floor_frac=2.0 ** -7):

@@ -6,6 +6,7 @@
    reference tree (tests/ut/op_kernel/mat_mul/matmul_data/gen_data.py and
    tests/ut/op_kernel/quant_batch_matmul/qbmm_data/gen_data.py), with numpy's global generator seeded so the run is
    repeatable.  They pin the "golden style" the oracle adopts: up-cast to float32, np.matmul, scale, cast.
+   ref_gen_kernels.npz holds further outputs of the same generators at tile-kernel shapes (A8W8 and fp16 matmul).
 2. narrow_float_casts.npz - float32 inputs with the E4M3 / E2M1 codes ml_dtypes assigns them (after the explicit
    clamp that turns its NaN-on-overflow into saturation) and torch's E8M0 encoding of powers of two: independent
    implementations of the public element formats.
@@ -46,6 +47,23 @@ def main():
         a, b, pts, sc, g = qb.gen_qbmm_data(16, 16, 16, tmp)
         out.update(qbmm_a=a, qbmm_b=b, qbmm_pertoken=pts, qbmm_scale=sc, qbmm_golden=g)
     np.savez_compressed(os.path.join(here, "ref_gen_data.npz"), **out)
+
+    # ref_gen_kernels.npz - the same two generators at shapes a GPU tile kernel has to work for (ragged against the
+    # 256 x 256 tiles and the 128-byte K blocks).  The A8W8 goldens are exact: the products are integers and K < 1024
+    # keeps every float32 partial sum below 2^24, so any implementation of int32 accumulate + conversion + cast must
+    # reproduce them bit for bit.  The fp16 golden depends on the summation order and pins results to a few ulp.
+    big = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        np.random.seed(20260104)
+        a, b, pts, sc, g = qb.gen_qbmm_data(300, 264, 96, tmp)
+        big.update(a8w8_300_a=a, a8w8_300_b=b, a8w8_300_golden=g)
+        np.random.seed(20260105)
+        a, b, pts, sc, g = qb.gen_qbmm_data(136, 264, 512, tmp)
+        big.update(a8w8_136_a=a, a8w8_136_b=b, a8w8_136_golden=g)
+        np.random.seed(20260106)
+        a, b, g = mm.gen_matmul_data(136, 264, 160, "float16", tmp)
+        big.update(mm_f16_136_a=a, mm_f16_136_b=b, mm_f16_136_golden=g)
+    np.savez_compressed(os.path.join(here, "ref_gen_kernels.npz"), **big)
 
     import ml_dtypes
     import torch

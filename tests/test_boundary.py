@@ -60,9 +60,9 @@ def test_handle_and_tensor_descriptor_checks(api):
     assert api.acltensorCreateTensorDescriptor(h, None, 2, lens, None, H.R_32F, 0) == H.STATUS_INVALID_VALUE
     assert api.acltensorCreateTensorDescriptor(h, C.byref(d), 2, None, None, H.R_32F, 0) == H.STATUS_INVALID_VALUE
     assert api.acltensorCreateTensorDescriptor(h, C.byref(d), 0, lens, None, H.R_32F, 0) == H.STATUS_INVALID_VALUE
-    for unsupported in (H.R_64F, H.R_8I, H.C_32F, H.R_8F_E5M2):
+    for unsupported in (H.R_64F, H.R_32U, H.C_32F, H.C_64F):
         assert api.acltensorCreateTensorDescriptor(h, C.byref(d), 2, lens, None, unsupported, 0) == H.STATUS_NOT_SUPPORTED
-    for ok in (H.R_32F, H.R_16BF, H.R_16F, H.R_8F_E4M3, H.R_4F_E2M1, H.R_8F_UE8M0, H.R_64I):
+    for ok in (H.R_32F, H.R_16BF, H.R_16F, H.R_8F_E4M3, H.R_4F_E2M1, H.R_8F_UE8M0, H.R_64I, H.R_8I, H.R_32I, H.R_8F_E5M2):
         assert api.acltensorCreateTensorDescriptor(h, C.byref(d), 2, lens, None, ok, 0) == H.STATUS_SUCCESS
         assert api.acltensorDestroyTensorDescriptor(d) == H.STATUS_SUCCESS
     assert api.acltensorDestroy(h) == H.STATUS_SUCCESS

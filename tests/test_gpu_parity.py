@@ -148,7 +148,7 @@ def test_quantisers_bit_exact(cuda_device, rows, K):
         x[2, :] = 0.0                                     # all-zero groups
         x[1, 5] = np.nan                                  # NaN marks its MX group
     xd = dev_tensor(x, cuda_device)
-    for dtype, name in ((H.R_8F_E4M3, "e4m3"), (H.R_4F_E2M1, "e2m1")):
+    for dtype, name in ((H.R_8F_E4M3, "e4m3"), (H.R_4F_E2M1, "e2m1"), (H.R_8F_E5M2, "e5m2")):
         codes, scales = H.quantize(xd, H.SCALE_MX_E8M0_VEC32, dtype)
         want_codes, want_scales = o.quant_mx(x, name)
         assert np.array_equal(to_np(scales), want_scales), name
@@ -373,6 +373,37 @@ def test_mx_shapes_and_tails(cuda_device, M, N, K, tile_n, cta_pair):
     got, qa, sa, qb, sb = run_mx(cuda_device, a, w, tile_n=tile_n, cta_pair=cta_pair)
     ref, gold = mx_reference(qa, sa, qb, sb, K)
     assert_gemm_ok(got, ref, gold)
+
+
+@pytest.mark.parametrize("a_dtype,b_dtype", [(H.R_8F_E5M2, H.R_8F_E5M2), (H.R_8F_E4M3, H.R_8F_E5M2),
+                                             (H.R_8F_E5M2, H.R_8F_E4M3), (H.R_8F_E5M2, H.R_4F_E2M1)])
+@pytest.mark.parametrize("M,N,K,cta_pair", [(300, 520, 1056, 2), (129, 232, 96, 1), (64, 1000, 4096, 1)])
+def test_mx_e5m2_operand_pairs(cuda_device, a_dtype, b_dtype, M, N, K, cta_pair):
+    """The 8-bit operand pairs of the reference's MX matmul (E4M3 or E5M2 on either side:
+    include/tensor_api/impl/tensor_api/arch/utils/check_data_type.h:41-50), plus E5M2 activations on a 4-bit weight:
+    codes and scales bit-equal to the oracle's quantiser, product within tolerance of the float64 reference."""
+    import torch
+    names = {H.R_8F_E4M3: "e4m3", H.R_8F_E5M2: "e5m2", H.R_4F_E2M1: "e2m1"}
+    MX = H.SCALE_MX_E8M0_VEC32
+    a = o.normal_f32(26, 0, (M, K), 1.0) * np.exp2(o.rng_for(26, 5).integers(-8, 9, size=(M, 1))).astype(np.float32)
+    w = o.normal_f32(26, 1, (N, K), 0.05)
+    bias = o.normal_f32(26, 2, (N,), 0.5)
+    qa, sa = H.quantize(dev_tensor(a, cuda_device), MX, a_dtype)
+    qb, sb = H.quantize(dev_tensor(w, cuda_device), MX, b_dtype)
+    ra, rsa = o.quant_mx(a, names[a_dtype])
+    rb, rsb = o.quant_mx(w, names[b_dtype])
+    assert np.array_equal(to_np(qa), ra) and np.array_equal(to_np(sa), rsa)
+    assert np.array_equal(to_np(qb), rb) and np.array_equal(to_np(sb), rsb)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    with H.Contraction(M, N, K, scale_mode_a=MX, scale_mode_b=MX, a_dtype=a_dtype, b_dtype=b_dtype, activation=H.OP_RELU,
+                       bias=True, cta_pair=cta_pair) as c:
+        c(qa, sa, qb, sb, out, bias=bf16_tensor(bias, cuda_device))
+    da = o.dequant_mx(ra, rsa, K, names[a_dtype])
+    db = o.dequant_mx(rb, rsb, K, names[b_dtype])
+    b16 = o.bf16_round(bias)
+    ref = o.matmul_ref64(da, db, b16, o.ACT_RELU)
+    gold = o.matmul_golden32(da.astype(np.float32), db.astype(np.float32), b16, o.ACT_RELU)
+    assert_gemm_ok(to_np(out), ref, gold)
 
 
 def test_mx_single_group_known_answer(cuda_device):

@@ -160,6 +160,52 @@ def test_reference_generator_goldens():
     assert np.allclose(mine, o.bf16_round(d["mm_f32_golden"]), rtol=2.0 ** -7, atol=1e-5)
 
 
+def test_a8w8_oracle_reproduces_the_reference_generator_bit_for_bit():
+    """The INT8 path is the one GEMM whose result the reference's own generator fixes exactly (integer products, every
+    float32 partial sum below 2^24 for K < 1024): the oracle's int32 sum -> float32 -> scale -> float16 must equal it."""
+    d = np.load(os.path.join(GOLDEN, "ref_gen_data.npz"))
+    k = np.load(os.path.join(GOLDEN, "ref_gen_kernels.npz"))
+    cases = [(d["qbmm_a"], d["qbmm_b"], d["qbmm_golden"]), (k["a8w8_300_a"], k["a8w8_300_b"], k["a8w8_300_golden"]),
+             (k["a8w8_136_a"], k["a8w8_136_b"], k["a8w8_136_golden"])]
+    for a, b, golden in cases:
+        b_nk = np.ascontiguousarray(b.T)                       # the generator stores B as [K][N]
+        got = o.a8w8_ref(a, b_nk, scale=np.float32(1.0) * np.float32(1.0))
+        assert got.dtype == np.float16 and np.array_equal(got.view(np.uint16), golden.view(np.uint16))
+        assert np.array_equal(o.a8w8_ref(a, b_nk).view(np.uint16), golden.view(np.uint16))      # no scale at all
+    # the scale loses its low 13 mantissa bits before it is applied (DEQ_SCALE_MUL)
+    s = np.float32(0.0123456789)
+    assert o.masked_scale(s).view(np.uint32) == (s.view(np.uint32) & 0xFFFFE000)
+    a, b = cases[1][0], np.ascontiguousarray(cases[1][1].T)
+    sums = o.a8w8_sums(a, b).astype(np.float32)
+    assert np.array_equal(o.a8w8_ref(a, b, scale=s), (sums * o.masked_scale(s)).astype(np.float16))
+    words = o.per_channel_scale_words(np.full(4, s, dtype=np.float32))
+    assert words.dtype == np.uint64 and int(words[0]) == int(s.view(np.uint32))
+
+
+def test_e5m2_codes_against_an_independent_cast_and_known_answers():
+    """E5M2 (IEEE-like: 5 exponent, 2 mantissa bits), the other 8-bit element type of the reference's MX operand pairs:
+    round to nearest even, saturating at 57344; checked against ml_dtypes' cast after the clamp that turns its
+    overflow-to-infinity into saturation."""
+    import ml_dtypes
+    rng = np.random.default_rng(11)
+    x = np.concatenate([rng.standard_normal(4096).astype(np.float32) * np.float32(s) for s in (1e-5, 1e-3, 1, 300, 3e4)])
+    x = np.concatenate([x, np.array([0.0, -0.0, 57344, 57345, 61440, 65535, 1e9, -1e9, 2.0 ** -16, 2.0 ** -17,
+                                     3 * 2.0 ** -17, 2.0 ** -14, 1.125, 1.375, 1.625, 1.875], dtype=np.float32)])
+    want = np.clip(x, -57344, 57344).astype(ml_dtypes.float8_e5m2).view(np.uint8)
+    got = o.e5m2_encode(x)
+    assert np.array_equal(got, want)
+    finite = np.array([c for c in range(256) if (c >> 2) & 0x1F != 31], dtype=np.uint8)
+    assert np.array_equal(o.e5m2_encode(o.e5m2_decode(finite)), finite)
+    # ties: 1.125 is halfway between 1.0 and 1.25 -> even mantissa (1.0); 1.375 -> 1.5; NaN -> 0x7F
+    assert list(o.e5m2_encode(np.array([1.125, 1.375, np.nan], dtype=np.float32))) == [0x3C, 0x3E, 0x7F]
+    # MX groups of E5M2: the shared exponent leaves the largest element in [2^15, 2^16), values above 57344 saturate
+    xs = np.zeros((1, 32), dtype=np.float32)
+    xs[0, :3] = [60000.0 * 8, 1.0, -3.0]
+    codes, scales = o.quant_mx(xs, "e5m2")
+    assert scales[0, 0] == 127 + 3 and codes[0, 0] == 0x7B                 # 480000 / 8 = 60000 -> 57344
+    assert np.array_equal(o.dequant_mx(codes, scales, 32, "e5m2")[0, 1:3], np.array([1.0, -3.0]))
+
+
 def test_bf16_rounding_is_nearest_even():
     x = np.array([1.0, 1.00390625, 1.01171875, -1.00390625, 3.0e38], dtype=np.float32)
     # 1 + 2^-8 ties to 1.0 (even), 1 + 3*2^-8 ties up to 1 + 2^-6
