@@ -49,6 +49,9 @@ WORKLOADS = {
     "c5": ("fp8sk", 128, 7168, 18432, "stream-K decode FP8 GEMM M=128, N=7168, K=18432 + bf16 residual"),
     # beyond the five configurations: C2's shape with both operands MXFP4, on kind::mxf4
     "c6": ("mxf4", 8192, 8192, 8192, "MXFP4 x MXFP4 GEMM 8192^3 + bf16 bias + GELU(tanh), bf16 out"),
+    # the unscaled GEMMs of the widened surface (single GPU; no end-to-end or CPU legs)
+    "a8w8": ("int8", 8192, 8192, 8192, "INT8 x INT8 GEMM 8192^3, de-quantised on store, half out"),
+    "bf16": ("bf16", 8192, 8192, 8192, "bf16 x bf16 GEMM 8192^3, bf16 out"),
 }
 TENSOR_BOUND = ("mx", "mx4", "mxf4")
 L2_BYTES = 126e6
@@ -468,12 +471,17 @@ def graph_of(env, step, count):
     return g
 
 
-def measure(env, step, steps, warmup, min_region_ms=40.0, graph_below_ms=0.2):
+GRAPH_BELOW_MS = [0.2]          # steps shorter than this are replayed from a CUDA graph (0 with --no-graph)
+
+
+def measure(env, step, steps, warmup, min_region_ms=40.0, graph_below_ms=None):
     """Warm-up, clock ramp, then `steps` timed steps (more when the region would be too short for the clock sampler to
     see it).  Steps shorter than `graph_below_ms` are replayed from a CUDA graph of several steps: with eight processes
     on one host the Python call path (tens of microseconds) would otherwise be what is timed.
     Returns (ms per step, steps timed, clock record, info)."""
     torch = env.torch
+    if graph_below_ms is None:
+        graph_below_ms = GRAPH_BELOW_MS[0]
     step()                                           # first call: module load, workspace allocation
     torch.cuda.synchronize()
     w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -545,6 +553,46 @@ def workload_entry(env, name, case, steps, warmup, peaks):
             "pct_of_published_dense_fp8_peak": round(100.0 * tf / 4500.0, 2),
             "roofline": roofline_of(case, ms, ms * n, peaks), "l2": case.l2_note(), "gpu_launches": case.launches * n,
             "clocks": clocks, **info}
+
+
+def dense_entry(env, label, dtype_name, M, N, K, steps, warmup, peaks):
+    """One of the unscaled GEMMs of the widened surface (INT8 A8W8 with per-tensor de-quantisation to half, or bf16
+    with a bf16 result) on seeded random operands, timed like the other workloads; tensor-bound, so the roofline is
+    the measured bf16 tensor peak (twice that for INT8, which runs at the 8-bit rate)."""
+    torch, native, dev = env.torch, env.native, env.dev
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    if dtype_name == "int8":
+        a = torch.randint(-128, 128, (M, K), dtype=torch.int8, device=dev, generator=g)
+        b = torch.randint(-128, 128, (N, K), dtype=torch.int8, device=dev, generator=g)
+        scale = torch.full((1,), 0.01, dtype=torch.float32, device=dev)
+        out = torch.empty((M, N), dtype=torch.float16, device=dev)
+        kw = dict(scale_a=scale, scale_b=scale)
+        abytes, rate = M * K + N * K + 2 * M * N + 8, 2.0
+        what = "INT8 x INT8 GEMM, int32 sums de-quantised on store (per-tensor scale), half out"
+    else:
+        a = torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
+        b = (torch.randn((N, K), device=dev, generator=g) * 0.05).to(torch.bfloat16)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        kw = {}
+        abytes, rate = 2 * (M * K + N * K + M * N), 1.0
+        what = "bf16 x bf16 GEMM, float32 accumulation, bf16 out"
+
+    def step():
+        native.dense_gemm(a, b, out=out, **kw)
+
+    ms, n, clocks, info = measure(env, step, steps, warmup)
+    flops = 2.0 * M * N * K
+    tf = flops / (ms * 1e-3) / 1e12
+    base = peaks["bf16_tflops_sustained"] if ms * n > 1000.0 else peaks["bf16_tflops"]
+    return {"workload": label, "description": f"{what}, {M}x{N}x{K}", "M": M, "N": N, "K": K, "groups": 0,
+            "ms_per_step": ms, "steps": n, "value": tf, "unit": "TFLOPS" if dtype_name != "int8" else "TOPS",
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": rate * base, "unit": "TFLOP/s", "frac": tf / (rate * base),
+                         "traffic": None, "peak_source": peaks["source"],
+                         "peak_is": ("2 x " if rate == 2.0 else "") + "measured bf16 tensor peak",
+                         "algorithmic_bytes": abytes, "flops": flops},
+            "l2": "operands + output exceed the 126 MB L2" if abytes > L2_BYTES else "fits in L2",
+            "gpu_launches": n, "clocks": clocks, **info}
 
 
 def library_mxfp8(env, case, steps):
@@ -758,6 +806,20 @@ def gpu_arm(args):
     wl = args.workload
     strong = args.shard == "strong" and world > 1
 
+    if WORKLOADS[wl][0] in ("int8", "bf16"):
+        kind, M, N, K, desc = WORKLOADS[wl]
+        e = dense_entry(env, wl, kind, M, N, K, steps, warmup, peaks)
+        if rank == 0:
+            print(json.dumps({"metric": "quantized GEMM TFLOPS", "value": e["value"], "unit": "TFLOPS", "n_gpus": 1,
+                              "steps": e["steps"], "warmup": warmup, "ms_per_step": e["ms_per_step"],
+                              "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                              "dtype": "int8" if kind == "int8" else "bf16", "data": "synthetic",
+                              "config": headline_config(wl, M, N, K, 0, 1, "single GPU", {"l2": e["l2"], "launch": e["launch"]}),
+                              "roofline": e["roofline"], "gpu_launches": e["gpu_launches"], "clocks": e["clocks"],
+                              "device_status": H.device_status()}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     full = Case(env, wl)
     if not strong and world > 1:
         # weak form: every rank runs the whole problem on weights of its own (seeded by rank): N replicas
@@ -819,7 +881,6 @@ def gpu_arm(args):
     library = sustained = None
     if world == 1 and not args.kernel_only and wl == "c2":
         library = library_mxfp8(env, full, max(5, min(steps, 50)))
-        sustained = sustained_run(env, full)
         for name, m_rows in (("c1", None), ("c3", None), ("c4", None), ("c5", 16), ("c5", 64), ("c5", 128)):
             c = Case(env, name, m_rows)
             label = name if m_rows is None else f"{name}_m{m_rows}"
@@ -827,6 +888,10 @@ def gpu_arm(args):
             c.close()
             del c
             torch.cuda.empty_cache()
+        # beyond the five configurations: the unscaled GEMMs the same API now serves
+        workloads.append(dense_entry(env, "a8w8_8192", "int8", 8192, 8192, 8192, steps, warmup, peaks))
+        workloads.append(dense_entry(env, "bf16_8192", "bf16", 8192, 8192, 8192, steps, warmup, peaks))
+        sustained = sustained_run(env, full)           # last: it leaves the GPU at its power cap
     status = H.device_status()
 
     if rank == 0:
@@ -901,9 +966,13 @@ def main():
                          "grouped workload; default); weak = every GPU runs the whole problem (N replicas)")
     ap.add_argument("--gather", default="fused", choices=["none", "fused"],
                     help="N > 1, MX workloads: also time the split GEMM with its output gathered on every rank")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every step from the host even when it is short (profiler captures see plain launches)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the headline loop (used for profiler captures): no end-to-end, CPU or other-workload legs")
     args = ap.parse_args()
+    if args.no_graph:
+        GRAPH_BELOW_MS[0] = 0.0
     if args.impl == "reference":
         args.steps = min(args.steps, 20)
         reference_arm(args)

@@ -121,7 +121,7 @@ struct Fp8WorkWalker {
             const int cta = (int)gridDim.x;
             const float whole = (float)((num_tiles + cta - 1) / cta) * (float)p.k_blocks;
             const long long units = (long long)num_tiles * p.k_blocks;
-            const float even = (float)((units + cta - 1) / cta) + 17.0f + (float)cta / (float)num_tiles;
+            const float even = (float)((units + cta - 1) / cta) + 17.0f + 4.7f * (float)cta / (float)num_tiles;
             split = p.k_blocks >= 2 && even < whole;
         }
         next_tile = blockIdx.x;

@@ -250,10 +250,19 @@ static int plan_mx(const blazeMxGemmArgs* a, int sms, MxPlan* pl, bool wide_scal
     pl->grid = (int)(tiles < eff_sms ? (tiles > 0 ? tiles : 1) : eff_sms);
     if (a->sched < BLAZE_SCHED_AUTO || a->sched > BLAZE_SCHED_STREAM_K) return ACLTENSOR_STATUS_INVALID_VALUE;
     if (!pl->pair && allow_split && tiles > 0 && pl->k_steps >= 2 && a->sched != BLAZE_SCHED_DATA_PARALLEL) {
+        // as in plan_fp8: all SMs, or every tile cut into s equal K ranges for the s whose modelled cost (K steps
+        // + fixed cost + 4.7 steps per CTA the owner has to wait for and add) is least
         const long long units = tiles * pl->k_steps;
-        const long long used = units < eff_sms ? units : eff_sms;
+        long long used = units < eff_sms ? units : eff_sms;
         const double whole_tiles = (double)((tiles + eff_sms - 1) / eff_sms) * pl->k_steps;
-        const double split = (double)((units + used - 1) / used) + 17.0 + (double)used / (double)tiles;
+        double split = (double)((units + used - 1) / used) + 17.0 + 4.7 * ((double)used / (double)tiles);
+        for (long long s_cut = 2; s_cut * tiles <= eff_sms && s_cut <= pl->k_steps; ++s_cut) {
+            const double c = (double)((pl->k_steps + s_cut - 1) / s_cut) + 12.0 + 4.7 * (double)(s_cut - 1);
+            if (c < split) {
+                split = c;
+                used = s_cut * tiles;
+            }
+        }
         if (a->sched == BLAZE_SCHED_STREAM_K || split < whole_tiles) {
             pl->stream_k = true;
             pl->grid = (int)used;
@@ -714,19 +723,28 @@ static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
     pl->m_tiles = a->groups > 0 ? (a->M + 127) / 128 + a->groups : (a->M + 127) / 128;   // grouped: upper bound
     const long long tiles = (long long)pl->m_tiles * pl->n_tiles;
     int stream_k = 0;
+    long long split_grid = 0;
     if (a->groups == 0 && tiles > 0 && pl->k_blocks >= 2) {
-        if (a->sched == BLAZE_SCHED_STREAM_K) {
+        // Cost of the schedules in units of one K block on one SM (about 0.35 us).  Whole tiles: rounds x K blocks.
+        // Split along K: the evenly split units, plus a fixed cost (partial tiles through L2, the hand-over marks) and
+        // the owner's serial walk over the other CTAs of its tile, ~1.5 us = 4.7 blocks each (measured: 7 tiles of
+        // 144 blocks cut 21 ways spent 30 us in that walk, 36.8 us in all; cut 6 ways they take 21.2 us).  So the
+        // number of CTAs is chosen too: every tile cut into s equal K ranges (s * tiles CTAs) for the s that costs
+        // least, or all SMs.
+        const long long units = tiles * pl->k_blocks;
+        const double whole_tiles = (double)((tiles + sms - 1) / sms) * pl->k_blocks;
+        long long best_grid = units < sms ? units : sms;
+        double best = (double)((units + best_grid - 1) / best_grid) + 17.0 + 4.7 * ((double)best_grid / (double)tiles);
+        for (long long s_cut = 2; s_cut * tiles <= sms && s_cut <= pl->k_blocks; ++s_cut) {
+            const double c = (double)((pl->k_blocks + s_cut - 1) / s_cut) + 12.0 + 4.7 * (double)(s_cut - 1);
+            if (c < best) {
+                best = c;
+                best_grid = s_cut * tiles;
+            }
+        }
+        if (a->sched == BLAZE_SCHED_STREAM_K || (a->sched == BLAZE_SCHED_AUTO && best < whole_tiles)) {
             stream_k = 1;
-        } else if (a->sched == BLAZE_SCHED_AUTO) {
-            // Cost of both schedules in units of one K block on one SM (about 0.47 us).  Whole tiles: waves x K blocks.
-            // Stream-K: the evenly split units, plus a fixed ~8 us (flag reset launch, partial tiles through L2, flag
-            // hand-over) and the owner's serial walk over the contributors of its tile.  Measured on seven shapes
-            // from 256x512x1024 to 128x7168x18432, the model picks the faster schedule on all of them.
-            const long long units = tiles * pl->k_blocks;
-            const long long used = units < sms ? units : sms;
-            const double whole_tiles = (double)((tiles + sms - 1) / sms) * pl->k_blocks;
-            const double split = (double)((units + used - 1) / used) + 17.0 + (double)used / (double)tiles;
-            if (split < whole_tiles) stream_k = 1;
+            split_grid = best_grid;
         }
     }
     if (a->groups > 0 && tiles > 0 && pl->k_blocks >= 2 && a->sched != BLAZE_SCHED_DATA_PARALLEL) {
@@ -738,7 +756,7 @@ static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
     long long grid = tiles < sms ? tiles : sms;
     if (stream_k) {
         const long long units = tiles * pl->k_blocks;
-        grid = units < sms ? units : sms;
+        grid = split_grid > 0 ? split_grid : (units < sms ? units : sms);
     }
     if (grid < 1) grid = 1;
     pl->grid = (int)grid;
