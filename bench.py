@@ -384,6 +384,8 @@ class Case:
             return f"rotates among {len(self.sets)} copies of every operand ({self.abytes * len(self.sets) / 1e6:.0f} MB)"
         if self.abytes > L2_BYTES:
             return "operands + output exceed the 126 MB L2"
+        if self.kind in TENSOR_BOUND:
+            return "operands + output fit in the 126 MB L2; the kernel is tensor-bound"
         return "fits in L2 (latency-bound configuration)"
 
     # ---- shards of this case (strong scaling): operands are slices of the full problem's device tensors ----------
@@ -519,6 +521,15 @@ def measure(env, step, steps, warmup, min_region_ms=40.0, graph_below_ms=None):
     return total_ms / n, n, clocks, {"clock_ramp_steps": ramp_steps, "launch": launch}
 
 
+def traffic_of(name):
+    """DRAM bytes of one launch of the workload's dominant kernel, from the committed ncu summaries (or None)."""
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if not os.path.exists(tpath):
+        return None
+    with open(tpath) as f:
+        return json.load(f).get(name)
+
+
 def roofline_of(case, ms, total_ms, peaks):
     tensor_bound = case.kind in TENSOR_BOUND
     if tensor_bound:
@@ -532,12 +543,7 @@ def roofline_of(case, ms, total_ms, peaks):
         peak = peaks["hbm_gbs"]
         achieved = case.abytes / (ms * 1e-3) / 1e9
         unit = "GB/s"
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tpath):
-        with open(tpath) as f:
-            t = json.load(f)
-        traffic = t.get(case.wl) if case.M == WORKLOADS[case.wl][1] and case.N == WORKLOADS[case.wl][2] else None
+    traffic = traffic_of(case.wl) if case.M == WORKLOADS[case.wl][1] and case.N == WORKLOADS[case.wl][2] else None
     return {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak, "unit": unit,
             "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
             "peak_is": ("2 x measured bf16 tensor peak (no FP8 entry in MEASURED_PEAKS.json)" if tensor_bound
@@ -588,7 +594,8 @@ def dense_entry(env, label, dtype_name, M, N, K, steps, warmup, peaks):
     return {"workload": label, "description": f"{what}, {M}x{N}x{K}", "M": M, "N": N, "K": K, "groups": 0,
             "ms_per_step": ms, "steps": n, "value": tf, "unit": "TFLOPS" if dtype_name != "int8" else "TOPS",
             "roofline": {"bound": "tensor", "achieved": tf, "peak": rate * base, "unit": "TFLOP/s", "frac": tf / (rate * base),
-                         "traffic": None, "peak_source": peaks["source"],
+                         "traffic": traffic_of(label.split("_")[0]) if (M, N, K) == (8192, 8192, 8192) else None,
+                         "peak_source": peaks["source"],
                          "peak_is": ("2 x " if rate == 2.0 else "") + "measured bf16 tensor peak",
                          "algorithmic_bytes": abytes, "flops": flops},
             "l2": "operands + output exceed the 126 MB L2" if abytes > L2_BYTES else "fits in L2",
