@@ -76,12 +76,15 @@ struct Fp8GemmSmem {
     static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
     static constexpr int kGroupOffset = kMiscOffset + 16;       // int row_start[G+1], int mtile_start[G+1]
     static constexpr int kAmaxOffset = kGroupOffset + 2 * (kFp8MaxGroups + 1) * 4;   // float amax[2 tiles][<= 4 column parts][128]
-    // 16-bit outputs leave through shared memory, one bulk copy of up to 128 contiguous bytes per thread: per promotion
-    // warp 32 rows of up to 64 columns, rows padded by 16 bytes against bank conflicts
+    // 16-bit outputs leave through shared memory.  A promotion warp whose 32 rows may all be written stages them as
+    // two 32 x 32 blocks (64-byte rows, 64-byte swizzle) and one lane hands both to the copy engine as tiled stores.
+    // A warp that must stop at a group's last row, or that also writes to peers, stages plain rows (padded by 16
+    // bytes against bank conflicts) and every thread issues a bulk copy of its own row.
     static constexpr int kStoreRowPitch = 64 * 2 + 16;
-    static constexpr int kStoreOffset = (kAmaxOffset + 2 * 4 * 128 * 4 + 127) & ~127;    // 16-byte vector accesses
-    static_assert(kStoreRowPitch % 16 == 0 && kStoreOffset % 16 == 0, "staged rows are read and written as uint4");
-    static constexpr int kTotal = kStoreOffset + 8 * 32 * kStoreRowPitch;
+    static constexpr int kStoreWarpBytes = 5 * 1024;                                     // >= 32 * kStoreRowPitch, >= 2 * 2048
+    static constexpr int kStoreOffset = (kAmaxOffset + 2 * 4 * 128 * 4 + 1023) & ~1023;  // swizzled blocks: 1 KB aligned
+    static_assert(kStoreRowPitch % 16 == 0 && 32 * kStoreRowPitch <= kStoreWarpBytes, "staged rows are read and written as uint4");
+    static constexpr int kTotal = kStoreOffset + 8 * kStoreWarpBytes;
     static constexpr int kDynamicBytes = kTotal + 1024;
     static constexpr uint32_t kTxBytes = kABytes + kBBytes;
 };
@@ -187,10 +190,19 @@ struct Fp8WorkWalker {
 template <int kStages, int kAct, int kIssuers = 1, int kParts = 2>
 __global__ void __launch_bounds__(128 * kParts + 32 + 32 * kIssuers, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const __grid_constant__ CUtensorMap tmap_d,
                 const Fp8GemmParams p) {
     grid_launch_dependents();        // the next kernel in the stream may start setting up as this one's CTAs retire
     using L = Fp8GemmSmem<kStages>;
     constexpr int kAccStages = L::kAccStages;
+    // With as many operand stages as accumulator stages, block g uses stage g % 4 of both rings, and one barrier says
+    // "go" for it: the 8 promotion warps' "accumulator stage free", the TMA thread's arrival and the tile bytes all
+    // complete the same phase.  The MMA issuer then waits on one barrier per K block instead of two (each wait costs
+    // the issuing thread ~100 cycles of a ~450-cycle iteration).
+#ifndef LAB_MERGED
+#define LAB_MERGED 1
+#endif
+    constexpr bool kMerged = LAB_MERGED && (kStages == kAccStages);
     static_assert(kStages <= L::kDoneBars && kAccStages <= kStages, "see Fp8GemmSmem::kDoneBars");
     static_assert(kParts == 2, "the output staging area holds eight warps' rows");
     constexpr uint32_t kTmemCols = 512;
@@ -221,7 +233,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full_bar[s], 1);
+            mbar_init(&full_bar[s], kMerged ? 1 + 4 * kParts : 1);
         }
         for (int s = 0; s < L::kDoneBars; ++s) mbar_init(&tmem_full_bar[s], 1);
         for (int s = 0; s < kAccStages; ++s) mbar_init(&tmem_empty_bar[s], kPromoWarps);
@@ -277,6 +289,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     if (warp == kTmaWarp && lane == 0) {
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_d);
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -353,7 +366,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         // A K block has its own accumulator stage, so blocks are independent and kIssuers threads (one per warp) take
         // them in turn: while one thread polls its barriers the other's MMAs keep the tensor core busy (the tensor
         // core's instruction queue is too short to cover one thread's waits).
-        static_assert(kIssuers == 1 || (Fp8GemmSmem<kStages>::kAccStages % kIssuers) == 0, "issuers own whole stages");
         if (lane == 0) {
             Fp8WorkWalker walk(p, row_start, mtile_start);
             Fp8Segment seg;
@@ -370,8 +382,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
                     if (kIssuers == 1 || (g % kIssuers) == my_turn) {
                         const uint32_t acc = g & 3;
-                        ok = mbar_wait_addr(tempty0 + acc * 8, ((g >> 2) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
-                        if (!ok) break;
+                        if (!kMerged) {
+                            ok = mbar_wait_addr(tempty0 + acc * 8, ((g >> 2) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                            if (!ok) break;
+                        }
                         ok = mbar_wait_addr(full0 + stage * 8, phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
                         if (!ok) break;
                         tcgen05_fence_after();
@@ -416,6 +430,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             }
         };
         Fp8Segment next_seg;
+        if (kMerged && lane == 0) {                     // the first use of each stage finds its accumulator free
+            for (int i = 0; i < kAccStages; ++i) mbar_arrive(&full_bar[i]);
+        }
         bool have = walk.next(seg);
         if (have) fetch_first_scales(seg);
         for (; ok && have; seg = next_seg) {
@@ -428,17 +445,24 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < kCols; ++j) accum[j] = 0.0f;
             for (int kb0 = seg.kb0; kb0 < seg.kb1 && ok; kb0 += kScaleAhead) {
+                // The scales of this batch of blocks were requested a batch ago: their products are taken out of the
+                // load registers BEFORE the next batch is requested, so that nothing inside the batch waits on a
+                // scoreboard that a load still in flight shares.
+                float s_cur[kScaleAhead];
+#pragma unroll
+                for (int u = 0; u < kScaleAhead; ++u) s_cur[u] = sa_q[u] * sb_q[u];
+#pragma unroll
+                for (int u = 0; u < kScaleAhead; ++u) {
+                    const int kq = kb0 + kScaleAhead + u;
+                    const bool in = row_ok && kq < seg.kb1;
+                    sa_q[u] = in ? __ldg(sa_row + kq) : 0.0f;
+                    sb_q[u] = in ? __ldg(sb_col + (long long)kq * p.n_blocks) : 0.0f;
+                }
 #pragma unroll
                 for (int u = 0; u < kScaleAhead; ++u) {
                     const int kb = kb0 + u;
                     if (kb >= seg.kb1) break;                                   // uniform across the CTA
-                    const float s = sa_q[u] * sb_q[u];
-                    {
-                        const int kq = kb + kScaleAhead;
-                        const bool in = row_ok && kq < seg.kb1;
-                        sa_q[u] = in ? __ldg(sa_row + kq) : 0.0f;
-                        sb_q[u] = in ? __ldg(sb_col + (long long)kq * p.n_blocks) : 0.0f;
-                    }
+                    const float s = s_cur[u];
                     const int acc = (int)(g & 3);
                     ok = mbar_wait(&tmem_full_bar[g & 7], (g >> 3) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
                     ok = __all_sync(0xffffffffu, ok);
@@ -451,13 +475,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                         tmem_ld_wait();
                         tcgen05_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);    // the block is in registers: free the stage
+                        if (lane == 0) mbar_arrive(kMerged ? &full_bar[acc] : &tmem_empty_bar[acc]);    // the block is in registers: free the stage
 #pragma unroll
                         for (int e = 0; e < kCols; e += 2) fma_f32x2(accum[e], accum[e + 1], v[e], v[e + 1], s);
                     } else {
                         tcgen05_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+                        if (lane == 0) mbar_arrive(kMerged ? &full_bar[acc] : &tmem_empty_bar[acc]);
                     }
                     ++g;
                 }
@@ -610,29 +634,62 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 }
             } else if (p.out_type != OUT_F32) {
                 // bf16 / f16: a thread holds kCols consecutive outputs of one row, so storing from registers would touch
-                // 32 different lines per instruction (2.2 us per 128x128 tile, a fifth of a 16-block tile's time).  Each
-                // thread writes its row into shared memory instead and hands it to the copy engine as one bulk copy of
-                // up to 128 contiguous bytes.
-                uint8_t* my_row = smem + L::kStoreOffset + (warp * 32 + lane) * L::kStoreRowPitch;
-                tma_store_wait_read<0>();                        // the previous tile's copy has read the row
-#pragma unroll
-                for (int q = 0; q < kCols / 8; ++q) {
-                    const float* x = accum + q * 8;
-                    uint4 o;
-                    if (p.out_type == OUT_F16) {
-                        o = make_uint4(pack_f16(x[0], x[1]), pack_f16(x[2], x[3]), pack_f16(x[4], x[5]), pack_f16(x[6], x[7]));
-                    } else {
-                        o = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
-                    }
-                    *reinterpret_cast<uint4*>(my_row + q * 16) = o;
-                }
-                fence_proxy_async();                             // the copy engine reads what this thread just wrote
+                // 32 different lines per instruction (2.2 us per 128x128 tile).  The rows go through shared memory to
+                // the copy engine instead.
+                uint8_t* warp_stage = smem + L::kStoreOffset + warp * L::kStoreWarpBytes;
                 const int n0 = seg.nt * 128 + c0;
-                if (row_ok && n0 < p.N) {
-                    const uint32_t bytes = (uint32_t)min(kCols, p.N - n0) * 2u;      // N is a multiple of 8
-                    const long long at = ((long long)row * p.ldd + n0) * 2;
-                    bulk_store(reinterpret_cast<uint8_t*>(p.D) + at, my_row, bytes);
-                    for (int q = 0; q < p.n_peers; ++q) bulk_store(p.peer_d[q] + at, my_row, bytes);
+                const int warp_row0 = seg.m0 + quad * 32;
+                tma_store_wait_read<0>();                        // the previous tile's copies have read the staging area
+                __syncwarp();
+                // tiled stores clip at the matrix edges only: usable when no row of this warp lies beyond the group's
+                // end (the next group's rows start there) - and 256 row copies per tile kept the copy engine busy for
+                // ~4000 cycles in which the promotion warps could not start the next tile
+                const bool tiled = p.n_peers == 0 && (p.groups == 0 || warp_row0 + 32 <= seg.row_end);
+                if (tiled) {
+                    const int sw = (lane >> 1) & 3;              // 64-byte swizzle: 16-byte slot ^= (row / 2) % 4
+#pragma unroll
+                    for (int h = 0; h < kCols / 32; ++h) {
+                        uint8_t* my_row = warp_stage + h * 2048 + lane * 64;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float* x = accum + h * 32 + q * 8;
+                            uint4 o;
+                            if (p.out_type == OUT_F16) {
+                                o = make_uint4(pack_f16(x[0], x[1]), pack_f16(x[2], x[3]), pack_f16(x[4], x[5]), pack_f16(x[6], x[7]));
+                            } else {
+                                o = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+                            }
+                            *reinterpret_cast<uint4*>(my_row + ((q ^ sw) << 4)) = o;
+                        }
+                    }
+                    fence_proxy_async();                         // the copy engine reads what this warp just wrote
+                    __syncwarp();
+                    if (lane == 0 && warp_row0 < seg.row_end) {
+#pragma unroll
+                        for (int h = 0; h < kCols / 32; ++h) {
+                            if (n0 + 32 * h < p.N) tma_store_2d(&tmap_d, warp_stage + h * 2048, n0 + 32 * h, warp_row0);
+                        }
+                    }
+                } else {
+                    uint8_t* my_row = warp_stage + lane * L::kStoreRowPitch;
+#pragma unroll
+                    for (int q = 0; q < kCols / 8; ++q) {
+                        const float* x = accum + q * 8;
+                        uint4 o;
+                        if (p.out_type == OUT_F16) {
+                            o = make_uint4(pack_f16(x[0], x[1]), pack_f16(x[2], x[3]), pack_f16(x[4], x[5]), pack_f16(x[6], x[7]));
+                        } else {
+                            o = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+                        }
+                        *reinterpret_cast<uint4*>(my_row + q * 16) = o;
+                    }
+                    fence_proxy_async();                         // the copy engine reads what this thread just wrote
+                    if (row_ok && n0 < p.N) {
+                        const uint32_t bytes = (uint32_t)min(kCols, p.N - n0) * 2u;      // N is a multiple of 8
+                        const long long at = ((long long)row * p.ldd + n0) * 2;
+                        bulk_store(reinterpret_cast<uint8_t*>(p.D) + at, my_row, bytes);
+                        for (int q = 0; q < p.n_peers; ++q) bulk_store(p.peer_d[q] + at, my_row, bytes);
+                    }
                 }
                 tma_store_commit();
             } else if (row_ok) {

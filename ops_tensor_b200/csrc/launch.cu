@@ -782,9 +782,12 @@ static unsigned long long next_stream_k_epoch() {
 }
 
 template <int kAct, int kStages>
-static cudaError_t launch_fp8_stages(const CUtensorMap& ta, const CUtensorMap& tb, const Fp8GemmParams& p, int grid,
-                                     cudaStream_t stream) {
-    constexpr int kIssuers = 2;
+static cudaError_t launch_fp8_stages(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                                     const Fp8GemmParams& p, int grid, cudaStream_t stream) {
+#ifndef LAB_ISSUERS
+#define LAB_ISSUERS 2
+#endif
+    constexpr int kIssuers = LAB_ISSUERS;
     using L = Fp8GemmSmem<kStages>;
     static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory per CTA");
     auto kernel = fp8_gemm_kernel<kStages, kAct, kIssuers>;
@@ -798,18 +801,18 @@ static cudaError_t launch_fp8_stages(const CUtensorMap& ta, const CUtensorMap& t
     }
     // behind whatever precedes it in the stream (the kernel that zeroes the fix-up flags, or the previous GEMM): set-up
     // overlaps that kernel's tail, every thread waits for it before the role loops start
-    return launch_after_prepass(kernel, grid, 288 + 32 * kIssuers, L::kDynamicBytes, stream, ta, tb, p);
+    return launch_after_prepass(kernel, grid, 288 + 32 * kIssuers, L::kDynamicBytes, stream, ta, tb, td, p);
 }
 
 template <int kAct>
-static cudaError_t launch_fp8_instance(const CUtensorMap& ta, const CUtensorMap& tb, const Fp8GemmParams& p, int grid,
-                                       cudaStream_t stream) {
+static cudaError_t launch_fp8_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                                       const Fp8GemmParams& p, int grid, cudaStream_t stream) {
     // One tcgen05.commit per K block serves the accumulator ring (4 TMEM stages) and the operand ring.  Two MMA-issuing
     // threads take the K blocks in turn.  Operand stages: 5 when the weights are streamed once by a single row of
     // tiles (decode, C5: 36.7 -> 35.7 us), else 4 (grouped C4: 115 us with 4, 118 us with 5 - those shapes are bound
     // by the L2 -> shared-memory traffic of 128x128 tiles, 32 KB per K block, not by load latency).
-    if (p.groups == 0 && p.m_tiles == 1) return launch_fp8_stages<kAct, 5>(ta, tb, p, grid, stream);
-    return launch_fp8_stages<kAct, 4>(ta, tb, p, grid, stream);
+    if (p.groups == 0 && p.m_tiles == 1) return launch_fp8_stages<kAct, 5>(ta, tb, td, p, grid, stream);
+    return launch_fp8_stages<kAct, 4>(ta, tb, td, p, grid, stream);
 }
 
 }  // namespace blaze
@@ -847,9 +850,12 @@ extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
 
     const int groups = a->groups;
     const uint64_t b_rows = (uint64_t)(groups > 0 ? groups : 1) * (uint64_t)a->N;
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, td;
+    // (the store map is used for 16-bit outputs only; the other output types get a valid map of their own shape)
+    const int td_type = a->d_type == BLAZE_OUT_FP8_128 ? BLAZE_OUT_MX_E4M3 : a->d_type;
     if (!make_tmap_bytes(&ta, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, 128) ||
-        !make_tmap_bytes(&tb, a->B, (uint64_t)a->K, b_rows, (uint64_t)a->ldb, 128))
+        !make_tmap_bytes(&tb, a->B, (uint64_t)a->K, b_rows, (uint64_t)a->ldb, 128) ||
+        !make_tmap_store(&td, a->D, (uint64_t)a->N, (uint64_t)a->M, (uint64_t)a->ldd, td_type))
         return ACLTENSOR_STATUS_INTERNAL_ERROR;
 
     Fp8GemmParams p;
@@ -889,12 +895,12 @@ extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
     }
     cudaError_t e;
     switch (a->activation) {
-        case BLAZE_ACT_RELU: e = launch_fp8_instance<ACT_RELU>(ta, tb, p, pl.grid, stream); break;
-        case BLAZE_ACT_GELU_TANH: e = launch_fp8_instance<ACT_GELU_TANH>(ta, tb, p, pl.grid, stream); break;
-        case BLAZE_ACT_SILU: e = launch_fp8_instance<ACT_SILU>(ta, tb, p, pl.grid, stream); break;
-        case BLAZE_ACT_SIGMOID: e = launch_fp8_instance<ACT_SIGMOID>(ta, tb, p, pl.grid, stream); break;
-        case BLAZE_ACT_TANH: e = launch_fp8_instance<ACT_TANH>(ta, tb, p, pl.grid, stream); break;
-        default: e = launch_fp8_instance<ACT_IDENTITY>(ta, tb, p, pl.grid, stream); break;
+        case BLAZE_ACT_RELU: e = launch_fp8_instance<ACT_RELU>(ta, tb, td, p, pl.grid, stream); break;
+        case BLAZE_ACT_GELU_TANH: e = launch_fp8_instance<ACT_GELU_TANH>(ta, tb, td, p, pl.grid, stream); break;
+        case BLAZE_ACT_SILU: e = launch_fp8_instance<ACT_SILU>(ta, tb, td, p, pl.grid, stream); break;
+        case BLAZE_ACT_SIGMOID: e = launch_fp8_instance<ACT_SIGMOID>(ta, tb, td, p, pl.grid, stream); break;
+        case BLAZE_ACT_TANH: e = launch_fp8_instance<ACT_TANH>(ta, tb, td, p, pl.grid, stream); break;
+        default: e = launch_fp8_instance<ACT_IDENTITY>(ta, tb, td, p, pl.grid, stream); break;
     }
     return status_of(e);
 }
