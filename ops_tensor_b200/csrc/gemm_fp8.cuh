@@ -124,7 +124,7 @@ struct Fp8WorkWalker {
             const int cta = (int)gridDim.x;
             const float whole = (float)((num_tiles + cta - 1) / cta) * (float)p.k_blocks;
             const long long units = (long long)num_tiles * p.k_blocks;
-            const float even = (float)((units + cta - 1) / cta) + 17.0f + 4.7f * (float)cta / (float)num_tiles;
+            const float even = (float)((units + cta - 1) / cta) + 17.0f + 2.8f * (float)cta / (float)num_tiles;
             split = p.k_blocks >= 2 && even < whole;
         }
         next_tile = blockIdx.x;
@@ -516,25 +516,37 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 // -------- owner of a split tile: add the later K ranges in CTA order
                 const long long total = (long long)walk.num_tiles * p.k_blocks;
                 const long long tile_end = (long long)(seg.tile + 1) * p.k_blocks;
+                int j_last = (int)blockIdx.x;                      // last CTA that holds a K range of this tile
                 for (int j = blockIdx.x + 1; j < (int)gridDim.x; ++j) {
-                    const long long lo_j = total * j / gridDim.x;
-                    if (lo_j >= tile_end) break;
-                    if (threadIdx.x == 0) {             // marks to clear when the kernel ends
-                        if (fix_range[1] < 0) fix_range[0] = j;
-                        fix_range[1] = j;
-                    }
-                    const long long t0 = clock64();
-                    while (ld_acquire_gpu_u64(p.flags + j) != p.epoch) {
-                        if (*abort_flag != 0) { ok = false; break; }
-                        if (clock64() - t0 > BLAZE_WAIT_LIMIT_CYCLES) {
-                            *abort_flag = 1;
-                            atomicCAS(p.status, 0, DEV_TIMEOUT_FIXUP_FLAG);
-                            ok = false;
-                            break;
+                    if (total * j / gridDim.x >= tile_end) break;
+                    j_last = j;
+                }
+                if (threadIdx.x == 0 && j_last > (int)blockIdx.x) {     // marks to clear when the kernel ends
+                    fix_range[0] = blockIdx.x + 1;
+                    fix_range[1] = j_last;
+                }
+                // All contributors finish at about the same time, so their marks are polled side by side - one lane
+                // per contributor, every warp for itself - instead of one L2 round trip after the other between the
+                // partial tiles.
+                for (int base = blockIdx.x + 1; base <= j_last && ok; base += 32) {
+                    const int j = base + lane;
+                    if (j <= j_last) {
+                        const long long t0 = clock64();
+                        while (ld_acquire_gpu_u64(p.flags + j) != p.epoch) {
+                            if (*abort_flag != 0) { ok = false; break; }
+                            if (clock64() - t0 > BLAZE_WAIT_LIMIT_CYCLES) {
+                                *abort_flag = 1;
+                                atomicCAS(p.status, 0, DEV_TIMEOUT_FIXUP_FLAG);
+                                ok = false;
+                                break;
+                            }
+                            __nanosleep(64);
                         }
-                        __nanosleep(64);
                     }
-                    if (!ok) break;
+                    ok = __all_sync(0xffffffffu, ok);      // re-converges the warp; orders the lanes' later loads
+                }
+                if (!ok) break;
+                for (int j = blockIdx.x + 1; j <= j_last; ++j) {
                     const float* slot = p.partials + (size_t)j * (128 * 128);
                     if (row_ok) {
                         const float4* slot4 = reinterpret_cast<const float4*>(slot) + (size_t)(c0 >> 2) * 128 + r_in_tile;

@@ -7,6 +7,7 @@
 #include <atomic>
 #include <chrono>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <random>
@@ -725,18 +726,19 @@ static int plan_fp8(const blazeFp8GemmArgs* a, int sm_count, Fp8Plan* pl) {
     int stream_k = 0;
     long long split_grid = 0;
     if (a->groups == 0 && tiles > 0 && pl->k_blocks >= 2) {
-        // Cost of the schedules in units of one K block on one SM (about 0.35 us).  Whole tiles: rounds x K blocks.
+        // Cost of the schedules in units of one K block on one SM (about 0.34 us).  Whole tiles: rounds x K blocks.
         // Split along K: the evenly split units, plus a fixed cost (partial tiles through L2, the hand-over marks) and
-        // the owner's serial walk over the other CTAs of its tile, ~1.5 us = 4.7 blocks each (measured: 7 tiles of
-        // 144 blocks cut 21 ways spent 30 us in that walk, 36.8 us in all; cut 6 ways they take 21.2 us).  So the
-        // number of CTAs is chosen too: every tile cut into s equal K ranges (s * tiles CTAs) for the s that costs
-        // least, or all SMs.
+        // 2.8 blocks (~0.9 us) for every other CTA of its tile whose 64 KB partial tile the owner reads and adds
+        // (measured on 7 tiles of 144 blocks, M = 128: cut 2 / 4 / 8 / 16 / 21 ways 30.8 / 21.3 / 18.9 / 22.9 / 27.1 us;
+        // the marks of all contributors are polled side by side, so the walk costs the reads only).  So the number
+        // of CTAs is chosen too: every tile cut into s equal K ranges (s * tiles CTAs) for the s that costs least, or
+        // all SMs.
         const long long units = tiles * pl->k_blocks;
         const double whole_tiles = (double)((tiles + sms - 1) / sms) * pl->k_blocks;
         long long best_grid = units < sms ? units : sms;
-        double best = (double)((units + best_grid - 1) / best_grid) + 17.0 + 4.7 * ((double)best_grid / (double)tiles);
+        double best = (double)((units + best_grid - 1) / best_grid) + 17.0 + 2.8 * ((double)best_grid / (double)tiles);
         for (long long s_cut = 2; s_cut * tiles <= sms && s_cut <= pl->k_blocks; ++s_cut) {
-            const double c = (double)((pl->k_blocks + s_cut - 1) / s_cut) + 12.0 + 4.7 * (double)(s_cut - 1);
+            const double c = (double)((pl->k_blocks + s_cut - 1) / s_cut) + 15.0 + 2.8 * (double)(s_cut - 1);
             if (c < best) {
                 best = c;
                 best_grid = s_cut * tiles;
