@@ -226,6 +226,27 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t acc_phase = 0;
             uint32_t tiles_done = 0;
             bool ok = true;
+            // constant words of the shared-memory descriptors and the four instruction descriptors of a K step
+            const uint32_t smem_base = smem_u32(smem);
+            const uint64_t sw0 = umma_desc_sw128(0);
+            const uint32_t sw_hi = (uint32_t)(sw0 >> 32);
+            const uint32_t sw_lo0 = (uint32_t)sw0 + (smem_base >> 4);
+            const uint32_t sf_hi = (uint32_t)(umma_desc_sf(0) >> 32);
+            const uint32_t sf_lo0 = (smem_base + L::kSfOffset) >> 4;
+            const uint32_t sf_wide_lead = (uint32_t)umma_desc_sf_wide(0, 4 * 512);      // leading-offset field, low word
+            const uint32_t full0 = smem_u32(&full_bar[0]);
+            const uint32_t empty0 = smem_u32(&empty_bar[0]);
+            uint32_t idesc_j[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if constexpr (kMxf4) {
+                    const uint32_t id = (uint32_t)(j & 1) * 2;
+                    idesc_j[j] = umma_idesc_mx(FMT_MXF4_E2M1, FMT_MXF4_E2M1, 256, kBN, id, id);
+                } else {
+                    idesc_j[j] = umma_idesc_mx(p.a_format, p.b_format, 256, kBN, j, j);
+                }
+            }
+            auto desc_of = [](uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; };
             MxPairWalker walk(p, num_tiles, pair, num_pairs);
             MxSegment seg;
             while (ok && walk.next(seg)) {
@@ -241,51 +262,48 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 const uint32_t d_tmem = tmem_base + acc * kAccStride;
                 for (int ks = seg.ks0; ks < seg.ks1; ++ks) {
                     const int first = ks == seg.ks0 ? 0 : 1;          // the segment's first MMA overwrites the accumulator
-                    ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
+                    ok = mbar_wait_addr(full0 + stage * 8, phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
                     tcgen05_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
-                    const uint32_t b_addr = a_addr + L::kABytes;
-                    const uint32_t sfa_addr = smem_u32(smem + L::kSfOffset + stage * (L::kSfaBytes + L::kSfbBytes));
-                    const uint32_t sfb_addr = sfa_addr + L::kSfaBytes;
-                    const uint64_t a_desc = umma_desc_sw128(a_addr);
-                    const uint64_t b_desc = umma_desc_sw128(b_addr);
+                    // descriptors from precomputed words: this thread's instruction count, not the tensor core, set the
+                    // pace of a K step when every descriptor was rebuilt from its address
+                    const uint32_t a_lo = sw_lo0 + stage * (L::kStageBytes >> 4);
+                    const uint32_t b_lo = a_lo + (L::kABytes >> 4);
+                    const uint32_t sfa_lo = sf_lo0 + stage * ((L::kSfaBytes + L::kSfbBytes) >> 4);
+                    const uint32_t sfb_lo = sfa_lo + (L::kSfaBytes >> 4);
                     if constexpr (kMxf4) {
                         // two 128-K scale blocks per stage: A's by the broadcasting copy, B's two atoms by one wide copy
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            utccp_sf<2>(tmem_base + kSfaCol + 4 * h, umma_desc_sf(sfa_addr + 512 * h));
+                            utccp_sf<2>(tmem_base + kSfaCol + 4 * h, desc_of(sfa_lo + (512 >> 4) * h, sf_hi));
                             utccp_sf_wide<2>(tmem_base + kSfbCol + 8 * h,
-                                             umma_desc_sf_wide(sfb_addr + h * (L::kSfbBytes / 2), 4 * 512));
+                                             desc_of((sfb_lo + h * ((L::kSfbBytes / 2) >> 4)) | sf_wide_lead, sf_hi));
                         }
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             // K = 64 per instruction = 32 bytes of packed codes; scale bytes 2 (j % 2) and + 1 of
                             // block j / 2
-                            const uint32_t id = (uint32_t)(j & 1) * 2;
-                            umma_mxf4_pair(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
-                                           umma_idesc_mx(FMT_MXF4_E2M1, FMT_MXF4_E2M1, 256, kBN, id, id),
+                            umma_mxf4_pair(d_tmem, desc_of(a_lo + 2 * j, sw_hi), desc_of(b_lo + 2 * j, sw_hi), idesc_j[j],
                                            (first | j) != 0 ? 1u : 0u, tmem_base + kSfaCol + 4 * (j >> 1),
                                            tmem_base + kSfbCol + 8 * (j >> 1));
                         }
                     } else {
-                    utccp_sf<2>(tmem_base + kSfaCol, umma_desc_sf(sfa_addr));
-                    if constexpr (L::kWideSfb) {
-                        utccp_sf_wide<2>(tmem_base + kSfbCol, umma_desc_sf_wide(sfb_addr, 4 * 512));
-                    } else {
+                        utccp_sf<2>(tmem_base + kSfaCol, desc_of(sfa_lo, sf_hi));
+                        if constexpr (L::kWideSfb) {
+                            utccp_sf_wide<2>(tmem_base + kSfbCol, desc_of(sfb_lo | sf_wide_lead, sf_hi));
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < L::kSfbAtoms; ++i) {
-                            utccp_sf<2>(tmem_base + kSfbCol + 4 * i, umma_desc_sf(sfb_addr + 512 * i));
+                            for (int i = 0; i < L::kSfbAtoms; ++i) {
+                                utccp_sf<2>(tmem_base + kSfbCol + 4 * i, desc_of(sfb_lo + (512 >> 4) * i, sf_hi));
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            umma_mx<2>(d_tmem, desc_of(a_lo + 2 * j, sw_hi), desc_of(b_lo + 2 * j, sw_hi), idesc_j[j],
+                                       (first | j) != 0 ? 1u : 0u, tmem_base + kSfaCol, tmem_base + kSfbCol);
                         }
                     }
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        umma_mx<2>(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
-                                   umma_idesc_mx(p.a_format, p.b_format, 256, kBN, j, j), (first | j) != 0 ? 1u : 0u,
-                                   tmem_base + kSfaCol, tmem_base + kSfbCol);
-                    }
-                    }
-                    umma_commit_pair(&empty_bar[stage], 0x3);
+                    umma_commit_pair_addr(empty0 + stage * 8, 0x3);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;

@@ -329,6 +329,13 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
         : "memory");
 }
 
+__device__ __forceinline__ void umma_commit_pair_addr(uint32_t bar, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+        "h"(cta_mask)
+        : "memory");
+}
+
 // Shared-memory operand descriptor for a K-major tile stored with the 128-byte swizzle TMA produces:
 // rows are 128 bytes apart, groups of 8 rows are 1024 bytes apart (stride byte offset), the tile base is
 // 1024-byte aligned and k steps inside the 128-byte row are taken by advancing the start address.
