@@ -219,7 +219,11 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------------ MMA issuer (leader CTA only)
-        if (lane == 0 && cta_rank == 0) {
+        // The whole warp walks the loop and one elected lane issues the tcgen05 instructions: with warp-uniform control
+        // flow the descriptors and addresses live in uniform registers, where those instructions take their operands;
+        // inside a single-lane branch every operand of every instruction was first moved there, and this thread's
+        // instruction stream - not the tensor core - set the pace of a K step.
+        if (cta_rank == 0) {
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -251,10 +255,12 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             MxSegment seg;
             while (ok && walk.next(seg)) {
                 ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 if (kOverlap && tiles_done != 0) {
                     // the previous tile's epilogue must have read the columns this accumulator shares with it
                     ok = mbar_wait(overlap_bar, (tiles_done - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                 }
                 ++tiles_done;
@@ -263,6 +269,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 for (int ks = seg.ks0; ks < seg.ks1; ++ks) {
                     const int first = ks == seg.ks0 ? 0 : 1;          // the segment's first MMA overwrites the accumulator
                     ok = mbar_wait_addr(full0 + stage * 8, phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tcgen05_fence_after();
                     // descriptors from precomputed words: this thread's instruction count, not the tensor core, set the
@@ -271,6 +278,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t b_lo = a_lo + (L::kABytes >> 4);
                     const uint32_t sfa_lo = sf_lo0 + stage * ((L::kSfaBytes + L::kSfbBytes) >> 4);
                     const uint32_t sfb_lo = sfa_lo + (L::kSfaBytes >> 4);
+                    if (elect_one()) {
                     if constexpr (kMxf4) {
                         // two 128-K scale blocks per stage: A's by the broadcasting copy, B's two atoms by one wide copy
 #pragma unroll
@@ -304,10 +312,13 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         }
                     }
                     umma_commit_pair_addr(empty0 + stage * 8, 0x3);
+                    }
+                    __syncwarp();
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                umma_commit_pair(&tmem_full_bar[acc], 0x3);
+                if (elect_one()) umma_commit_pair(&tmem_full_bar[acc], 0x3);
+                __syncwarp();
                 if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
             }
         }
