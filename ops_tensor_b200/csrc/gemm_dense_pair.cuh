@@ -147,7 +147,9 @@ dense_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 
     if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
-        if (lane == 0) {
+        // The whole warp walks the loop and an elected lane issues: with warp-uniform control flow the addresses and
+        // descriptors live in uniform registers, where the copy-engine and tensor-core instructions take their operands.
+        {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -159,19 +161,24 @@ dense_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 const int b_row = nt * kBN + (int)cta_rank * (kBN / 2);
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     uint8_t* a_dst = smem + stage * L::kStageBytes;
-                    if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * L::kTxBytesPerCta);
                     const uint32_t bar = map_to_cta(&full_bar[stage], 0);
-                    tma_load_2d_to_pair_bar(a_dst, &tmap_a, bar, ks * kElemsPerBlock, a_row, kEvictNormal);
-                    tma_load_2d_to_pair_bar(a_dst + L::kABytes, &tmap_b, bar, ks * kElemsPerBlock, b_row, kEvictNormal);
+                    if (elect_one()) {
+                        if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * L::kTxBytesPerCta);
+                        tma_load_2d_to_pair_bar(a_dst, &tmap_a, bar, ks * kElemsPerBlock, a_row, kEvictNormal);
+                        tma_load_2d_to_pair_bar(a_dst + L::kABytes, &tmap_b, bar, ks * kElemsPerBlock, b_row, kEvictNormal);
+                    }
+                    __syncwarp();
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 5) {
-        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
-        if (lane == 0 && cta_rank == 0) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only; whole warp,
+        // elected lane issues)
+        if (cta_rank == 0) {
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -180,25 +187,31 @@ dense_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             constexpr uint32_t idesc = kKind == DENSE_S8 ? umma_idesc_s8(256, kBN) : umma_idesc_f16(kKind == DENSE_BF16, 256, kBN);
             for (int t = pair; t < num_tiles && ok; t += num_pairs) {
                 ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kBN;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
                     const uint64_t a_desc = umma_desc_sw128(a_addr);
                     const uint64_t b_desc = umma_desc_sw128(a_addr + L::kABytes);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {        // 32 bytes of K per instruction = 2 units of 16 bytes
-                        umma_dense_pair<kKind>(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, (ks | j) != 0 ? 1u : 0u);
+                        for (int j = 0; j < 4; ++j) {        // 32 bytes of K per instruction = 2 units of 16 bytes
+                            umma_dense_pair<kKind>(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, (ks | j) != 0 ? 1u : 0u);
+                        }
+                        umma_commit_pair(&empty_bar[stage], 0x3);
                     }
-                    umma_commit_pair(&empty_bar[stage], 0x3);
+                    __syncwarp();
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                umma_commit_pair(&tmem_full_bar[acc], 0x3);
+                if (elect_one()) umma_commit_pair(&tmem_full_bar[acc], 0x3);
+                __syncwarp();
                 if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
             }
         }

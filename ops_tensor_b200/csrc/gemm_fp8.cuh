@@ -310,7 +310,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
     if (warp == kTmaWarp) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // The whole warp walks the loop and an elected lane issues: with warp-uniform control flow the addresses live in
+        // uniform registers, where the copy-engine (and tensor-core) instructions take their operands; inside a
+        // single-lane branch every operand of every such instruction is first moved there.
+        {
             Fp8WorkWalker walk(p, row_start, mtile_start);
             Fp8Segment seg;
             uint32_t stage = 0;
@@ -327,9 +330,12 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 while (early < (uint32_t)kStages && ahead.next(sg)) {
                     for (int kb = sg.kb0; kb < sg.kb1 && early < (uint32_t)kStages; ++kb, ++early) {
                         const uint32_t bar = full0 + early * 8;
-                        mbar_arrive_expect_tx_addr(bar, L::kTxBytes);
-                        tma_load_2d_addr(smem_base + early * L::kStageBytes + L::kABytes, &tmap_b, bar, kb * 128,
-                                         sg.nt * 128, b_hint);
+                        if (elect_one()) {
+                            mbar_arrive_expect_tx_addr(bar, L::kTxBytes);
+                            tma_load_2d_addr(smem_base + early * L::kStageBytes + L::kABytes, &tmap_b, bar, kb * 128,
+                                             sg.nt * 128, b_hint);
+                        }
+                        __syncwarp();
                     }
                 }
             }
@@ -338,8 +344,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 const int b_row = seg.group * p.N + seg.nt * 128;
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
                     if (g < early) {                 // stage armed and B requested above: only A is missing
-                        tma_load_2d_addr(smem_base + stage * L::kStageBytes, &tmap_a, full0 + stage * 8, kb * 128, seg.m0,
-                                         kEvictNormal);
+                        if (elect_one()) {
+                            tma_load_2d_addr(smem_base + stage * L::kStageBytes, &tmap_a, full0 + stage * 8, kb * 128, seg.m0,
+                                             kEvictNormal);
+                        }
+                        __syncwarp();
                         if (++stage == kStages) stage = 0;
                         ++g;
                         continue;
@@ -349,13 +358,17 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     if (g >= (uint32_t)kStages) {
                         const uint32_t d = g - kStages;
                         ok = mbar_wait_addr(tfull0 + (d & 7) * 8, (d >> 3) & 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
+                        ok = __all_sync(0xffffffffu, ok);
                         if (!ok) break;
                     }
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
                     const uint32_t bar = full0 + stage * 8;
-                    mbar_arrive_expect_tx_addr(bar, L::kTxBytes);
-                    tma_load_2d_addr(a_dst, &tmap_a, bar, kb * 128, seg.m0, kEvictNormal);
-                    tma_load_2d_addr(a_dst + L::kABytes, &tmap_b, bar, kb * 128, b_row, b_hint);
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx_addr(bar, L::kTxBytes);
+                        tma_load_2d_addr(a_dst, &tmap_a, bar, kb * 128, seg.m0, kEvictNormal);
+                        tma_load_2d_addr(a_dst + L::kABytes, &tmap_b, bar, kb * 128, b_row, b_hint);
+                    }
+                    __syncwarp();
                     if (++stage == kStages) stage = 0;
                     ++g;
                 }
@@ -366,7 +379,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         // A K block has its own accumulator stage, so blocks are independent and kIssuers threads (one per warp) take
         // them in turn: while one thread polls its barriers the other's MMAs keep the tensor core busy (the tensor
         // core's instruction queue is too short to cover one thread's waits).
-        if (lane == 0) {
+        // (whole warp, elected lane issues: see the TMA producer)
+        {
             Fp8WorkWalker walk(p, row_start, mtile_start);
             Fp8Segment seg;
             uint32_t stage = 0;
@@ -384,14 +398,19 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                         const uint32_t acc = g & 3;
                         if (!kMerged) {
                             ok = mbar_wait_addr(tempty0 + acc * 8, ((g >> 2) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                            ok = __all_sync(0xffffffffu, ok);
                             if (!ok) break;
                         }
                         ok = mbar_wait_addr(full0 + stage * 8, phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
+                        ok = __all_sync(0xffffffffu, ok);
                         if (!ok) break;
                         tcgen05_fence_after();
                         const uint32_t a_lo = desc_lo0 + stage * (L::kStageBytes >> 4);
-                        umma_f8_kblock(tmem_base + acc * 128, a_lo, a_lo + (L::kABytes >> 4), desc_hi, idesc);
-                        umma_commit_addr(tfull0 + (g & 7) * 8);
+                        if (elect_one()) {
+                            umma_f8_kblock(tmem_base + acc * 128, a_lo, a_lo + (L::kABytes >> 4), desc_hi, idesc);
+                            umma_commit_addr(tfull0 + (g & 7) * 8);
+                        }
+                        __syncwarp();
                     }
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                     ++g;

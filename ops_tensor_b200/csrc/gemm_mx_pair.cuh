@@ -180,7 +180,8 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
     if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
-        if (lane == 0) {
+        // (the whole warp walks the loop, an elected lane issues: see the MMA issuer below)
+        {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -198,21 +199,25 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 const int sfb_row = nt * p.sf_k_steps * L::kSfbBlocksPerK;
                 for (int ks = seg.ks0; ks < seg.ks1; ++ks) {
                     ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     uint8_t* a_dst = smem + stage * L::kStageBytes;
                     uint8_t* b_dst = a_dst + L::kABytes;
                     uint8_t* sfa_dst = smem + L::kSfOffset + stage * (L::kSfaBytes + L::kSfbBytes);
                     uint8_t* sfb_dst = sfa_dst + L::kSfaBytes;
-                    if (cta_rank == 0) {
-                        mbar_arrive_expect_tx(&full_bar[stage], 2 * (L::kTxBytesPerCta - L::kBHalfBytes - L::kABytes +
-                                                                     (L::kBHalfBytes >> p.b_tx_shift) +
-                                                                     (L::kABytes >> p.a_tx_shift)));
-                    }
                     const uint32_t bar = map_to_cta(&full_bar[stage], 0);
-                    tma_load_2d_to_pair_bar(a_dst, &tmap_a, bar, ks * L::kBK, a_row, kEvictNormal);
-                    tma_load_2d_to_pair_bar(b_dst, &tmap_b, bar, ks * L::kBK, b_row, kEvictNormal);
-                    tma_load_2d_to_pair_bar(sfa_dst, &tmap_sfa, bar, 0, sfa_row + ks * L::kSfKPerStage, kEvictNormal);
-                    tma_load_2d_to_pair_bar(sfb_dst, &tmap_sfb, bar, 0, sfb_row + ks * L::kSfbBlocks, kEvictNormal);
+                    if (elect_one()) {
+                        if (cta_rank == 0) {
+                            mbar_arrive_expect_tx(&full_bar[stage], 2 * (L::kTxBytesPerCta - L::kBHalfBytes - L::kABytes +
+                                                                         (L::kBHalfBytes >> p.b_tx_shift) +
+                                                                         (L::kABytes >> p.a_tx_shift)));
+                        }
+                        tma_load_2d_to_pair_bar(a_dst, &tmap_a, bar, ks * L::kBK, a_row, kEvictNormal);
+                        tma_load_2d_to_pair_bar(b_dst, &tmap_b, bar, ks * L::kBK, b_row, kEvictNormal);
+                        tma_load_2d_to_pair_bar(sfa_dst, &tmap_sfa, bar, 0, sfa_row + ks * L::kSfKPerStage, kEvictNormal);
+                        tma_load_2d_to_pair_bar(sfb_dst, &tmap_sfb, bar, 0, sfb_row + ks * L::kSfbBlocks, kEvictNormal);
+                    }
+                    __syncwarp();
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
