@@ -179,7 +179,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // The whole warp walks the loop and an elected lane issues: with warp-uniform control flow the addresses and
+        // descriptors live in uniform registers, where the copy-engine and tensor-core instructions take their operands.
+        {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -193,24 +195,28 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 const uint8_t* sfb_src = p.sfb_tiled + (size_t)nt * p.k_steps * L::kSfbBytes;
                 for (int ks = seg.ks0; ks < seg.ks1; ++ks) {
                     ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     uint8_t* a_dst = smem + stage * L::kStageBytes;
                     uint8_t* b_dst = a_dst + L::kABytes;
                     uint8_t* sfa_dst = smem + L::kSfOffset + stage * (L::kSfaBytes + L::kSfbBytes);
                     uint8_t* sfb_dst = sfa_dst + L::kSfaBytes;
-                    mbar_arrive_expect_tx(&full_bar[stage], L::kTxBytes - L::kBBytes - L::kABytes + (L::kBBytes >> p.b_tx_shift) +
-                                                                 (L::kABytes >> p.a_tx_shift));
-                    tma_load_2d(a_dst, &tmap_a, &full_bar[stage], ks * L::kBK, mt * L::kBM, kEvictNormal);
-                    tma_load_2d(b_dst, &tmap_b, &full_bar[stage], ks * L::kBK, nt * kBN, kEvictNormal);
-                    bulk_load(sfa_dst, sfa_src + (size_t)ks * L::kSfaBytes, L::kSfaBytes, &full_bar[stage]);
-                    bulk_load(sfb_dst, sfb_src + (size_t)ks * L::kSfbBytes, L::kSfbBytes, &full_bar[stage]);
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(&full_bar[stage], L::kTxBytes - L::kBBytes - L::kABytes + (L::kBBytes >> p.b_tx_shift) +
+                                                                     (L::kABytes >> p.a_tx_shift));
+                        tma_load_2d(a_dst, &tmap_a, &full_bar[stage], ks * L::kBK, mt * L::kBM, kEvictNormal);
+                        tma_load_2d(b_dst, &tmap_b, &full_bar[stage], ks * L::kBK, nt * kBN, kEvictNormal);
+                        bulk_load(sfa_dst, sfa_src + (size_t)ks * L::kSfaBytes, L::kSfaBytes, &full_bar[stage]);
+                        bulk_load(sfb_dst, sfb_src + (size_t)ks * L::kSfbBytes, L::kSfbBytes, &full_bar[stage]);
+                    }
+                    __syncwarp();
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 5) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer (whole warp, elected lane issues)
+        {
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -220,17 +226,20 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             MxSegment seg;
             while (ok && walk.next(seg)) {
                 ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kBN;
                 for (int ks = seg.ks0; ks < seg.ks1; ++ks) {
                     ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, DEV_TIMEOUT_SMEM_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
                     const uint32_t b_addr = a_addr + L::kABytes;
                     const uint32_t sfa_addr = smem_u32(smem + L::kSfOffset + stage * (L::kSfaBytes + L::kSfbBytes));
                     const uint32_t sfb_addr = sfa_addr + L::kSfaBytes;
+                    if (elect_one()) {
                     utccp_sf<1>(tmem_base + kSfaCol, umma_desc_sf(sfa_addr));
 #pragma unroll
                     for (int i = 0; i < L::kSfbBytes / 512; ++i) {
@@ -246,10 +255,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                    (ks != seg.ks0 || j != 0) ? 1u : 0u, tmem_base + kSfaCol, tmem_base + kSfbCol);
                     }
                     umma_commit(&empty_bar[stage]);
+                    }
+                    __syncwarp();
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                umma_commit(&tmem_full_bar[acc]);
+                if (elect_one()) umma_commit(&tmem_full_bar[acc]);
+                __syncwarp();
                 if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
             }
         }
