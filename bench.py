@@ -788,6 +788,13 @@ def gather_leg(env, full, part, steps, warmup, gemm_only_ms):
     def step_fused():
         shard.gemm_gather_fused(run_fused, fused)
 
+    def step_fused_allreduce():
+        shard.gemm_gather_fused(run_fused, fused, signal="allreduce")
+
+    for _ in range(warmup):
+        step_fused_allreduce()
+    torch.cuda.synchronize()
+    fused_allreduce_ms = timed_loop(env, step_fused_allreduce, steps) / steps
     for _ in range(warmup):
         step_fused()
     torch.cuda.synchronize()
@@ -798,9 +805,12 @@ def gather_leg(env, full, part, steps, warmup, gemm_only_ms):
     same = torch.equal(fused.gathered[0].view(torch.int16), whole.view(torch.int16))
     flag = torch.tensor([1.0 if same else 0.0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    info.update(fused_ms=fused_ms, bit_equal=bool(flag.item() == 1.0),
+    info.update(fused_ms=fused_ms, fused_with_allreduce_signal_ms=fused_allreduce_ms, bit_equal=bool(flag.item() == 1.0),
+                device_status=env.H.device_status(),
                 how="epilogue TMA-stores every tile to the local and the peers' gathered buffers (symmetric memory); "
-                    "one-element all-reduce behind the GEMM as the closing signal")
+                    "closing signal: a step counter stored into the peers' flag arrays and a bounded wait on this GPU's own "
+                    "(blazePeerSignal; peer stores and local loads only); fused_with_allreduce_signal_ms uses a "
+                    "one-element all-reduce instead")
     return info
 
 

@@ -285,6 +285,27 @@ BLAZE_API int blazeAddF32(const void* A, const void* C, void* D, int64_t n, void
  * no status pointer.  Synchronises the device.  reset != 0 clears it. */
 BLAZE_API int blazeDeviceStatus(int32_t* value, int32_t reset);
 
+/* Closing signal of a fused gather (the GEMM's epilogue stored its tiles into the peers' buffers, `peerD`): tells every
+ * peer "all stores of my launches up to `value` have been issued and completed", and waits until every peer has said
+ * the same.  One CTA, behind the GEMM on `stream`: it stores `value` (system scope, release) into slot `my_rank` of each
+ * peer's flag array - peer STORES only, no load ever reads another GPU's memory - and then polls this GPU's own array
+ * until the slots of all `peer_ranks` hold a value >= `value`.  The wait is bounded (`limit_cycles` SM cycles, <= 2^33;
+ * 0 = ~1 s): when it expires the kernel records code 6 in the device status word and returns.  `value` must grow from
+ * call to call (a step counter); the arrays (uint64 per rank, zero before the first call) live in memory every rank has
+ * mapped, e.g. torch symmetric memory.  Replaces a one-element all-reduce (~14 us of collective launch and handshake).
+ * No counterpart in the reference (its ranks exchange nothing on this path). */
+typedef struct blazePeerSignalArgs {
+    size_t struct_size;                        /* sizeof(blazePeerSignalArgs) */
+    int32_t my_rank;
+    int32_t n_peers;                           /* 1 .. BLAZE_MAX_PEERS */
+    int32_t peer_ranks[BLAZE_MAX_PEERS];       /* rank of peer q (its slot in this GPU's array) */
+    void* local_flags;                         /* this GPU's array, uint64 [ranks] */
+    void* peer_flags[BLAZE_MAX_PEERS];         /* peer q's array as mapped into this process, uint64 [ranks] */
+    uint64_t value;
+    int64_t limit_cycles;
+} blazePeerSignalArgs;
+BLAZE_API int blazePeerSignal(const blazePeerSignalArgs* args, void* stream);
+
 /* Diagnostic of the failure-reporting path (no counterpart in the reference): launches one CTA that waits, for at most
  * `limit_cycles` SM cycles (<= 2^31), on a barrier nothing signals.  The wait expires, the kernel returns normally, and
  * the next blazeDeviceStatus / acltensorGetDeviceStatus reports code 7.  Nothing hangs or faults. */

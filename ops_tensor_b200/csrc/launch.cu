@@ -1157,6 +1157,62 @@ extern "C" int blazeSelfTestWaitTimeout(int64_t limit_cycles, void* stream) {
     return status_of(cudaGetLastError());
 }
 
+// Closing signal of a fused gather: lane q stores `value` into slot `my_rank` of peer q's flag array (release, system
+// scope: the GEMM before this kernel in the stream has completed, its stores into the peer's memory with it), then polls
+// this GPU's own array for peer q's slot.  Peer stores and local loads only.  The wait is bounded.
+struct PeerSignalParams {
+    unsigned long long* local_flags;
+    unsigned long long* peer_flags[BLAZE_MAX_PEERS];
+    int peer_ranks[BLAZE_MAX_PEERS];
+    int n_peers;
+    int my_rank;
+    unsigned long long value;
+    long long limit_cycles;
+    int* status;
+};
+
+__global__ void peer_signal_kernel(const PeerSignalParams p) {
+    const int q = (int)threadIdx.x;
+    if (q >= p.n_peers) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p.peer_flags[q] + p.my_rank), "l"(p.value) : "memory");
+    const unsigned long long* mine = p.local_flags + p.peer_ranks[q];
+    const long long t0 = clock64();
+    for (;;) {
+        unsigned long long seen;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(mine) : "memory");
+        if (seen >= p.value) break;
+        if (clock64() - t0 > p.limit_cycles) {
+            atomicCAS(p.status, 0, blaze::DEV_TIMEOUT_PEER);
+            break;
+        }
+        __nanosleep(100);
+    }
+}
+
+extern "C" int blazePeerSignal(const blazePeerSignalArgs* a, void* stream) {
+    if (!a || a->struct_size < sizeof(blazePeerSignalArgs)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->n_peers < 1 || a->n_peers > BLAZE_MAX_PEERS || !a->local_flags || a->my_rank < 0)
+        return ACLTENSOR_STATUS_INVALID_VALUE;
+    if (a->limit_cycles < 0 || a->limit_cycles > (1LL << 33)) return ACLTENSOR_STATUS_INVALID_VALUE;
+    DeviceContext* ctx = current_context();
+    if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;
+    PeerSignalParams p;
+    p.local_flags = static_cast<unsigned long long*>(a->local_flags);
+    for (int q = 0; q < a->n_peers; ++q) {
+        if (!a->peer_flags[q] || a->peer_ranks[q] < 0 || a->peer_ranks[q] == a->my_rank) return ACLTENSOR_STATUS_INVALID_VALUE;
+        p.peer_flags[q] = static_cast<unsigned long long*>(a->peer_flags[q]);
+        p.peer_ranks[q] = a->peer_ranks[q];
+    }
+    p.n_peers = a->n_peers;
+    p.my_rank = a->my_rank;
+    p.value = a->value;
+    p.limit_cycles = a->limit_cycles > 0 ? a->limit_cycles : (1LL << 31);
+    p.status = ctx->status_word;
+    peer_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return status_of(cudaGetLastError());
+}
+
 extern "C" int blazeDeviceInfo(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor) {
     DeviceContext* ctx = current_context();
     if (!ctx) return ACLTENSOR_STATUS_NOT_INITIALIZED;

@@ -389,6 +389,41 @@ def dense_gemm(a, b, *, out=None, out_dtype=None, scale_a=None, scale_b=None, sc
     return out
 
 
+MAX_PEERS = 7          # BLAZE_MAX_PEERS
+
+
+class PeerSignalArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_size_t),
+        ("my_rank", C.c_int32),
+        ("n_peers", C.c_int32),
+        ("peer_ranks", C.c_int32 * MAX_PEERS),
+        ("local_flags", C.c_void_p),
+        ("peer_flags", C.c_void_p * MAX_PEERS),
+        ("value", C.c_uint64),
+        ("limit_cycles", C.c_int64),
+    ]
+
+
+def peer_signal(local_flags, peer_flags, my_rank: int, peer_ranks, value: int, limit_cycles: int = 0) -> None:
+    """Closing signal of a fused gather (`blazePeerSignal`): stores `value` into slot `my_rank` of every peer's flag
+    array and waits, bounded, until this GPU's own array shows `value` from every peer.  `local_flags`: this rank's
+    int64 tensor [ranks]; `peer_flags`: the peers' arrays as mapped into this process, in the order of `peer_ranks`."""
+    args = PeerSignalArgs()
+    args.struct_size = C.sizeof(PeerSignalArgs)
+    args.my_rank = my_rank
+    args.n_peers = len(peer_flags)
+    for q, (t, r) in enumerate(zip(peer_flags, peer_ranks)):
+        args.peer_flags[q] = t.data_ptr()
+        args.peer_ranks[q] = r
+    args.local_flags = local_flags.data_ptr()
+    args.value = value
+    args.limit_cycles = limit_cycles
+    l = lib()
+    l.blazePeerSignal.restype = C.c_int
+    check(l.blazePeerSignal(C.byref(args), _stream()), "blazePeerSignal")
+
+
 def add_f32(a, c, out=None):
     import torch
     if out is None:

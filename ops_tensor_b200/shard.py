@@ -153,23 +153,39 @@ class PeerGatherBuffers:
                                     for p in range(world)])
             offset += count
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
+        # flag arrays for the closing signal of the fused form (one int64 per rank, in symmetric memory as well)
+        self.flags = symm.empty(world, dtype=torch.int64, device=device)
+        self.flags.zero_()
+        self.flag_handle = symm.rendezvous(self.flags, group if group is not None else dist.group.WORLD)
+        self.peer_ranks = [p for p in range(world) if p != rank]
+        self.peer_flags = [self.flag_handle.get_buffer(p, (world,), torch.int64, 0) for p in self.peer_ranks]
+        self.step = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)                      # every rank's flags are zero before anyone signals
 
 
-def gemm_gather_fused(run_gemm, peer_buffers: "PeerGatherBuffers", group=None):
+def gemm_gather_fused(run_gemm, peer_buffers: "PeerGatherBuffers", group=None, signal: str = "flag"):
     """N-sharded GEMM whose epilogue itself writes every output tile into all ranks' gathered buffers.
 
     `peer_buffers` must have one chunk.  `run_gemm(out, peer_outs)` launches one GEMM on the current stream that stores
     its result to `out` (this rank's slot of its own buffer) and to each tensor of `peer_outs` (this rank's slot in the
     peers' buffers; `native.mx_gemm(..., peer_outs=...)`).  The stores cross NVLink tile by tile while later tiles
-    compute; a one-element all-reduce behind the GEMM tells every rank that its peers' GEMMs, and with them their
-    stores, have finished.  Returns this rank's [world, M, width] buffer.
+    compute.  Behind the GEMM every rank stores a step counter into its slot of the peers' flag arrays and waits
+    (bounded, on the device) for the peers' counters in its own array (`signal="flag"`, `native.peer_signal`: peer
+    stores and local loads only), or - `signal="allreduce"` - a one-element all-reduce tells every rank that its peers'
+    GEMMs, and with them their stores, have finished.  Returns this rank's [world, M, width] buffer.
     """
     import torch.distributed as dist
     pb = peer_buffers
     if len(pb.ranges) != 1:
         raise ValueError("the fused form writes the whole shard at once: build the buffers with chunks=1")
     run_gemm(pb.gathered[0][pb.rank], [slot for slot in pb.peer_slots[0] if slot is not None])
-    dist.all_reduce(pb.token, group=group)
+    if signal == "flag":
+        from . import native
+        pb.step += 1
+        native.peer_signal(pb.flags, pb.peer_flags, pb.rank, pb.peer_ranks, pb.step)
+    else:
+        dist.all_reduce(pb.token, group=group)
     return pb.gathered[0]
 
 

@@ -75,12 +75,16 @@ def _worker(rank, world, port, results):
         def run_fused(out, peers):
             native.mx_gemm(qa, sa, qb, sb, out=out, bias=bias, activation=native.ACT_GELU_TANH, peer_outs=peers)
 
-        for _ in range(2):
-            g = shard.gemm_gather_fused(run_fused, fused)
+        # closing signal: the step counter in the peers' flag arrays (twice: the counter grows), then the all-reduce
+        for sig in ("flag", "flag", "allreduce"):
+            fused.gathered[0].zero_()
             torch.cuda.synchronize()
+            dist.barrier()                                # nobody's zeroing lands on a peer's fresh tiles
+            g = shard.gemm_gather_fused(run_fused, fused, signal=sig)
+            torch.cuda.synchronize()                      # this rank's signal kernel has seen every peer's counter
+            whole_f = torch.cat([g[r] for r in range(world)], dim=1)
+            same = same and bool(torch.equal(whole_f.view(torch.int16), whole_after.view(torch.int16)))
             dist.barrier()
-        whole_f = torch.cat([g[r] for r in range(world)], dim=1)
-        same = same and bool(torch.equal(whole_f.view(torch.int16), whole_after.view(torch.int16)))
         # the FP8 kernel (stream-K decode shape): output rows go to both GPUs as bulk copies
         Mf, Kf = 128, 2048
         af = torch.from_numpy(syn.normal_f32(8, 0, (Mf, Kf), 1.0)).to(dev)
