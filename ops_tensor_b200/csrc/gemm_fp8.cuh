@@ -59,6 +59,11 @@ struct Fp8GemmParams {
     int n_peers;                    // this GPU's slot in the other GPUs' gathered outputs
 };
 
+// Tensor maps of the further copies of D (`peer_d`), for the tiled output copies; entries beyond n_peers are unused.
+struct Fp8PeerMaps {
+    CUtensorMap m[7];
+};
+
 template <int kStages>
 struct Fp8GemmSmem {
     static constexpr int kTile = 128;
@@ -78,8 +83,9 @@ struct Fp8GemmSmem {
     static constexpr int kAmaxOffset = kGroupOffset + 2 * (kFp8MaxGroups + 1) * 4;   // float amax[2 tiles][<= 4 column parts][128]
     // 16-bit outputs leave through shared memory.  A promotion warp whose 32 rows may all be written stages them as
     // two 32 x 32 blocks (64-byte rows, 64-byte swizzle) and one lane hands both to the copy engine as tiled stores.
-    // A warp that must stop at a group's last row, or that also writes to peers, stages plain rows (padded by 16
-    // bytes against bank conflicts) and every thread issues a bulk copy of its own row.
+    // (The same blocks go to every peer copy of D through the peers' tensor maps.)  A warp that must stop at a group's
+    // last row stages plain rows (padded by 16 bytes against bank conflicts) and every thread issues a bulk copy of its
+    // own row, to D and to each peer.
     static constexpr int kStoreRowPitch = 64 * 2 + 16;
     static constexpr int kStoreWarpBytes = 5 * 1024;                                     // >= 32 * kStoreRowPitch, >= 2 * 2048
     static constexpr int kStoreOffset = (kAmaxOffset + 2 * 4 * 128 * 4 + 1023) & ~1023;  // swizzled blocks: 1 KB aligned
@@ -190,7 +196,7 @@ struct Fp8WorkWalker {
 template <int kStages, int kAct, int kIssuers = 1, int kParts = 2>
 __global__ void __launch_bounds__(128 * kParts + 32 + 32 * kIssuers, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                const __grid_constant__ CUtensorMap tmap_d,
+                const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ Fp8PeerMaps peer_maps,
                 const Fp8GemmParams p) {
     grid_launch_dependents();        // the next kernel in the stream may start setting up as this one's CTAs retire
     using L = Fp8GemmSmem<kStages>;
@@ -673,9 +679,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 tma_store_wait_read<0>();                        // the previous tile's copies have read the staging area
                 __syncwarp();
                 // tiled stores clip at the matrix edges only: usable when no row of this warp lies beyond the group's
-                // end (the next group's rows start there) - and 256 row copies per tile kept the copy engine busy for
-                // ~4000 cycles in which the promotion warps could not start the next tile
-                const bool tiled = p.n_peers == 0 && (p.groups == 0 || warp_row0 + 32 <= seg.row_end);
+                // end (the next group's rows start there); 256 row copies per tile (times the number of copies of D)
+                // kept the copy engine busy for ~4000 cycles in which the promotion warps could not start the next tile
+                const bool tiled = p.groups == 0 || warp_row0 + 32 <= seg.row_end;
                 if (tiled) {
                     const int sw = (lane >> 1) & 3;              // 64-byte swizzle: 16-byte slot ^= (row / 2) % 4
 #pragma unroll
@@ -698,7 +704,12 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     if (lane == 0 && warp_row0 < seg.row_end) {
 #pragma unroll
                         for (int h = 0; h < kCols / 32; ++h) {
-                            if (n0 + 32 * h < p.N) tma_store_2d(&tmap_d, warp_stage + h * 2048, n0 + 32 * h, warp_row0);
+                            if (n0 + 32 * h < p.N) {
+                                tma_store_2d(&tmap_d, warp_stage + h * 2048, n0 + 32 * h, warp_row0);
+                                for (int q = 0; q < p.n_peers; ++q) {
+                                    tma_store_2d(&peer_maps.m[q], warp_stage + h * 2048, n0 + 32 * h, warp_row0);
+                                }
+                            }
                         }
                     }
                 } else {

@@ -785,7 +785,7 @@ static unsigned long long next_stream_k_epoch() {
 
 template <int kAct, int kStages>
 static cudaError_t launch_fp8_stages(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
-                                     const Fp8GemmParams& p, int grid, cudaStream_t stream) {
+                                     const Fp8PeerMaps& pm, const Fp8GemmParams& p, int grid, cudaStream_t stream) {
 #ifndef LAB_ISSUERS
 #define LAB_ISSUERS 2
 #endif
@@ -803,18 +803,18 @@ static cudaError_t launch_fp8_stages(const CUtensorMap& ta, const CUtensorMap& t
     }
     // behind whatever precedes it in the stream (the kernel that zeroes the fix-up flags, or the previous GEMM): set-up
     // overlaps that kernel's tail, every thread waits for it before the role loops start
-    return launch_after_prepass(kernel, grid, 288 + 32 * kIssuers, L::kDynamicBytes, stream, ta, tb, td, p);
+    return launch_after_prepass(kernel, grid, 288 + 32 * kIssuers, L::kDynamicBytes, stream, ta, tb, td, pm, p);
 }
 
 template <int kAct>
 static cudaError_t launch_fp8_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
-                                       const Fp8GemmParams& p, int grid, cudaStream_t stream) {
+                                       const Fp8PeerMaps& pm, const Fp8GemmParams& p, int grid, cudaStream_t stream) {
     // One tcgen05.commit per K block serves the accumulator ring (4 TMEM stages) and the operand ring.  Two MMA-issuing
     // threads take the K blocks in turn.  Operand stages: 5 when the weights are streamed once by a single row of
     // tiles (decode, C5: 36.7 -> 35.7 us), else 4 (grouped C4: 115 us with 4, 118 us with 5 - those shapes are bound
     // by the L2 -> shared-memory traffic of 128x128 tiles, 32 KB per K block, not by load latency).
-    if (p.groups == 0 && p.m_tiles == 1) return launch_fp8_stages<kAct, 5>(ta, tb, td, p, grid, stream);
-    return launch_fp8_stages<kAct, 4>(ta, tb, td, p, grid, stream);
+    if (p.groups == 0 && p.m_tiles == 1) return launch_fp8_stages<kAct, 5>(ta, tb, td, pm, p, grid, stream);
+    return launch_fp8_stages<kAct, 4>(ta, tb, td, pm, p, grid, stream);
 }
 
 }  // namespace blaze
@@ -880,9 +880,15 @@ extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
     p.scale_d = static_cast<float*>(a->scaleD);
     if (a->d_type == BLAZE_OUT_FP8_128 && (!a->scaleD || (a->ldd % 16) != 0)) return ACLTENSOR_STATUS_INVALID_VALUE;
     p.n_peers = a->n_peers;
+    Fp8PeerMaps pm;
+    std::memset(&pm, 0, sizeof(pm));
     for (int i = 0; i < BLAZE_MAX_PEERS; ++i) {
         p.peer_d[i] = i < a->n_peers ? static_cast<uint8_t*>(a->peerD[i]) : nullptr;
         if (i < a->n_peers && (!a->peerD[i] || !aligned16(a->peerD[i]))) return ACLTENSOR_STATUS_INVALID_VALUE;
+        // the tiled output copies reach a peer through its own tensor map (same shape, pitch and type as D)
+        if (i < a->n_peers &&
+            !make_tmap_store(&pm.m[i], a->peerD[i], (uint64_t)a->N, (uint64_t)a->M, (uint64_t)a->ldd, a->d_type))
+            return ACLTENSOR_STATUS_INTERNAL_ERROR;
     }
     p.stream_k = pl.stream_k;
     p.flags = nullptr;
@@ -897,12 +903,12 @@ extern "C" int blazeFp8Gemm(const blazeFp8GemmArgs* a, void* stream_v) {
     }
     cudaError_t e;
     switch (a->activation) {
-        case BLAZE_ACT_RELU: e = launch_fp8_instance<ACT_RELU>(ta, tb, td, p, pl.grid, stream); break;
-        case BLAZE_ACT_GELU_TANH: e = launch_fp8_instance<ACT_GELU_TANH>(ta, tb, td, p, pl.grid, stream); break;
-        case BLAZE_ACT_SILU: e = launch_fp8_instance<ACT_SILU>(ta, tb, td, p, pl.grid, stream); break;
-        case BLAZE_ACT_SIGMOID: e = launch_fp8_instance<ACT_SIGMOID>(ta, tb, td, p, pl.grid, stream); break;
-        case BLAZE_ACT_TANH: e = launch_fp8_instance<ACT_TANH>(ta, tb, td, p, pl.grid, stream); break;
-        default: e = launch_fp8_instance<ACT_IDENTITY>(ta, tb, td, p, pl.grid, stream); break;
+        case BLAZE_ACT_RELU: e = launch_fp8_instance<ACT_RELU>(ta, tb, td, pm, p, pl.grid, stream); break;
+        case BLAZE_ACT_GELU_TANH: e = launch_fp8_instance<ACT_GELU_TANH>(ta, tb, td, pm, p, pl.grid, stream); break;
+        case BLAZE_ACT_SILU: e = launch_fp8_instance<ACT_SILU>(ta, tb, td, pm, p, pl.grid, stream); break;
+        case BLAZE_ACT_SIGMOID: e = launch_fp8_instance<ACT_SIGMOID>(ta, tb, td, pm, p, pl.grid, stream); break;
+        case BLAZE_ACT_TANH: e = launch_fp8_instance<ACT_TANH>(ta, tb, td, pm, p, pl.grid, stream); break;
+        default: e = launch_fp8_instance<ACT_IDENTITY>(ta, tb, td, pm, p, pl.grid, stream); break;
     }
     return status_of(e);
 }
@@ -1172,6 +1178,11 @@ struct PeerSignalParams {
 };
 
 __global__ void peer_signal_kernel(const PeerSignalParams p) {
+    // launched with programmatic stream serialisation: the next kernel in the stream may set itself up while this one
+    // waits for its peers, and this one is resident before the GEMM ahead of it has drained; it signals only after
+    // that GEMM has completed
+    blaze::grid_launch_dependents();
+    blaze::grid_dependency_wait();
     const int q = (int)threadIdx.x;
     if (q >= p.n_peers) return;
     __threadfence_system();
@@ -1209,8 +1220,7 @@ extern "C" int blazePeerSignal(const blazePeerSignalArgs* a, void* stream) {
     p.value = a->value;
     p.limit_cycles = a->limit_cycles > 0 ? a->limit_cycles : (1LL << 31);
     p.status = ctx->status_word;
-    peer_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    return status_of(cudaGetLastError());
+    return status_of(launch_after_prepass(peer_signal_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), p));
 }
 
 extern "C" int blazeDeviceInfo(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor) {
