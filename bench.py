@@ -814,6 +814,54 @@ def gather_leg(env, full, part, steps, warmup, gemm_only_ms):
     return info
 
 
+def decode_gather_leg(env, part, steps, warmup):
+    """The split decode GEMM (C5, FP8 kernel) with the whole output on every rank: the shape where the closing signal's
+    cost decides.  GEMM alone, GEMM + NCCL all-gather, and the fused form closed by the flag signal or by a one-element
+    all-reduce; all must give the same bits."""
+    torch, dist, native, shard = env.torch, env.dist, env.native, env.shard
+    world, rank, dev = env.world, env.rank, env.dev
+    M, N = part.M, part.N
+    whole = torch.empty((world, M, N), dtype=torch.bfloat16, device=dev)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    try:
+        fused = shard.PeerGatherBuffers(M, N, world, rank, 1, torch.bfloat16, dev, 128)
+        ok = torch.ones(1, device=dev)
+    except Exception as exc:                             # no symmetric memory on this box
+        fused, ok = None, torch.zeros(1, device=dev)
+        why = repr(exc)[:200]
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if ok.item() == 0 or fused is None:
+        return {"workload": part.wl, "fused_unavailable": why if fused is None else "a peer has no symmetric memory"}
+
+    def gemm(o, peers=None):
+        native.fp8_gemm(part.qa, part.sa, part.qb, part.sb, out=o, residual=part.residual, peer_outs=peers)
+
+    def step_after():
+        gemm(out)
+        dist.all_gather_into_tensor(whole.view(world * M, N), out)
+
+    legs = {"gemm_only_ms": lambda: gemm(out), "nccl_after_ms": step_after,
+            "fused_ms": lambda: shard.gemm_gather_fused(gemm, fused),
+            "fused_with_allreduce_signal_ms": lambda: shard.gemm_gather_fused(gemm, fused, signal="allreduce")}
+    info = {"workload": part.wl, "M": M, "N_per_rank": N, "K": part.K, "gathered_bytes_per_rank": (world - 1) * M * N * 2}
+    n = max(steps, 100)
+    for key, fn in legs.items():
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        info[key] = timed_loop(env, fn, n) / n
+    step_after()
+    shard.gemm_gather_fused(gemm, fused)
+    torch.cuda.synchronize()
+    same = torch.equal(fused.gathered[0].view(torch.int16), whole.view(torch.int16))
+    flag = torch.tensor([1.0 if same else 0.0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    info.update(bit_equal=bool(flag.item() == 1.0), device_status=env.H.device_status(), steps=n,
+                how="FP8 kernel: tiled output copies to D and, through a tensor map per peer, to every peer's gathered "
+                    "buffer; closing signal blazePeerSignal")
+    return info
+
+
 def gpu_arm(args):
     env = Env()
     torch, dist, H = env.torch, env.dist, env.H
@@ -885,8 +933,17 @@ def gpu_arm(args):
                 torch.cuda.empty_cache()
 
     gather_info = None
+    gather_decode = None
     if strong and full.kind in TENSOR_BOUND and not args.kernel_only and args.gather != "none":
         gather_info = gather_leg(env, full, case, max(5, min(steps, 50)), warmup, ms_per_step)
+        # and the decode shape, where the closing signal's cost decides
+        c5_full = Case(env, "c5")
+        c5_part = c5_full.n_split(world, rank)
+        gather_decode = decode_gather_leg(env, c5_part, steps, warmup)
+        c5_part.close()
+        c5_full.close()
+        del c5_part, c5_full
+        torch.cuda.empty_cache()
 
     e2e_ms = None
     e2e = None
@@ -955,6 +1012,8 @@ def gpu_arm(args):
             line["strong"] = strong_list
         if gather_info:
             line["gather"] = gather_info
+        if gather_decode:
+            line["gather_decode"] = gather_decode
         if world == 1 and not args.kernel_only:
             run, cpu_flops, sample, fraction = make_cpu_golden(wl)
             times = time_cpu_golden(run, 3)

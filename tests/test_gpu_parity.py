@@ -306,6 +306,8 @@ def test_grouped_small_with_empty_groups(cuda_device):
 @pytest.mark.parametrize("rows,N,K", [
     ([0, 5, 128, 0, 129, 1, 300, 0], 264, 1040),               # a handful of tiles, far fewer than SMs
     ([700, 0, 64, 1500, 333, 1, 0, 2050, 129, 127], 768, 2048),   # ~1.7 tiles per SM: the case the split is for
+    ([100], 128, 20480),                                       # one tile, 160 K blocks: every SM contributes to it, so
+                                                               # the owner polls far more than 32 marks
 ])
 def test_grouped_split_along_k(cuda_device, split, rows, N, K):
     """Grouped matmul with the (tile, K block) units dealt evenly over the SMs: partial tiles of ragged groups go
