@@ -309,6 +309,17 @@ def test_kernel_abi_argument_checks(built_library):
     assert l.blazeQuantizeMx(None, 0, 4, 32, 0, None, 0, None, None) == H.STATUS_INVALID_VALUE
     assert l.blazeAddF32(None, None, None, 0, None) == H.STATUS_SUCCESS
     assert l.blazeAddF32(None, None, None, -1, None) == H.STATUS_INVALID_VALUE
+    # the closing signal of a fused gather refuses incomplete arguments before it touches a device
+    l.blazePeerSignal.restype = C.c_int
+    assert l.blazePeerSignal(None, None) == H.STATUS_INVALID_VALUE
+    ps = native.PeerSignalArgs()
+    ps.struct_size = C.sizeof(ps)
+    ps.n_peers = 0
+    assert l.blazePeerSignal(C.byref(ps), None) == H.STATUS_INVALID_VALUE          # no peers
+    ps.n_peers, ps.my_rank = native.MAX_PEERS + 1, 0
+    assert l.blazePeerSignal(C.byref(ps), None) == H.STATUS_INVALID_VALUE          # too many
+    ps.n_peers = 1
+    assert l.blazePeerSignal(C.byref(ps), None) == H.STATUS_INVALID_VALUE          # no flag arrays
 
 
 def test_benchmark_generators_match_the_oracle():
