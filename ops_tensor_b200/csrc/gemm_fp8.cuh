@@ -441,18 +441,35 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         // tile's epilogue, so the first scales of the next segment are requested before the epilogue starts.
         constexpr int kScaleAhead = 4;
         float sa_q[kScaleAhead], sb_q[kScaleAhead];
+        const bool sa_vec_ok = (p.k_blocks & 3) == 0 && (reinterpret_cast<uintptr_t>(p.sa) & 15) == 0;
+        // requests the scales of blocks kb_first .. kb_first + 3 of a segment: A's as one 16-byte load when the batch is
+        // whole and aligned (the usual case), B's four by pointer steps
+        auto fetch_scales = [&](const float* sa_r, const float* sb_c, int kb_first, int kb_end, bool rows_in) {
+            if (sa_vec_ok && (kb_first & 3) == 0 && kb_first + kScaleAhead <= kb_end) {
+                const float4 a4 = rows_in ? __ldg(reinterpret_cast<const float4*>(sa_r + kb_first))
+                                          : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                sa_q[0] = a4.x; sa_q[1] = a4.y; sa_q[2] = a4.z; sa_q[3] = a4.w;
+                const float* b = sb_c + (long long)kb_first * p.n_blocks;
+#pragma unroll
+                for (int u = 0; u < kScaleAhead; ++u) {
+                    sb_q[u] = __ldg(b);
+                    b += p.n_blocks;
+                }
+                return;
+            }
+#pragma unroll
+            for (int u = 0; u < kScaleAhead; ++u) {
+                const int kq = kb_first + u;
+                const bool in = rows_in && kq < kb_end;
+                sa_q[u] = in ? __ldg(sa_r + kq) : 0.0f;
+                sb_q[u] = kq < kb_end ? __ldg(sb_c + (long long)kq * p.n_blocks) : 0.0f;
+            }
+        };
         auto fetch_first_scales = [&](const Fp8Segment& sg) {
             const int row_f = sg.m0 + r_in_tile;
             const bool in_rows = row_f < sg.row_end;
-            const float* sa_f = p.sa + (long long)(in_rows ? row_f : 0) * p.k_blocks;
-            const float* sb_f = p.sb + (long long)sg.group * p.k_blocks * p.n_blocks + sg.nt;
-#pragma unroll
-            for (int u = 0; u < kScaleAhead; ++u) {
-                const int kq = sg.kb0 + u;
-                const bool in = in_rows && kq < sg.kb1;
-                sa_q[u] = in ? __ldg(sa_f + kq) : 0.0f;
-                sb_q[u] = in ? __ldg(sb_f + (long long)kq * p.n_blocks) : 0.0f;
-            }
+            fetch_scales(p.sa + (long long)(in_rows ? row_f : 0) * p.k_blocks,
+                         p.sb + (long long)sg.group * p.k_blocks * p.n_blocks + sg.nt, sg.kb0, sg.kb1, in_rows);
         };
         Fp8Segment next_seg;
         if (kMerged && lane == 0) {                     // the first use of each stage finds its accumulator free
@@ -463,7 +480,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         for (; ok && have; seg = next_seg) {
             const int row = seg.m0 + r_in_tile;
             const bool row_ok = row < seg.row_end;
-            const bool warp_has_rows = seg.m0 + quad * 32 < seg.row_end;      // warp-uniform
             const float* sa_row = p.sa + (long long)(row_ok ? row : 0) * p.k_blocks;
             const float* sb_col = p.sb + (long long)seg.group * p.k_blocks * p.n_blocks + seg.nt;
             float accum[kCols];
@@ -476,24 +492,23 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 float s_cur[kScaleAhead];
 #pragma unroll
                 for (int u = 0; u < kScaleAhead; ++u) s_cur[u] = sa_q[u] * sb_q[u];
-#pragma unroll
-                for (int u = 0; u < kScaleAhead; ++u) {
-                    const int kq = kb0 + kScaleAhead + u;
-                    const bool in = row_ok && kq < seg.kb1;
-                    sa_q[u] = in ? __ldg(sa_row + kq) : 0.0f;
-                    sb_q[u] = in ? __ldg(sb_col + (long long)kq * p.n_blocks) : 0.0f;
-                }
+                fetch_scales(sa_row, sb_col, kb0 + kScaleAhead, seg.kb1, row_ok);
 #pragma unroll
                 for (int u = 0; u < kScaleAhead; ++u) {
                     const int kb = kb0 + u;
                     if (kb >= seg.kb1) break;                                   // uniform across the CTA
                     const float s = s_cur[u];
                     const int acc = (int)(g & 3);
-                    ok = mbar_wait(&tmem_full_bar[g & 7], (g >> 3) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
+                    // one probe and a vote in the usual case (the block is done); the bounded wait only behind a miss
+                    if (!__all_sync(0xffffffffu, mbar_try_wait(&tmem_full_bar[g & 7], (g >> 3) & 1))) {
+                        ok = mbar_wait(&tmem_full_bar[g & 7], (g >> 3) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_FULL);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                    }
                     tcgen05_fence_after();
-                    if (warp_has_rows) {
+                    // (a warp whose rows all lie beyond the group's end promotes them anyway: they are never stored, and
+                    // a branch here cost every warp ~40 cycles per block)
+                    {
                         uint32_t v[kCols];
                         if constexpr (kCols == 64) tmem_ld_32x64(tmem_base + lane_base + acc * 128 + c0, v);
                         else tmem_ld_32x32(tmem_base + lane_base + acc * 128 + c0, v);
@@ -503,10 +518,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                         if (lane == 0) mbar_arrive(kMerged ? &full_bar[acc] : &tmem_empty_bar[acc]);    // the block is in registers: free the stage
 #pragma unroll
                         for (int e = 0; e < kCols; e += 2) fma_f32x2(accum[e], accum[e + 1], v[e], v[e + 1], s);
-                    } else {
-                        tcgen05_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(kMerged ? &full_bar[acc] : &tmem_empty_bar[acc]);
                     }
                     ++g;
                 }
